@@ -1,0 +1,67 @@
+"""Non-differentiable tensor helpers. Parity: reference `genesis/functional.py:12-240`."""
+import torch
+
+from .tensor import Tensor
+from .ops import dispatch as K
+
+
+def _r(x):
+    return x._t if isinstance(x, Tensor) else x
+
+
+def _w(t):
+    return Tensor._wrap(t)
+
+
+def triu(a, k=0):
+    return _w(torch.triu(a._t, diagonal=k))
+
+
+def tril(a, k=0):
+    return _w(torch.tril(a._t, diagonal=k))
+
+
+def isinf(a):
+    return _w(torch.isinf(a._t))
+
+
+def isnan(a):
+    return _w(torch.isnan(a._t))
+
+
+def isfinite(a):
+    return _w(torch.isfinite(a._t))
+
+
+def argsort(a, dim=-1, descending=False):
+    return _w(torch.argsort(a._t, dim=dim, descending=descending, stable=True))
+
+
+def sort(a, dim=-1, descending=False):
+    v, i = torch.sort(a._t, dim=dim, descending=descending, stable=True)
+    return _w(v), _w(i)
+
+
+def bincount(a, weights=None, minlength=0):
+    return _w(torch.bincount(a._t.reshape(-1).long(), weights=None if weights is None else _r(weights),
+                             minlength=minlength))
+
+
+def nonzero(a, as_tuple=False):
+    out = torch.nonzero(a._t, as_tuple=as_tuple)
+    return tuple(_w(o) for o in out) if as_tuple else _w(out)
+
+
+def allclose(a, b, rtol=1e-5, atol=1e-8, equal_nan=False):
+    return bool(torch.allclose(a._t.float(), b._t.float().to(a._t.device), rtol=rtol, atol=atol,
+                               equal_nan=equal_nan))
+
+
+def _cmp(name):
+    def f(a, b):
+        return _w(K.compare(name, a._t, _r(b)))
+    f.__name__ = name
+    return f
+
+
+eq, ne, gt, ge, lt, le = (_cmp(n) for n in ("eq", "ne", "gt", "ge", "lt", "le"))

@@ -1,0 +1,131 @@
+"""Qwen-style dense decoder. Parity: reference `genesis/models/transformers/dense.py:30-320`
+(module tree and state-dict keys: `embed_tokens`, `layers.{i}.self_attn.{q,k,v,o}_proj`,
+`layers.{i}.mlp.{gate,up,down}_proj`, `layers.{i}.{input,post_attention}_layernorm`, `norm`,
+`lm_head`; q/k/v projections carry a bias, o_proj does not).
+
+What differs underneath: activations stay in `[B, S, H, D]` layout so no transpose copies
+are made; RoPE is one fused kernel; attention is the GQA flash kernel (K/V are never
+replicated); the MLP uses the fused SwiGLU kernel; `tie_word_embeddings=True` really shares
+one Parameter between `embed_tokens` and `lm_head`; `QwenForCausalLM(idx, labels=...)` runs the
+fused cross-entropy and returns `(loss, logits)`.
+"""
+from ... import nn
+from ...nn import functional as F
+from ...tensor import Tensor
+from .components import RotaryEmbedding, apply_rope, find_multiple  # noqa: F401
+from .config import TransformerConfig, get_transformer_config
+
+ModelArgs = TransformerConfig
+
+
+class Attention(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.num_heads = config.num_attention_heads
+        self.num_kv_heads = config.num_key_value_heads
+        self.head_dim = config.head_dim
+        self.num_key_value_groups = self.num_heads // self.num_kv_heads
+        # Qwen2 always biases q/k/v (reference `dense.py:230-238`)
+        self.q_proj = nn.Linear(self.hidden_size, self.num_heads * self.head_dim, bias=True)
+        self.k_proj = nn.Linear(self.hidden_size, self.num_kv_heads * self.head_dim, bias=True)
+        self.v_proj = nn.Linear(self.hidden_size, self.num_kv_heads * self.head_dim, bias=True)
+        self.o_proj = nn.Linear(self.num_heads * self.head_dim, self.hidden_size, bias=False)
+        self.rotary_emb = RotaryEmbedding(self.head_dim, max_position_embeddings=config.max_position_embeddings,
+                                          base=config.rope_theta)
+
+    def forward(self, x, position_ids=None, mask=None):
+        B, S, _ = x.shape
+        q = F.reshape(self.q_proj(x), (B, S, self.num_heads, self.head_dim))
+        k = F.reshape(self.k_proj(x), (B, S, self.num_kv_heads, self.head_dim))
+        v = F.reshape(self.v_proj(x), (B, S, self.num_kv_heads, self.head_dim))
+        q = apply_rope(q, self.rotary_emb, position_ids)
+        k = apply_rope(k, self.rotary_emb, position_ids)
+        o = F.flash_attention(q, k, v, causal=True)
+        return self.o_proj(F.reshape(o, (B, S, self.num_heads * self.head_dim)))
+
+
+class FeedForward(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.gate_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=config.mlp_bias)
+        self.up_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=config.mlp_bias)
+        self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=config.mlp_bias)
+
+    def forward(self, x):
+        return self.down_proj(F.swiglu(self.gate_proj(x), self.up_proj(x)))
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.self_attn = Attention(config)
+        self.mlp = FeedForward(config)
+        self.input_layernorm = nn.RMSNorm(config.hidden_size, eps=config.norm_eps)
+        self.post_attention_layernorm = nn.RMSNorm(config.hidden_size, eps=config.norm_eps)
+
+    def forward(self, x, input_pos=None, position_ids=None, mask=None):
+        h = x + self.self_attn(self.input_layernorm(x), position_ids, mask)
+        return h + self.mlp(self.post_attention_layernorm(h))
+
+
+class QwenModel(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size)
+        self.layers = nn.ModuleList(TransformerBlock(config) for _ in range(config.n_layer))
+        self.norm = nn.RMSNorm(config.hidden_size, eps=config.norm_eps)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        if config.tie_word_embeddings:
+            self.lm_head.weight = self.embed_tokens.weight
+        self.max_batch_size = -1
+        self.max_seq_length = -1
+
+    def setup_caches(self, max_batch_size, max_seq_length):
+        if self.max_seq_length >= max_seq_length and self.max_batch_size >= max_batch_size:
+            return
+        self.max_seq_length = find_multiple(max_seq_length, 8)
+        self.max_batch_size = max_batch_size
+
+    def hidden_states(self, idx, position_ids=None):
+        x = self.embed_tokens(idx)
+        for layer in self.layers:
+            x = layer(x, position_ids, position_ids, None)
+        return self.norm(x)
+
+    def forward(self, idx, position_ids=None):
+        return self.lm_head(self.hidden_states(idx, position_ids))
+
+    @classmethod
+    def from_name(cls, name):
+        return cls(get_transformer_config(name))
+
+
+class QwenForCausalLM(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.model = QwenModel(config)
+
+    def forward(self, idx, labels=None, return_logits=True, **kwargs):
+        """Logits `[B, S, V]`; with `labels` (already aligned with the logits, -100 = ignore)
+        returns `(loss, logits)` using the fused cross-entropy.  `return_logits=False` returns
+        only the loss and lets the backward pass overwrite the logits buffer with their gradient."""
+        logits = self.model(idx, **kwargs)
+        if labels is None:
+            return logits
+        V = logits.shape[-1]
+        loss = F.cross_entropy(F.reshape(logits, (-1, V)), labels, ignore_index=-100,
+                               _inplace_backward=not return_logits)
+        return (loss, logits) if return_logits else loss
+
+    def load_state_dict(self, state_dict, strict=True):
+        sd = dict(state_dict)
+        if "model.lm_head.weight" not in sd and "model.embed_tokens.weight" in sd:
+            sd["model.lm_head.weight"] = sd["model.embed_tokens.weight"]
+        return super().load_state_dict(sd, strict)
+
+    @classmethod
+    def from_name(cls, name):
+        return cls(get_transformer_config(name))

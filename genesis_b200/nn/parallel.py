@@ -1,0 +1,309 @@
+"""`DistributedDataParallel` with bucketed, overlapped, fused gradient all-reduce.
+
+API parity: reference `genesis/nn/parallel.py:19-209` (constructor arguments, `.module` /
+`.model`, delegation of `state_dict` & co., `__getattr__` fall-through, initial broadcast
+from rank 0, the `DDP: Initialized model on rank r/w` line).  The reference registers one
+blocking NCCL all-reduce per parameter in a tensor hook that its backward engine never
+fires (`genesis/function.py:33-44`); here:
+
+* parameters are grouped into buckets (default 25 MB, reverse registration order, so the
+  first bucket to complete holds the last layers' gradients);
+* every gradient is written straight into its slot of the bucket's flat buffer
+  (`Tensor._grad_buf`), which on CUDA lives in the symmetric heap;
+* when the last gradient of bucket i has been accumulated (post-accumulate hook) and
+  buckets 0..i-1 are launched, the bucket's all-reduce is enqueued on a communication
+  stream, overlapping the rest of backward;
+* on CUDA the all-reduce is one kernel that pulls the rank's slice from all peers over
+  NVLink, accumulates in float32, multiplies by inv_scale/world (AMP unscale), raises the
+  overflow flag on Inf/NaN, and pushes the result into every peer's buffer — no NCCL call;
+  on CPU ranks (gloo) the same bucket logic runs over `torch.distributed.all_reduce`;
+* `no_sync()` accumulates locally for gradient accumulation.
+"""
+import contextlib
+import os
+
+import torch
+import torch.distributed as tdist
+
+from ..tensor import Tensor, _backward_end_callbacks
+from ..distributed import process_group as pg
+from ..distributed import symm
+from ..distributed.collectives import comm_mode
+from .modules.module import Module
+
+
+class _Bucket:
+    __slots__ = ("index", "params", "offsets", "numel", "dtype", "flat", "symm_buf", "pending", "launched",
+                 "ready_event")
+
+    def __init__(self, index, dtype):
+        self.index, self.dtype = index, dtype
+        self.params, self.offsets = [], []
+        self.numel = 0
+        self.flat = None
+        self.symm_buf = None
+        self.pending = 0
+        self.launched = False
+        self.ready_event = None
+
+
+class DistributedDataParallel(Module):
+    def __init__(self, model, device_ids=None, output_device=None, broadcast_buffers=True,
+                 find_unused_parameters=False, gradient_as_bucket_view=False, bucket_cap_mb=None,
+                 grad_scaler=None):
+        super().__init__()
+        if not pg.is_initialized():
+            raise RuntimeError("Process group not initialized. Call genesis.distributed.init_process_group() first")
+        object.__setattr__(self, "module", model)
+        self.world_size = pg.get_world_size()
+        self.rank = pg.get_rank()
+        if device_ids is None:
+            device_ids = [torch.cuda.current_device()] if torch.cuda.is_available() and pg._backend == "nccl" else None
+        self.device_ids = device_ids
+        self.output_device = output_device if output_device is not None else (device_ids[0] if device_ids else None)
+        self.broadcast_buffers = broadcast_buffers
+        self.find_unused_parameters = find_unused_parameters
+        self.bucket_cap_bytes = int(float(bucket_cap_mb if bucket_cap_mb is not None
+                                          else os.environ.get("GENESIS_DDP_BUCKET_MB", 25)) * 1024 * 1024)
+        self._sync = True
+        self._scaler = grad_scaler
+        self._buckets = []
+        self._param_bucket = {}
+        self._next_launch = 0
+        self._armed = False
+        self._comm_stream = None
+        self._use_symm = False
+        all_params = [p for p in model.parameters() if p.requires_grad]
+        # expert-parallel shards are not replicated: no all-reduce, only the 1/world factor
+        self._sharded = [p for p in all_params if getattr(p, "_no_ddp", False)]
+        params = [p for p in all_params if not getattr(p, "_no_ddp", False)]
+        self._on_cuda = bool(params) and params[0]._t.is_cuda
+        if self.world_size > 1:
+            self._broadcast_initial(model)
+            self._build_buckets(params)
+            for p in params:
+                p.register_post_accumulate_grad_hook(self._make_hook())
+        print(f"DDP: Initialized model on rank {self.rank}/{self.world_size}")
+
+    # `.model` is the reference's second name for the wrapped module
+    @property
+    def model(self):
+        return self.module
+
+    # ---- construction ---------------------------------------------------------------
+    def _broadcast_initial(self, model):
+        tensors = [p._t for p in model.parameters() if not getattr(p, "_no_ddp", False)]
+        if self.broadcast_buffers:
+            tensors += [b._t for _, b in model.named_buffers()]
+        # one flat broadcast per dtype instead of one per tensor
+        by_dtype = {}
+        for t in tensors:
+            by_dtype.setdefault(t.dtype, []).append(t)
+        for dt, ts in by_dtype.items():
+            flat = torch.cat([t.reshape(-1) for t in ts])
+            tdist.broadcast(flat, src=0)
+            off = 0
+            for t in ts:
+                n = t.numel()
+                t.copy_(flat[off:off + n].reshape(t.shape))
+                off += n
+
+    def _build_buckets(self, params):
+        cur = {}
+        for p in reversed(params):
+            dt = p._t.dtype
+            b = cur.get(dt)
+            nbytes = p._t.numel() * p._t.element_size()
+            if b is None or (b.numel * p._t.element_size() + nbytes > self.bucket_cap_bytes and b.numel > 0):
+                b = _Bucket(len(self._buckets), dt)
+                self._buckets.append(b)
+                cur[dt] = b
+            # 16-byte aligned slots so vector loads never straddle parameters
+            align = 16 // p._t.element_size()
+            b.numel = (b.numel + align - 1) // align * align
+            b.offsets.append(b.numel)
+            b.params.append(p)
+            b.numel += p._t.numel()
+            self._param_bucket[id(p)] = b
+        self._use_symm = self._on_cuda and comm_mode() == "p2p" and symm.available()
+        if self._on_cuda:
+            self._comm_stream = torch.cuda.Stream()
+        for b in self._buckets:
+            esz = torch.empty(0, dtype=b.dtype).element_size()
+            pad = (b.numel + 1023) // 1024 * 1024          # slices stay 16-byte aligned for any world size <= 64
+            if self._use_symm:
+                b.symm_buf = symm.alloc(pad * esz)
+                b.flat = b.symm_buf.view(b.dtype, 0, pad)
+            else:
+                b.flat = torch.zeros(pad, dtype=b.dtype, device=b.params[0]._t.device)
+            for p, off in zip(b.params, b.offsets):
+                p._grad_buf = b.flat[off:off + p._t.numel()].view(p._t.shape)
+            b.pending = len(b.params)
+
+    # ---- backward-time machinery ------------------------------------------------------
+    def _make_hook(self):
+        def hook(p):
+            if not self._sync or not self._armed:
+                return
+            b = self._param_bucket[id(p)]
+            b.pending -= 1
+            if b.pending == 0:
+                if self._on_cuda:
+                    b.ready_event = torch.cuda.Event()
+                    b.ready_event.record()
+                self._launch_ready()
+        return hook
+
+    def _launch_ready(self):
+        while self._next_launch < len(self._buckets):
+            b = self._buckets[self._next_launch]
+            if b.pending != 0:
+                break
+            self._reduce_bucket(b)
+            self._next_launch += 1
+
+    def _reduce_bucket(self, b):
+        b.launched = True
+        scaler = self._scaler
+        if self._on_cuda:
+            st = self._comm_stream
+            if b.ready_event is not None:
+                st.wait_event(b.ready_event)
+            else:
+                st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                if self._use_symm:
+                    from ..ops import native as N
+                    inv = found = None
+                    if scaler is not None and scaler.is_enabled():
+                        scaler._lazy_init(b.flat.device)
+                        inv, found = scaler._scale, scaler._found_inf
+                    N.allreduce_fused(symm.state(), b.symm_buf, 0, b.flat.numel(), b.dtype, b.flat,
+                                      inv_scale=inv, found_inf=found, prescale=1.0 / self.world_size,
+                                      scale_is_reciprocal=True)
+                else:
+                    tdist.all_reduce(b.flat)
+                    b.flat.mul_(1.0 / self.world_size)
+        else:
+            tdist.all_reduce(b.flat)
+            b.flat.mul_(1.0 / self.world_size)
+
+    def _finish_backward(self):
+        """End of backward: flush buckets whose parameters got no gradient, join the comm stream."""
+        if not self._armed:
+            return
+        self._armed = False
+        if not self._sync:
+            return
+        for b in self._buckets[self._next_launch:]:
+            # parameters without a gradient this step contribute zeros
+            for p in b.params:
+                if p.grad is None:
+                    p._grad_buf.zero_()
+                    if not self.find_unused_parameters:
+                        p.grad = Tensor._wrap(p._grad_buf)
+            b.pending = 0
+            b.ready_event = None
+            self._reduce_bucket(b)
+        self._next_launch = len(self._buckets)
+        if self._sharded:
+            from ..ops import dispatch as K
+            for p in self._sharded:
+                if p.grad is not None:
+                    K.mul_(p.grad._t, 1.0 / self.world_size)
+        if self._on_cuda:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+        if self._use_symm and self._scaler is not None and self._scaler.is_enabled():
+            self._scaler._external_unscale = True
+
+    def _arm(self):
+        self._armed = True
+        self._next_launch = 0
+        for b in self._buckets:
+            b.pending = len(b.params)
+            b.launched = False
+            b.ready_event = None
+        if self._finish_backward not in _backward_end_callbacks:
+            _backward_end_callbacks.append(self._finish_backward)
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Skip gradient synchronisation inside the block (gradient accumulation)."""
+        prev = self._sync
+        self._sync = False
+        try:
+            yield
+        finally:
+            self._sync = prev
+
+    def set_grad_scaler(self, scaler):
+        self._scaler = scaler
+
+    # ---- Module surface -----------------------------------------------------------------
+    def forward(self, *inputs, **kwargs):
+        if self.device_ids and self._on_cuda:
+            dev = f"cuda:{self.device_ids[0]}"
+            inputs = tuple(x.to(dev) if isinstance(x, Tensor) and not x._t.is_cuda else x for x in inputs)
+            kwargs = {k: (v.to(dev) if isinstance(v, Tensor) and not v._t.is_cuda else v) for k, v in kwargs.items()}
+        if self.world_size > 1:
+            from .. import grad_mode
+            if grad_mode.is_grad_enabled():
+                self._arm()
+        return self.module(*inputs, **kwargs)
+
+    def state_dict(self, *a, **k):
+        return self.module.state_dict(*a, **k)
+
+    def load_state_dict(self, *a, **k):
+        return self.module.load_state_dict(*a, **k)
+
+    def parameters(self):
+        return self.module.parameters()
+
+    def named_parameters(self, *a, **k):
+        return self.module.named_parameters(*a, **k)
+
+    def buffers(self):
+        return self.module.buffers()
+
+    def named_buffers(self, *a, **k):
+        return self.module.named_buffers(*a, **k)
+
+    def modules(self):
+        return self.module.modules()
+
+    def named_modules(self, *a, **k):
+        return self.module.named_modules(*a, **k)
+
+    def train(self, mode=True):
+        self.module.train(mode)
+        self.training = mode
+        return self
+
+    def eval(self):
+        return self.train(False)
+
+    def to(self, *a, **k):
+        self.module.to(*a, **k)
+        return self
+
+    def cuda(self, *a, **k):
+        self.module.cuda(*a, **k)
+        return self
+
+    def cpu(self):
+        self.module.cpu()
+        return self
+
+    def zero_grad(self):
+        self.module.zero_grad()
+
+    def __getattr__(self, name):
+        # only reached when normal lookup fails: fall through to the wrapped module
+        mod = self.__dict__.get("module")
+        if mod is not None and name != "module":
+            return getattr(mod, name)
+        raise AttributeError(name)
+
+
+DDP = DistributedDataParallel

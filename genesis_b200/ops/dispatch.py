@@ -1,0 +1,773 @@
+"""Kernel entry points on raw `torch.Tensor`s.
+
+One device path per device: CUDA tensors go to the sm_100a kernels of
+`genesis_b200.ops.native` (hand-written CUDA loaded through ctypes); CPU tensors
+use torch CPU math, which is also the numerical oracle of the test-suite (the
+reference's CPU backend is the same thing, `genesis/ops/cpu/*.py`).
+
+A native wrapper returns `NotImplemented` for a layout/dtype it does not cover
+(e.g. float64 or >4-D strided broadcasting); only then is the generic torch op
+used on CUDA.
+"""
+import math
+
+import torch
+
+from . import native as N
+
+_F32 = torch.float32
+_LOW = (torch.float16, torch.bfloat16)
+
+
+def _cuda(t):
+    return t.is_cuda
+
+
+# =============================== data movement ===================================
+def to_dtype(t, dtype):
+    if t.dtype == dtype:
+        return t
+    if t.is_cuda:
+        r = N.cast(t, dtype)
+        if r is not NotImplemented:
+            return r
+    return t.to(dtype)
+
+
+def copy_(dst, src):
+    if dst.is_cuda and src.is_cuda:
+        r = N.copy_(dst, src)
+        if r is not NotImplemented:
+            return dst
+    dst.copy_(src)
+    return dst
+
+
+def contiguous(t):
+    if t.is_contiguous():
+        return t
+    if t.is_cuda:
+        r = N.contiguous(t)
+        if r is not NotImplemented:
+            return r
+    return t.contiguous()
+
+
+def clone(t):
+    if t.is_cuda:
+        out = torch.empty(t.shape, dtype=t.dtype, device=t.device)
+        copy_(out, t)
+        return out
+    return t.clone(memory_format=torch.contiguous_format)
+
+
+def fill_(t, value):
+    if t.is_cuda:
+        r = N.fill_(t, value)
+        if r is not NotImplemented:
+            return t
+    t.fill_(value)
+    return t
+
+
+# ================================ elementwise ====================================
+def _binary(name, torch_fn, a, b):
+    ta = a if isinstance(a, torch.Tensor) else b
+    if ta.is_cuda:
+        r = N.binary(name, a, b)
+        if r is not NotImplemented:
+            return r
+    return torch_fn(a, b)
+
+
+def add(a, b):
+    return _binary("add", torch.add, a, b)
+
+
+def sub(a, b):
+    return _binary("sub", torch.sub, a, b)
+
+
+def mul(a, b):
+    return _binary("mul", torch.mul, a, b)
+
+
+def div(a, b):
+    return _binary("div", torch.true_divide, a, b)
+
+
+def maximum(a, b):
+    return _binary("max", torch.maximum, a, b)
+
+
+def minimum(a, b):
+    return _binary("min", torch.minimum, a, b)
+
+
+def add_(a, b):
+    """a += b (same shape)."""
+    if a.is_cuda and isinstance(b, torch.Tensor):
+        r = N.add_(a, b)
+        if r is not NotImplemented:
+            return a
+    a.add_(b)
+    return a
+
+
+def axpy_(a, b, alpha):
+    """a += alpha * b."""
+    if a.is_cuda:
+        r = N.add_(a, b, alpha)
+        if r is not NotImplemented:
+            return a
+    a.add_(b, alpha=alpha)
+    return a
+
+
+def mul_(a, b):
+    if a.is_cuda:
+        r = N.mul_(a, b)
+        if r is not NotImplemented:
+            return a
+    a.mul_(b)
+    return a
+
+
+_UNARY_TORCH = {
+    "neg": torch.neg, "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt,
+    "sin": torch.sin, "cos": torch.cos, "tanh": torch.tanh, "sigmoid": torch.sigmoid,
+    "relu": torch.relu, "abs": torch.abs, "sign": torch.sign,
+    "silu": torch.nn.functional.silu,
+    "gelu": lambda x: torch.nn.functional.gelu(x, approximate="tanh"),
+    "reciprocal": torch.reciprocal,
+}
+
+
+def unary(name, t):
+    if t.is_cuda:
+        r = N.unary(name, t)
+        if r is not NotImplemented:
+            return r
+    return _UNARY_TORCH[name](t)
+
+
+def unary_bwd(name, g, x, y=None):
+    """dL/dx for y = f(x), given g = dL/dy. `y` is passed where cheaper (exp, sqrt, tanh, sigmoid)."""
+    if g.is_cuda:
+        r = N.unary_bwd(name, g, x if x is not None else y, y)
+        if r is not NotImplemented:
+            return r
+    if name == "neg":
+        return -g
+    if name == "exp":
+        return g * y
+    if name == "log":
+        return g / x
+    if name == "sqrt":
+        return g / (2 * y)
+    if name == "sin":
+        return g * torch.cos(x)
+    if name == "cos":
+        return -g * torch.sin(x)
+    if name == "tanh":
+        return g * (1 - y * y)
+    if name == "sigmoid":
+        return g * y * (1 - y)
+    if name == "relu":
+        return g * (x > 0).to(g.dtype)
+    if name == "abs":
+        return g * torch.sign(x)
+    if name == "silu":
+        xf = x.float()
+        s = torch.sigmoid(xf)
+        return (g.float() * (s * (1 + xf * (1 - s)))).to(g.dtype)
+    if name == "gelu":
+        xf = x.float()
+        c = math.sqrt(2.0 / math.pi)
+        inner = c * (xf + 0.044715 * xf ** 3)
+        th = torch.tanh(inner)
+        d = 0.5 * (1 + th) + 0.5 * xf * (1 - th * th) * c * (1 + 3 * 0.044715 * xf * xf)
+        return (g.float() * d).to(g.dtype)
+    raise KeyError(name)
+
+
+def pow_scalar(t, p):
+    if t.is_cuda:
+        r = N.scalar_op("pow", t, p)
+        if r is not NotImplemented:
+            return r
+    return torch.pow(t, p)
+
+
+def rpow_scalar(t, base):
+    if t.is_cuda:
+        r = N.scalar_op("rpow", t, base)
+        if r is not NotImplemented:
+            return r
+    return torch.pow(torch.tensor(base, dtype=t.dtype, device=t.device), t)
+
+
+def clamp(t, lo, hi):
+    if t.is_cuda:
+        r = N.clamp(t, lo, hi)
+        if r is not NotImplemented:
+            return r
+    return torch.clamp(t, lo, hi)
+
+
+def where(c, a, b):
+    if c.is_cuda:
+        r = N.where(c, a, b)
+        if r is not NotImplemented:
+            return r
+    if not isinstance(a, torch.Tensor):
+        ref = b if isinstance(b, torch.Tensor) else None
+        a = torch.tensor(a, dtype=ref.dtype if ref is not None else torch.float32, device=c.device)
+    if not isinstance(b, torch.Tensor):
+        b = torch.tensor(b, dtype=a.dtype, device=c.device)
+    return torch.where(c, a, b)
+
+
+_CMP_TORCH = {"eq": torch.eq, "ne": torch.ne, "lt": torch.lt, "le": torch.le, "gt": torch.gt, "ge": torch.ge}
+
+
+def compare(name, a, b):
+    if a.is_cuda:
+        r = N.compare(name, a, b)
+        if r is not NotImplemented:
+            return r
+    return _CMP_TORCH[name](a, b)
+
+
+# ================================= reductions ====================================
+def _norm_dims(t, dims):
+    if dims is None:
+        return None
+    if isinstance(dims, int):
+        dims = (dims,)
+    return tuple(sorted(d % max(t.dim(), 1) for d in dims))
+
+
+def reduce(name, t, dims=None, keepdim=False):
+    """sum / mean / max / min over `dims` (None = all). max/min return values only."""
+    dims = _norm_dims(t, dims)
+    if t.is_cuda:
+        r = N.reduce(name, t, dims, keepdim)
+        if r is not NotImplemented:
+            return r
+    if name == "sum":
+        return t.sum() if dims is None else t.sum(dim=dims, keepdim=keepdim)
+    if name == "mean":
+        return t.mean() if dims is None else t.mean(dim=dims, keepdim=keepdim)
+    fn = torch.amax if name == "max" else torch.amin
+    if dims is None:
+        out = fn(t)
+        return out.reshape((1,) * t.dim()) if keepdim else out
+    return fn(t, dim=dims, keepdim=keepdim)
+
+
+def sum_to_shape(t, shape):
+    """Sum broadcast dimensions of `t` so that the result has `shape`."""
+    shape = tuple(shape)
+    if tuple(t.shape) == shape:
+        return t
+    lead = t.dim() - len(shape)
+    dims = list(range(lead))
+    for i, s in enumerate(shape):
+        if s == 1 and t.shape[lead + i] != 1:
+            dims.append(lead + i)
+    out = reduce("sum", t, tuple(dims), keepdim=True) if dims else t
+    return out.reshape(shape)
+
+
+# ================================== matmul =======================================
+def matmul(a, b):
+    if a.is_cuda:
+        r = N.matmul(a, b)
+        if r is not NotImplemented:
+            return r
+    return torch.matmul(a, b)
+
+
+def linear(x, w, bias=None, out_dtype=None):
+    """y = x @ w.T (+ bias); x [..., K], w [N, K]."""
+    if x.is_cuda:
+        r = N.linear(x, w, bias, out_dtype)
+        if r is not NotImplemented:
+            return r
+    y = torch.nn.functional.linear(x, w, None if bias is None else bias.to(x.dtype))
+    return y if out_dtype is None else y.to(out_dtype)
+
+
+def linear_dgrad(gy, w):
+    """dx = gy @ w; gy [..., N], w [N, K]."""
+    if gy.is_cuda:
+        r = N.linear_dgrad(gy, w)
+        if r is not NotImplemented:
+            return r
+    return torch.matmul(gy, w)
+
+
+def linear_wgrad(gy, x, out_dtype=None, accum=None):
+    """dw = gy^T @ x over all leading dims; optional `accum` (fp32, [N, K]) gets += dw in place."""
+    if gy.is_cuda:
+        r = N.linear_wgrad(gy, x, out_dtype, accum)
+        if r is not NotImplemented:
+            return r
+    g2 = gy.reshape(-1, gy.shape[-1])
+    x2 = x.reshape(-1, x.shape[-1])
+    dw = torch.matmul(g2.t().float(), x2.float()) if g2.dtype in _LOW else torch.matmul(g2.t(), x2)
+    if accum is not None:
+        accum.add_(dw.to(accum.dtype))
+        return accum
+    return dw.to(out_dtype or gy.dtype)
+
+
+def bias_grad(gy, out_dtype=None):
+    """db = sum of gy over all leading dims (fp32 accumulate)."""
+    g2 = gy.reshape(-1, gy.shape[-1])
+    r = reduce("sum", g2.float() if (not g2.is_cuda and g2.dtype in _LOW) else g2, (0,), False)
+    return r.to(out_dtype or gy.dtype)
+
+
+# ============================= normalisation / softmax ===========================
+def rmsnorm_fwd(x, w, eps):
+    """Returns (y, rstd[rows] fp32)."""
+    if x.is_cuda:
+        r = N.rmsnorm_fwd(x, w, eps)
+        if r is not NotImplemented:
+            return r
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    y = (xf * rstd * w.float()).to(x.dtype)
+    return y, rstd.reshape(-1)
+
+
+def rmsnorm_bwd(g, x, w, rstd):
+    """Returns (dx, dw fp32)."""
+    if g.is_cuda:
+        r = N.rmsnorm_bwd(g, x, w, rstd)
+        if r is not NotImplemented:
+            return r
+    n = x.shape[-1]
+    xf, gf, wf = x.float(), g.float(), w.float()
+    rs = rstd.reshape(*x.shape[:-1], 1)
+    xhat = xf * rs
+    gw = gf * wf
+    dx = rs * (gw - xhat * (gw * xhat).sum(-1, keepdim=True) / n)
+    dw = (gf * xhat).reshape(-1, n).sum(0)
+    return dx.to(x.dtype), dw
+
+
+def layernorm_fwd(x, w, b, eps):
+    """Returns (y, mean[rows], rstd[rows])."""
+    if x.is_cuda:
+        r = N.layernorm_fwd(x, w, b, eps)
+        if r is not NotImplemented:
+            return r
+    xf = x.float()
+    mean = xf.mean(-1, keepdim=True)
+    var = xf.var(-1, unbiased=False, keepdim=True)
+    rstd = torch.rsqrt(var + eps)
+    y = (xf - mean) * rstd
+    if w is not None:
+        y = y * w.float()
+    if b is not None:
+        y = y + b.float()
+    return y.to(x.dtype), mean.reshape(-1), rstd.reshape(-1)
+
+
+def layernorm_bwd(g, x, w, mean, rstd):
+    """Returns (dx, dw fp32, db fp32)."""
+    if g.is_cuda:
+        r = N.layernorm_bwd(g, x, w, mean, rstd)
+        if r is not NotImplemented:
+            return r
+    n = x.shape[-1]
+    xf, gf = x.float(), g.float()
+    mu = mean.reshape(*x.shape[:-1], 1)
+    rs = rstd.reshape(*x.shape[:-1], 1)
+    xhat = (xf - mu) * rs
+    gw = gf * w.float() if w is not None else gf
+    dx = rs * (gw - gw.mean(-1, keepdim=True) - xhat * (gw * xhat).mean(-1, keepdim=True))
+    dw = (gf * xhat).reshape(-1, n).sum(0)
+    db = gf.reshape(-1, n).sum(0)
+    return dx.to(x.dtype), dw, db
+
+
+def softmax_fwd(x, dim, log=False):
+    if x.is_cuda:
+        r = N.softmax_fwd(x, dim, log)
+        if r is not NotImplemented:
+            return r
+    return torch.log_softmax(x, dim) if log else torch.softmax(x, dim)
+
+
+def softmax_bwd(g, y, dim, log=False):
+    if g.is_cuda:
+        r = N.softmax_bwd(g, y, dim, log)
+        if r is not NotImplemented:
+            return r
+    if log:
+        return g - torch.exp(y) * g.sum(dim, keepdim=True)
+    return y * (g - (g * y).sum(dim, keepdim=True))
+
+
+def cross_entropy_fwd(logits, target, ignore_index):
+    """Per-row loss (fp32, 0 where ignored) and log-sum-exp (fp32). logits [N, C]."""
+    if logits.is_cuda:
+        r = N.cross_entropy_fwd(logits, target, ignore_index)
+        if r is not NotImplemented:
+            return r
+    lf = logits.float()
+    lse = torch.logsumexp(lf, -1)
+    valid = target != ignore_index
+    tgt = torch.where(valid, target, torch.zeros_like(target))
+    picked = lf.gather(1, tgt.reshape(-1, 1).long()).reshape(-1)
+    loss = torch.where(valid, lse - picked, torch.zeros_like(lse))
+    return loss, lse
+
+
+def cross_entropy_bwd(logits, target, lse, grad_rows, ignore_index, inplace=False):
+    """dlogits = (softmax - onehot) * grad_rows[row]; zero for ignored rows."""
+    if logits.is_cuda:
+        r = N.cross_entropy_bwd(logits, target, lse, grad_rows, ignore_index, inplace)
+        if r is not NotImplemented:
+            return r
+    lf = logits.float()
+    p = torch.exp(lf - lse.reshape(-1, 1))
+    valid = target != ignore_index
+    tgt = torch.where(valid, target, torch.zeros_like(target)).long()
+    p.scatter_add_(1, tgt.reshape(-1, 1), -torch.ones_like(lse).reshape(-1, 1))
+    p = p * (grad_rows * valid.to(grad_rows.dtype)).reshape(-1, 1)
+    return p.to(logits.dtype)
+
+
+# ============================== transformer pieces ===============================
+def swiglu_fwd(gate, up):
+    if gate.is_cuda:
+        r = N.swiglu_fwd(gate, up)
+        if r is not NotImplemented:
+            return r
+    return (torch.nn.functional.silu(gate.float()) * up.float()).to(gate.dtype)
+
+
+def swiglu_bwd(g, gate, up):
+    if g.is_cuda:
+        r = N.swiglu_bwd(g, gate, up)
+        if r is not NotImplemented:
+            return r
+    gf, a, b = g.float(), gate.float(), up.float()
+    s = torch.sigmoid(a)
+    dgate = gf * b * s * (1 + a * (1 - s))
+    dup = gf * a * s
+    return dgate.to(gate.dtype), dup.to(up.dtype)
+
+
+def rope_fwd(x, cos, sin, positions=None, inverse=False):
+    """Rotate-half RoPE on x [B, S, H, D]; cos/sin [max_pos, D] (halves duplicated).
+    `inverse=True` applies the transposed rotation (the backward)."""
+    if x.is_cuda:
+        r = N.rope(x, cos, sin, positions, inverse)
+        if r is not NotImplemented:
+            return r
+    B, S, H, D = x.shape
+    if positions is None:
+        c, s = cos[:S].reshape(1, S, 1, D), sin[:S].reshape(1, S, 1, D)
+    else:
+        c, s = cos[positions].reshape(B, S, 1, D), sin[positions].reshape(B, S, 1, D)
+    xf = x.float()
+    c, s = c.float(), s.float()
+    if inverse:
+        s = -s
+    x1, x2 = xf[..., : D // 2], xf[..., D // 2:]
+    rot = torch.cat((-x2, x1), -1)
+    return (xf * c + rot * s).to(x.dtype)
+
+
+def embedding_fwd(weight, idx):
+    if weight.is_cuda:
+        r = N.embedding_fwd(weight, idx)
+        if r is not NotImplemented:
+            return r
+    return weight[idx.long()]
+
+
+def embedding_bwd(g, idx, num_rows, out_dtype=None):
+    """Accumulating scatter of g rows into a [num_rows, D] gradient (duplicates add up)."""
+    if g.is_cuda:
+        r = N.embedding_bwd(g, idx, num_rows, out_dtype)
+        if r is not NotImplemented:
+            return r
+    D = g.shape[-1]
+    out = torch.zeros(num_rows, D, dtype=torch.float32, device=g.device)
+    out.index_add_(0, idx.reshape(-1).long(), g.reshape(-1, D).float())
+    return out.to(out_dtype or g.dtype)
+
+
+def attention_fwd(q, k, v, causal, scale):
+    """q [B, S, Hq, D], k/v [B, S, Hkv, D] -> (o [B, S, Hq, D], lse [B, Hq, S] fp32, natural log)."""
+    if q.is_cuda:
+        r = N.attention_fwd(q, k, v, causal, scale)
+        if r is not NotImplemented:
+            return r
+    B, S, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    g = Hq // Hkv
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, 1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, 1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(S, Sk, dtype=torch.bool, device=q.device).tril(Sk - S)
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3).contiguous()
+    return o.to(q.dtype), lse
+
+
+def attention_bwd(do, q, k, v, o, lse, causal, scale):
+    if q.is_cuda:
+        r = N.attention_bwd(do, q, k, v, o, lse, causal, scale)
+        if r is not NotImplemented:
+            return r
+    B, S, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    g = Hq // Hkv
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, 1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, 1)
+    dof = do.float().permute(0, 2, 1, 3)
+    of = o.float().permute(0, 2, 1, 3)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(S, Sk, dtype=torch.bool, device=q.device).tril(Sk - S)
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.exp(s - lse.unsqueeze(-1))
+    dv = torch.matmul(p.transpose(-1, -2), dof)
+    dp = torch.matmul(dof, vf.transpose(-1, -2))
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = torch.matmul(ds, kf)
+    dk = torch.matmul(ds.transpose(-1, -2), qf)
+    dk = dk.reshape(B, Hkv, g, Sk, D).sum(2)
+    dv = dv.reshape(B, Hkv, g, Sk, D).sum(2)
+    return (dq.permute(0, 2, 1, 3).contiguous().to(q.dtype),
+            dk.permute(0, 2, 1, 3).contiguous().to(k.dtype),
+            dv.permute(0, 2, 1, 3).contiguous().to(v.dtype))
+
+
+# ================================== random =======================================
+def dropout_mask_apply(x, p, seed, offset):
+    """y = x * keep / (1-p), keep ~ Bernoulli(1-p) from Philox(seed, offset). Returns (y, mask uint8)."""
+    if x.is_cuda:
+        r = N.dropout_fwd(x, p, seed, offset)
+        if r is not NotImplemented:
+            return r
+    # Same draw and arithmetic order as the reference's CPU dropout (`nn/modules/dropout.py:16-22`):
+    # u ~ U[0,1), keep where u <= 1-p, y = x * keep / (1-p).
+    keep = (torch.rand(x.shape, device=x.device) <= (1.0 - p))
+    return (x * keep.to(x.dtype)) / (1.0 - p), keep.to(torch.uint8)
+
+
+def random_fill(kind, shape, dtype, device, seed, offset, a=0.0, b=1.0):
+    """kind: 'uniform' in [a, b), 'normal' mean a std b, 'randint' integers in [a, b)."""
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        r = N.random_fill(kind, shape, dtype, dev, seed, offset, a, b)
+        if r is not NotImplemented:
+            return r
+    if kind == "uniform":
+        return torch.rand(shape, dtype=torch.float32, device=dev).mul_(b - a).add_(a).to(dtype)
+    if kind == "normal":
+        return torch.randn(shape, dtype=torch.float32, device=dev).mul_(b).add_(a).to(dtype)
+    return torch.randint(int(a), int(b), shape, device=dev).to(dtype)
+
+
+# ================================== optimisers ===================================
+def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled=True,
+               grad_scale=None, found_inf=None, shadows=None):
+    """Multi-tensor Adam/AdamW over lists of tensors, in place.
+
+    decoupled=True: p *= 1 - lr*wd, then Adam update (AdamW, reference `optim/adamw.py:9-64`);
+    decoupled=False: g += wd * p (Adam with L2, reference `optim/optimizer.py:95-150`).
+    `grad_scale` (1-elem fp32 tensor) multiplies gradients; `found_inf` (1-elem fp32
+    tensor, non-zero = skip) turns the whole step into a no-op without a host sync.
+    `shadows`: optional low-precision copies of the parameters refreshed by the same pass.
+    """
+    if params and params[0].is_cuda:
+        r = N.adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled,
+                         grad_scale, found_inf, shadows)
+        if r is not NotImplemented:
+            return
+    if found_inf is not None and float(found_inf.item()) != 0.0:
+        return
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    for i, (p, g, m, v) in enumerate(zip(params, grads, ms, vs)):
+        g = g.to(torch.float32) if g.dtype != p.dtype else g
+        if grad_scale is not None:
+            g = g * grad_scale.to(g.dtype)
+        if decoupled:
+            if weight_decay != 0:
+                p.mul_(1.0 - lr * weight_decay)
+        elif weight_decay != 0:
+            g = g + weight_decay * p
+        m.mul_(beta1).add_(g, alpha=1.0 - beta1)
+        v.mul_(beta2).addcmul_(g, g, value=1.0 - beta2)
+        mhat = m / bc1
+        vhat = v / bc2
+        p.sub_(lr * mhat / (vhat.sqrt() + eps))
+        if shadows is not None and shadows[i] is not None:
+            shadows[i].copy_(p)
+
+
+def sgd_step(params, grads, bufs, lr, momentum, weight_decay):
+    """u = momentum*u + (1-momentum)*(g + wd*p); p -= lr*u (reference `optim/optimizer.py:56-92`)."""
+    if params and params[0].is_cuda:
+        r = N.sgd_step(params, grads, bufs, lr, momentum, weight_decay)
+        if r is not NotImplemented:
+            return
+    for p, g, u in zip(params, grads, bufs):
+        g = g.to(p.dtype)
+        if weight_decay != 0:
+            g = g + weight_decay * p
+        u.mul_(momentum).add_(g, alpha=1.0 - momentum)
+        p.sub_(lr * u)
+
+
+def unscale_and_check(grads, inv_scale, found_inf):
+    """grads *= inv_scale in place (skipped when None); found_inf (1-elem fp32) set to 1 if any value is non-finite."""
+    if grads and grads[0].is_cuda:
+        r = N.unscale_and_check(grads, inv_scale, found_inf)
+        if r is not NotImplemented:
+            return
+    bad = False
+    for g in grads:
+        if inv_scale is not None:
+            g.mul_(inv_scale.to(g.dtype) if isinstance(inv_scale, torch.Tensor) else inv_scale)
+        if not bool(torch.isfinite(g).all()):
+            bad = True
+    if bad:
+        found_inf.fill_(1.0)
+
+
+def grad_norm_sq(grads, out):
+    """out (1-elem fp32) += sum of squares of all grads."""
+    if grads and grads[0].is_cuda:
+        r = N.grad_norm_sq(grads, out)
+        if r is not NotImplemented:
+            return
+    tot = sum(float(g.float().pow(2).sum()) for g in grads)
+    out.add_(tot)
+
+
+# =================================== MoE =========================================
+def moe_router(logits, k, renorm):
+    """softmax over experts, top-k, optional renormalisation.
+    Returns (weights [T,k] fp32, experts [T,k] int32, probs [T,E] fp32, counts [E] int32)."""
+    if logits.is_cuda:
+        r = N.moe_router(logits, k, renorm)
+        if r is not NotImplemented:
+            return r
+    probs = torch.softmax(logits.float(), -1)
+    w, e = torch.topk(probs, k, dim=-1, sorted=False)
+    if renorm:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    counts = torch.bincount(e.reshape(-1), minlength=logits.shape[-1]).to(torch.int32)
+    return w, e.to(torch.int32), probs, counts
+
+
+def moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm):
+    """Gradient of `moe_router` w.r.t. the logits. `dweights` [T,k] / `dprobs` [T,E] may be None."""
+    if probs.is_cuda:
+        r = N.moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm)
+        if r is not NotImplemented:
+            return r
+    idx = experts.long()
+    total = torch.zeros_like(probs) if dprobs is None else dprobs.float().clone()
+    if dweights is not None:
+        dw = dweights.float()
+        if renorm:
+            raw = probs.gather(1, idx)
+            s = raw.sum(-1, keepdim=True) + 1e-20
+            dw = (dw - (dw * weights).sum(-1, keepdim=True)) / s
+        total.scatter_add_(1, idx, dw)
+    return probs * (total - (probs * total).sum(-1, keepdim=True))
+
+
+def moe_sort(experts, num_experts):
+    """Stable sort of the T*k (token, slot) pairs by expert id.
+    Returns (perm [T*k] int64: sorted position -> flat pair index, offsets [E+1] int64)."""
+    if experts.is_cuda:
+        r = N.moe_sort(experts, num_experts)
+        if r is not NotImplemented:
+            return r
+    flat = experts.reshape(-1).long()
+    perm = torch.sort(flat, stable=True)[1]
+    counts = torch.bincount(flat, minlength=num_experts)
+    offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=experts.device)
+    offsets[1:] = torch.cumsum(counts, 0)
+    return perm, offsets
+
+
+def gather_rows(x, rows):
+    """x[rows] for a 2-D x."""
+    if x.is_cuda:
+        r = N.gather_rows(x, rows)
+        if r is not NotImplemented:
+            return r
+    return x.index_select(0, rows.long())
+
+
+def scatter_add_rows(src, rows, num_rows, out_dtype=None):
+    """out[rows[i]] += src[i], fp32 accumulate."""
+    if src.is_cuda:
+        r = N.scatter_add_rows(src, rows, num_rows, out_dtype)
+        if r is not NotImplemented:
+            return r
+    out = torch.zeros(num_rows, src.shape[1], dtype=torch.float32, device=src.device)
+    out.index_add_(0, rows.long(), src.float())
+    return out.to(out_dtype or src.dtype)
+
+
+def _seg(offsets):
+    o = offsets.tolist()
+    return [(e, o[e], o[e + 1]) for e in range(len(o) - 1) if o[e + 1] > o[e]]
+
+
+def grouped_linear(x, w, offsets):
+    """y[s:e] = x[s:e] @ w[g].T for each group g with rows offsets[g]:offsets[g+1]. x [M,K], w [G,N,K]."""
+    if x.is_cuda:
+        r = N.grouped_linear(x, w, offsets)
+        if r is not NotImplemented:
+            return r
+    y = torch.zeros(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+    for g, s, e in _seg(offsets):
+        y[s:e] = x[s:e] @ w[g].t()
+    return y
+
+
+def grouped_dgrad(gy, w, offsets):
+    """dx[s:e] = gy[s:e] @ w[g]. gy [M,N], w [G,N,K]."""
+    if gy.is_cuda:
+        r = N.grouped_dgrad(gy, w, offsets)
+        if r is not NotImplemented:
+            return r
+    dx = torch.zeros(gy.shape[0], w.shape[2], dtype=gy.dtype, device=gy.device)
+    for g, s, e in _seg(offsets):
+        dx[s:e] = gy[s:e] @ w[g]
+    return dx
+
+
+def grouped_wgrad(gy, x, offsets, num_groups, out_dtype=None):
+    """dw[g] = gy[s:e].T @ x[s:e] (fp32 accumulate). Returns [G,N,K]."""
+    if gy.is_cuda:
+        r = N.grouped_wgrad(gy, x, offsets, num_groups, out_dtype)
+        if r is not NotImplemented:
+            return r
+    dw = torch.zeros(num_groups, gy.shape[1], x.shape[1], dtype=torch.float32, device=gy.device)
+    for g, s, e in _seg(offsets):
+        dw[g] = gy[s:e].float().t() @ x[s:e].float()
+    return dw.to(out_dtype or gy.dtype)

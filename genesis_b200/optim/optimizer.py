@@ -1,0 +1,140 @@
+"""Optimizers. Parity: reference `genesis/optim/optimizer.py:11-150`, `optim/adamw.py:66-176`.
+
+Every `step()` is ONE multi-tensor kernel launch over all parameters (the reference
+launches once per parameter).  State is kept as `m`/`v`/`u` dicts keyed by parameter
+index, the layout the reference exposes through `state_dict()`; `load_state_dict` is
+real here (the reference's is a no-op, `optimizer.py:49-53`).
+
+AMP integration: `GradScaler.step` hands `grad_scale` / `found_inf` device scalars to
+the kernel, which unscales on the fly and skips the update when an overflow was
+found, with no host synchronisation.
+"""
+import torch
+
+from ..tensor import Tensor
+from ..ops import dispatch as K
+
+
+class Optimizer:
+    def __init__(self, params):
+        self.params = list(params)
+        # set by GradScaler for one step
+        self._grad_scale = None
+        self._found_inf = None
+
+    def zero_grad(self, set_to_none=True):
+        for p in self.params:
+            if set_to_none or p.grad is None:
+                p.grad = None
+            else:
+                K.fill_(p.grad._t, 0)
+
+    reset_grad = zero_grad
+
+    def step(self):
+        raise NotImplementedError
+
+    _STATE_TENSORS = ("m", "v", "u")
+
+    def state_dict(self):
+        out = {}
+        for k, v in self.__dict__.items():
+            if k == "params" or k.startswith("_"):
+                continue
+            if k in self._STATE_TENSORS:
+                out[k] = {i: Tensor._wrap(t) for i, t in v.items()}
+            else:
+                out[k] = v
+        return out
+
+    def load_state_dict(self, state):
+        for k, v in state.items():
+            if k in self._STATE_TENSORS:
+                cur = {}
+                for i, t in v.items():
+                    raw = t._t if isinstance(t, Tensor) else torch.as_tensor(t)
+                    p = self.params[int(i)]._t
+                    cur[int(i)] = raw.to(device=p.device, dtype=torch.float32).clone()
+                setattr(self, k, cur)
+            elif k != "params":
+                setattr(self, k, v)
+
+    def _active(self):
+        idx = [i for i, p in enumerate(self.params) if p.grad is not None]
+        return idx
+
+    def _state(self, store, i):
+        t = store.get(i)
+        if t is None:
+            p = self.params[i]._t
+            t = torch.zeros(p.shape, dtype=torch.float32 if p.dtype.is_floating_point else p.dtype,
+                            device=p.device)
+            store[i] = t
+        return t
+
+
+class SGD(Optimizer):
+    """u = momentum*u + (1-momentum)*(g + wd*p); p -= lr*u."""
+
+    def __init__(self, params, lr=0.01, momentum=0.0, weight_decay=0.0):
+        super().__init__(params)
+        self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
+        self.u = {}
+
+    def step(self):
+        idx = self._active()
+        if not idx:
+            return
+        ps = [self.params[i]._t for i in idx]
+        gs = [self.params[i].grad._t for i in idx]
+        us = [self._state(self.u, i) for i in idx]
+        K.sgd_step(ps, gs, us, self.lr, self.momentum, self.weight_decay)
+        for i in idx:
+            self.params[i]._version += 1
+
+
+class _AdamBase(Optimizer):
+    decoupled = True
+
+    def __init__(self, params, lr, beta1, beta2, eps, weight_decay):
+        super().__init__(params)
+        self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = lr, beta1, beta2, eps, weight_decay
+        self.t = 0
+        self.m, self.v = {}, {}
+        self._shadows = None
+
+    def step(self):
+        idx = self._active()
+        if not idx:
+            return
+        self.t += 1
+        ps = [self.params[i]._t for i in idx]
+        gs = [self.params[i].grad._t for i in idx]
+        ms = [self._state(self.m, i) for i in idx]
+        vs = [self._state(self.v, i) for i in idx]
+        sh = None if self._shadows is None else [self._shadows.get(i) for i in idx]
+        K.adamw_step(ps, gs, ms, vs, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.t,
+                     self.decoupled, self._grad_scale, self._found_inf, sh)
+        for i in idx:
+            self.params[i]._version += 1
+
+
+class Adam(_AdamBase):
+    """Adam with L2 weight decay folded into the gradient."""
+    decoupled = False
+
+    def __init__(self, params, lr=0.01, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
+        super().__init__(params, lr, beta1, beta2, eps, weight_decay)
+
+
+class AdamW(_AdamBase):
+    """AdamW with decoupled weight decay. `fused` is accepted for API parity: the CUDA path is
+    always the fused multi-tensor kernel, the CPU path always plain math."""
+    decoupled = True
+
+    def __init__(self, params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, fused=True,
+                 betas=None):
+        if betas is not None:
+            beta1, beta2 = betas
+        super().__init__(params, lr, beta1, beta2, eps, weight_decay)
+        self.fused = fused
