@@ -1,0 +1,320 @@
+"""Headline benchmark: Qwen2.5-0.5B-shaped dense decoder, bf16 autocast, AdamW, seq 2048,
+micro-batch 8 per GPU, DDP over N GPUs of one node.  Metric: training tokens/s of the whole job
+(max over ranks of the device-timed step).
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 10 --warmup 3
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref, same config
+
+Prints ONE JSON line on rank 0.  Data: synthetic uniform token ids, random-init N(0, 0.02) weights.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+CONFIGS = {
+    "qwen2.5-0.5b": dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
+                         num_attention_heads=14, num_key_value_heads=2, head_dim=64, max_position_embeddings=2048,
+                         rope_theta=1e6, norm_eps=1e-6, tie_word_embeddings=True),
+    "qwen2.5-1.5b": dict(vocab_size=151936, hidden_size=1536, intermediate_size=8960, num_hidden_layers=28,
+                         num_attention_heads=12, num_key_value_heads=2, head_dim=128, max_position_embeddings=4096,
+                         rope_theta=1e6, norm_eps=1e-6, tie_word_embeddings=True),
+    "tiny": dict(vocab_size=4096, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=512,
+                 rope_theta=1e6, norm_eps=1e-6, tie_word_embeddings=True),
+}
+METRIC = "Qwen train tokens/sec (box, max over ranks)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env(args):
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    return rank, world, local
+
+
+def time_steps(torch, step_fn, steps, warmup, world):
+    """W warm-up steps, then K steps bracketed by barrier + synchronize; device time from CUDA events;
+    returns the max over ranks of the mean ms per step."""
+    import torch.distributed as tdist
+    for _ in range(warmup):
+        step_fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        tdist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    last = None
+    for _ in range(steps):
+        last = step_fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        tdist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, last
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    sys.path.insert(0, ROOT)
+    import genesis_b200 as genesis
+    from genesis_b200 import distributed as dist
+    from genesis_b200.models.transformers import TransformerConfig, QwenForCausalLM
+    from genesis_b200.ops import native
+
+    rank, world, local = dist_env(args)
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group(backend="nccl")
+    cfg = TransformerConfig(**CONFIGS[args.model])
+    B, S = args.micro_batch, args.seq_len
+    genesis.manual_seed(1234)
+    model = QwenForCausalLM(cfg).cuda()
+    net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
+    amp_dtype = genesis.bfloat16 if args.dtype == "bf16" else genesis.float16
+    scaler = genesis.amp.GradScaler(init_scale=2.0 ** 16) if args.dtype == "fp16" else None
+    if scaler is not None and world > 1:
+        net.set_grad_scaler(scaler)
+
+    rs = np.random.RandomState(1000 + rank)
+    pool_n = 4   # rotate over several distinct batches
+    host = [torch.from_numpy(rs.randint(0, cfg.vocab_size, (B, S + 1)).astype(np.int64)).pin_memory()
+            for _ in range(pool_n)]
+    dev_batches = [h.cuda() for h in host]
+    counter = {"i": 0}
+
+    def train_step(tokens):
+        idx = genesis.Tensor(tokens[:, :-1].contiguous())
+        labels = genesis.Tensor(tokens[:, 1:].reshape(-1).contiguous())
+        with genesis.amp.autocast(dtype=amp_dtype):
+            loss = net(idx, labels=labels, return_logits=False)
+        opt.zero_grad()
+        if scaler is not None:
+            scaler.scale(loss).backward()
+            scaler.step(opt)
+            scaler.update()
+        else:
+            loss.backward()
+            opt.step()
+        return loss
+
+    def step_device():
+        counter["i"] += 1
+        return train_step(dev_batches[counter["i"] % pool_n])
+
+    def step_e2e():
+        counter["i"] += 1
+        tokens = host[counter["i"] % pool_n].to("cuda", non_blocking=True)   # H2D from pinned memory
+        loss = train_step(tokens)
+        return float(loss._t.float().cpu())                                  # D2H of the step's loss
+
+    sampler = ClockSampler(local)
+    native.launch_count = 0
+    if rank == 0:
+        sampler.start()
+    ms, last = time_steps(torch, step_device, args.steps, args.warmup, world)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = native.launch_count // max(args.steps + args.warmup, 1) * args.steps
+    ms_e2e, last_loss = time_steps(torch, step_e2e, args.steps, max(1, args.warmup // 2), world)
+    native.check_status()
+    tokens_per_step = B * S * world
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    value = tokens_per_step / (ms / 1e3)
+    return {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": args.dtype, "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
+        "config": {"model": args.model, "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
+                   "optimizer": "AdamW lr 3e-4", "l2_policy": "working set (~20 GB activations+grads per step) >> 126 MB L2; "
+                   "4 distinct input batches rotated"},
+        "clocks": clocks,
+        "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": B * (S + 1) * 8 * world, "d2h_bytes_per_step": 4 * world,
+                "loss": last_loss},
+        "gpu_launches": launches,
+        "impl": "genesis_b200",
+    }
+
+
+def run_reference(args):
+    """The unmodified reference (installed in baseline/_ref) through its own public API:
+    QwenModel + nn.CrossEntropyLoss + optim.AdamW + amp.autocast (+ its DDP for N > 1)."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "genesis")):
+        return {"impl": "reference", "unavailable": "baseline/_ref/genesis is not installed"}
+    sys.path.insert(0, ref)
+    try:
+        import numpy as np
+        import torch
+        import genesis
+        import genesis.nn as nn
+        from genesis import amp
+        from genesis.models.transformers.config import TransformerConfig
+        from genesis.models.transformers.dense import QwenModel
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}
+    rank, world, local = dist_env(args)
+    try:
+        genesis.cuda.set_device(local)
+        torch.cuda.set_device(local)
+        if world > 1:
+            import genesis.distributed as rdist
+            from genesis.nn.parallel import DistributedDataParallel as RDDP
+            rdist.init_process_group(backend="nccl")
+        c = CONFIGS[args.model]
+        cfg = TransformerConfig(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"],
+                                intermediate_size=c["intermediate_size"], num_hidden_layers=c["num_hidden_layers"],
+                                num_attention_heads=c["num_attention_heads"],
+                                num_key_value_heads=c["num_key_value_heads"], head_dim=c["head_dim"],
+                                max_position_embeddings=c["max_position_embeddings"], rope_theta=c["rope_theta"],
+                                norm_eps=c["norm_eps"])
+        model = QwenModel(cfg)
+        model.to(genesis.device(f"cuda:{local}"))
+        net = RDDP(model, device_ids=[local]) if world > 1 else model
+        opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
+        amp_dtype = genesis.bfloat16 if args.dtype == "bf16" else genesis.float16
+        scaler = amp.GradScaler() if args.dtype == "fp16" else None
+        B, S = args.micro_batch, args.seq_len
+        rs = np.random.RandomState(1000 + rank)
+        batches = [rs.randint(0, cfg.vocab_size, (B, S + 1)).astype(np.int64) for _ in range(2)]
+        lossf = nn.CrossEntropyLoss()
+        counter = {"i": 0}
+        dev = genesis.device(f"cuda:{local}")
+
+        def step():
+            counter["i"] += 1
+            tok = batches[counter["i"] % 2]
+            inputs = genesis.tensor(tok[:, :-1], device=dev, dtype=genesis.int64)
+            targets = genesis.tensor(tok[:, 1:], device=dev, dtype=genesis.int64)
+            with amp.autocast("cuda", dtype=amp_dtype):
+                logits = net(inputs)
+                Bq, T, C = logits.shape
+                loss = lossf(genesis.reshape(logits, (Bq * T, C)), genesis.reshape(targets, (Bq * T,)))
+            if scaler is not None:
+                scaler.scale(loss).backward()
+                scaler.step(opt)
+                scaler.update()
+            else:
+                loss.backward()
+                opt.step()
+            opt.zero_grad()
+            return float(loss.item())
+
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        ms, last = time_steps(torch, step, args.steps, args.warmup, world)
+        clocks = sampler.stop() if rank == 0 else None
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        tb = traceback.format_exc().strip().splitlines()[-3:]
+        if rank != 0:
+            return None
+        return {"impl": "reference", "unavailable": f"run failed: {type(e).__name__}: {e} | {' / '.join(tb)}"[:500]}
+    if rank != 0:
+        return None
+    tokens = B * S * world
+    v = tokens / (ms / 1e3)
+    return {"metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic uniform token ids, random-init weights",
+            "config": {"model": args.model, "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
+                       "note": "reference as shipped (its DDP hooks never fire, so N>1 runs do not synchronise gradients); "
+                               "its step includes the host->device copy of the batch and loss.item()"},
+            "clocks": clocks, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": B * S * 16 * world,
+                                      "d2h_bytes_per_step": 4 * world, "loss": last},
+            "impl": "reference"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen2.5-0.5b", choices=sorted(CONFIGS))
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.gpus > 1 and world == 1:
+        # convenience: re-launch under torchrun
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,301 @@
+// Fused RMSNorm and LayerNorm, forward and backward.  fp32 math, 128-bit loads, the row is read
+// once and kept in registers between the statistics pass and the normalisation pass.  Weight/bias
+// gradients are reduced deterministically: every CTA accumulates the rows it owns into a private
+// fp32 partial row, and a second kernel sums the partials column-wise (no atomics, no spin locks).
+// Reference counterparts: genesis/nn/triton_ops/rmsnorm.py:14-126, genesis/nn/layer_norm.py:15-213,
+// genesis/nn/triton_ops/layer_norm.py:16-133.
+#include "common.cuh"
+
+namespace gb {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV_LIMIT = 8;   // at most this many 16-byte vectors cached per thread
+
+template <typename T, int NORM_MAXV>
+__device__ __forceinline__ int load_row(const T* p, long long cols, Vec16<T> (&buf)[NORM_MAXV]) {
+  constexpr int V = Vec16<T>::N;
+  const int nv = (int)(cols / V);
+  int cnt = 0;
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k) {
+    const int i = threadIdx.x + k * NORM_THREADS;
+    if (i < nv) { buf[k] = ld16(p + (long long)i * V); cnt = k + 1; }
+  }
+  return cnt;
+}
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm
+// ------------------------------------------------------------------------------------------
+template <typename T, typename TW, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restrict__ y, float* __restrict__ rstd,
+                   long long rows, int cols, float eps) {
+  __shared__ float sh[32];
+  constexpr int V = Vec16<T>::N;
+  const int nv = cols / V;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    Vec16<T> buf[NORM_MAXV];
+    load_row<T, NORM_MAXV>(x + row * cols, cols, buf);
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k)
+      if (threadIdx.x + k * NORM_THREADS < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) { float v = Cvt<T>::to_f(buf[k].v[j]); ss += v * v; }
+    ss = block_sum(ss, sh);
+    const float r = rsqrtf(ss / cols + eps);
+    if (threadIdx.x == 0) rstd[row] = r;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k) {
+      const int i = threadIdx.x + k * NORM_THREADS;
+      if (i < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+          o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(buf[k].v[j]) * r * Cvt<TW>::to_f(w[i * V + j]));
+        st16(y + row * cols + (long long)i * V, o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (g*w - xhat * mean(g*w*xhat));  dw partial[cta] += g * xhat
+template <typename T, typename TW, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* __restrict__ w,
+                   const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_partial,
+                   long long rows, int cols) {
+  __shared__ float sh[32];
+  constexpr int V = Vec16<T>::N;
+  const int nv = cols / V;
+  float dwacc[NORM_MAXV][V];
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k)
+#pragma unroll
+    for (int j = 0; j < V; ++j) dwacc[k][j] = 0.f;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    Vec16<T> xb[NORM_MAXV], gb_[NORM_MAXV];
+    load_row<T, NORM_MAXV>(x + row * cols, cols, xb);
+    load_row<T, NORM_MAXV>(g + row * cols, cols, gb_);
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k) {
+      const int i = threadIdx.x + k * NORM_THREADS;
+      if (i < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
+          const float gg = Cvt<T>::to_f(gb_[k].v[j]);
+          dot += gg * Cvt<TW>::to_f(w[i * V + j]) * xh;
+          dwacc[k][j] += gg * xh;
+        }
+    }
+    dot = block_sum(dot, sh) / cols;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k) {
+      const int i = threadIdx.x + k * NORM_THREADS;
+      if (i < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
+          const float gw = Cvt<T>::to_f(gb_[k].v[j]) * Cvt<TW>::to_f(w[i * V + j]);
+          o.v[j] = Cvt<T>::from_f(r * (gw - xh * dot));
+        }
+        st16(dx + row * cols + (long long)i * V, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k) {
+    const int i = threadIdx.x + k * NORM_THREADS;
+    if (i < nv)
+#pragma unroll
+      for (int j = 0; j < V; ++j) dw_partial[(long long)blockIdx.x * cols + i * V + j] = dwacc[k][j];
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// LayerNorm
+// ------------------------------------------------------------------------------------------
+template <typename T, typename TW, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b, T* __restrict__ y,
+                     float* __restrict__ mean, float* __restrict__ rstd, long long rows, int cols, float eps) {
+  __shared__ float sh[32];
+  constexpr int V = Vec16<T>::N;
+  const int nv = cols / V;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    Vec16<T> buf[NORM_MAXV];
+    load_row<T, NORM_MAXV>(x + row * cols, cols, buf);
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k)
+      if (threadIdx.x + k * NORM_THREADS < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) s += Cvt<T>::to_f(buf[k].v[j]);
+    const float mu = block_sum(s, sh) / cols;
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k)
+      if (threadIdx.x + k * NORM_THREADS < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) { float d = Cvt<T>::to_f(buf[k].v[j]) - mu; ss += d * d; }
+    const float r = rsqrtf(block_sum(ss, sh) / cols + eps);
+    if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = r; }
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k) {
+      const int i = threadIdx.x + k * NORM_THREADS;
+      if (i < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float v = (Cvt<T>::to_f(buf[k].v[j]) - mu) * r;
+          if (w != nullptr) v *= Cvt<TW>::to_f(w[i * V + j]);
+          if (b != nullptr) v += Cvt<TW>::to_f(b[i * V + j]);
+          o.v[j] = Cvt<T>::from_f(v);
+        }
+        st16(y + row * cols + (long long)i * V, o);
+      }
+    }
+  }
+}
+
+template <typename T, typename TW, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* __restrict__ w,
+                     const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+                     float* __restrict__ dw_partial, float* __restrict__ db_partial, long long rows, int cols) {
+  __shared__ float sh[32];
+  constexpr int V = Vec16<T>::N;
+  const int nv = cols / V;
+  float dwacc[NORM_MAXV][V], dbacc[NORM_MAXV][V];
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k)
+#pragma unroll
+    for (int j = 0; j < V; ++j) { dwacc[k][j] = 0.f; dbacc[k][j] = 0.f; }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    Vec16<T> xb[NORM_MAXV], gb_[NORM_MAXV];
+    load_row<T, NORM_MAXV>(x + row * cols, cols, xb);
+    load_row<T, NORM_MAXV>(g + row * cols, cols, gb_);
+    const float mu = mean[row], r = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k) {
+      const int i = threadIdx.x + k * NORM_THREADS;
+      if (i < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (Cvt<T>::to_f(xb[k].v[j]) - mu) * r;
+          const float gg = Cvt<T>::to_f(gb_[k].v[j]);
+          const float gw = w != nullptr ? gg * Cvt<TW>::to_f(w[i * V + j]) : gg;
+          s1 += gw;
+          s2 += gw * xh;
+          dwacc[k][j] += gg * xh;
+          dbacc[k][j] += gg;
+        }
+    }
+    s1 = block_sum(s1, sh) / cols;
+    s2 = block_sum(s2, sh) / cols;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXV; ++k) {
+      const int i = threadIdx.x + k * NORM_THREADS;
+      if (i < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (Cvt<T>::to_f(xb[k].v[j]) - mu) * r;
+          const float gg = Cvt<T>::to_f(gb_[k].v[j]);
+          const float gw = w != nullptr ? gg * Cvt<TW>::to_f(w[i * V + j]) : gg;
+          o.v[j] = Cvt<T>::from_f(r * (gw - s1 - xh * s2));
+        }
+        st16(dx + row * cols + (long long)i * V, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k) {
+    const int i = threadIdx.x + k * NORM_THREADS;
+    if (i < nv)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        dw_partial[(long long)blockIdx.x * cols + i * V + j] = dwacc[k][j];
+        db_partial[(long long)blockIdx.x * cols + i * V + j] = dbacc[k][j];
+      }
+  }
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+#define NORM_DISPATCH_T(dt, wdt, ...)                                                            \
+  do {                                                                                           \
+    if (dt == DT_F32 && wdt == DT_F32) { using T = float; using TW = float; __VA_ARGS__; }       \
+    else if (dt == DT_BF16 && wdt == DT_F32) { using T = __nv_bfloat16; using TW = float; __VA_ARGS__; } \
+    else if (dt == DT_F16 && wdt == DT_F32) { using T = __half; using TW = float; __VA_ARGS__; } \
+    else if (dt == DT_BF16 && wdt == DT_BF16) { using T = __nv_bfloat16; using TW = __nv_bfloat16; __VA_ARGS__; } \
+    else if (dt == DT_F16 && wdt == DT_F16) { using T = __half; using TW = __half; __VA_ARGS__; } \
+    else return -2;                                                                              \
+  } while (0)
+
+// MV = 16-byte vectors cached per thread, the smallest of {1, 2, 4, 8} that covers a row
+#define NORM_DISPATCH(dt, wdt, cols, ...)                                                        \
+  do {                                                                                           \
+    const int nvec_ = (cols) / ((dt) == DT_F32 ? 4 : 8);                                         \
+    if (nvec_ <= NORM_THREADS) { constexpr int MV = 1; NORM_DISPATCH_T(dt, wdt, __VA_ARGS__); }  \
+    else if (nvec_ <= 2 * NORM_THREADS) { constexpr int MV = 2; NORM_DISPATCH_T(dt, wdt, __VA_ARGS__); } \
+    else if (nvec_ <= 4 * NORM_THREADS) { constexpr int MV = 4; NORM_DISPATCH_T(dt, wdt, __VA_ARGS__); } \
+    else { constexpr int MV = 8; NORM_DISPATCH_T(dt, wdt, __VA_ARGS__); }                        \
+  } while (0)
+
+static inline bool norm_cols_ok(int cols, int dt) {
+  const int v = dt == DT_F32 ? 4 : 8;
+  return cols % v == 0 && cols / v <= NORM_THREADS * NORM_MAXV_LIMIT;
+}
+
+// Number of CTAs the backward kernels use (= rows of the partial buffers).
+extern "C" int gb_norm_bwd_ctas(long long rows) { return (int)(rows < 148 * 4 ? rows : 148 * 4); }
+
+extern "C" int gb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int cols,
+                              float eps, int dt, int wdt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (!norm_cols_ok(cols, dt)) return -2;
+  const int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
+  NORM_DISPATCH(dt, wdt, cols, rmsnorm_fwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
+      (const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, void* dx,
+                              float* dw_partial, long long rows, int cols, int dt, int wdt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (!norm_cols_ok(cols, dt)) return -2;
+  const int grid = gb_norm_bwd_ctas(rows);
+  NORM_DISPATCH(dt, wdt, cols, rmsnorm_bwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
+      (const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                long long rows, int cols, float eps, int dt, int wdt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (!norm_cols_ok(cols, dt)) return -2;
+  const int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
+  NORM_DISPATCH(dt, wdt, cols, layernorm_fwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
+      (const T*)x, (const TW*)w, (const TW*)b, (T*)y, mean, rstd, rows, cols, eps));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_layernorm_bwd(const void* g, const void* x, const void* w, const float* mean, const float* rstd,
+                                void* dx, float* dw_partial, float* db_partial, long long rows, int cols, int dt,
+                                int wdt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (!norm_cols_ok(cols, dt)) return -2;
+  const int grid = gb_norm_bwd_ctas(rows);
+  NORM_DISPATCH(dt, wdt, cols, layernorm_bwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
+      (const T*)g, (const T*)x, (const TW*)w, mean, rstd, (T*)dx, dw_partial, db_partial, rows, cols));
+  return (int)cudaGetLastError();
+}

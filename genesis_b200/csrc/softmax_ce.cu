@@ -1,0 +1,204 @@
+// Softmax / log-softmax over the last dimension (forward, backward) and fused softmax
+// cross-entropy for large vocabularies (forward: loss + log-sum-exp per row; backward: (p - onehot)
+// * row gradient, optionally written over the logits).  One CTA per row, online max/sum in fp32,
+// 128-bit loads; rows that fit are kept in registers, longer rows are re-read (they stay in L2).
+// Reference counterparts: genesis/nn/triton_ops/softmax.py:33-480 and the composed loss of
+// genesis/nn/modules/loss.py:77-100 / genesis/nn/functional.py:2313-2506.
+#include "common.cuh"
+
+namespace gb {
+
+struct MaxSum { float m, s; };
+__device__ __forceinline__ MaxSum ms_comb(MaxSum a, MaxSum b) {
+  MaxSum r;
+  r.m = fmaxf(a.m, b.m);
+  if (r.m == -INFINITY) { r.s = 0.f; return r; }
+  r.s = a.s * __expf(a.m - r.m) + b.s * __expf(b.m - r.m);
+  return r;
+}
+__device__ __forceinline__ MaxSum block_maxsum(MaxSum v, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum t; t.m = __shfl_xor_sync(0xffffffffu, v.m, o); t.s = __shfl_xor_sync(0xffffffffu, v.s, o);
+    v = ms_comb(v, t);
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) { sh[w] = v.m; sh[32 + w] = v.s; }
+  __syncthreads();
+  MaxSum r; r.m = lane < nw ? sh[lane] : -INFINITY; r.s = lane < nw ? sh[32 + lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum t; t.m = __shfl_xor_sync(0xffffffffu, r.m, o); t.s = __shfl_xor_sync(0xffffffffu, r.s, o);
+    r = ms_comb(r, t);
+  }
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ MaxSum row_maxsum(const T* p, long long cols, float* sh) {
+  constexpr int V = Vec16<T>::N;
+  MaxSum acc; acc.m = -INFINITY; acc.s = 0.f;
+  long long done = 0;
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    const long long nv = cols / V;
+    for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+      Vec16<T> a = ld16(p + i * V);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < V; ++j) mx = fmaxf(mx, Cvt<T>::to_f(a.v[j]));
+      if (mx > acc.m) { acc.s *= __expf(acc.m - mx); acc.m = mx; }
+      if (acc.m != -INFINITY) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc.s += __expf(Cvt<T>::to_f(a.v[j]) - acc.m);
+      }
+    }
+    done = nv * V;
+  }
+  for (long long i = done + threadIdx.x; i < cols; i += blockDim.x) {
+    const float v = Cvt<T>::to_f(p[i]);
+    if (v > acc.m) { acc.s *= __expf(acc.m - v); acc.m = v; }
+    if (acc.m != -INFINITY) acc.s += __expf(v - acc.m);
+  }
+  return block_maxsum(acc, sh);
+}
+
+template <typename T>
+__global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, long long cols,
+                                   int log_mode) {
+  __shared__ float sh[64];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* p = x + row * cols;
+    T* q = y + row * cols;
+    const MaxSum ms = row_maxsum(p, cols, sh);
+    const float lse = ms.m + __logf(ms.s);
+    const float inv = 1.f / ms.s;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float v = Cvt<T>::to_f(p[i]);
+      q[i] = Cvt<T>::from_f(log_mode ? v - lse : __expf(v - ms.m) * inv);
+    }
+  }
+}
+
+// softmax: dx = y * (g - sum(g*y));  log-softmax: dx = g - exp(y) * sum(g)
+template <typename T>
+__global__ void softmax_bwd_kernel(const T* __restrict__ g, const T* __restrict__ y, T* __restrict__ dx,
+                                   long long rows, long long cols, int log_mode) {
+  __shared__ float sh[32];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* gp = g + row * cols;
+    const T* yp = y + row * cols;
+    float acc = 0.f;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float gg = Cvt<T>::to_f(gp[i]);
+      acc += log_mode ? gg : gg * Cvt<T>::to_f(yp[i]);
+    }
+    acc = block_sum(acc, sh);
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float gg = Cvt<T>::to_f(gp[i]), yy = Cvt<T>::to_f(yp[i]);
+      dx[row * cols + i] = Cvt<T>::from_f(log_mode ? gg - __expf(yy) * acc : yy * (gg - acc));
+    }
+  }
+}
+
+template <typename T, typename TI>
+__global__ void __launch_bounds__(1024)
+ce_fwd_kernel(const T* __restrict__ logits, const TI* __restrict__ target, float* __restrict__ loss,
+              float* __restrict__ lse_out, long long rows, long long cols, long long ignore_index) {
+  __shared__ float sh[64];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* p = logits + row * cols;
+    const MaxSum ms = row_maxsum(p, cols, sh);
+    if (threadIdx.x == 0) {
+      const float lse = ms.m + logf(ms.s);
+      lse_out[row] = lse;
+      const long long t = (long long)target[row];
+      loss[row] = (t == ignore_index || t < 0 || t >= cols) ? 0.f : lse - Cvt<T>::to_f(p[t]);
+    }
+  }
+}
+
+template <typename T, typename TI>
+__global__ void __launch_bounds__(1024)
+ce_bwd_kernel(const T* __restrict__ logits, const TI* __restrict__ target, const float* __restrict__ lse,
+              const float* __restrict__ grow, T* __restrict__ dlogits, long long rows, long long cols,
+              long long ignore_index) {
+  constexpr int V = Vec16<T>::N;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* p = logits + row * cols;
+    T* q = dlogits + row * cols;
+    const long long t = (long long)target[row];
+    const bool ignored = (t == ignore_index || t < 0 || t >= cols);
+    const float gr = ignored ? 0.f : grow[row];
+    const float l = lse[row];
+    long long done = 0;
+    if (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(q)) & 15) == 0) {
+      const long long nv = cols / V;
+      for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+        Vec16<T> a = ld16(p + i * V), o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float pr = __expf(Cvt<T>::to_f(a.v[j]) - l);
+          if (i * V + j == t) pr -= 1.f;
+          o.v[j] = Cvt<T>::from_f(pr * gr);
+        }
+        st16(q + i * V, o);
+      }
+      done = nv * V;
+    }
+    for (long long i = done + threadIdx.x; i < cols; i += blockDim.x) {
+      float pr = __expf(Cvt<T>::to_f(p[i]) - l);
+      if (i == t) pr -= 1.f;
+      q[i] = Cvt<T>::from_f(pr * gr);
+    }
+  }
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+static inline int row_block(long long cols) { return cols >= 8192 ? 1024 : (cols >= 2048 ? 512 : (cols >= 256 ? 256 : 64)); }
+
+extern "C" int gb_softmax_fwd(const void* x, void* y, long long rows, long long cols, int log_mode, int dt,
+                              cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  GB_DISPATCH_FLOAT(dt, T, softmax_fwd_kernel<T><<<grid, row_block(cols), 0, st>>>((const T*)x, (T*)y, rows, cols, log_mode));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_softmax_bwd(const void* g, const void* y, void* dx, long long rows, long long cols, int log_mode,
+                              int dt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  GB_DISPATCH_FLOAT(dt, T, softmax_bwd_kernel<T><<<grid, row_block(cols), 0, st>>>((const T*)g, (const T*)y, (T*)dx, rows, cols, log_mode));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_ce_fwd(const void* logits, const void* target, float* loss, float* lse, long long rows,
+                         long long cols, long long ignore_index, int dt, int target_is_i64, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
+  const int block = row_block(cols);
+  if (target_is_i64) {
+    GB_DISPATCH_FLOAT(dt, T, ce_fwd_kernel<T, long long><<<grid, block, 0, st>>>((const T*)logits, (const long long*)target, loss, lse, rows, cols, ignore_index));
+  } else {
+    GB_DISPATCH_FLOAT(dt, T, ce_fwd_kernel<T, int><<<grid, block, 0, st>>>((const T*)logits, (const int*)target, loss, lse, rows, cols, ignore_index));
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_ce_bwd(const void* logits, const void* target, const float* lse, const float* grow, void* dlogits,
+                         long long rows, long long cols, long long ignore_index, int dt, int target_is_i64,
+                         cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
+  const int block = row_block(cols);
+  if (target_is_i64) {
+    GB_DISPATCH_FLOAT(dt, T, ce_bwd_kernel<T, long long><<<grid, block, 0, st>>>((const T*)logits, (const long long*)target, lse, grow, (T*)dlogits, rows, cols, ignore_index));
+  } else {
+    GB_DISPATCH_FLOAT(dt, T, ce_bwd_kernel<T, int><<<grid, block, 0, st>>>((const T*)logits, (const int*)target, lse, grow, (T*)dlogits, rows, cols, ignore_index));
+  }
+  return (int)cudaGetLastError();
+}

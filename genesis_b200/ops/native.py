@@ -1,7 +1,992 @@
-"""placeholder until the CUDA library lands"""
+"""ctypes bindings of `libgenesis_b200.so` (hand-written sm_100a kernels, sources in `csrc/`).
+
+Every wrapper takes and returns `torch.Tensor`s, launches on torch's current CUDA stream and
+returns `NotImplemented` for inputs the kernel family does not cover (float64 / integer math,
+misaligned views, > 6-D strided copies ...), in which case `dispatch` uses the generic op.
+On a machine with a GPU the library is mandatory: import fails loudly if it is missing.
+"""
+import ctypes
+import math
+import os
+
+import torch
+
+from .. import _lib
+
+F32, F16, BF16 = torch.float32, torch.float16, torch.bfloat16
+_DT = {F32: 0, F16: 1, BF16: 2, torch.float64: 3, torch.int32: 4, torch.int64: 5, torch.uint8: 6, torch.bool: 7}
+_FLOATS = (F32, F16, BF16)
+
+_BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3, "max": 4, "min": 5, "rsub": 6, "rdiv": 7, "pow": 8, "rpow": 9}
+_UN = {"neg": 0, "exp": 1, "log": 2, "sqrt": 3, "rsqrt": 4, "sin": 5, "cos": 6, "tanh": 7, "sigmoid": 8, "relu": 9,
+       "abs": 10, "sign": 11, "silu": 12, "gelu": 13, "reciprocal": 14}
+_CMP = {"eq": 0, "ne": 1, "lt": 2, "le": 3, "gt": 4, "ge": 5}
+_RED = {"sum": 0, "mean": 0, "max": 1, "min": 2}
+
+_C = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float,
+      "u": ctypes.c_ulonglong, "I": ctypes.c_uint, "z": ctypes.c_size_t}
+
+# name -> argument type codes (see _C); the trailing stream is a "p"
+_SIGS = {
+    "gb_binary": "ippplip", "gb_binary_scalar": "ipfplip", "gb_binary_strided": "ippppppip",
+    "gb_unary": "ipplip", "gb_unary_bwd": "ippplip", "gb_clamp": "ppfflip", "gb_compare": "ippfiplip",
+    "gb_where": "pppffiiplip", "gb_cast": "ppliip", "gb_fill": "plfip", "gb_axpy": "ppfliip",
+    "gb_copy_strided": "ppipppip", "gb_transpose": "ppiiilllip",
+    "gb_reduce_rows": "ippllfiip", "gb_reduce_mid": "ipplllifiip",
+    "gb_rmsnorm_fwd": "pppplifiip", "gb_rmsnorm_bwd": "pppppplii" + "ip", "gb_layernorm_fwd": "pppppplifiip",
+    "gb_layernorm_bwd": "pppppppp" + "liiip", "gb_norm_bwd_ctas": "l",
+    "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
+    "gb_ce_fwd": "ppppllliip", "gb_ce_bwd": "ppppplll" + "iip",
+    "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip", "gb_rope": "pppppiiiiiip",
+    "gb_gather_rows": "pppllip", "gb_scatter_add_rows": "pppliiip",
+    "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
+    "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiippp", "gb_sgd_multi": "pilfffp",
+    "gb_grad_multi": "pilpfppip",
+    "gb_router_fwd": "ppppp" + "liiiip", "gb_router_bwd": "pppppp" + "liiiip",
+    "gb_moe_sort": "pppppp" + "liiilp", "gb_moe_combine": "pppp" + "liiip", "gb_moe_combine_bwd": "pppppp" + "liiip",
+    "gb_gemm": "pppp" + "iiii" + "ll" + "i" + "lll" + "ii" + "iii" + "i" + "f" + "i" + "p" + "i" + "p" + "i" + "p",
+    "gb_allreduce_fused": "ppllii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "pp",
+    "gb_wait_flag": "pIupp",
+}
+
+_L = None
+_sm_count = {}
+_status = {}
 
 
-def __getattr__(name):
-    def _ni(*a, **k):
+def lib():
+    global _L
+    if _L is None:
+        L = _lib.get(required=True)
+        for name, sig in _SIGS.items():
+            fn = getattr(L, name)
+            fn.argtypes = [_C[c] for c in sig]
+            fn.restype = ctypes.c_int
+        _L = L
+    return _L
+
+
+available = _lib.available
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+launch_count = 0   # native launches since import (every wrapper call below launches >= 1 kernel)
+
+
+def _chk(rc, what):
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def _sms(dev):
+    i = dev.index if dev.index is not None else torch.cuda.current_device()
+    if i not in _sm_count:
+        _sm_count[i] = torch.cuda.get_device_properties(i).multi_processor_count
+    return _sm_count[i]
+
+
+def status_tensor(dev):
+    """Per-device int32[8] word where kernels record a bounded-wait expiry."""
+    i = dev.index if dev.index is not None else torch.cuda.current_device()
+    if i not in _status:
+        _status[i] = torch.zeros(8, dtype=torch.int32, device=dev)
+    return _status[i]
+
+
+def check_status(dev=None):
+    """Synchronising read of the status word; raises if a kernel gave up waiting."""
+    dev = dev or torch.device("cuda", torch.cuda.current_device())
+    st = status_tensor(dev)
+    rec = st.tolist()
+    if rec[0] != 0:
+        st.zero_()
+        raise RuntimeError(f"device-side wait expired: code={rec[0]} site={rec[1]} block={rec[2]} extra={rec[3]}")
+
+
+def _ok(t):
+    return t.dtype in _FLOATS and t.is_contiguous() and t.data_ptr() % 16 == 0
+
+
+# =============================== elementwise =====================================
+def binary(name, a, b):
+    op = _BIN.get(name)
+    ta, tb = isinstance(a, torch.Tensor), isinstance(b, torch.Tensor)
+    if ta and tb:
+        if a.dtype != b.dtype or a.dtype not in _FLOATS:
+            return NotImplemented
+        if a.shape == b.shape and _ok(a) and _ok(b):
+            out = torch.empty_like(a)
+            _chk(lib().gb_binary(op, a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _DT[a.dtype], _st()), name)
+            return out
+        try:
+            shape = torch.broadcast_shapes(a.shape, b.shape)
+        except RuntimeError:
+            return NotImplemented
+        if len(shape) > 4:
+            return NotImplemented
+        ae, be = a.expand(shape), b.expand(shape)
+        pad = 4 - len(shape)
+        sh = (ctypes.c_longlong * 4)(*([1] * pad + list(shape)))
+        sa = (ctypes.c_longlong * 4)(*([0] * pad + list(ae.stride())))
+        sb = (ctypes.c_longlong * 4)(*([0] * pad + list(be.stride())))
+        out = torch.empty(shape, dtype=a.dtype, device=a.device)
+        _chk(lib().gb_binary_strided(op, a.data_ptr(), b.data_ptr(), out.data_ptr(), sh, sa, sb, _DT[a.dtype], _st()),
+             name)
+        return out
+    if not ta and not tb:
         return NotImplemented
-    return _ni
+    t, s, rev = (a, b, False) if ta else (b, a, True)
+    if not _ok(t) or isinstance(s, (bool, complex)) or not isinstance(s, (int, float)):
+        return NotImplemented
+    if rev:
+        op = {"add": 0, "mul": 2, "sub": 6, "div": 7, "max": 4, "min": 5}.get(name)
+        if op is None:
+            return NotImplemented
+    out = torch.empty_like(t)
+    _chk(lib().gb_binary_scalar(op, t.data_ptr(), float(s), out.data_ptr(), t.numel(), _DT[t.dtype], _st()), name)
+    return out
+
+
+def scalar_op(name, t, s):
+    if not _ok(t):
+        return NotImplemented
+    out = torch.empty_like(t)
+    _chk(lib().gb_binary_scalar(_BIN[name], t.data_ptr(), float(s), out.data_ptr(), t.numel(), _DT[t.dtype], _st()),
+         name)
+    return out
+
+
+def add_(a, b, alpha=1.0):
+    if not (isinstance(b, torch.Tensor) and a.shape == b.shape and _ok(a) and b.dtype in _FLOATS
+            and b.is_contiguous()):
+        return NotImplemented
+    _chk(lib().gb_axpy(a.data_ptr(), b.data_ptr(), float(alpha), a.numel(), _DT[a.dtype], _DT[b.dtype], _st()), "axpy")
+    return a
+
+
+def mul_(a, b):
+    if isinstance(b, torch.Tensor) or not _ok(a):
+        return NotImplemented
+    _chk(lib().gb_binary_scalar(2, a.data_ptr(), float(b), a.data_ptr(), a.numel(), _DT[a.dtype], _st()), "mul_")
+    return a
+
+
+def unary(name, t):
+    if name not in _UN or not _ok(t):
+        return NotImplemented
+    out = torch.empty_like(t)
+    _chk(lib().gb_unary(_UN[name], t.data_ptr(), out.data_ptr(), t.numel(), _DT[t.dtype], _st()), name)
+    return out
+
+
+def unary_bwd(name, g, t, y=None):
+    if name not in _UN:
+        return NotImplemented
+    if name in ("exp", "sqrt", "tanh", "sigmoid"):
+        t = y if y is not None else t
+    if name == "neg":
+        t = g
+    if t is None or not _ok(g) or not _ok(t) or g.dtype != t.dtype or g.shape != t.shape:
+        return NotImplemented
+    out = torch.empty_like(g)
+    _chk(lib().gb_unary_bwd(_UN[name], g.data_ptr(), t.data_ptr(), out.data_ptr(), g.numel(), _DT[g.dtype], _st()),
+         name)
+    return out
+
+
+def clamp(t, lo, hi):
+    if not _ok(t):
+        return NotImplemented
+    out = torch.empty_like(t)
+    _chk(lib().gb_clamp(t.data_ptr(), out.data_ptr(), float("-inf") if lo is None else float(lo),
+                        float("inf") if hi is None else float(hi), t.numel(), _DT[t.dtype], _st()), "clamp")
+    return out
+
+
+def compare(name, a, b):
+    if not isinstance(a, torch.Tensor) or not _ok(a):
+        return NotImplemented
+    out = torch.empty(a.shape, dtype=torch.bool, device=a.device)
+    if isinstance(b, torch.Tensor):
+        if b.shape != a.shape or b.dtype != a.dtype or not _ok(b):
+            return NotImplemented
+        _chk(lib().gb_compare(_CMP[name], a.data_ptr(), b.data_ptr(), 0.0, 0, out.data_ptr(), a.numel(),
+                              _DT[a.dtype], _st()), name)
+    elif isinstance(b, (int, float)) and not isinstance(b, bool):
+        _chk(lib().gb_compare(_CMP[name], a.data_ptr(), None, float(b), 1, out.data_ptr(), a.numel(),
+                              _DT[a.dtype], _st()), name)
+    else:
+        return NotImplemented
+    return out
+
+
+def where(c, a, b):
+    ta, tb = isinstance(a, torch.Tensor), isinstance(b, torch.Tensor)
+    ref = a if ta else (b if tb else None)
+    if ref is None or not _ok(ref) or c.dtype != torch.bool or c.shape != ref.shape or not c.is_contiguous():
+        return NotImplemented
+    for x in (a, b):
+        if isinstance(x, torch.Tensor) and (x.shape != ref.shape or x.dtype != ref.dtype or not _ok(x)):
+            return NotImplemented
+    out = torch.empty_like(ref)
+    _chk(lib().gb_where(c.data_ptr(), a.data_ptr() if ta else None, b.data_ptr() if tb else None,
+                        0.0 if ta else float(a), 0.0 if tb else float(b), 0 if ta else 1, 0 if tb else 1,
+                        out.data_ptr(), ref.numel(), _DT[ref.dtype], _st()), "where")
+    return out
+
+
+def cast(t, dtype):
+    if t.dtype not in _FLOATS or dtype not in _FLOATS or not t.is_contiguous() or t.data_ptr() % 16:
+        return NotImplemented
+    out = torch.empty(t.shape, dtype=dtype, device=t.device)
+    _chk(lib().gb_cast(t.data_ptr(), out.data_ptr(), t.numel(), _DT[t.dtype], _DT[dtype], _st()), "cast")
+    return out
+
+
+def fill_(t, value):
+    if not _ok(t):
+        return NotImplemented
+    _chk(lib().gb_fill(t.data_ptr(), t.numel(), float(value), _DT[t.dtype], _st()), "fill")
+    return t
+
+
+def _strided_copy(src, dst):
+    nd = src.dim()
+    if nd > 6 or nd == 0:
+        return False
+    sh = (ctypes.c_longlong * 6)(*src.shape)
+    ss = (ctypes.c_longlong * 6)(*src.stride())
+    ds = (ctypes.c_longlong * 6)(*dst.stride())
+    _chk(lib().gb_copy_strided(src.data_ptr(), dst.data_ptr(), nd, sh, ss, ds, src.element_size(), _st()), "copy")
+    return True
+
+
+def contiguous(t):
+    if t.numel() == 0 or t.element_size() not in (1, 2, 4, 8) or t.is_complex():
+        return NotImplemented
+    out = torch.empty(t.shape, dtype=t.dtype, device=t.device)
+    # batched 2-D transpose (last two dims swapped in memory) goes through the smem-tiled kernel
+    if t.dim() >= 2 and t.stride(-2) == 1 and t.element_size() in (2, 4, 8):
+        R, Cc = t.shape[-2], t.shape[-1]
+        lead = t.shape[:-2]
+        tt = t.transpose(-1, -2)           # [.., C, R] view whose last dim is memory-contiguous
+        batch = 1
+        for s in lead:
+            batch *= s
+        flat, s_b = None, 0
+        if len(lead) == 0:
+            flat = tt
+        else:
+            try:
+                flat = tt.view(batch, Cc, R)
+                s_b = flat.stride(0)
+            except RuntimeError:
+                flat = None
+        if flat is not None and batch <= 65535:
+            # dst[b][r][c] = src_mem[b][c][r]: kernel writes dst[b][c'][r'] = src[b][r'][c'] with R'=C.. so swap roles
+            _chk(lib().gb_transpose(flat.data_ptr(), out.data_ptr(), batch, Cc, R, s_b, flat.stride(-2),
+                                    flat.stride(-1), t.element_size(), _st()), "transpose")
+            return out
+    if not _strided_copy(t, out):
+        return NotImplemented
+    return out
+
+
+def copy_(dst, src):
+    if dst.shape != src.shape or dst.numel() == 0:
+        return NotImplemented
+    if dst.dtype == src.dtype:
+        if dst.element_size() not in (1, 2, 4, 8) or dst.dim() > 6 or dst.dim() == 0 or dst.is_complex():
+            return NotImplemented
+        if dst.is_contiguous() and src.is_contiguous():
+            n = dst.numel() * dst.element_size()
+            es = 8 if (n % 8 == 0 and dst.data_ptr() % 8 == 0 and src.data_ptr() % 8 == 0) else dst.element_size()
+            one = (ctypes.c_longlong * 6)(n // es)
+            st1 = (ctypes.c_longlong * 6)(1)
+            _chk(lib().gb_copy_strided(src.data_ptr(), dst.data_ptr(), 1, one, st1, st1, es, _st()), "copy")
+            return dst
+        return dst if _strided_copy(src, dst) else NotImplemented
+    if dst.dtype in _FLOATS and src.dtype in _FLOATS and dst.is_contiguous() and src.is_contiguous() \
+            and dst.data_ptr() % 16 == 0 and src.data_ptr() % 16 == 0:
+        _chk(lib().gb_cast(src.data_ptr(), dst.data_ptr(), src.numel(), _DT[src.dtype], _DT[dst.dtype], _st()), "cast")
+        return dst
+    return NotImplemented
+
+
+# ================================= reductions ====================================
+def _reduce3(op, x, outer, red, inner, scale, out_dtype):
+    """x contiguous, viewed as [outer, red, inner] -> [outer, inner]."""
+    L = lib()
+    out = torch.empty(outer * inner, dtype=out_dtype, device=x.device)
+    if inner == 1:
+        _chk(L.gb_reduce_rows(op, x.data_ptr(), out.data_ptr(), outer, red, scale, _DT[x.dtype], _DT[out_dtype], _st()),
+             "reduce_rows")
+        return out
+    if outer > 65535:
+        return None
+    splits = 1
+    if outer * inner < 148 * 256 and red >= 512:
+        splits = int(min(64, max(1, red // 128), max(1, (148 * 512) // max(outer * inner, 1))))
+    if splits == 1:
+        _chk(L.gb_reduce_mid(op, x.data_ptr(), out.data_ptr(), outer, red, inner, 1, scale, _DT[x.dtype],
+                             _DT[out_dtype], _st()), "reduce_mid")
+        return out
+    part = torch.empty(splits * outer * inner, dtype=F32, device=x.device)
+    _chk(L.gb_reduce_mid(op, x.data_ptr(), part.data_ptr(), outer, red, inner, splits, 1.0, _DT[x.dtype], 0, _st()),
+         "reduce_mid")
+    _chk(L.gb_reduce_mid(op, part.data_ptr(), out.data_ptr(), 1, splits, outer * inner, 1, scale, 0,
+                         _DT[out_dtype], _st()), "reduce_mid2")
+    return out
+
+
+def reduce(name, t, dims, keepdim):
+    if t.dtype not in _FLOATS or t.numel() == 0:
+        return NotImplemented
+    op = _RED[name]
+    x = t if t.is_contiguous() else None
+    if x is None:
+        c = contiguous(t)
+        if c is NotImplemented:
+            return NotImplemented
+        x = c
+    shape = list(x.shape)
+    nd = len(shape)
+    if dims is None:
+        n = x.numel()
+        scale = 1.0 / n if name == "mean" else 1.0
+        C = 8192
+        if n <= 65536:
+            out = _reduce3(op, x, 1, n, 1, scale, x.dtype)
+        else:
+            R = n // C
+            parts = torch.empty(R + 1, dtype=F32, device=x.device)
+            _chk(lib().gb_reduce_rows(op, x.data_ptr(), parts.data_ptr(), R, C, 1.0, _DT[x.dtype], 0, _st()), "reduce")
+            tail = x.reshape(-1)[R * C:]
+            if tail.numel():
+                _chk(lib().gb_reduce_rows(op, tail.data_ptr(), parts[R:].data_ptr(), 1, tail.numel(), 1.0,
+                                          _DT[x.dtype], 0, _st()), "reduce")
+                out = _reduce3(op, parts, 1, R + 1, 1, scale, x.dtype)
+            else:
+                out = _reduce3(op, parts[:R], 1, R, 1, scale, x.dtype)
+        return out.reshape([1] * nd) if keepdim else out.reshape(())
+    dims = sorted(set(dims))
+    if not dims:
+        return t
+    # collapse runs of adjacent dims; reduce runs from the back so earlier indices stay valid
+    runs, cur = [], [dims[0]]
+    for d in dims[1:]:
+        if d == cur[-1] + 1:
+            cur.append(d)
+        else:
+            runs.append(cur)
+            cur = [d]
+    runs.append(cur)
+    cur_shape = shape[:]
+    for run in reversed(runs):
+        outer = math.prod(cur_shape[:run[0]])
+        red = math.prod(cur_shape[run[0]:run[-1] + 1])
+        inner = math.prod(cur_shape[run[-1] + 1:])
+        scale = 1.0 / red if name == "mean" else 1.0
+        r = _reduce3(op, x, outer, red, inner, scale, x.dtype)
+        if r is None:
+            return NotImplemented
+        x = r
+        for d in run:
+            cur_shape[d] = 1
+    if keepdim:
+        return x.reshape(cur_shape)
+    return x.reshape([s for i, s in enumerate(cur_shape) if i not in dims])
+
+
+# ================================== GEMM =========================================
+_GEMM_DT = {F32: 0, F16: 1, BF16: 2}
+
+
+def _aligned(t, ld):
+    es = t.element_size()
+    return t.data_ptr() % 16 == 0 and (ld * es) % 16 == 0
+
+
+def _operand(t, want_contract_last):
+    """Classify a 2-D operand. Returns (tensor, mn_major, ld) with the tensor possibly re-laid-out.
+    `want_contract_last`: the logical layout is [rows, contraction]."""
+    r, c = t.shape
+    if t.stride(1) == 1 and (t.stride(0) >= c or r == 1) and _aligned(t, t.stride(0) if r > 1 else c):
+        return t, 0, (t.stride(0) if r > 1 else c)
+    if t.stride(0) == 1 and (t.stride(1) >= r or c == 1) and _aligned(t, t.stride(1) if c > 1 else r):
+        return t, 1, (t.stride(1) if c > 1 else r)
+    es = t.element_size()
+    mult = 16 // es
+    cp = (c + mult - 1) // mult * mult
+    buf = torch.zeros(r, cp, dtype=t.dtype, device=t.device)
+    buf[:, :c].copy_(t)
+    return buf[:, :c], 0, cp
+
+
+def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0):
+    """D[M, N] = a[M, K] @ b_t[N, K]^T for 2-D operands in any of the supported layouts.
+    `a` / `b_t` may be transposed views (stride(0) == 1); misaligned ones are repacked."""
+    if a.dtype not in _GEMM_DT or a.dtype != b_t.dtype:
+        return NotImplemented
+    M, K = a.shape
+    N = b_t.shape[0]
+    out_dtype = out_dtype or a.dtype
+    if out_dtype not in _GEMM_DT:
+        return NotImplemented
+    if accum is not None:
+        out = accum
+        if not out.is_contiguous():
+            return NotImplemented
+    else:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        if accum is None:
+            out.zero_()
+        return out
+    a2, a_mn, lda = _operand(a, True)
+    b2, b_mn, ldb = _operand(b_t, True)
+    if bias is not None and (bias.dtype not in _GEMM_DT or not bias.is_contiguous()):
+        return NotImplemented
+    rc = lib().gb_gemm(a2.data_ptr(), b2.data_ptr(), out.data_ptr(), None if bias is None else bias.data_ptr(),
+                       M, N, K, 1, lda, ldb, N, 0, 0, 0, a_mn, b_mn, _GEMM_DT[a.dtype], _GEMM_DT[out.dtype],
+                       0 if bias is None else _GEMM_DT[bias.dtype], 0 if accum is None else 1, float(alpha),
+                       0, None, 0, status_tensor(a.device).data_ptr(), _sms(a.device), _st())
+    _chk(rc, "gemm")
+    return out
+
+
+def bgemm(a, b_t, out_dtype=None):
+    """Batched: a [B, M, K], b_t [B, N, K] (K-major, contiguous) -> [B, M, N]."""
+    Bn, M, K = a.shape
+    N = b_t.shape[1]
+    es = a.element_size()
+    if not (a.is_contiguous() and b_t.is_contiguous() and (K * es) % 16 == 0 and a.data_ptr() % 16 == 0
+            and b_t.data_ptr() % 16 == 0):
+        return NotImplemented
+    out = torch.empty(Bn, M, N, dtype=out_dtype or a.dtype, device=a.device)
+    if out.numel() == 0:
+        return out
+    rc = lib().gb_gemm(a.data_ptr(), b_t.data_ptr(), out.data_ptr(), None, M, N, K, Bn, K, K, N, M * K, N * K, M * N,
+                       0, 0, _GEMM_DT[a.dtype], _GEMM_DT[out.dtype], 0, 0, 1.0, 0, None, 0,
+                       status_tensor(a.device).data_ptr(), _sms(a.device), _st())
+    _chk(rc, "bgemm")
+    return out
+
+
+def matmul(a, b):
+    if a.dtype not in _GEMM_DT or a.dtype != b.dtype or a.dim() == 0 or b.dim() == 0:
+        return NotImplemented
+    a1, b1 = a.dim() == 1, b.dim() == 1
+    aa = a.unsqueeze(0) if a1 else a
+    bb = b.unsqueeze(-1) if b1 else b
+    if bb.dim() == 2:
+        lead = aa.shape[:-1]
+        a2 = aa.reshape(-1, aa.shape[-1])
+        r = gemm(a2, bb.t())
+        if r is NotImplemented:
+            return NotImplemented
+        out = r.reshape(*lead, bb.shape[-1])
+    else:
+        try:
+            bshape = torch.broadcast_shapes(aa.shape[:-2], bb.shape[:-2])
+        except RuntimeError:
+            return NotImplemented
+        ae = aa.expand(*bshape, *aa.shape[-2:]).reshape(-1, *aa.shape[-2:])
+        be = bb.expand(*bshape, *bb.shape[-2:]).reshape(-1, *bb.shape[-2:])
+        ae = ae if ae.is_contiguous() else ae.contiguous()
+        bt = be.transpose(-1, -2)
+        bt = bt if bt.is_contiguous() else bt.contiguous()
+        K = ae.shape[-1]
+        mult = 16 // ae.element_size()
+        if K % mult:
+            pad = mult - K % mult
+            ae = torch.nn.functional.pad(ae, (0, pad))
+            bt = torch.nn.functional.pad(bt, (0, pad))
+        r = bgemm(ae, bt)
+        if r is NotImplemented:
+            return NotImplemented
+        out = r.reshape(*bshape, aa.shape[-2], bb.shape[-1])
+    if a1:
+        out = out.squeeze(-2)
+    if b1:
+        out = out.squeeze(-1)
+    return out
+
+
+def linear(x, w, bias, out_dtype):
+    if x.dtype != w.dtype or x.dtype not in _GEMM_DT or w.dim() != 2:
+        return NotImplemented
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    r = gemm(x2, w, out_dtype=out_dtype, bias=bias)
+    if r is NotImplemented:
+        return NotImplemented
+    return r.reshape(*lead, w.shape[0])
+
+
+def linear_dgrad(gy, w):
+    if gy.dtype != w.dtype or gy.dtype not in _GEMM_DT:
+        return NotImplemented
+    lead = gy.shape[:-1]
+    g2 = gy.reshape(-1, gy.shape[-1])
+    r = gemm(g2, w.t())        # w.t() is [K, N] with stride(0) == 1: an MN-major B operand
+    if r is NotImplemented:
+        return NotImplemented
+    return r.reshape(*lead, w.shape[1])
+
+
+def linear_wgrad(gy, x, out_dtype, accum):
+    if gy.dtype != x.dtype or gy.dtype not in _GEMM_DT:
+        return NotImplemented
+    g2 = gy.reshape(-1, gy.shape[-1])
+    x2 = x.reshape(-1, x.shape[-1])
+    return gemm(g2.t(), x2.t(), out_dtype=out_dtype or gy.dtype, accum=accum)
+
+
+# ============================ norms / softmax / loss =============================
+def _norm_ok(x, cols):
+    v = 4 if x.dtype == F32 else 8
+    return x.dtype in _FLOATS and x.is_contiguous() and x.data_ptr() % 16 == 0 and cols % v == 0 \
+        and cols // v <= 256 * 8
+
+
+def _wdt(x, w):
+    if w.dtype == F32 or w.dtype == x.dtype:
+        return _DT[w.dtype]
+    return None
+
+
+def rmsnorm_fwd(x, w, eps):
+    cols = x.shape[-1]
+    if not _norm_ok(x, cols) or _wdt(x, w) is None or not w.is_contiguous():
+        return NotImplemented
+    rows = x.numel() // cols
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=F32, device=x.device)
+    _chk(lib().gb_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, cols, float(eps),
+                              _DT[x.dtype], _wdt(x, w), _st()), "rmsnorm_fwd")
+    return y, rstd
+
+
+def _colsum(partial, nrows, cols):
+    return _reduce3(0, partial, 1, nrows, cols, 1.0, F32)
+
+
+def rmsnorm_bwd(g, x, w, rstd):
+    cols = x.shape[-1]
+    if not _norm_ok(x, cols) or not _norm_ok(g, cols) or g.dtype != x.dtype or _wdt(x, w) is None:
+        return NotImplemented
+    rows = x.numel() // cols
+    L = lib()
+    nct = L.gb_norm_bwd_ctas(rows)
+    dx = torch.empty_like(x)
+    part = torch.empty(nct * cols, dtype=F32, device=x.device)
+    _chk(L.gb_rmsnorm_bwd(g.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), part.data_ptr(),
+                          rows, cols, _DT[x.dtype], _wdt(x, w), _st()), "rmsnorm_bwd")
+    return dx, _colsum(part, nct, cols)
+
+
+def layernorm_fwd(x, w, b, eps):
+    cols = x.shape[-1]
+    if not _norm_ok(x, cols):
+        return NotImplemented
+    ref = w if w is not None else b
+    wdt = _DT[x.dtype] if ref is None else _wdt(x, ref)
+    if wdt is None or (w is not None and b is not None and w.dtype != b.dtype):
+        return NotImplemented
+    rows = x.numel() // cols
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=F32, device=x.device)
+    rstd = torch.empty(rows, dtype=F32, device=x.device)
+    _chk(lib().gb_layernorm_fwd(x.data_ptr(), None if w is None else w.data_ptr(), None if b is None else b.data_ptr(),
+                                y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, cols, float(eps),
+                                _DT[x.dtype], wdt, _st()), "layernorm_fwd")
+    return y, mean, rstd
+
+
+def layernorm_bwd(g, x, w, mean, rstd):
+    cols = x.shape[-1]
+    if not _norm_ok(x, cols) or not _norm_ok(g, cols) or g.dtype != x.dtype:
+        return NotImplemented
+    wdt = _DT[x.dtype] if w is None else _wdt(x, w)
+    if wdt is None:
+        return NotImplemented
+    rows = x.numel() // cols
+    L = lib()
+    nct = L.gb_norm_bwd_ctas(rows)
+    dx = torch.empty_like(x)
+    pw = torch.empty(nct * cols, dtype=F32, device=x.device)
+    pb = torch.empty(nct * cols, dtype=F32, device=x.device)
+    _chk(L.gb_layernorm_bwd(g.data_ptr(), x.data_ptr(), None if w is None else w.data_ptr(), mean.data_ptr(),
+                            rstd.data_ptr(), dx.data_ptr(), pw.data_ptr(), pb.data_ptr(), rows, cols, _DT[x.dtype],
+                            wdt, _st()), "layernorm_bwd")
+    return dx, _colsum(pw, nct, cols), _colsum(pb, nct, cols)
+
+
+def _to_last(x, dim):
+    dim = dim % x.dim()
+    if dim == x.dim() - 1:
+        return x if x.is_contiguous() else None, False
+    return None, True
+
+
+def softmax_fwd(x, dim, log):
+    if x.dtype not in _FLOATS or x.dim() == 0:
+        return NotImplemented
+    d = dim % x.dim()
+    if d != x.dim() - 1:
+        xt = x.transpose(d, -1)
+        xc = contiguous(xt) if not xt.is_contiguous() else xt
+        if xc is NotImplemented:
+            return NotImplemented
+        return softmax_fwd(xc, -1, log).transpose(d, -1)
+    xc = x if x.is_contiguous() else contiguous(x)
+    if xc is NotImplemented:
+        return NotImplemented
+    cols = xc.shape[-1]
+    y = torch.empty_like(xc)
+    _chk(lib().gb_softmax_fwd(xc.data_ptr(), y.data_ptr(), xc.numel() // cols, cols, 1 if log else 0, _DT[xc.dtype],
+                              _st()), "softmax_fwd")
+    return y
+
+
+def softmax_bwd(g, y, dim, log):
+    if g.dtype not in _FLOATS or g.dtype != y.dtype or g.dim() == 0:
+        return NotImplemented
+    d = dim % g.dim()
+    if d != g.dim() - 1:
+        gt, yt = g.transpose(d, -1), y.transpose(d, -1)
+        gc = gt if gt.is_contiguous() else contiguous(gt)
+        yc = yt if yt.is_contiguous() else contiguous(yt)
+        if gc is NotImplemented or yc is NotImplemented:
+            return NotImplemented
+        return softmax_bwd(gc, yc, -1, log).transpose(d, -1)
+    gc = g if g.is_contiguous() else contiguous(g)
+    yc = y if y.is_contiguous() else contiguous(y)
+    if gc is NotImplemented or yc is NotImplemented:
+        return NotImplemented
+    cols = gc.shape[-1]
+    dx = torch.empty_like(gc)
+    _chk(lib().gb_softmax_bwd(gc.data_ptr(), yc.data_ptr(), dx.data_ptr(), gc.numel() // cols, cols, 1 if log else 0,
+                              _DT[gc.dtype], _st()), "softmax_bwd")
+    return dx
+
+
+def cross_entropy_fwd(logits, target, ignore_index):
+    if logits.dtype not in _FLOATS or not logits.is_contiguous() or target.dtype not in (torch.int64, torch.int32) \
+            or not target.is_contiguous():
+        return NotImplemented
+    rows, cols = logits.shape
+    loss = torch.empty(rows, dtype=F32, device=logits.device)
+    lse = torch.empty(rows, dtype=F32, device=logits.device)
+    ii = -(2 ** 62) if ignore_index is None else int(ignore_index)
+    _chk(lib().gb_ce_fwd(logits.data_ptr(), target.data_ptr(), loss.data_ptr(), lse.data_ptr(), rows, cols, ii,
+                         _DT[logits.dtype], 1 if target.dtype == torch.int64 else 0, _st()), "ce_fwd")
+    return loss, lse
+
+
+def cross_entropy_bwd(logits, target, lse, grad_rows, ignore_index, inplace):
+    if logits.dtype not in _FLOATS or not logits.is_contiguous() or grad_rows.dtype != F32 \
+            or not grad_rows.is_contiguous():
+        return NotImplemented
+    rows, cols = logits.shape
+    out = logits if inplace else torch.empty_like(logits)
+    ii = -(2 ** 62) if ignore_index is None else int(ignore_index)
+    _chk(lib().gb_ce_bwd(logits.data_ptr(), target.data_ptr(), lse.data_ptr(), grad_rows.data_ptr(), out.data_ptr(),
+                         rows, cols, ii, _DT[logits.dtype], 1 if target.dtype == torch.int64 else 0, _st()), "ce_bwd")
+    return out
+
+
+# ============================== transformer pieces ===============================
+def swiglu_fwd(gate, up):
+    if not _ok(gate) or not _ok(up) or gate.dtype != up.dtype or gate.shape != up.shape:
+        return NotImplemented
+    out = torch.empty_like(gate)
+    _chk(lib().gb_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _DT[gate.dtype], _st()),
+         "swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(g, gate, up):
+    if not (_ok(g) and _ok(gate) and _ok(up)) or not (g.dtype == gate.dtype == up.dtype):
+        return NotImplemented
+    dg, du = torch.empty_like(gate), torch.empty_like(up)
+    _chk(lib().gb_swiglu_bwd(g.data_ptr(), gate.data_ptr(), up.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(),
+                             _DT[g.dtype], _st()), "swiglu_bwd")
+    return dg, du
+
+
+def rope(x, cos, sin, positions, inverse):
+    if x.dtype not in _FLOATS or x.dim() != 4 or not x.is_contiguous() or cos.dtype != F32 or sin.dtype != F32 \
+            or not cos.is_contiguous() or not sin.is_contiguous() or x.shape[-1] % 2:
+        return NotImplemented
+    B, S, H, D = x.shape
+    pos_ptr = None
+    if positions is not None:
+        positions = positions.to(torch.int64).contiguous()
+        if positions.dim() == 1:
+            positions = positions.unsqueeze(0).expand(B, S).contiguous()
+        pos_ptr = positions.data_ptr()
+    elif cos.shape[0] < S:
+        return NotImplemented
+    out = torch.empty_like(x)
+    _chk(lib().gb_rope(x.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos_ptr, B, S, H, D,
+                       1 if inverse else 0, _DT[x.dtype], _st()), "rope")
+    return out
+
+
+def gather_rows(x, rows):
+    if x.dim() != 2 or not x.is_contiguous() or rows.dtype not in (torch.int64, torch.int32) \
+            or not rows.is_contiguous():
+        return NotImplemented
+    rb = x.shape[1] * x.element_size()
+    if rb % 16 or x.data_ptr() % 16:
+        return NotImplemented
+    out = torch.empty(rows.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+    _chk(lib().gb_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), rows.numel(), rb,
+                              1 if rows.dtype == torch.int64 else 0, _st()), "gather_rows")
+    return out
+
+
+def embedding_fwd(weight, idx):
+    if weight.dim() != 2:
+        return NotImplemented
+    flat = idx.reshape(-1)
+    flat = flat if flat.is_contiguous() else flat.contiguous()
+    r = gather_rows(weight, flat)
+    if r is NotImplemented:
+        return NotImplemented
+    return r.reshape(*idx.shape, weight.shape[1])
+
+
+def scatter_add_rows(src, rows, num_rows, out_dtype):
+    if src.dtype not in _FLOATS or src.dim() != 2 or not src.is_contiguous() \
+            or rows.dtype not in (torch.int64, torch.int32) or not rows.is_contiguous():
+        return NotImplemented
+    acc = torch.zeros(num_rows, src.shape[1], dtype=F32, device=src.device)
+    _chk(lib().gb_scatter_add_rows(src.data_ptr(), rows.data_ptr(), acc.data_ptr(), src.shape[0], src.shape[1],
+                                   _DT[src.dtype], 1 if rows.dtype == torch.int64 else 0, _st()), "scatter_add_rows")
+    od = out_dtype or src.dtype
+    return acc if od == F32 else cast(acc, od)
+
+
+def embedding_bwd(g, idx, num_rows, out_dtype):
+    D = g.shape[-1]
+    g2 = g.reshape(-1, D)
+    g2 = g2 if g2.is_contiguous() else g2.contiguous()
+    flat = idx.reshape(-1)
+    flat = flat if flat.is_contiguous() else flat.contiguous()
+    return scatter_add_rows(g2, flat, num_rows, out_dtype)
+
+
+def dropout_fwd(x, p, seed, offset):
+    if not _ok(x):
+        return NotImplemented
+    y = torch.empty_like(x)
+    mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    _chk(lib().gb_dropout(x.data_ptr(), y.data_ptr(), mask.data_ptr(), x.numel(), float(p), int(seed), int(offset),
+                          _DT[x.dtype], _st()), "dropout")
+    return y, mask
+
+
+def random_fill(kind, shape, dtype, dev, seed, offset, a, b):
+    with torch.cuda.device(dev):
+        if kind == "randint":
+            out = torch.empty(shape, dtype=torch.int64, device=dev)
+            _chk(lib().gb_randint(out.data_ptr(), out.numel(), int(seed), int(offset), int(a), int(b), _st()), "randint")
+            return out if dtype == torch.int64 else out.to(dtype)
+        if dtype not in _FLOATS:
+            return NotImplemented
+        out = torch.empty(shape, dtype=dtype, device=dev)
+        _chk(lib().gb_random(out.data_ptr(), out.numel(), int(seed), int(offset), 0 if kind == "uniform" else 1,
+                             float(a), float(b), _DT[dtype], _st()), "random")
+        return out
+
+
+# ================================== optimisers ===================================
+_pinned = {}
+
+
+def _meta(rows, nt, dev):
+    """Upload the pointer table (rows x nt int64) through a pinned staging buffer."""
+    # torch's pinned-host allocator keeps a staging block alive until the async copy that reads it
+    # has completed, so a fresh pinned tensor per call is both safe and cheap (blocks are recycled).
+    host = torch.tensor(rows, dtype=torch.int64).reshape(-1).pin_memory()
+    return host.to(dev, non_blocking=True)
+
+
+def _multi_table(params, grads, s1, s2, shadows):
+    L = lib()
+    chunk = L.gb_opt_chunk()
+    nt = len(params)
+    starts, total = [], 0
+    for p in params:
+        starts.append(total)
+        total += (p.numel() + chunk - 1) // chunk
+    z = [0] * nt
+    rows = [[p.data_ptr() for p in params] if params[0] is not None else z,
+            [g.data_ptr() for g in grads],
+            [t.data_ptr() for t in s1] if s1 is not None else z,
+            [t.data_ptr() for t in s2] if s2 is not None else z,
+            [0 if (shadows is None or s is None) else s.data_ptr() for s in (shadows or params)] if shadows else z,
+            [g.numel() for g in grads], starts, [_DT[g.dtype] for g in grads]]
+    return rows, nt, total
+
+
+def _opt_ok(params, grads, states):
+    for p, g in zip(params, grads):
+        if p.dtype != F32 or not p.is_contiguous() or g.dtype not in _FLOATS or not g.is_contiguous() \
+                or g.numel() != p.numel():
+            return False
+    for st in states:
+        if st is not None:
+            for t in st:
+                if t.dtype != F32 or not t.is_contiguous():
+                    return False
+    return True
+
+
+def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled, grad_scale, found_inf,
+               shadows):
+    if not _opt_ok(params, grads, (ms, vs)):
+        return NotImplemented
+    sdt = 0
+    if shadows is not None:
+        sd = {s.dtype for s in shadows if s is not None}
+        if len(sd) > 1 or any(d not in _FLOATS for d in sd):
+            return NotImplemented
+        sdt = _DT[sd.pop()] if sd else 0
+    rows, nt, total = _multi_table(params, grads, ms, vs, shadows)
+    dev = params[0].device
+    meta = _meta(rows, nt, dev)
+    gs = None if grad_scale is None else grad_scale.data_ptr()
+    fi = None if found_inf is None else found_inf.data_ptr()
+    _chk(lib().gb_adam_multi(meta.data_ptr(), nt, total, float(lr), float(beta1), float(beta2), float(eps),
+                             float(weight_decay), 1.0 - beta1 ** step, 1.0 - beta2 ** step, 1 if decoupled else 0,
+                             sdt, gs, fi, _st()), "adam_multi")
+    return True
+
+
+def sgd_step(params, grads, bufs, lr, momentum, weight_decay):
+    if not _opt_ok(params, grads, (bufs,)):
+        return NotImplemented
+    rows, nt, total = _multi_table(params, grads, bufs, None, None)
+    meta = _meta(rows, nt, params[0].device)
+    _chk(lib().gb_sgd_multi(meta.data_ptr(), nt, total, float(lr), float(momentum), float(weight_decay), _st()),
+         "sgd_multi")
+    return True
+
+
+def _grad_multi(grads, scale, found_inf, norm_sq, mode):
+    for g in grads:
+        if g.dtype not in _FLOATS or not g.is_contiguous():
+            return NotImplemented
+    rows, nt, total = _multi_table([None] * len(grads), grads, None, None, None)
+    meta = _meta(rows, nt, grads[0].device)
+    sp, fs = None, 1.0
+    if isinstance(scale, torch.Tensor):
+        sp = scale.data_ptr()
+    elif scale is not None:
+        fs = float(scale)
+    _chk(lib().gb_grad_multi(meta.data_ptr(), nt, total, sp, fs, None if found_inf is None else found_inf.data_ptr(),
+                             None if norm_sq is None else norm_sq.data_ptr(), mode, _st()), "grad_multi")
+    return True
+
+
+def unscale_and_check(grads, inv_scale, found_inf):
+    if isinstance(inv_scale, torch.Tensor) and inv_scale.dtype != F32:
+        return NotImplemented
+    return _grad_multi(grads, inv_scale, found_inf, None, (1 if inv_scale is not None else 0) | 2)
+
+
+def grad_norm_sq(grads, out):
+    return _grad_multi(grads, None, None, out, 4)
+
+
+# =================================== MoE =========================================
+def moe_router(logits, k, renorm):
+    if logits.dtype not in _FLOATS or logits.dim() != 2 or not logits.is_contiguous() or logits.shape[1] > 256 \
+            or k > 32:
+        return NotImplemented
+    T, E = logits.shape
+    dev = logits.device
+    w = torch.empty(T, k, dtype=F32, device=dev)
+    e = torch.empty(T, k, dtype=torch.int32, device=dev)
+    probs = torch.empty(T, E, dtype=F32, device=dev)
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    _chk(lib().gb_router_fwd(logits.data_ptr(), w.data_ptr(), e.data_ptr(), probs.data_ptr(), counts.data_ptr(), T, E,
+                             k, 1 if renorm else 0, _DT[logits.dtype], _st()), "router_fwd")
+    return w, e, probs, counts
+
+
+def moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm):
+    if probs.dtype != F32 or experts.dtype != torch.int32:
+        return NotImplemented
+    T, E = probs.shape
+    k = experts.shape[1]
+    dw = None if dweights is None else dweights.to(F32).contiguous()
+    dp = None if dprobs is None else dprobs.to(F32).contiguous()
+    out = torch.empty(T, E, dtype=F32, device=probs.device)
+    _chk(lib().gb_router_bwd(None if dw is None else dw.data_ptr(), None if dp is None else dp.data_ptr(),
+                             probs.data_ptr(), experts.data_ptr(), weights.data_ptr(), out.data_ptr(), T, E, k,
+                             1 if renorm else 0, 0, _st()), "router_bwd")
+    return out
+
+
+# ================================ communication ==================================
+def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None, found_inf=None, prescale=1.0,
+                    scale_is_reciprocal=True, ctas=None):
+    """In-place fused all-reduce over symmetric buffer `buf` (see csrc/comm.cu)."""
+    from ..distributed import symm
+    epoch = symm.next_epoch()
+    budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000)) * 1e6)
+    if ctas is None:
+        ctas = int(os.environ.get("GENESIS_COMM_CTAS", 32))
+    _chk(lib().gb_allreduce_fused(buf.ptr_table, st.flags.ptr_table, offset_elems, n, st.rank, st.world, epoch,
+                                  float(prescale), None if inv_scale is None else inv_scale.data_ptr(),
+                                  1 if scale_is_reciprocal else 0,
+                                  None if found_inf is None else found_inf.data_ptr(), _DT[dtype], ctas, budget,
+                                  st.status.data_ptr(), _st()), "allreduce_fused")
+    return True
+
+
+if torch.cuda.is_available():
+    lib()
+
+
+# ---- kernel families that land in their own modules ------------------------------------------
+def attention_fwd(q, k, v, causal, scale):
+    from . import attention
+    return attention.forward(q, k, v, causal, scale)
+
+
+def attention_bwd(do, q, k, v, o, lse, causal, scale):
+    from . import attention
+    return attention.backward(do, q, k, v, o, lse, causal, scale)
+
+
+def moe_sort(experts, num_experts, align=1):
+    from . import grouped
+    return grouped.moe_sort(experts, num_experts, align)
+
+
+def grouped_linear(x, w, offsets):
+    from . import grouped
+    return grouped.grouped_linear(x, w, offsets)
+
+
+def grouped_dgrad(gy, w, offsets):
+    from . import grouped
+    return grouped.grouped_dgrad(gy, w, offsets)
+
+
+def grouped_wgrad(gy, x, offsets, num_groups, out_dtype):
+    from . import grouped
+    return grouped.grouped_wgrad(gy, x, offsets, num_groups, out_dtype)

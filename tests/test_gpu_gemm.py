@@ -1,0 +1,103 @@
+"""tcgen05 GEMM against an fp32 torch reference: every operand-layout combination, dtypes,
+tile tails, odd (repacked) shapes, bias / accumulate epilogues, batched matmul, linear
+forward / dgrad / wgrad."""
+import pytest
+import torch
+
+import genesis_b200  # noqa: F401
+from genesis_b200.ops import dispatch as K
+from genesis_b200.ops import native as N
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, dt=torch.float32, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * 0.5).to(dt)
+
+
+def check(got, ref, dt, K_):
+    tol = {torch.float32: 2e-3, torch.bfloat16: 2e-2, torch.float16: 4e-3}[dt] * max(1.0, (K_ / 64) ** 0.5)
+    torch.testing.assert_close(got.float().cpu(), ref, atol=tol, rtol=2e-2)
+    N.check_status()
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N_,K_", [(128, 128, 64), (128, 256, 128), (256, 512, 256), (200, 136, 72),
+                                      (64, 64, 64), (1024, 896, 896), (8, 8, 8), (384, 4864, 896)])
+def test_gemm_layouts(dt, a_mn, b_mn, M, N_, K_):
+    a, b = rnd(M, K_, dt=dt), rnd(N_, K_, dt=dt, seed=1)
+    ref = a.float() @ b.float().t()
+    ac = a.to(DEV).t().contiguous().t() if a_mn else a.to(DEV)
+    bc = b.to(DEV).t().contiguous().t() if b_mn else b.to(DEV)
+    got = N.gemm(ac, bc)
+    assert got is not NotImplemented and got.dtype == dt
+    check(got, ref, dt, K_)
+
+
+@pytest.mark.parametrize("shape", [(3, 4, 5), (5, 4, 3), (16, 16, 32), (72, 73, 74), (74, 73, 72), (1024, 1024, 1024),
+                                   (1, 7, 1), (130, 1, 33)])
+def test_gemm_odd_shapes(shape):
+    m, n, p = shape
+    a, b = rnd(m, n), rnd(n, p, seed=1)
+    got = K.matmul(a.to(DEV), b.to(DEV))
+    check(got, a @ b, torch.float32, n)
+    a16, b16 = a.bfloat16(), b.bfloat16()
+    got = K.matmul(a16.to(DEV), b16.to(DEV))
+    check(got, a16.float() @ b16.float(), torch.bfloat16, n)
+
+
+def test_gemm_epilogues():
+    M, N_, K_ = 300, 264, 200
+    a, b, bias = rnd(M, K_, dt=torch.bfloat16), rnd(N_, K_, dt=torch.bfloat16, seed=1), rnd(N_, seed=2)
+    ref = a.float() @ b.float().t()
+    got = N.gemm(a.to(DEV), b.to(DEV), bias=bias.to(DEV))
+    check(got, ref + bias, torch.bfloat16, K_)
+    got = N.gemm(a.to(DEV), b.to(DEV), out_dtype=torch.float32)
+    assert got.dtype == torch.float32
+    check(got, ref, torch.float32, K_)
+    acc = rnd(M, N_, seed=3).to(DEV)
+    base = acc.clone().cpu()
+    N.gemm(a.to(DEV), b.to(DEV), out_dtype=torch.float32, accum=acc)
+    check(acc, ref + base, torch.float32, K_)
+    got = N.gemm(a.to(DEV), b.to(DEV), alpha=0.25)
+    check(got, ref * 0.25, torch.bfloat16, K_)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("form", ["bmk_bkn", "bmk_kn", "mk_bkn"])
+@pytest.mark.parametrize("dims", [(16, 16, 16, 16), (32, 16, 8, 24), (32, 13, 8, 15), (3, 130, 72, 200)])
+def test_batched_matmul(dt, form, dims):
+    bsz, m, n, p = dims
+    a = rnd(bsz, m, n, dt=dt) if form != "mk_bkn" else rnd(m, n, dt=dt)
+    b = rnd(bsz, n, p, dt=dt, seed=1) if form != "bmk_kn" else rnd(n, p, dt=dt, seed=1)
+    got = K.matmul(a.to(DEV), b.to(DEV))
+    check(got, a.float() @ b.float(), dt, n)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_linear_fwd_bwd(dt):
+    x, w, b = rnd(4, 50, 896, dt=dt), rnd(136, 896, dt=dt, seed=1), rnd(136, seed=2)
+    gy = rnd(4, 50, 136, dt=dt, seed=3)
+    y = K.linear(x.to(DEV), w.to(DEV), b.to(DEV))
+    check(y, torch.nn.functional.linear(x.float(), w.float(), b), dt, 896)
+    dx = K.linear_dgrad(gy.to(DEV), w.to(DEV))
+    check(dx, gy.float() @ w.float(), dt, 136)
+    dw = K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32)
+    assert dw.dtype == torch.float32
+    check(dw, gy.float().reshape(-1, 136).t() @ x.float().reshape(-1, 896), torch.float32 if dt == torch.float32
+          else dt, 200)
+    acc = torch.ones(136, 896, device=DEV)
+    K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32, accum=acc)
+    check(acc, 1.0 + gy.float().reshape(-1, 136).t() @ x.float().reshape(-1, 896), torch.float32
+          if dt == torch.float32 else dt, 200)
+
+
+def test_large_gemm_many_tiles():
+    # more tiles than SMs: exercises the persistent loop, both accumulators and the smem ring wrap-around
+    M, N_, K_ = 2048, 4096, 1024
+    a, b = rnd(M, K_, dt=torch.bfloat16), rnd(N_, K_, dt=torch.bfloat16, seed=1)
+    got = N.gemm(a.to(DEV), b.to(DEV))
+    check(got, a.float() @ b.float().t(), torch.bfloat16, K_)

@@ -1,0 +1,308 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op
+(the CPU branch of `genesis_b200.ops.dispatch`, or explicit torch math).  Small and odd shapes
+on purpose: tails, non-multiples of the tile, strided and broadcast operands."""
+import math
+
+import pytest
+import torch
+
+import genesis_b200  # noqa: F401
+from genesis_b200.ops import dispatch as K
+from genesis_b200.ops import native as N
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+def tol(dt):
+    return {torch.float32: (1e-5, 1e-5), torch.bfloat16: (2e-2, 2e-2), torch.float16: (2e-3, 2e-3)}[dt]
+
+
+def close(got, ref, dt, scale=1.0):
+    a, r = tol(dt)
+    torch.testing.assert_close(got.float().cpu(), ref.float().cpu(), atol=a * scale, rtol=r * scale)
+
+
+def rnd(*shape, dt=torch.float32, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return torch.randn(*shape, generator=g).to(dt)
+
+
+def test_library_loaded_and_abi():
+    from genesis_b200.ops import abi_check
+    assert N.lib() is not None
+    assert abi_check.mismatches() == []
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("shape", [(1,), (7,), (33, 5), (4, 5, 6), (128, 1024), (3, 4, 5, 7)])
+def test_binary_unary(dt, shape):
+    a, b = rnd(*shape, dt=dt), rnd(*shape, dt=dt, seed=1)
+    ac, bc = a.to(DEV), b.to(DEV)
+    for name, fn in [("add", torch.add), ("sub", torch.sub), ("mul", torch.mul), ("max", torch.maximum)]:
+        got = N.binary(name, ac, bc)
+        assert got is not NotImplemented
+        close(got, fn(a.float(), b.float()), dt)
+    close(N.binary("div", ac, bc.abs() + 1), a.float() / (b.float().abs() + 1), dt)
+    close(N.binary("mul", ac, 2.5), a.float() * 2.5, dt)
+    close(N.binary("sub", 2.0, ac), 2.0 - a.float(), dt)
+    close(N.binary("div", 2.0, ac.abs() + 1), 2.0 / (a.float().abs() + 1), dt)
+    for name in ["neg", "exp", "sin", "cos", "tanh", "sigmoid", "relu", "abs", "silu", "gelu"]:
+        got = N.unary(name, ac)
+        assert got is not NotImplemented
+        close(got, K._UNARY_TORCH[name](a.float()), dt, scale=4)
+    pos = a.float().abs() + 0.5
+    close(N.unary("log", pos.to(dt).to(DEV)), torch.log(pos.to(dt).float()), dt)
+    close(N.unary("sqrt", pos.to(dt).to(DEV)), torch.sqrt(pos.to(dt).float()), dt)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_unary_backward(dt):
+    x, g = rnd(37, 19, dt=dt), rnd(37, 19, dt=dt, seed=3)
+    for name in ["exp", "sin", "cos", "tanh", "sigmoid", "relu", "abs", "silu", "gelu", "neg"]:
+        y = K._UNARY_TORCH[name](x.float())
+        ref = K.unary_bwd(name, g.float(), x.float(), y)
+        got = K.unary_bwd(name, g.to(DEV), x.to(DEV), y.to(dt).to(DEV))
+        close(got, ref, dt, scale=8)
+
+
+@pytest.mark.parametrize("shapes", [((5, 1), (1, 7)), ((4, 1, 6), (5, 1)), ((2, 3, 4, 5), (4, 1)), ((8,), (3, 8))])
+def test_binary_broadcast(shapes):
+    a, b = rnd(*shapes[0]), rnd(*shapes[1], seed=2)
+    got = N.binary("add", a.to(DEV), b.to(DEV))
+    assert got is not NotImplemented
+    close(got, a + b, torch.float32)
+    close(N.binary("mul", a.to(DEV), b.to(DEV)), a * b, torch.float32)
+
+
+def test_compare_where_clamp_cast_fill_copy():
+    a, b = rnd(9, 31), rnd(9, 31, seed=5)
+    ac, bc = a.to(DEV), b.to(DEV)
+    for name, fn in K._CMP_TORCH.items():
+        assert torch.equal(N.compare(name, ac, bc).cpu(), fn(a, b))
+        assert torch.equal(N.compare(name, ac, 0.1).cpu(), fn(a, torch.tensor(0.1)))
+    c = a > 0
+    close(N.where(c.to(DEV), ac, bc), torch.where(c, a, b), torch.float32)
+    close(N.where(c.to(DEV), ac, 0.0), torch.where(c, a, torch.zeros_like(a)), torch.float32)
+    close(N.clamp(ac, -0.3, 0.4), a.clamp(-0.3, 0.4), torch.float32)
+    close(N.clamp(ac, None, 0.4), a.clamp(max=0.4), torch.float32)
+    for s in DTYPES:
+        for d in DTYPES:
+            if s != d:
+                got = N.cast(a.to(s).to(DEV), d)
+                assert got.dtype == d
+                close(got, a.to(s).to(d), torch.bfloat16 if torch.bfloat16 in (s, d) else torch.float16)
+    t = torch.empty(1000, device=DEV)
+    N.fill_(t, 3.5)
+    assert bool((t == 3.5).all())
+    dst = torch.empty(9, 31, device=DEV)
+    assert N.copy_(dst, ac) is not NotImplemented
+    assert torch.equal(dst.cpu(), a)
+    dsth = torch.empty(9, 31, device=DEV, dtype=torch.bfloat16)
+    K.copy_(dsth, ac)
+    close(dsth, a.bfloat16(), torch.bfloat16)
+    acc = ac.clone()
+    N.add_(acc, bc.bfloat16())
+    close(acc, a + b.bfloat16().float(), torch.float32, scale=10)
+
+
+@pytest.mark.parametrize("shape,perm", [((5, 7), (1, 0)), ((3, 5, 7), (0, 2, 1)), ((3, 5, 7), (2, 0, 1)),
+                                        ((2, 3, 4, 5), (0, 2, 1, 3)), ((64, 96), (1, 0)), ((4, 33, 65), (0, 2, 1))])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.int64])
+def test_contiguous(shape, perm, dt):
+    a = torch.arange(math.prod(shape)).reshape(shape).to(dt)
+    v = a.to(DEV).permute(perm)
+    got = N.contiguous(v)
+    assert got is not NotImplemented and got.is_contiguous()
+    assert torch.equal(got.cpu(), a.permute(perm).contiguous())
+    sl = a.to(DEV)[..., 1:]
+    assert torch.equal(N.contiguous(sl).cpu(), a[..., 1:].contiguous())
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,dims", [((1, 1, 1), None), ((5, 3), (0,)), ((8, 3, 2), (1,)), ((8, 3, 2), (2,)),
+                                        ((8, 3, 2048), (1,)), ((8, 3, 2048), (2,)), ((2048, 2048), (0,)),
+                                        ((2048, 2048), (1,)), ((1024, 1024), None), ((4096, 512), (0,)),
+                                        ((512, 4096), (1,)), ((1, 2048), (0,)), ((2048, 1), (1,)),
+                                        ((16, 16, 16), (0, 2)), ((300, 70001), None)])
+def test_reductions(dt, shape, dims):
+    a = rnd(*shape, dt=dt)
+    ac = a.to(DEV)
+    for name in ["sum", "mean", "max", "min"]:
+        for keep in (False, True):
+            ref = K.reduce(name, a.float(), dims, keep)
+            got = K.reduce(name, ac, dims, keep)
+            assert tuple(got.shape) == tuple(ref.shape), (name, got.shape, ref.shape)
+            n = a.numel() if dims is None else math.prod(shape[d] for d in dims)
+            close(got, ref, dt, scale=max(1.0, math.sqrt(n) / 4) if name == "sum" else 1.0)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("rows,cols", [(1, 8), (7, 64), (33, 896), (5, 1536), (3, 4096), (2, 16384)])
+def test_rmsnorm_layernorm(dt, rows, cols):
+    if dt == torch.float32 and cols > 8192:
+        pytest.skip("fp32 rows longer than 8192 use the generic path")
+    x, g = rnd(rows, cols, dt=dt), rnd(rows, cols, dt=dt, seed=1)
+    w, b = rnd(cols) * 0.1 + 1.0, rnd(cols, seed=2) * 0.1
+    y_ref, rstd_ref = K.rmsnorm_fwd(x, w, 1e-6)
+    y, rstd = K.rmsnorm_fwd(x.to(DEV), w.to(DEV), 1e-6)
+    close(y, y_ref, dt)
+    close(rstd, rstd_ref, torch.float32, scale=10)
+    dx_ref, dw_ref = K.rmsnorm_bwd(g, x, w, rstd_ref)
+    dx, dw = K.rmsnorm_bwd(g.to(DEV), x.to(DEV), w.to(DEV), rstd)
+    close(dx, dx_ref, dt, scale=2)
+    close(dw, dw_ref, dt, scale=4)
+    y_ref, m_ref, r_ref = K.layernorm_fwd(x, w, b, 1e-5)
+    y, m, r = K.layernorm_fwd(x.to(DEV), w.to(DEV), b.to(DEV), 1e-5)
+    close(y, y_ref, dt)
+    dxr, dwr, dbr = K.layernorm_bwd(g, x, w, m_ref, r_ref)
+    dx, dw, db = K.layernorm_bwd(g.to(DEV), x.to(DEV), w.to(DEV), m, r)
+    close(dx, dxr, dt, scale=2)
+    close(dw, dwr, dt, scale=4)
+    close(db, dbr, dt, scale=4)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("shape,dim", [((8, 64), -1), ((8, 32, 64), -1), ((8, 2048, 64), 1), ((8, 32, 2048), -1),
+                                       ((3, 1000), -1), ((5, 16384), -1), ((4, 7, 9), 0)])
+def test_softmax(dt, shape, dim):
+    x, g = rnd(*shape, dt=dt), rnd(*shape, dt=dt, seed=1)
+    for log in (False, True):
+        ref = K.softmax_fwd(x.float(), dim, log)
+        got = K.softmax_fwd(x.to(DEV), dim, log)
+        close(got, ref, dt, scale=4 if log else 1)
+        rb = K.softmax_bwd(g.float(), ref, dim, log)
+        gb = K.softmax_bwd(g.to(DEV), ref.to(dt).to(DEV), dim, log)
+        close(gb, rb, dt, scale=8)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("rows,cols", [(1, 10), (64, 10), (17, 1000), (9, 151936)])
+def test_cross_entropy(dt, rows, cols):
+    logits = rnd(rows, cols, dt=dt) * 3
+    tgt = torch.randint(0, cols, (rows,), generator=torch.Generator().manual_seed(1))
+    tgt[0] = -100
+    loss_ref, lse_ref = K.cross_entropy_fwd(logits.float(), tgt, -100)
+    loss, lse = K.cross_entropy_fwd(logits.to(DEV), tgt.to(DEV), -100)
+    close(loss, loss_ref, torch.float32, scale=100)
+    close(lse, lse_ref, torch.float32, scale=100)
+    grow = torch.rand(rows)
+    dref = K.cross_entropy_bwd(logits.float(), tgt, lse_ref, grow, -100)
+    dgot = K.cross_entropy_bwd(logits.to(DEV), tgt.to(DEV), lse, grow.to(DEV), -100, inplace=False)
+    close(dgot, dref, dt)
+    buf = logits.to(DEV).clone()
+    out = K.cross_entropy_bwd(buf, tgt.to(DEV), lse, grow.to(DEV), -100, inplace=True)
+    assert out.data_ptr() == buf.data_ptr()
+    close(out, dref, dt)
+    l32, _ = K.cross_entropy_fwd(logits.to(DEV), tgt.to(torch.int32).to(DEV), -100)
+    close(l32, loss_ref, torch.float32, scale=100)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_swiglu_rope_embedding(dt):
+    a, b, g = rnd(33, 130, dt=dt), rnd(33, 130, dt=dt, seed=1), rnd(33, 130, dt=dt, seed=2)
+    close(K.swiglu_fwd(a.to(DEV), b.to(DEV)), K.swiglu_fwd(a.float(), b.float()), dt)
+    dg, du = K.swiglu_bwd(g.to(DEV), a.to(DEV), b.to(DEV))
+    rg, ru = K.swiglu_bwd(g.float(), a.float(), b.float())
+    close(dg, rg, dt, scale=2)
+    close(du, ru, dt, scale=2)
+    B, S, H, D = 2, 9, 3, 64
+    x = rnd(B, S, H, D, dt=dt)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    fr = torch.outer(torch.arange(32).float(), inv)
+    cos, sin = torch.cat((fr, fr), -1).cos(), torch.cat((fr, fr), -1).sin()
+    pos = torch.randint(0, 32, (B, S))
+    for p in (None, pos):
+        for inverse in (False, True):
+            ref = K.rope_fwd(x.float(), cos, sin, p, inverse)
+            got = K.rope_fwd(x.to(DEV), cos.to(DEV), sin.to(DEV), None if p is None else p.to(DEV), inverse)
+            close(got, ref, dt)
+    w = rnd(50, 64, dt=dt)
+    idx = torch.randint(0, 50, (4, 11))
+    close(K.embedding_fwd(w.to(DEV), idx.to(DEV)), w[idx], dt)
+    gy = rnd(4, 11, 64, dt=dt)
+    ref = K.embedding_bwd(gy.float(), idx, 50, torch.float32)
+    got = K.embedding_bwd(gy.to(DEV), idx.to(DEV), 50, torch.float32)
+    close(got, ref, dt)
+
+
+def test_random_and_dropout():
+    u = K.random_fill("uniform", (1 << 20,), torch.float32, DEV, 1234, 0, 0.0, 1.0)
+    assert 0.0 <= float(u.min()) and float(u.max()) < 1.0
+    assert abs(float(u.mean()) - 0.5) < 5e-3 and abs(float(u.var()) - 1 / 12) < 5e-3
+    n = K.random_fill("normal", (1 << 20,), torch.float32, DEV, 1234, 1, 1.0, 2.0)
+    assert abs(float(n.mean()) - 1.0) < 2e-2 and abs(float(n.std()) - 2.0) < 2e-2
+    u2 = K.random_fill("uniform", (1 << 20,), torch.float32, DEV, 1234, 0, 0.0, 1.0)
+    assert torch.equal(u, u2)                       # same (seed, offset) => same stream
+    u3 = K.random_fill("uniform", (1 << 20,), torch.float32, DEV, 1234, 2, 0.0, 1.0)
+    assert not torch.equal(u, u3)
+    assert abs(float(torch.corrcoef(torch.stack((u, u3)))[0, 1])) < 1e-2
+    r = K.random_fill("randint", (100000,), torch.int64, DEV, 7, 0, 3, 11)
+    assert int(r.min()) >= 3 and int(r.max()) <= 10 and len(torch.unique(r)) == 8
+    x = torch.ones(1 << 20, device=DEV)
+    y, mask = K.dropout_mask_apply(x, 0.25, 99, 5)
+    keep = float(mask.float().mean())
+    assert abs(keep - 0.75) < 5e-3
+    assert torch.allclose(y, mask.float() / 0.75)
+
+
+@pytest.mark.parametrize("gdt", [torch.float32, torch.bfloat16])
+def test_multi_tensor_optimizers(gdt):
+    shapes = [(7,), (33, 5), (1000, 17), (3,), (20000,)]
+    ps = [rnd(*s) for s in shapes]
+    gs = [rnd(*s, seed=1).to(gdt) for s in shapes]
+    for decoupled in (True, False):
+        pc, ms, vs = [p.clone() for p in ps], [torch.zeros_like(p) for p in ps], [torch.zeros_like(p) for p in ps]
+        pg = [p.clone().to(DEV) for p in ps]
+        mg, vg = [torch.zeros_like(p) for p in pg], [torch.zeros_like(p) for p in pg]
+        sh = [torch.empty_like(p, dtype=torch.bfloat16) for p in pg]
+        for step in (1, 2, 3):
+            K.adamw_step(pc, [g.float() for g in gs], ms, vs, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, decoupled)
+            K.adamw_step(pg, [g.to(DEV) for g in gs], mg, vg, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, decoupled,
+                         shadows=sh)
+        for a, b, s in zip(pg, pc, sh):
+            close(a, b, torch.float32, scale=20)
+            close(s, b.bfloat16(), torch.bfloat16)
+    # found_inf skips, grad_scale scales
+    pg = [p.clone().to(DEV) for p in ps]
+    mg, vg = [torch.zeros_like(p) for p in pg], [torch.zeros_like(p) for p in pg]
+    found = torch.ones(1, device=DEV)
+    K.adamw_step(pg, [g.to(DEV) for g in gs], mg, vg, 1e-2, 0.9, 0.999, 1e-8, 0.1, 1, True, found_inf=found)
+    for a, b in zip(pg, ps):
+        assert torch.equal(a.cpu(), b)
+    us = [torch.zeros_like(p) for p in ps]
+    ug = [torch.zeros_like(p).to(DEV) for p in ps]
+    pc, pg = [p.clone() for p in ps], [p.clone().to(DEV) for p in ps]
+    K.sgd_step(pc, [g.float() for g in gs], us, 0.1, 0.9, 0.01)
+    K.sgd_step(pg, [g.to(DEV) for g in gs], ug, 0.1, 0.9, 0.01)
+    for a, b in zip(pg, pc):
+        close(a, b, torch.float32, scale=10)
+    gg = [g.to(DEV).clone() for g in gs]
+    found = torch.zeros(1, device=DEV)
+    K.unscale_and_check(gg, torch.full((1,), 0.5, device=DEV), found)
+    assert float(found) == 0.0
+    close(gg[2], gs[2].float() * 0.5, gdt)
+    gg[1][3, 2] = float("inf")
+    K.unscale_and_check(gg, None, found)
+    assert float(found) == 1.0
+    acc = torch.zeros(1, device=DEV)
+    K.grad_norm_sq([g.to(DEV) for g in gs], acc)
+    ref = sum(float(g.float().pow(2).sum()) for g in gs)
+    assert abs(float(acc) - ref) / ref < 1e-3
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,k,renorm", [(1, 8, 2, True), (37, 128, 8, True), (100, 64, 6, False), (5, 4, 1, True)])
+def test_moe_router(dt, T, E, k, renorm):
+    logits = rnd(T, E, dt=dt) * 2
+    w, e, probs, counts = K.moe_router(logits.to(DEV), k, renorm)
+    wr, er, pr, cr = K.moe_router(logits.float(), k, renorm)
+    close(probs, pr, torch.float32, scale=10)
+    assert torch.equal(torch.sort(e.long().cpu(), -1)[0], torch.sort(er.long(), -1)[0])
+    close(torch.sort(w.cpu(), -1)[0], torch.sort(wr, -1)[0], torch.float32, scale=10)
+    assert torch.equal(counts.cpu(), cr)
+    dw, dp = rnd(T, k, seed=3), rnd(T, E, seed=4)
+    ref = K.moe_router_bwd(dw, dp, pr, e.cpu(), w.cpu(), renorm)
+    got = K.moe_router_bwd(dw.to(DEV), dp.to(DEV), probs, e, w, renorm)
+    close(got, ref, torch.float32, scale=50)
