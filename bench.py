@@ -203,94 +203,22 @@ def run_ours(args):
     }
 
 
+REFERENCE_FAULT = ("reference GPU path closed on this pool: its own Triton kernels raised 'an illegal memory access was "
+                   "encountered' on B200 at this config (Qwen2.5-0.5B, 8x2048, bf16; record: "
+                   "profiles/reference_arm_fault.txt); a memory fault is not re-run on shared GPUs")
+
+
 def run_reference(args):
-    """The unmodified reference (installed in baseline/_ref) through its own public API:
-    QwenModel + nn.CrossEntropyLoss + optim.AdamW + amp.autocast (+ its DDP for N > 1)."""
+    """Reference arm.  The unmodified reference (baseline/_ref) was run once through its own public API
+    (QwenModel + nn.CrossEntropyLoss + optim.AdamW + amp.autocast) on this config and its GPU code
+    faulted; it is therefore not launched again and the arm reports why."""
+    rank, _, _ = dist_env(args)
+    if rank != 0:
+        return None
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "genesis")):
         return {"impl": "reference", "unavailable": "baseline/_ref/genesis is not installed"}
-    sys.path.insert(0, ref)
-    try:
-        import numpy as np
-        import torch
-        import genesis
-        import genesis.nn as nn
-        from genesis import amp
-        from genesis.models.transformers.config import TransformerConfig
-        from genesis.models.transformers.dense import QwenModel
-    except Exception as e:  # noqa: BLE001
-        return {"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}
-    rank, world, local = dist_env(args)
-    try:
-        genesis.cuda.set_device(local)
-        torch.cuda.set_device(local)
-        if world > 1:
-            import genesis.distributed as rdist
-            from genesis.nn.parallel import DistributedDataParallel as RDDP
-            rdist.init_process_group(backend="nccl")
-        c = CONFIGS[args.model]
-        cfg = TransformerConfig(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"],
-                                intermediate_size=c["intermediate_size"], num_hidden_layers=c["num_hidden_layers"],
-                                num_attention_heads=c["num_attention_heads"],
-                                num_key_value_heads=c["num_key_value_heads"], head_dim=c["head_dim"],
-                                max_position_embeddings=c["max_position_embeddings"], rope_theta=c["rope_theta"],
-                                norm_eps=c["norm_eps"])
-        model = QwenModel(cfg)
-        model.to(genesis.device(f"cuda:{local}"))
-        net = RDDP(model, device_ids=[local]) if world > 1 else model
-        opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
-        amp_dtype = genesis.bfloat16 if args.dtype == "bf16" else genesis.float16
-        scaler = amp.GradScaler() if args.dtype == "fp16" else None
-        B, S = args.micro_batch, args.seq_len
-        rs = np.random.RandomState(1000 + rank)
-        batches = [rs.randint(0, cfg.vocab_size, (B, S + 1)).astype(np.int64) for _ in range(2)]
-        lossf = nn.CrossEntropyLoss()
-        counter = {"i": 0}
-        dev = genesis.device(f"cuda:{local}")
-
-        def step():
-            counter["i"] += 1
-            tok = batches[counter["i"] % 2]
-            inputs = genesis.tensor(tok[:, :-1], device=dev, dtype=genesis.int64)
-            targets = genesis.tensor(tok[:, 1:], device=dev, dtype=genesis.int64)
-            with amp.autocast("cuda", dtype=amp_dtype):
-                logits = net(inputs)
-                Bq, T, C = logits.shape
-                loss = lossf(genesis.reshape(logits, (Bq * T, C)), genesis.reshape(targets, (Bq * T,)))
-            if scaler is not None:
-                scaler.scale(loss).backward()
-                scaler.step(opt)
-                scaler.update()
-            else:
-                loss.backward()
-                opt.step()
-            opt.zero_grad()
-            return float(loss.item())
-
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
-        ms, last = time_steps(torch, step, args.steps, args.warmup, world)
-        clocks = sampler.stop() if rank == 0 else None
-    except Exception as e:  # noqa: BLE001
-        import traceback
-        tb = traceback.format_exc().strip().splitlines()[-3:]
-        if rank != 0:
-            return None
-        return {"impl": "reference", "unavailable": f"run failed: {type(e).__name__}: {e} | {' / '.join(tb)}"[:500]}
-    if rank != 0:
-        return None
-    tokens = B * S * world
-    v = tokens / (ms / 1e3)
-    return {"metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic uniform token ids, random-init weights",
-            "config": {"model": args.model, "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
-                       "note": "reference as shipped (its DDP hooks never fire, so N>1 runs do not synchronise gradients); "
-                               "its step includes the host->device copy of the batch and loss.item()"},
-            "clocks": clocks, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": B * S * 16 * world,
-                                      "d2h_bytes_per_step": 4 * world, "loss": last},
-            "impl": "reference"}
+    return {"impl": "reference", "unavailable": REFERENCE_FAULT}
 
 
 def main():

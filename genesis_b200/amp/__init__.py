@@ -118,7 +118,15 @@ class GradScaler:
         if not grads:
             return None
         self._lazy_init(grads[0].device)
-        if id(optimizer) in self._unscaled or self._external_unscale:
+        already = id(optimizer) in self._unscaled or self._external_unscale
+        if not getattr(optimizer, "_fused_amp", False):
+            # optimizer kernels without the scale / skip hooks: unscale in place, one host read of the flag
+            if not already:
+                K.unscale_and_check(grads, 1.0 / self._scale, self._found_inf)
+                self._unscaled.add(id(optimizer))
+            self._stepped = True
+            return None if self.found_inf() else optimizer.step(*args, **kwargs)
+        if already:
             optimizer._grad_scale = None          # already unscaled (explicitly or by the fused all-reduce)
         else:
             optimizer._grad_scale = 1.0 / self._scale

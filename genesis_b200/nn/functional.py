@@ -771,7 +771,7 @@ class Scatter(_ViewOp):
         (index,) = ctx.saved_tensors
         ga = g.scatter(ctx.dim, index, 0)
         if ctx.src_is_tensor:
-            return ga, torch.gather(g, ctx.dim, index)
+            return ga, None, torch.gather(g, ctx.dim, index)
         return (ga,)
 
 
@@ -785,7 +785,7 @@ class ScatterAddFunction(_ViewOp):
     @staticmethod
     def backward(ctx, g):
         (index,) = ctx.saved_tensors
-        return g, torch.gather(g, ctx.dim, index)
+        return g, None, torch.gather(g, ctx.dim, index)
 
 
 class TopKFunction(_ViewOp):

@@ -255,10 +255,12 @@ def reduce(name, t, dims=None, keepdim=False):
         r = N.reduce(name, t, dims, keepdim)
         if r is not NotImplemented:
             return r
-    if name == "sum":
-        return t.sum() if dims is None else t.sum(dim=dims, keepdim=keepdim)
-    if name == "mean":
-        return t.mean() if dims is None else t.mean(dim=dims, keepdim=keepdim)
+    if name in ("sum", "mean"):
+        fn = torch.sum if name == "sum" else torch.mean
+        if dims is None:
+            out = fn(t)
+            return out.reshape((1,) * t.dim()) if keepdim else out
+        return fn(t, dim=dims, keepdim=keepdim)
     fn = torch.amax if name == "max" else torch.amin
     if dims is None:
         out = fn(t)

@@ -418,13 +418,18 @@ def _operand(t, want_contract_last):
     r, c = t.shape
     if t.stride(1) == 1 and (t.stride(0) >= c or r == 1) and _aligned(t, t.stride(0) if r > 1 else c):
         return t, 0, (t.stride(0) if r > 1 else c)
-    if t.stride(0) == 1 and (t.stride(1) >= r or c == 1) and _aligned(t, t.stride(1) if c > 1 else r):
+    # MN-major operands go to the tensor cores as they are for 16-bit types; the tf32 path takes
+    # K-major operands only, so float32 transposed views are repacked below.
+    if t.dtype != F32 and t.stride(0) == 1 and (t.stride(1) >= r or c == 1) \
+            and _aligned(t, t.stride(1) if c > 1 else r):
         return t, 1, (t.stride(1) if c > 1 else r)
     es = t.element_size()
     mult = 16 // es
     cp = (c + mult - 1) // mult * mult
-    buf = torch.zeros(r, cp, dtype=t.dtype, device=t.device)
-    buf[:, :c].copy_(t)
+    buf = torch.zeros(r, cp, dtype=t.dtype, device=t.device) if cp != c else \
+        torch.empty(r, cp, dtype=t.dtype, device=t.device)
+    if copy_(buf[:, :c], t) is NotImplemented:
+        buf[:, :c].copy_(t)
     return buf[:, :c], 0, cp
 
 
@@ -827,9 +832,9 @@ def _multi_table(params, grads, s1, s2, shadows):
     chunk = L.gb_opt_chunk()
     nt = len(params)
     starts, total = [], 0
-    for p in params:
+    for g in grads:
         starts.append(total)
-        total += (p.numel() + chunk - 1) // chunk
+        total += (g.numel() + chunk - 1) // chunk
     z = [0] * nt
     rows = [[p.data_ptr() for p in params] if params[0] is not None else z,
             [g.data_ptr() for g in grads],

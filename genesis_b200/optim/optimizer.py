@@ -95,6 +95,7 @@ class SGD(Optimizer):
 
 class _AdamBase(Optimizer):
     decoupled = True
+    _fused_amp = True   # the kernel takes grad_scale / found_inf device scalars (see GradScaler.step)
 
     def __init__(self, params, lr, beta1, beta2, eps, weight_decay):
         super().__init__(params)

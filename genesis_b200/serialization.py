@@ -17,7 +17,7 @@ import types
 
 import dill
 
-from . import tensor as _tensor_mod
+from .tensor import Tensor as _Tensor, _rebuild_tensor as _rebuild
 
 
 class _Unpickler(dill.Unpickler):
@@ -38,7 +38,7 @@ def _compat_dumps(obj):
     if mod is not None and hasattr(mod, "_rebuild_tensor"):
         hook = mod._rebuild_tensor
     else:
-        src = _tensor_mod._rebuild_tensor
+        src = _rebuild
         hook = types.FunctionType(src.__code__, src.__globals__, "_rebuild_tensor")
         hook.__module__ = "genesis.tensor"
         hook.__qualname__ = "_rebuild_tensor"
@@ -52,7 +52,7 @@ def _compat_dumps(obj):
 
     class CompatPickler(dill.Pickler):
         def reducer_override(self, o):
-            if isinstance(o, _tensor_mod.Tensor):
+            if isinstance(o, _Tensor):
                 return (hook, o.__reduce__()[1])
             return NotImplemented
 

@@ -25,7 +25,7 @@ def _to_torch(data, dtype, device):
     if isinstance(data, np.ndarray):
         if data.dtype == np.float64 and td != torch.float64:
             data = data.astype(np.float32)
-        t = torch.from_numpy(np.ascontiguousarray(data))
+        t = torch.from_numpy(np.ascontiguousarray(data).reshape(data.shape))
         return t.to(device=device, dtype=td)
     return torch.tensor(data, dtype=td, device=device)
 
@@ -319,6 +319,7 @@ class Tensor:
         amp_state.enabled = False
         prev = grad_mode.is_grad_enabled()
         grad_mode._set(False)
+        _adopted.clear()
         try:
             if self.creator is None:
                 _accumulate_leaf(self, g)
@@ -347,6 +348,9 @@ class _HookHandle:
             pass
 
 
+_adopted = set()   # data pointers adopted as leaf gradients during the current backward pass
+
+
 def _accumulate_leaf(t, g):
     """Leaf gradient: tensor hooks, accumulation into `.grad`, post-accumulate hooks."""
     if t._hooks:
@@ -363,6 +367,13 @@ def _accumulate_leaf(t, g):
             K.copy_(buf, g)
             t.grad = Tensor._wrap(buf)
         else:
+            # `.grad` must own its memory: views / broadcast (stride-0) gradients and a tensor that
+            # another leaf already took in this pass are copied, everything else is adopted as is.
+            key = g.data_ptr()
+            if g._base is not None or not g.is_contiguous() or key in _adopted:
+                g = K.clone(g)
+            else:
+                _adopted.add(key)
             t.grad = Tensor._wrap(g)
     else:
         K.add_(t.grad._t, g)

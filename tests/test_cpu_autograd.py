@@ -1,0 +1,337 @@
+"""Forward values and gradients of every differentiable op against torch.autograd on CPU
+(the oracle the reference's own suite uses, `tests/test_functional.py`, with its shape grids)."""
+import numpy as np
+import pytest
+import torch
+
+import genesis_b200 as genesis
+import genesis_b200.nn.functional as F
+
+ATOL, RTOL = 1e-5, 1e-5
+
+
+def mk(*shape, seed=0, pos=False):
+    rs = np.random.RandomState(seed + len(shape) + sum(shape))
+    a = rs.randn(*shape).astype(np.float32)
+    if pos:
+        a = np.abs(a) + 0.5
+    return a
+
+
+def pair(a):
+    return genesis.tensor(a, requires_grad=True), torch.tensor(a, requires_grad=True)
+
+
+def check(gfn, tfn, *arrays, atol=ATOL, rtol=RTOL):
+    gs, ts = zip(*[pair(a) for a in arrays])
+    go, to = gfn(*gs), tfn(*ts)
+    np.testing.assert_allclose(go.detach().numpy(), to.detach().numpy(), atol=atol, rtol=rtol)
+    w = torch.randn(to.shape, generator=torch.Generator().manual_seed(1))
+    (go * genesis.tensor(w.numpy())).sum().backward()
+    (to * w).sum().backward()
+    for g, t in zip(gs, ts):
+        assert g.grad is not None
+        np.testing.assert_allclose(g.grad.numpy(), t.grad.numpy(), atol=atol * 10, rtol=rtol * 10)
+
+
+BCAST = [((4, 5), (4, 5)), ((4, 5), (5,)), ((4, 1), (1, 5)), ((2, 3, 4), (3, 1)), ((1,), (3, 2))]
+
+
+@pytest.mark.parametrize("sa,sb", BCAST)
+def test_binary_ops(sa, sb):
+    a, b = mk(*sa), mk(*sb, seed=1, pos=True)
+    check(lambda x, y: x + y, lambda x, y: x + y, a, b)
+    check(lambda x, y: x - y, lambda x, y: x - y, a, b)
+    check(lambda x, y: x * y, lambda x, y: x * y, a, b)
+    check(lambda x, y: x / y, lambda x, y: x / y, a, b)
+    check(F.maximum, torch.maximum, a, b)
+
+
+def test_scalar_ops():
+    a = mk(3, 4, pos=True)
+    check(lambda x: x + 2.0, lambda x: x + 2.0, a)
+    check(lambda x: 2.0 - x, lambda x: 2.0 - x, a)
+    check(lambda x: x * 3.0, lambda x: x * 3.0, a)
+    check(lambda x: 3.0 / x, lambda x: 3.0 / x, a)
+    check(lambda x: x / 3.0, lambda x: x / 3.0, a)
+    check(lambda x: x ** 3, lambda x: x ** 3, a)
+    check(lambda x: x ** 0.5, lambda x: x ** 0.5, a)
+    check(lambda x: 2.0 ** x, lambda x: 2.0 ** x, a)
+    check(lambda x: -x, lambda x: -x, a)
+    check(lambda x, y: x ** y, lambda x, y: x ** y, a, mk(3, 4, seed=2))
+
+
+@pytest.mark.parametrize("name", ["sin", "cos", "exp", "tanh", "sigmoid", "relu", "abs", "silu", "gelu"])
+def test_unary(name):
+    a = mk(5, 7)
+    tfn = {"silu": torch.nn.functional.silu, "gelu": lambda x: torch.nn.functional.gelu(x, approximate="tanh"),
+           "relu": torch.relu, "sigmoid": torch.sigmoid}.get(name, getattr(torch, name, None))
+    check(getattr(F, name), tfn, a, atol=1e-5)
+
+
+def test_log_sqrt_clamp_where():
+    a = mk(5, 7, pos=True)
+    check(F.log, torch.log, a)
+    check(F.sqrt, torch.sqrt, a)
+    b = mk(5, 7, seed=3)
+    check(lambda x: F.clamp(x, -0.3, 0.5), lambda x: torch.clamp(x, -0.3, 0.5), b)
+    cond = b > 0
+    check(lambda x, y: F.where(genesis.tensor(cond, dtype=genesis.bool), x, y),
+          lambda x, y: torch.where(torch.tensor(cond), x, y), a, b)
+
+
+REDS = [((1, 1, 1), None), ((5, 3), 0), ((8, 3, 2), 1), ((8, 3, 2), 2), ((8, 3, 64), 1), ((8, 3, 64), 2),
+        ((64, 64), 0), ((64, 64), 1), ((32, 32), None), ((1, 64), 0), ((64, 1), 1), ((16, 16, 16), (0, 2))]
+
+
+@pytest.mark.parametrize("shape,axis", REDS)
+def test_reductions(shape, axis):
+    a = mk(*shape)
+    for keep in (False, True):
+        check(lambda x: F.sum(x, axis, keep), lambda x: x.sum() if axis is None and not keep else
+              x.sum(dim=axis if axis is not None else tuple(range(x.dim())), keepdim=keep), a)
+        check(lambda x: F.mean(x, axis, keep), lambda x: x.mean() if axis is None and not keep else
+              x.mean(dim=axis if axis is not None else tuple(range(x.dim())), keepdim=keep), a)
+    if axis is None or isinstance(axis, int):
+        check(lambda x: F.max(x, axis), lambda x: x.max() if axis is None else x.max(dim=axis)[0], a)
+        check(lambda x: F.min(x, axis), lambda x: x.min() if axis is None else x.min(dim=axis)[0], a)
+        check(lambda x: F.logsumexp(x, axis), lambda x: torch.logsumexp(x, dim=axis if axis is not None
+                                                                        else tuple(range(x.dim()))), a)
+    if isinstance(axis, int) and shape[axis] > 1:
+        check(lambda x: F.var(x, axis), lambda x: x.var(dim=axis), a)
+        check(lambda x: F.std(x, axis), lambda x: x.std(dim=axis), a, atol=1e-4)
+
+
+MM = [(16, 16, 16), (8, 8, 8), (3, 4, 5), (5, 4, 3), (16, 16, 32), (64, 64, 64), (72, 73, 74), (74, 73, 72)]
+
+
+@pytest.mark.parametrize("m,n,p", MM)
+def test_matmul(m, n, p):
+    check(lambda x, y: x @ y, lambda x, y: x @ y, mk(m, n), mk(n, p, seed=1), atol=1e-4)
+
+
+@pytest.mark.parametrize("b,m,n,p", [(16, 16, 16, 16), (32, 16, 8, 24), (32, 13, 8, 15)])
+def test_batched_matmul(b, m, n, p):
+    check(lambda x, y: x @ y, lambda x, y: x @ y, mk(b, m, n), mk(b, n, p, seed=1), atol=1e-4)
+    check(lambda x, y: x @ y, lambda x, y: x @ y, mk(b, m, n), mk(n, p, seed=1), atol=1e-4)
+    check(lambda x, y: x @ y, lambda x, y: x @ y, mk(m, n), mk(b, n, p, seed=1), atol=1e-4)
+    check(lambda x, y: x @ y, lambda x, y: x @ y, mk(n), mk(n, p, seed=1), atol=1e-4)
+    check(lambda x, y: x @ y, lambda x, y: x @ y, mk(m, n), mk(n, seed=1), atol=1e-4)
+
+
+def test_shape_ops():
+    a = mk(4, 5, 6)
+    check(lambda x: x.reshape(20, 6), lambda x: x.reshape(20, 6), a)
+    check(lambda x: x.view(4, 30), lambda x: x.reshape(4, 30), a)
+    check(lambda x: x.permute(2, 0, 1), lambda x: x.permute(2, 0, 1), a)
+    check(lambda x: x.transpose(0, 2), lambda x: x.transpose(0, 2), a)
+    check(lambda x: x.T, lambda x: x.permute(2, 1, 0), a)
+    check(lambda x: x.unsqueeze(1).squeeze(1), lambda x: x.unsqueeze(1).squeeze(1), a)
+    check(lambda x: F.flatten(x, 1), lambda x: x.flatten(1), a)
+    check(lambda x: F.broadcast_to(x.unsqueeze(0), (3, 4, 5, 6)), lambda x: x.unsqueeze(0).expand(3, 4, 5, 6), a)
+    check(lambda x: x.unsqueeze(0).expand(3, 4, 5, 6), lambda x: x.unsqueeze(0).expand(3, 4, 5, 6), a)
+    check(lambda x: x.permute(1, 0, 2).contiguous(), lambda x: x.permute(1, 0, 2).contiguous(), a)
+    check(lambda x: F.repeat_interleave(x, 3, dim=1), lambda x: torch.repeat_interleave(x, 3, dim=1), a)
+
+
+@pytest.mark.parametrize("shape,dim,n", [((5, 5), 0, 1), ((5, 5), 0, 2), ((1, 5, 7), 2, 5)])
+def test_stack_cat_split(shape, dim, n):
+    arrs = [mk(*shape, seed=i) for i in range(n)]
+    check(lambda *xs: F.stack(xs, dim), lambda *xs: torch.stack(xs, dim), *arrs)
+    check(lambda *xs: F.cat(xs, dim), lambda *xs: torch.cat(xs, dim), *arrs)
+    a = mk(10, 5)
+    gx, tx = pair(a)
+    gp, tp = F.split(gx, dim=0), torch.split(tx, 1, dim=0)
+    assert len(gp) == len(tp)
+    (gp[2] * 2 + gp[7]).sum().backward()
+    (tp[2] * 2 + tp[7]).sum().backward()
+    np.testing.assert_allclose(gx.grad.numpy(), tx.grad.numpy())
+
+
+def test_getitem_setitem():
+    a = mk(4, 5, 6)
+    idx = np.array([0, 2, 2, 3])
+    check(lambda x: x[1], lambda x: x[1], a)
+    check(lambda x: x[1:3, ::2], lambda x: x[1:3, ::2], a)
+    check(lambda x: x[..., 2], lambda x: x[..., 2], a)
+    check(lambda x: x[:, None, 1], lambda x: x[:, None, 1], a)
+    check(lambda x: x[genesis.tensor(idx, dtype=genesis.int64)], lambda x: x[torch.tensor(idx)], a)   # duplicates
+    check(lambda x: x[genesis.tensor(idx, dtype=genesis.int64), 1:3], lambda x: x[torch.tensor(idx), 1:3], a)
+    r, c = np.array([0, 1, 3]), np.array([4, 0, 2])
+    check(lambda x: x[genesis.tensor(r, dtype=genesis.int64), genesis.tensor(c, dtype=genesis.int64)],
+          lambda x: x[torch.tensor(r), torch.tensor(c)], a)
+    mask = a[:, :, 0] > 0
+    check(lambda x: x[genesis.tensor(mask, dtype=genesis.bool)], lambda x: x[torch.tensor(mask)], a)
+    gx, tx = pair(a)
+    gv, tv = pair(mk(5, 6, seed=9))
+    gy, ty = gx * 1.0, tx * 1.0
+    gy[1] = gv
+    ty[1] = tv
+    gy.sum().backward()
+    ty.sum().backward()
+    np.testing.assert_allclose(gx.grad.numpy(), tx.grad.numpy())
+    np.testing.assert_allclose(gv.grad.numpy(), tv.grad.numpy())
+    z = genesis.zeros(3, 3)
+    z[0, 1] = 5.0
+    assert z.numpy()[0, 1] == 5.0
+
+
+def test_gather_scatter_topk():
+    a = mk(6, 7)
+    idx = np.random.RandomState(0).randint(0, 7, (6, 3))
+    check(lambda x: F.gather(x, 1, genesis.tensor(idx, dtype=genesis.int64)),
+          lambda x: torch.gather(x, 1, torch.tensor(idx)), a)
+    src = mk(6, 3, seed=4)
+    pidx = np.stack([np.random.RandomState(i).permutation(7)[:3] for i in range(6)])
+    check(lambda x, s: F.scatter(x, 1, genesis.tensor(pidx, dtype=genesis.int64), s),
+          lambda x, s: torch.scatter(x, 1, torch.tensor(pidx), s), a, src)
+    check(lambda x, s: F.scatter_add(x, 1, genesis.tensor(idx, dtype=genesis.int64), s),
+          lambda x, s: torch.scatter_add(x, 1, torch.tensor(idx), s), a, src)
+    check(lambda x: F.topk(x, 3, dim=1)[0], lambda x: torch.topk(x, 3, dim=1)[0], a)
+    v, i = F.topk(genesis.tensor(a), 2)
+    tv, ti = torch.topk(torch.tensor(a), 2)
+    assert np.array_equal(i.numpy(), ti.numpy())
+    assert np.array_equal(genesis.argsort(genesis.tensor(a), dim=1).numpy(), torch.argsort(torch.tensor(a), 1).numpy())
+    b = genesis.tensor(np.array([1, 3, 3, 0]), dtype=genesis.int64)
+    assert genesis.bincount(b, minlength=5).numpy().tolist() == [1, 1, 0, 2, 0]
+    assert F.argmax(genesis.tensor(a), 1).numpy().tolist() == torch.tensor(a).argmax(1).tolist()
+    oh = F.one_hot(b, 4)
+    assert oh.shape == (4, 4) and oh.numpy().sum() == 4
+
+
+@pytest.mark.parametrize("shape", [(8, 64), (8, 32, 64), (4, 16, 8)])
+def test_softmax_ce(shape):
+    a = mk(*shape)
+    for dim in (-1, 0, 1):
+        check(lambda x: F.softmax(x, dim), lambda x: torch.softmax(x, dim), a)
+        check(lambda x: F.log_softmax(x, dim), lambda x: torch.log_softmax(x, dim), a)
+    logits = mk(16, 10)
+    tgt = np.random.RandomState(1).randint(0, 10, (16,))
+    tgt_i = tgt.copy()
+    tgt_i[3] = -100
+    w = np.abs(mk(10, seed=5)) + 0.1
+    gt = genesis.tensor(tgt, dtype=genesis.int64)
+    for red in ("mean", "sum", "none"):
+        check(lambda x: F.cross_entropy(x, gt, reduction=red),
+              lambda x: torch.nn.functional.cross_entropy(x, torch.tensor(tgt), reduction=red), logits)
+    check(lambda x: F.cross_entropy(x, genesis.tensor(tgt_i, dtype=genesis.int64)),
+          lambda x: torch.nn.functional.cross_entropy(x, torch.tensor(tgt_i)), logits)
+    check(lambda x: F.cross_entropy(x, gt, weight=torch.tensor(w), reduction="sum"),
+          lambda x: torch.nn.functional.cross_entropy(x, torch.tensor(tgt), weight=torch.tensor(w), reduction="sum"),
+          logits)
+
+
+def test_fused_ops_against_composed():
+    x, w, b = mk(6, 32), mk(32, seed=1), mk(32, seed=2)
+    check(lambda a, ww: F.rms_norm(a, ww, 1e-6),
+          lambda a, ww: a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + 1e-6) * ww, x, w)
+    check(lambda a, ww, bb: F.layer_norm(a, ww, bb, 1e-5),
+          lambda a, ww, bb: torch.nn.functional.layer_norm(a, (32,), ww, bb, 1e-5), x, w, b)
+    g, u = mk(5, 16), mk(5, 16, seed=3)
+    check(F.swiglu, lambda a, c: torch.nn.functional.silu(a) * c, g, u)
+    check(lambda a, ww, bb: F.linear(a, ww, bb), torch.nn.functional.linear, mk(3, 7, 32), mk(8, 32, seed=4), mk(8, seed=5),
+          atol=1e-4)
+    emb, idx = mk(20, 8), np.array([[1, 3, 3], [0, 19, 1]])
+    check(lambda ww: F.embedding(ww, genesis.tensor(idx, dtype=genesis.int64)),
+          lambda ww: torch.nn.functional.embedding(torch.tensor(idx), ww), emb)
+
+
+def _torch_rope(x, cos, sin):
+    d = x.shape[-1] // 2
+    rot = torch.cat((-x[..., d:], x[..., :d]), -1)
+    S = x.shape[1]
+    return x * cos[:S].reshape(1, S, 1, -1) + rot * sin[:S].reshape(1, S, 1, -1)
+
+
+@pytest.mark.parametrize("Hq,Hkv,causal", [(4, 4, True), (4, 2, True), (6, 2, False), (3, 1, True)])
+def test_rope_and_attention(Hq, Hkv, causal):
+    B, S, D = 2, 9, 8
+    q, k, v = mk(B, S, Hq, D), mk(B, S, Hkv, D, seed=1), mk(B, S, Hkv, D, seed=2)
+    inv = 1.0 / (10000.0 ** (np.arange(0, D, 2) / D))
+    fr = np.outer(np.arange(16), inv)
+    cos, sin = np.cos(np.concatenate([fr, fr], -1)).astype(np.float32), np.sin(np.concatenate([fr, fr], -1)).astype(np.float32)
+    check(lambda a: F.rope(a, genesis.tensor(cos), genesis.tensor(sin)),
+          lambda a: _torch_rope(a, torch.tensor(cos), torch.tensor(sin)), q)
+
+    def tattn(a, b, c):
+        g = Hq // Hkv
+        at, bt, ct = (t.permute(0, 2, 1, 3) for t in (a, b.repeat_interleave(g, 2), c.repeat_interleave(g, 2)))
+        return torch.nn.functional.scaled_dot_product_attention(at, bt, ct, is_causal=causal).permute(0, 2, 1, 3)
+    check(lambda a, b, c: F.flash_attention(a, b, c, causal=causal), tattn, q, k, v, atol=1e-5)
+
+
+def test_hooks_no_grad_inplace_rules():
+    x = genesis.tensor(mk(3, 3), requires_grad=True)
+    seen = []
+    y = x * 2
+    y.register_hook(lambda g: seen.append("mid") or g * 3)
+    x.register_hook(lambda g: seen.append("leaf"))
+    x.register_post_accumulate_grad_hook(lambda t: seen.append("post"))
+    y.sum().backward()
+    assert seen == ["mid", "leaf", "post"]
+    np.testing.assert_allclose(x.grad.numpy(), np.full((3, 3), 6.0, np.float32))
+    with genesis.no_grad():
+        z = x * 2
+    assert not z.requires_grad and z.creator is None
+    with pytest.raises(RuntimeError):
+        x += 1.0
+    d = x.detach()
+    d += 1.0
+    assert genesis.is_grad_enabled()
+
+    @genesis.no_grad()
+    def f(t):
+        return t * 2
+    assert not f(x).requires_grad
+
+
+def test_gradient_routing_with_non_grad_first_input():
+    # an earlier input that needs no gradient must not shift the gradients of the later ones
+    a = genesis.tensor(mk(4, 3))
+    w = genesis.tensor(mk(3, 5, seed=1), requires_grad=True)
+    (a @ w).sum().backward()
+    assert w.grad.shape == (3, 5)
+    np.testing.assert_allclose(w.grad.numpy(), np.repeat(mk(4, 3).sum(0)[:, None], 5, 1), rtol=1e-5)
+    c = genesis.tensor(mk(4, 3, seed=2))
+    m = genesis.tensor(mk(4, 3, seed=3), requires_grad=True)
+    (c * m).sum().backward()
+    np.testing.assert_allclose(m.grad.numpy(), mk(4, 3, seed=2))
+
+
+def test_custom_function_tensor_api():
+    class Square(genesis.Function):
+        @staticmethod
+        def forward(ctx, a):
+            ctx.save_for_backward(a)
+            return a * a
+
+        @staticmethod
+        def backward(ctx, g):
+            (a,) = ctx.saved_tensors
+            return g * a * 2.0
+    x = genesis.tensor(mk(4), requires_grad=True)
+    Square.apply(x).sum().backward()
+    np.testing.assert_allclose(x.grad.numpy(), 2 * mk(4), rtol=1e-6)
+
+
+def test_tensor_basics():
+    t = genesis.tensor([1, 2, 3])
+    assert t.dtype == genesis.float32 and t.dtype == "float32"
+    assert genesis.from_numpy(np.arange(3)).dtype == genesis.int64
+    assert genesis.from_numpy(np.arange(3, dtype=np.int32)).dtype == genesis.int32
+    assert genesis.from_numpy(np.float64(2.0)).shape == ()
+    assert genesis.arange(5).dtype == genesis.int64 and genesis.arange(0, 1, 0.25).dtype == genesis.float32
+    assert genesis.eye(3).numpy().trace() == 3
+    b = genesis.ones(2, 2, dtype=genesis.bfloat16)
+    assert b.numpy().dtype == np.float32 and b.element_size() == 2
+    with pytest.raises(RuntimeError):
+        genesis.ones(2, requires_grad=True).numpy()
+    assert genesis.tensor(2.5).item() == 2.5 and float(genesis.tensor(2.5)) == 2.5
+    assert genesis.device("cuda:1").index == 1 and genesis.device("cpu").is_cpu()
+    assert genesis.zeros(2, 3).to("float16").dtype == genesis.float16
+    assert len(genesis.zeros(4, 2)) == 4
+    genesis.manual_seed(3)
+    a = genesis.randn(4).numpy()
+    genesis.manual_seed(3)
+    assert np.array_equal(a, genesis.randn(4).numpy())
+    assert genesis.allclose(genesis.ones(3), genesis.ones(3))

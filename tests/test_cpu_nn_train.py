@@ -1,0 +1,396 @@
+"""nn modules against torch.nn, optimizers / schedulers / AMP / serialization, and the config-1
+workload (MLP 784-256-10, AdamW, 100 steps, seed 0) against a plain-torch restatement that follows
+the reference's CPU path draw for draw."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import genesis_b200 as genesis
+import genesis_b200.nn as nn
+import genesis_b200.nn.functional as F
+from genesis_b200 import optim
+
+
+def arr(*shape, seed=0):
+    return np.random.RandomState(seed + sum(shape)).randn(*shape).astype(np.float32)
+
+
+# ------------------------------------------------------------------ modules vs torch.nn
+@pytest.mark.parametrize("shape", [(8, 64), (32, 32), (4, 16, 64)])
+def test_linear_layernorm_rmsnorm_embedding(shape):
+    x = arr(*shape)
+    d = shape[-1]
+    lin, tlin = nn.Linear(d, 24), torch.nn.Linear(d, 24)
+    tlin.weight.data = lin.weight._t.clone()
+    tlin.bias.data = lin.bias._t.clone()
+    gx, tx = genesis.tensor(x, requires_grad=True), torch.tensor(x, requires_grad=True)
+    gy, ty = lin(gx), tlin(tx)
+    np.testing.assert_allclose(gy.detach().numpy(), ty.detach().numpy(), atol=2e-5, rtol=1e-5)
+    gy.sum().backward()
+    ty.sum().backward()
+    np.testing.assert_allclose(lin.weight.grad.numpy(), tlin.weight.grad.numpy(), atol=2e-5, rtol=1e-5)
+    np.testing.assert_allclose(lin.bias.grad.numpy(), tlin.bias.grad.numpy(), atol=2e-5, rtol=1e-5)
+    np.testing.assert_allclose(gx.grad.numpy(), tx.grad.numpy(), atol=2e-5, rtol=1e-5)
+    ln, tln = nn.LayerNorm(d), torch.nn.LayerNorm(d)
+    np.testing.assert_allclose(ln(genesis.tensor(x)).detach().numpy(), tln(torch.tensor(x)).detach().numpy(), atol=2e-5)
+    rn = nn.RMSNorm(d)
+    ref = x / np.sqrt((x ** 2).mean(-1, keepdims=True) + 1e-6)
+    np.testing.assert_allclose(rn(genesis.tensor(x)).detach().numpy(), ref, atol=1e-4)
+    assert nn.FusedLayerNorm(d).eps == 1e-6
+
+
+def test_batchnorm_dropout_activations_losses():
+    x = arr(16, 8)
+    bn, tbn = nn.BatchNorm1d(8), torch.nn.BatchNorm1d(8)
+    np.testing.assert_allclose(bn(genesis.tensor(x)).detach().numpy(), tbn(torch.tensor(x)).detach().numpy(), atol=1e-5)
+    np.testing.assert_allclose(bn.running_mean.numpy(), tbn.running_mean.numpy(), atol=1e-6)
+    bn.eval()
+    tbn.eval()
+    tbn.running_var.data = bn.running_var._t.clone()     # torch keeps the unbiased estimate; align before comparing
+    np.testing.assert_allclose(bn(genesis.tensor(x)).detach().numpy(), tbn(torch.tensor(x)).detach().numpy(), atol=1e-5)
+    dr = nn.Dropout(0.5)
+    y = dr(genesis.ones(1000, 10)).numpy()
+    assert set(np.unique(y)).issubset({0.0, 2.0}) and 0.4 < (y > 0).mean() < 0.6
+    dr.eval()
+    assert np.array_equal(dr(genesis.ones(4, 4)).numpy(), np.ones((4, 4), np.float32))
+    for mod, tf in [(nn.ReLU(), torch.relu), (nn.SiLU(), torch.nn.functional.silu), (nn.Softmax(-1), lambda t: t.softmax(-1)),
+                    (nn.Sigmoid(), torch.sigmoid), (nn.Tanh(), torch.tanh)]:
+        np.testing.assert_allclose(mod(genesis.tensor(x)).numpy(), tf(torch.tensor(x)).numpy(), atol=1e-6)
+    res = nn.Residual(nn.ReLU())
+    np.testing.assert_allclose(res(genesis.tensor(x)).numpy(), np.maximum(x, 0) + x)
+    a, b = arr(6, 5), arr(6, 5, seed=1)
+    tgt01 = (b > 0).astype(np.float32)
+    prob = 1 / (1 + np.exp(-a))
+    pairs = [(nn.MSELoss(), torch.nn.MSELoss(), a, b), (nn.L1Loss(), torch.nn.L1Loss(), a, b),
+             (nn.BCELoss(), torch.nn.BCELoss(), prob, tgt01),
+             (nn.BCEWithLogitsLoss(), torch.nn.BCEWithLogitsLoss(), a, tgt01)]
+    for gl, tl, p, t in pairs:
+        gp, tp = genesis.tensor(p, requires_grad=True), torch.tensor(p, requires_grad=True)
+        lg, lt = gl(gp, genesis.tensor(t)), tl(tp, torch.tensor(t))
+        np.testing.assert_allclose(lg.item(), lt.item(), rtol=1e-5)
+        lg.backward()
+        lt.backward()
+        np.testing.assert_allclose(gp.grad.numpy(), tp.grad.numpy(), atol=1e-6, rtol=1e-4)
+    logits, y = arr(7, 5), np.array([0, 4, 2, 2, 1, 3, 0])
+    ce = nn.CrossEntropyLoss()(genesis.tensor(logits), genesis.tensor(y, dtype=genesis.int64))
+    np.testing.assert_allclose(ce.item(), torch.nn.functional.cross_entropy(torch.tensor(logits), torch.tensor(y)).item(),
+                               rtol=1e-6)
+    assert abs(nn.SoftmaxLoss()(genesis.tensor(logits), genesis.tensor(y, dtype=genesis.int64)).item() - ce.item()) < 1e-7
+
+
+def test_attention_modules_and_containers():
+    x = genesis.tensor(arr(2, 12, 32))
+    mha = nn.MultiheadAttention(32, 4)
+    out, att = mha(x)
+    assert out.shape == (2, 12, 32) and att.shape == (2, 4, 12, 12)
+    att = att.detach()
+    np.testing.assert_allclose(att.numpy().sum(-1), 1.0, atol=1e-5)
+    assert np.allclose(np.triu(att.numpy()[0, 0], 1), 0)
+    fused = nn.FusedMultiheadAttention(32, 4)
+    fused.w_qkv, fused.w_out = mha.w_qkv, mha.w_out
+    fo, none = fused(x)
+    assert none is None
+    np.testing.assert_allclose(fo.detach().numpy(), out.detach().numpy(), atol=1e-4)
+    ff = nn.FeedFowardSwiGLU(32, 64)
+    ff.eval()
+    assert ff(x).shape == (2, 12, 32)
+    seq = nn.Sequential(nn.Linear(4, 8), nn.ReLU(), nn.Linear(8, 2))
+    assert len(seq.parameters()) == 4                      # every parameter once
+    assert sorted(seq.state_dict()) == ["0.bias", "0.weight", "2.bias", "2.weight"]
+    ml = nn.ModuleList([nn.Linear(2, 2) for _ in range(3)])
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = ml
+            self.head = seq
+            self.register_buffer("scale", genesis.ones(1))
+            self.register_buffer("cache", genesis.zeros(2), persistent=False)
+    net = Net()
+    keys = list(net.state_dict())
+    assert "layers.0.weight" in keys and "head.2.bias" in keys and "scale" in keys and "cache" not in keys
+    assert "cache" in net.state_dict(compat=True)
+    assert net.num_parameters() == 3 * 6 + (4 * 8 + 8 + 8 * 2 + 2)
+    sd = {k: genesis.tensor(v.numpy() * 0 + 1) for k, v in net.state_dict().items()}
+    net.load_state_dict(sd)
+    assert float(net.head[0].weight.detach().numpy().mean()) == 1.0
+    with pytest.raises(KeyError):
+        net.load_state_dict({"nope": genesis.ones(1)})
+    net.load_state_dict({"_0.weight": genesis.zeros(8, 4)}, strict=False)
+    assert len(list(net.modules())) >= 8 and net.training
+    net.eval()
+    assert not net.head[0].training
+    emb = nn.Embedding(10, 4)
+    assert emb(genesis.tensor([[1, 2]], dtype=genesis.int64)).shape == (1, 2, 4)
+    cos, sin = nn.RotaryEmbedding(8, 32)(None, seq_len=5)
+    assert cos.shape == (1, 1, 5, 8)
+
+
+# ------------------------------------------------------------------ optimizers / schedulers
+@pytest.mark.parametrize("kind", ["sgd", "sgd_m", "adam", "adamw"])
+def test_optimizers_match_torch(kind):
+    w0 = arr(5, 3)
+    gp = nn.Parameter(genesis.tensor(w0))
+    tp = torch.nn.Parameter(torch.tensor(w0))
+    if kind == "sgd":
+        go, to = optim.SGD([gp], lr=0.1, weight_decay=0.01), torch.optim.SGD([tp], lr=0.1, weight_decay=0.01)
+    elif kind == "sgd_m":
+        # the reference's momentum form u = m*u + (1-m)*g from u = 0 (`optim/optimizer.py:56-92`)
+        go = optim.SGD([gp], lr=0.1, momentum=0.9)
+        w, u = w0.copy(), np.zeros_like(w0)
+        for step in range(5):
+            g = arr(5, 3, seed=step + 1)
+            gp.grad = genesis.tensor(g)
+            go.step()
+            u = 0.9 * u + 0.1 * g
+            w = w - 0.1 * u
+        np.testing.assert_allclose(gp.detach().numpy(), w, atol=2e-6, rtol=1e-5)
+        return
+    elif kind == "adam":
+        go, to = optim.Adam([gp], lr=0.01, weight_decay=0.1), torch.optim.Adam([tp], lr=0.01, weight_decay=0.1)
+    else:
+        go, to = optim.AdamW([gp], lr=0.01, weight_decay=0.1), torch.optim.AdamW([tp], lr=0.01, weight_decay=0.1)
+    for step in range(5):
+        g = arr(5, 3, seed=step + 1)
+        gp.grad = genesis.tensor(g)
+        tp.grad = torch.tensor(g)
+        go.step()
+        to.step()
+    np.testing.assert_allclose(gp.numpy() if not gp.requires_grad else gp.detach().numpy(), tp.detach().numpy(),
+                               atol=2e-6, rtol=1e-5)
+    go.zero_grad()
+    assert gp.grad is None
+
+
+def test_optimizer_state_dict_roundtrip_and_schedulers(tmp_path):
+    p = nn.Parameter(genesis.tensor(arr(4)))
+    o = optim.AdamW([p], lr=1e-2)
+    p.grad = genesis.tensor(arr(4, seed=1))
+    o.step()
+    sd = o.state_dict()
+    assert set(sd) == {"lr", "beta1", "beta2", "eps", "weight_decay", "t", "m", "v", "fused"} and 0 in sd["m"]
+    genesis.save({"opt": sd}, tmp_path / "o.pkl")
+    p2 = nn.Parameter(genesis.tensor(p.detach().numpy()))
+    o2 = optim.AdamW([p2], lr=5.0)
+    o2.load_state_dict(genesis.load(tmp_path / "o.pkl")["opt"])
+    assert o2.lr == 1e-2 and o2.t == 1
+    for opt_, par in ((o, p), (o2, p2)):
+        par.grad = genesis.tensor(arr(4, seed=2))
+        opt_.step()
+    np.testing.assert_allclose(p.detach().numpy(), p2.detach().numpy(), rtol=1e-6)
+    o3 = optim.SGD([p], lr=1e-3)
+    sch = optim.lr_scheduler.get_cosine_schedule_with_warmup(o3, 2, 10)
+    lrs = []
+    for _ in range(4):
+        sch.step()
+        lrs.append(o3.lr)
+    np.testing.assert_allclose(lrs, [0.0, 5e-4, 1e-3, 9.619e-4], rtol=1e-3, atol=1e-9)
+    st = sch.state_dict()
+    sch.load_state_dict(st)
+    assert sch.get_last_lr() == o3.lr
+    o4 = optim.SGD([p], lr=1.0)
+    s2 = optim.lr_scheduler.StepLR(o4, 2, 0.5)
+    got = []
+    for _ in range(5):
+        s2.step()
+        got.append(o4.lr)
+    assert got == [1.0, 1.0, 0.5, 0.5, 0.25]
+    o5 = optim.SGD([p], lr=1.0)
+    s3 = optim.lr_scheduler.CosineAnnealingLR(o5, 10)
+    s3.step(10)
+    assert abs(o5.lr) < 1e-9
+    o6 = optim.SGD([p], lr=1.0)
+    optim.lr_scheduler.ExponentialLR(o6, 0.5).step(3)
+    assert o6.lr == 0.125
+    total = nn.utils.clip_grad_norm_([p], 0.1)
+    assert total > 0 and abs(float(np.linalg.norm(p.grad.numpy())) - 0.1) < 1e-3
+
+
+# ------------------------------------------------------------------ AMP
+def test_autocast_policy_and_cast_cache():
+    lin = nn.Linear(8, 4)
+    x = genesis.tensor(arr(3, 8), requires_grad=True)
+    with genesis.amp.autocast(dtype=genesis.bfloat16):
+        assert genesis.amp.is_autocast_enabled() and genesis.enable_autocast
+        y = lin(x)
+        assert y.dtype == genesis.bfloat16
+        s = F.softmax(y, -1)
+        assert s.dtype == genesis.float32                      # fp32 policy
+        r = F.relu(x)
+        assert r.dtype == genesis.bfloat16                     # low-precision policy
+        z = y + genesis.ones(3, 4)
+        assert z.dtype == genesis.float32                      # promotion
+        m = x @ lin.weight.T
+        assert m.dtype == genesis.bfloat16
+        a, b = genesis.function.cast(lin.weight, torch.bfloat16), genesis.function.cast(lin.weight, torch.bfloat16)
+        assert a is b                                          # parameter casts are cached per region
+        loss = F.sum(s * s) + F.sum(m.float())
+    assert not genesis.amp.is_autocast_enabled()
+    loss.backward()
+    assert lin.weight.grad.dtype == genesis.float32 and x.grad.dtype == genesis.float32
+    y32 = lin(x)
+    assert y32.dtype == genesis.float32
+
+
+def test_grad_scaler_skips_and_grows():
+    p = nn.Parameter(genesis.tensor(np.ones(4, np.float32)))
+    o = optim.SGD([p], lr=0.1)
+    sc = genesis.amp.GradScaler(init_scale=1024.0, growth_interval=2)
+    for i in range(2):
+        o.zero_grad()
+        loss = F.sum(p * 2.0)
+        sc.scale(loss).backward()
+        assert abs(p.grad.numpy()[0] - 2048.0) < 1e-3
+        sc.step(o)
+        sc.update()
+    np.testing.assert_allclose(p.detach().numpy(), 1.0 - 2 * 0.2, rtol=1e-6)
+    assert sc.get_scale() == 2048.0                            # grew after 2 good steps
+    o.zero_grad()
+    sc.scale(F.sum(p * float("inf"))).backward()
+    before = p.detach().numpy().copy()
+    sc.step(o)
+    assert sc.found_inf()
+    sc.update()
+    assert np.array_equal(p.detach().numpy(), before) and sc.get_scale() == 1024.0
+    o.zero_grad()
+    sc.scale(F.sum(p)).backward()
+    sc.unscale_(o)
+    np.testing.assert_allclose(p.grad.numpy(), 1.0, rtol=1e-6)
+    with pytest.raises(RuntimeError):
+        sc.unscale_(o)
+    sc.step(o)
+    sc.update()
+    st = sc.state_dict()
+    sc2 = genesis.amp.GradScaler()
+    sc2.load_state_dict(st)
+    assert sc2.get_scale() == sc.get_scale()
+
+
+# ------------------------------------------------------------------ serialization
+def test_save_load_roundtrip_and_atomicity(tmp_path):
+    sd = {"w": genesis.tensor(arr(3, 4)), "h": genesis.ones(2, dtype=genesis.float16),
+          "b": genesis.tensor(arr(5), dtype=genesis.bfloat16), "i": genesis.tensor([1, 2], dtype=genesis.int64),
+          "nested": {"step": 7, "lr": 0.1}, "p": nn.Parameter(genesis.ones(2))}
+    path = tmp_path / "ck.pkl"
+    genesis.save(sd, path)
+    assert len(sd) == 6 and not os.path.exists(str(path) + ".genesis.bak")     # caller's dict untouched
+    back = genesis.load(path)
+    assert back["nested"] == {"step": 7, "lr": 0.1}
+    for k in ("w", "h", "b", "i"):
+        assert back[k].dtype == sd[k].dtype and back[k].device == "cpu"
+        assert np.array_equal(back[k].numpy(), sd[k].numpy())
+    assert back["p"].requires_grad
+    genesis.save({"w": genesis.ones(1)}, path)                                   # overwrite keeps no backup behind
+    assert not os.path.exists(str(path) + ".genesis.bak")
+
+    class Boom:
+        def __reduce__(self):
+            raise RuntimeError("boom")
+    with pytest.raises(RuntimeError):
+        genesis.save({"x": Boom()}, path)
+    assert np.array_equal(genesis.load(path)["w"].numpy(), np.ones(1, np.float32))   # old file restored
+    assert not os.path.exists(str(path) + ".tmp")
+    genesis.save_checkpoint({"a": genesis.ones(1)}, {"t": 3}, tmp_path / "c.pkl")
+    m, o = genesis.load_checkpoint(tmp_path / "c.pkl")
+    assert o == {"t": 3} and m["a"].shape == (1,)
+
+
+def test_compat_stream_names_reference_hook(tmp_path):
+    path = tmp_path / "compat.pkl"
+    genesis.save({"w": genesis.tensor(arr(2, 2), dtype=genesis.bfloat16)}, path, compat=True)
+    raw = open(path, "rb").read()
+    assert b"genesis.tensor" in raw and b"_rebuild_tensor" in raw and b"genesis_b200" not in raw
+    back = genesis.load(path)
+    assert back["w"].dtype == genesis.bfloat16
+
+
+def test_cross_load_with_reference_package(tmp_path):
+    """A file written by the reference itself loads here, and a compat file written here loads there."""
+    import subprocess
+    import sys
+    ref = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "genesis")):
+        pytest.skip("reference not installed under baseline/_ref")
+    ours = tmp_path / "ours.pkl"
+    theirs = tmp_path / "theirs.pkl"
+    a = arr(3, 5)
+    genesis.save({"w": genesis.tensor(a), "n": {"k": 1}}, ours, compat=True)
+    code = (
+        "import sys, numpy as np\n"
+        f"sys.path.insert(0, {ref!r})\n"
+        "import genesis\n"
+        f"sd = genesis.load({str(ours)!r})\n"
+        "assert sd['n'] == {'k': 1} and sd['w'].shape == (3, 5)\n"
+        f"genesis.save({{'w': genesis.tensor(np.asarray(sd['w'].numpy()) * 2.0), 'b': genesis.tensor(np.ones(4), dtype=genesis.bfloat16)}}, {str(theirs)!r})\n"
+        "print('REF_OK')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    if "REF_OK" not in r.stdout:
+        pytest.skip(f"reference could not run here: {r.stderr[-300:]}")
+    back = genesis.load(theirs)
+    np.testing.assert_allclose(back["w"].numpy(), a * 2.0, rtol=1e-6)
+    assert back["b"].dtype == genesis.bfloat16
+
+
+# ------------------------------------------------------------------ config 1
+class Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.fc1 = nn.Linear(784, 256)
+        self.fc2 = nn.Linear(256, 10)
+        self.dropout = nn.Dropout(0.2)
+
+    def forward(self, x):
+        return self.fc2(self.dropout(self.fc1(x).relu()))
+
+
+def test_mlp_training_parity_with_torch_restatement(tmp_path):
+    rs = np.random.RandomState(0)
+    X = rs.randn(100, 64, 784).astype(np.float32)
+    Y = rs.randint(0, 10, (100, 64))
+    # ---- ours
+    torch.manual_seed(0)
+    net = Net()
+    opt = optim.AdamW(net.parameters(), lr=1e-3, weight_decay=0.01)
+    lossf = nn.CrossEntropyLoss()
+    ours, g0 = [], None
+    for i in range(100):
+        loss = lossf(net(genesis.tensor(X[i])), genesis.tensor(Y[i], dtype=genesis.int64))
+        opt.zero_grad()
+        loss.backward()
+        if i == 0:
+            g0 = net.fc1.weight.grad.numpy().copy()
+        opt.step()
+        ours.append(loss.item())
+    # ---- plain torch with the same draw order (weights randn*0.02 in construction order, one rand mask per step)
+    torch.manual_seed(0)
+    w1 = (torch.randn(256, 784) * 0.02).requires_grad_()
+    b1 = torch.zeros(256, requires_grad=True)
+    w2 = (torch.randn(10, 256) * 0.02).requires_grad_()
+    b2 = torch.zeros(10, requires_grad=True)
+    topt = torch.optim.AdamW([w1, b1, w2, b2], lr=1e-3, weight_decay=0.01, betas=(0.9, 0.999), eps=1e-8)
+    theirs, tg0 = [], None
+    for i in range(100):
+        h = torch.relu(torch.nn.functional.linear(torch.tensor(X[i]), w1, b1))
+        mask = (torch.rand(64, 256) <= 0.8).float()
+        h = h * mask / 0.8
+        loss = torch.nn.functional.cross_entropy(torch.nn.functional.linear(h, w2, b2), torch.tensor(Y[i]))
+        topt.zero_grad()
+        loss.backward()
+        if i == 0:
+            tg0 = w1.grad.numpy().copy()
+        topt.step()
+        theirs.append(loss.item())
+    assert np.max(np.abs(np.array(ours) - np.array(theirs))) <= 2e-6
+    assert np.max(np.abs(g0 - tg0)) <= 1e-7
+    # values the reference itself produces for this recipe (its CPU path, seed 0)
+    np.testing.assert_allclose([ours[0], ours[1], ours[50], ours[99]],
+                               [2.3119795, 2.2996368, 2.3197243, 2.3251529], atol=5e-6)
+    path = tmp_path / "mlp.pkl"
+    genesis.save(net.state_dict(), path)
+    net2 = Net()
+    net2.load_state_dict(genesis.load(path))
+    for (k, a), (_, b) in zip(net.named_parameters(), net2.named_parameters()):
+        assert np.array_equal(a.detach().numpy(), b.detach().numpy()), k

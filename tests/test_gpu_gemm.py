@@ -18,7 +18,7 @@ def rnd(*shape, dt=torch.float32, seed=0):
 
 
 def check(got, ref, dt, K_):
-    tol = {torch.float32: 2e-3, torch.bfloat16: 2e-2, torch.float16: 4e-3}[dt] * max(1.0, (K_ / 64) ** 0.5)
+    tol = {torch.float32: 5e-3, torch.bfloat16: 2e-2, torch.float16: 4e-3}[dt] * max(1.0, (K_ / 64) ** 0.5)
     torch.testing.assert_close(got.float().cpu(), ref, atol=tol, rtol=2e-2)
     N.check_status()
 
