@@ -59,6 +59,8 @@ def main():
     ap.add_argument("--what", default="gemm,norm,softmax,adamw")
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--torch", action="store_true", help="also time the torch/cuBLAS op for comparison")
+    ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D of a single attention case")
+    ap.add_argument("--iters", type=int, default=5)
     a = ap.parse_args()
     hbm, tf, src = peaks()
     what = a.what.split(",")
@@ -114,8 +116,10 @@ def main():
         print(json.dumps({"kernel": "adamw_multi_tensor", "params": n, "ms": ms, "GBs": gbs,
                           "frac_of_" + src: gbs / hbm}), flush=True)
     if "attn" in what:
-        for S in [1024, 4096] + ([] if a.quick else [16384]):
-            B, Hq, Hkv, D = 8, 16, 4, 128
+        cases = [(8, S, 16, 4, 128) for S in [1024, 4096] + ([] if a.quick else [16384])]
+        if a.attn_shape:
+            cases = [tuple(int(x) for x in a.attn_shape.split(","))]
+        for (B, S, Hq, Hkv, D) in cases:
             q = torch.randn(B, S, Hq, D, device=dev, dtype=torch.bfloat16)
             k = torch.randn(B, S, Hkv, D, device=dev, dtype=torch.bfloat16)
             v = torch.randn(B, S, Hkv, D, device=dev, dtype=torch.bfloat16)
@@ -123,14 +127,16 @@ def main():
             if r is NotImplemented:
                 print(json.dumps({"kernel": "attention_fwd", "S": S, "status": "not implemented"}))
                 continue
-            ms = timeit(lambda: N.attention_fwd(q, k, v, True, D ** -0.5), iters=5)
+            ms = timeit(lambda: N.attention_fwd(q, k, v, True, D ** -0.5), iters=a.iters, warmup=min(3, a.iters))
             fl = 4 * B * Hq * S * S * D / 2
-            rec = {"kernel": "attention_fwd", "S": S, "ms": ms, "tflops": fl / ms / 1e9}
+            rec = {"kernel": "attention_fwd", "B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "D": D, "ms": ms,
+                   "tflops": fl / ms / 1e9}
             o, lse = r
             do = torch.randn_like(o)
             rb = N.attention_bwd(do, q, k, v, o, lse, True, D ** -0.5)
             if rb is not NotImplemented:
-                msb = timeit(lambda: N.attention_bwd(do, q, k, v, o, lse, True, D ** -0.5), iters=5)
+                msb = timeit(lambda: N.attention_bwd(do, q, k, v, o, lse, True, D ** -0.5), iters=a.iters,
+                             warmup=min(3, a.iters))
                 rec.update({"bwd_ms": msb, "bwd_tflops": 2.5 * fl / msb / 1e9})
             print(json.dumps(rec), flush=True)
     N.check_status()

@@ -75,13 +75,28 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, ui
 // =====================================================================================================
 // forward
 // =====================================================================================================
-template <int D>
-__global__ void __launch_bounds__(192, 1)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// SB = number of score buffers in TMEM.  D = 64: one buffer, 256 TMEM columns and ~113 KB of shared
+// memory, so two CTAs share an SM and cover each other's soft-max / MMA bubbles.  D = 128: two score
+// buffers, 512 columns, one CTA per SM.
+template <int D, int SB>
+__global__ void __launch_bounds__(192, SB == 1 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                 const __grid_constant__ CUtensorMap tmv, const AttnParams p) {
   constexpr int TILE = AT_BM * D * 2;            // bytes of one [128 x D] 16-bit tile
   constexpr int PB = AT_BM * AT_BN * 2;
+  constexpr uint32_t TCOLS = SB == 1 ? 256 : 512;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (SB == 1 && (reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {
+    // the two-CTA-per-SM configuration has no room for an alignment pad; refuse rather than overrun
+    if (threadIdx.x == 0) report_error(p.status, GB_ERR_BAD_ARG, 1, 0);
+    return;
+  }
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE;          // 2 stages
@@ -124,12 +139,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 4) { tmem_alloc(tmem_slot, TCOLS); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tO = tmem + 2 * AT_BN;
+  const uint32_t tO = tmem + SB * AT_BN;
+  // score buffer and barrier phase of kv block j
+  auto sbuf = [](int j) { return SB == 2 ? (j & 1) : 0; };
+  auto sphase = [](int j) { return (uint32_t)(SB == 2 ? ((j >> 1) & 1) : (j & 1)); };
 
   if (warp == 4) {
     if (lane == 0) {   // ---------------- TMA ----------------
@@ -158,14 +176,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!AT_WAIT(&k_full[s], ph, 21)) return false;
-        if (!AT_WAIT(&s_empty[s], ph ^ 1, 22)) return false;
+        if (!AT_WAIT(&s_empty[sbuf(j)], sphase(j) ^ 1, 22)) return false;
         tc_fence_after_sync();
         const uint32_t aK = smem_u32(sK + s * TILE);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16(tmem + s * AT_BN, desc_kmajor(aQ, kk, AT_BM), desc_kmajor(aK, kk, AT_BN), idesc_qk, kk > 0);
+          umma_f16(tmem + sbuf(j) * AT_BN, desc_kmajor(aQ, kk, AT_BM), desc_kmajor(aK, kk, AT_BN), idesc_qk, kk > 0);
         umma_commit(&k_empty[s]);
-        umma_commit(&s_full[s]);
+        umma_commit(&s_full[sbuf(j)]);
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -190,66 +208,64 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     const int row = m0 + t;
     const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
     const float sl2 = p.scale * LOG2E;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;     // running max (scaled, log2 domain) and sum
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!__all_sync(0xffffffffu, AT_WAIT(&s_full[s], ph, 30))) { ok = false; break; }
+      const int sb = sbuf(j);
+      if (!__all_sync(0xffffffffu, AT_WAIT(&s_full[sb], sphase(j), 30))) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t tS = tmem + lane_base + s * AT_BN;
+      const uint32_t tS = tmem + lane_base + sb * AT_BN;
+      // the whole score row goes to registers in one go, then the TMEM buffer is handed back
+      uint32_t r[4][32];
+      tmem_ld_32x32b_x32(tS, r[0]);
+      tmem_ld_32x32b_x32(tS + 32, r[1]);
+      tmem_ld_32x32b_x32(tS + 64, r[2]);
+      tmem_ld_32x32b_x32(tS + 96, r[3]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&s_empty[sb]);
       const int col0 = j * AT_BN;
       const bool need_mask = (col0 + AT_BN > p.Sk) || (p.causal && (col0 + AT_BN - 1 > m0 + off));
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < AT_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tS + c * 32, r);
-        tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]) * sl2;
-          if (need_mask) {
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
             const int col = col0 + c * 32 + i;
-            if (col >= p.Sk || (p.causal && col > row + off)) v = -INFINITY;
+            if (col >= p.Sk || (p.causal && col > row + off)) r[c][i] = 0xff800000u;   // -inf
           }
-          mx = fmaxf(mx, v);
-        }
       }
-      const float m_new = fmaxf(m, mx);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+      const float m_new = fmaxf(m, mx * sl2);
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m - m_safe);
+      const float alpha = fast_exp2(m - m_safe);
       if (j > 0) {
         if (!__all_sync(0xffffffffu, AT_WAIT(pv_done, (j - 1) & 1, 31))) { ok = false; break; }
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tO + lane_base + c * 32, r);
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tO + lane_base + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(tO + lane_base + c * 32, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x32(tO + lane_base + c * 32, o);
           }
           tmem_st_wait();
         }
       }
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < AT_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tS + c * 32, r);
-        tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         float pv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]) * sl2;
-          if (need_mask) {
-            const int col = col0 + c * 32 + i;
-            if (col >= p.Sk || (p.causal && col > row + off)) v = -INFINITY;
-          }
-          pv[i] = exp2f(v - m_safe);
+          pv[i] = fast_exp2(fmaf(__uint_as_float(r[c][i]), sl2, -m_safe));
           rowsum += pv[i];
         }
         store_row_chunk(sP, t, c * 32, pv, p.is_bf16, AT_BM * 128);
@@ -259,7 +275,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(p_full);
-      mbar_arrive(&s_empty[s]);
     }
     if (ok && __all_sync(0xffffffffu, AT_WAIT(pv_done, (n_kv - 1) & 1, 32))) {
       tc_fence_after_sync();
@@ -268,17 +283,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (((size_t)b * p.S + row) * p.Hq + h) * D;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tO + lane_base + c * 32, r);
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tO + lane_base + c * 32, o);
         tmem_ld_wait();
         if (row < p.S) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 w;
-            w.x = pack2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv, dt);
-            w.y = pack2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv, dt);
-            w.z = pack2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv, dt);
-            w.w = pack2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv, dt);
+            w.x = pack2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv, dt);
+            w.y = pack2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv, dt);
+            w.z = pack2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv, dt);
+            w.w = pack2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv, dt);
             *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
           }
         }
@@ -288,9 +303,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) { tc_fence_after_sync(); tmem_dealloc(tmem, 512); }
+  if (warp == 4) { tc_fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
 }
-
 // =====================================================================================================
 // backward: dQ
 // =====================================================================================================
@@ -399,7 +413,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
         for (int i = 0; i < 32; ++i) {
           const int col = col0 + c * 32 + i;
           const bool valid = row < p.S && col < p.Sk && (!p.causal || col <= row + off);
-          const float pr = valid ? exp2f(__uint_as_float(rs[i]) * sl2 - lse2) : 0.f;
+          const float pr = valid ? fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2)) : 0.f;
           ds[i] = pr * (__uint_as_float(rp[i]) - dl) * p.scale;
         }
         store_row_chunk(sdS, t, c * 32, ds, p.is_bf16, AT_BM * 128);
@@ -559,7 +573,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
         for (int i = 0; i < 32; ++i) {
           const int qcol = q0 + c * 32 + i;
           const bool valid = kvrow < p.Sk && qcol < p.S && (!p.causal || kvrow <= qcol + off);
-          const float pr = valid ? exp2f(__uint_as_float(rs[i]) * sl2 - lse_s[c * 32 + i]) : 0.f;
+          const float pr = valid ? fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse_s[c * 32 + i])) : 0.f;
           pt[i] = pr;
           dst[i] = pr * (__uint_as_float(rp[i]) - dl_s[c * 32 + i]) * p.scale;
         }
@@ -684,15 +698,16 @@ extern "C" int gb_attn_fwd(const void* q, const void* k, const void* v, void* o,
   p.o = o; p.lse = lse; p.status = status; p.B = B; p.S = S; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
   p.causal = causal; p.is_bf16 = is_bf16; p.scale = scale;
   dim3 grid((S + AT_BM - 1) / AT_BM, Hq, B);
-  const int smem = 5 * AT_BM * D * 2 + AT_BM * AT_BN * 2 + 256 + 1024;
+  // D = 64 runs two CTAs per SM: 2 x (114,944 + 1 KB reserved) just fits, an alignment pad would not
+  const int smem = 5 * AT_BM * D * 2 + AT_BM * AT_BN * 2 + 256 + (D == 64 ? 0 : 1024);
   if (D == 64) {
     static bool cfg = false;
-    if (!cfg) { if ((r = set_smem(attn_fwd_kernel<64>, smem)) != 0) return r; cfg = true; }
-    attn_fwd_kernel<64><<<grid, 192, smem, st>>>(tq, tk, tv, p);
+    if (!cfg) { if ((r = set_smem(attn_fwd_kernel<64, 1>, smem)) != 0) return r; cfg = true; }
+    attn_fwd_kernel<64, 1><<<grid, 192, smem, st>>>(tq, tk, tv, p);
   } else {
     static bool cfg = false;
-    if (!cfg) { if ((r = set_smem(attn_fwd_kernel<128>, smem)) != 0) return r; cfg = true; }
-    attn_fwd_kernel<128><<<grid, 192, smem, st>>>(tq, tk, tv, p);
+    if (!cfg) { if ((r = set_smem(attn_fwd_kernel<128, 2>, smem)) != 0) return r; cfg = true; }
+    attn_fwd_kernel<128, 2><<<grid, 192, smem, st>>>(tq, tk, tv, p);
   }
   return (int)cudaGetLastError();
 }

@@ -828,10 +828,13 @@ class EmbeddingFunction(Function):
     amp_policy = AMPPolicy.PRESERVE
 
     @staticmethod
-    def forward(ctx, weight, idx):
+    def forward(ctx, weight, idx, compute_dtype=None):
         ctx.save_for_backward(idx)
         ctx.meta = (weight.shape[0], weight.dtype)
-        return K.embedding_fwd(weight, idx)
+        # under autocast the rows come from the cached low-precision copy of the table (shared with a
+        # tied lm_head), so the residual stream of the model runs in the autocast dtype
+        w = _cached_param_cast(weight, compute_dtype) if compute_dtype is not None else weight
+        return K.embedding_fwd(w, idx)
 
     @staticmethod
     def backward(ctx, g):
@@ -927,6 +930,8 @@ class FusedRMSNormFunction(Function):
     @staticmethod
     def backward(ctx, g):
         x, w, rstd = ctx.saved_tensors
+        if g.dtype != x.dtype:
+            g = K.to_dtype(g, x.dtype)
         dx, dw = K.rmsnorm_bwd(g if g.is_contiguous() else K.contiguous(g), x, w, rstd)
         return dx, (dw if dw.dtype == w.dtype else dw.to(w.dtype))
 
@@ -1389,7 +1394,8 @@ def one_hot(indices, num_classes, dtype=None):
 
 
 def embedding(weight, idx):
-    return EmbeddingFunction.apply(weight, idx)
+    cd = amp_state.dtype if (amp_state.enabled and weight._t.dtype == torch.float32) else None
+    return EmbeddingFunction.apply(weight, idx, cd)
 
 
 def softmax(input, dim=-1):
