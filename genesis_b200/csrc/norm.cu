@@ -299,3 +299,102 @@ extern "C" int gb_layernorm_bwd(const void* g, const void* x, const void* w, con
       (const T*)g, (const T*)x, (const TW*)w, mean, rstd, (T*)dx, dw_partial, db_partial, rows, cols));
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation (declared in noalloc.h; no counterpart in the reference)
+// ------------------------------------------------------------------------------------------------
+// The regular entry point takes its per-CTA partial sums of the weight gradient from a buffer the
+// caller allocates.  Some callers cannot allocate at all at the point where they need this kernel:
+// code that runs under somebody else's memory manager with a fixed budget (a serving process that
+// pre-sized its pools, a plugin inside another runtime) and code in a latency-critical loop where
+// cudaMalloc / cudaFree are off limits because they synchronise the whole device.  For them the
+// scratch lives in the library image itself.
+namespace gb {
+
+constexpr int NOALLOC_MAX_CTAS = 296;    // two CTAs per SM on a 148-SM part
+constexpr int NOALLOC_MAX_COLS = 4096;   // widest row this entry point accepts
+
+// 296 x 4096 floats = 4.6 MiB, resident on every GPU that loads the library until the process exits.
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[NOALLOC_MAX_CTAS * NOALLOC_MAX_COLS];
+
+// dw[c] = sum over the nct partial rows; one thread per column, fixed order => deterministic
+__global__ void noalloc_colsum_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nct, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.f;
+  for (int r = 0; r < nct; ++r) acc += partial[(long long)r * cols + c];
+  dw[c] = acc;
+}
+
+}  // namespace gb
+
+#include <mutex>
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+float* g_scratch_ptr[kNoallocMaxDevices] = {nullptr};
+std::mutex g_scratch_mu;
+}  // namespace
+
+extern "C" const char* gb_rmsnorm_bwd_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -10: return "rmsnorm_bwd_noalloc: cols exceeds the built-in scratch (max 4096 columns)";
+    case -11: return "rmsnorm_bwd_noalloc: cols must be a multiple of 8 (16-bit) or 4 (float32) elements";
+    case -12: return "rmsnorm_bwd_noalloc: unsupported dtype combination";
+    case -13: return "rmsnorm_bwd_noalloc: device index out of range";
+    default: return "rmsnorm_bwd_noalloc: CUDA runtime error (code is the cudaError_t value)";
+  }
+}
+
+extern "C" int gb_rmsnorm_bwd_noalloc_max_cols() { return gb::NOALLOC_MAX_COLS; }
+
+extern "C" int gb_rmsnorm_bwd_noalloc(const void* g, const void* x, const void* w, const float* rstd, void* dx,
+                                      float* dw, long long rows, int cols, int dt, int wdt, cudaStream_t st) {
+  if (cols > gb::NOALLOC_MAX_COLS) return -10;
+  if (cols % (dt == DT_F32 ? 4 : 8) != 0 || cols <= 0) return -11;
+  if (rows <= 0) return 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoallocMaxDevices) return -13;
+  float* scratch;
+  {
+    // Set-up, once per device, with that device current: inside host code the array's name is only a
+    // stand-in, the address a kernel may use comes from cudaGetSymbolAddress.
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    if (g_scratch_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, gb::g_rmsnorm_bwd_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_scratch_ptr[dev];
+  }
+  const int grid = (int)(rows < gb::NOALLOC_MAX_CTAS ? rows : gb::NOALLOC_MAX_CTAS);
+  // every CTA overwrites its whole partial row, so nothing in the scratch has to be cleared first
+  do {
+    const int nvec_ = cols / (dt == DT_F32 ? 4 : 8);
+    if (nvec_ <= NORM_THREADS) {
+      constexpr int MV = 1;
+      if (dt == DT_F32 && wdt == DT_F32) rmsnorm_bwd_kernel<float, float, MV><<<grid, NORM_THREADS, 0, st>>>((const float*)g, (const float*)x, (const float*)w, rstd, (float*)dx, scratch, rows, cols);
+      else if (dt == DT_BF16 && wdt == DT_F32) rmsnorm_bwd_kernel<__nv_bfloat16, float, MV><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const float*)w, rstd, (__nv_bfloat16*)dx, scratch, rows, cols);
+      else if (dt == DT_F16 && wdt == DT_F32) rmsnorm_bwd_kernel<__half, float, MV><<<grid, NORM_THREADS, 0, st>>>((const __half*)g, (const __half*)x, (const float*)w, rstd, (__half*)dx, scratch, rows, cols);
+      else if (dt == DT_BF16 && wdt == DT_BF16) rmsnorm_bwd_kernel<__nv_bfloat16, __nv_bfloat16, MV><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, scratch, rows, cols);
+      else if (dt == DT_F16 && wdt == DT_F16) rmsnorm_bwd_kernel<__half, __half, MV><<<grid, NORM_THREADS, 0, st>>>((const __half*)g, (const __half*)x, (const __half*)w, rstd, (__half*)dx, scratch, rows, cols);
+      else return -12;
+    } else {
+      constexpr int MV = 4;   // up to 4 vectors per thread covers 4096 fp32 / 8192 16-bit columns
+      if (dt == DT_F32 && wdt == DT_F32) rmsnorm_bwd_kernel<float, float, MV><<<grid, NORM_THREADS, 0, st>>>((const float*)g, (const float*)x, (const float*)w, rstd, (float*)dx, scratch, rows, cols);
+      else if (dt == DT_BF16 && wdt == DT_F32) rmsnorm_bwd_kernel<__nv_bfloat16, float, MV><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const float*)w, rstd, (__nv_bfloat16*)dx, scratch, rows, cols);
+      else if (dt == DT_F16 && wdt == DT_F32) rmsnorm_bwd_kernel<__half, float, MV><<<grid, NORM_THREADS, 0, st>>>((const __half*)g, (const __half*)x, (const float*)w, rstd, (__half*)dx, scratch, rows, cols);
+      else if (dt == DT_BF16 && wdt == DT_BF16) rmsnorm_bwd_kernel<__nv_bfloat16, __nv_bfloat16, MV><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, scratch, rows, cols);
+      else if (dt == DT_F16 && wdt == DT_F16) rmsnorm_bwd_kernel<__half, __half, MV><<<grid, NORM_THREADS, 0, st>>>((const __half*)g, (const __half*)x, (const __half*)w, rstd, (__half*)dx, scratch, rows, cols);
+      else return -12;
+    }
+  } while (0);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  gb::noalloc_colsum_kernel<<<(cols + 127) / 128, 128, 0, st>>>(scratch, dw, grid, cols);
+  return (int)cudaGetLastError();
+}
