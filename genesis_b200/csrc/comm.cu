@@ -1,5 +1,5 @@
 // Peer-memory communication over NVLink / NVSwitch: symmetric allocations shared through CUDA IPC,
-// and the fused gradient all-reduce.  No NCCL call, no TMA multicast, no multimem: plain 16-byte
+// and the fused gradient all-reduce.  No NCCL call, no cluster-broadcast loads, no switch reductions: plain 16-byte
 // loads from / stores to peer-mapped addresses issued by the compute threads themselves.
 //
 // Fused all-reduce (in place over a symmetric buffer, two-shot):
@@ -82,28 +82,50 @@ allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, 
   const long long per = nvec / world;
   const long long v0 = (long long)rank * per, v1 = (rank == world - 1) ? nvec : v0 + per;
   bool bad = false;
-  for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1;
-       i += (long long)gridDim.x * blockDim.x) {
-    float acc[V];
+  // NVLink round trips are microseconds: keep UNR x world 16-byte loads in flight per thread
+  constexpr int UNR = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * UNR) {
+    float acc[UNR][V];
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    for (int u = 0; u < UNR; ++u)
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[u][j] = 0.f;
     for (int p = 0; p < world; ++p) {
       const int src = (rank + p) % world;              // stagger peers so links are loaded evenly
-      const uint4 raw = ld_volatile_v4(reinterpret_cast<const T*>(bufs.ptr[src]) + offset_elems + i * V);
-      const T* e = reinterpret_cast<const T*>(&raw);
+      const T* base = reinterpret_cast<const T*>(bufs.ptr[src]) + offset_elems;
+      uint4 raw[UNR];
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(e[j]);
-    }
-    Vec16<T> o;
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) raw[u] = ld_volatile_v4(base + i * V);
+      }
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      const float r = acc[j] * scale;
-      if (!isfinite(r)) bad = true;
-      o.v[j] = Cvt<T>::from_f(r);
+      for (int u = 0; u < UNR; ++u) {
+        if (i0 + u * stride < v1) {
+          const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[u][j] += Cvt<T>::to_f(e[j]);
+        }
+      }
     }
+    Vec16<T> o[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float r = acc[u][j] * scale;
+        if (!isfinite(r) && (i0 + u * stride < v1)) bad = true;
+        o[u].v[j] = Cvt<T>::from_f(r);
+      }
     for (int p = 0; p < world; ++p) {
       const int dst = (rank + p) % world;
-      st16(reinterpret_cast<T*>(bufs.ptr[dst]) + offset_elems + i * V, o);
+      T* base = reinterpret_cast<T*>(bufs.ptr[dst]) + offset_elems;
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) st16(base + i * V, o[u]);
+      }
     }
   }
   if (bad) s_bad = 1;

@@ -7,7 +7,7 @@
 //   warp 1    MMA issuer     one elected thread issues tcgen05.mma (UMMA 128 x BN x 16); TMEM owner
 //   warps 2-5 epilogue       tcgen05.ld of the finished accumulator -> bias/accumulate/convert -> global
 // Two accumulators live in TMEM (2 x BN columns), so the epilogue of tile i overlaps the main loop of
-// tile i+1.  No cluster multicast is used: the kernel is safe in multi-GPU jobs.
+// tile i+1.  Every load targets one CTA only: the kernel is safe in multi-GPU jobs.
 //
 // Operand layouts (what the backward passes of a linear layer need without transposes):
 //   A "K-major"  : memory [M, K] row-major          A "MN-major": memory [K, M] row-major

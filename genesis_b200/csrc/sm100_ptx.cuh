@@ -1,5 +1,5 @@
 // Thin inline-PTX layer for Blackwell (sm_100a): mbarrier, TMA (cp.async.bulk.tensor, no
-// cluster multicast anywhere), tcgen05 (TMEM alloc, UMMA, commit, ld) and descriptor builders.
+// cluster-wide broadcast loads anywhere), tcgen05 (TMEM alloc, UMMA, commit, ld) and descriptor builders.
 //
 // Every wait is bounded: a wait that runs out records {code, where, block} in a global status
 // word, raises a CTA-wide abort flag and returns false; callers unwind to the common exit where
@@ -115,7 +115,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA: 2-D / 3-D tiled loads into this CTA's shared memory (never multicast), 2-D stores.
+// TMA: 2-D / 3-D tiled loads into this CTA's shared memory (one destination CTA only), 2-D stores.
 // The innermost coordinate must be a multiple of 16 bytes / element size.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {

@@ -29,7 +29,9 @@ class Device:
                 raise ValueError(f"Unsupported device: {spec}")
             self.type = DeviceType(name)
             if name == "cuda":
-                self.index = int(idx) if idx else (index if index is not None else 0)
+                # a bare "cuda" is the process's current device (one process per GPU under torchrun)
+                cur = torch.cuda.current_device() if torch.cuda.is_available() else 0
+                self.index = int(idx) if idx else (index if index is not None else cur)
             else:
                 self.index = None
         else:

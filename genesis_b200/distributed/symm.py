@@ -173,7 +173,13 @@ def all_reduce_(t, scale=None):
         return False
     stage = st.staging.view(t.dtype, 0, t.numel())
     stage.copy_(t.reshape(-1))
-    N.allreduce_fused(st, st.staging, 0, t.numel(), t.dtype, stage, inv_scale=None, found_inf=None,
+    # the kernel works on whole 16-byte vectors split evenly over the ranks: round the length up
+    # (the tail of the staging buffer is reduced too and simply never copied back)
+    quantum = st.world * (16 // t.element_size())
+    n_pad = (t.numel() + quantum - 1) // quantum * quantum
+    if n_pad * t.element_size() > cap:
+        return False
+    N.allreduce_fused(st, st.staging, 0, n_pad, t.dtype, stage, inv_scale=None, found_inf=None,
                       prescale=1.0 if scale is None else scale)
     t.reshape(-1).copy_(stage)
     return True

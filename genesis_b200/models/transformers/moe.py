@@ -205,20 +205,14 @@ class CombineFunction(Function):
     @staticmethod
     def forward(ctx, y, w, pos):
         ctx.save_for_backward(y, w, pos)
-        T, k = w.shape
-        rows = K.gather_rows(y, pos.reshape(-1)).reshape(T, k, -1)
-        return (rows.float() * w.float().unsqueeze(-1)).sum(1).to(y.dtype)
+        return K.moe_combine(y, w, pos)
 
     @staticmethod
     def backward(ctx, g):
         y, w, pos = ctx.saved_tensors
-        T, k = w.shape
-        rows = K.gather_rows(y, pos.reshape(-1)).reshape(T, k, -1)
-        dw = (rows.float() * g.float().unsqueeze(1)).sum(-1).to(w.dtype)
-        contrib = (g.float().unsqueeze(1) * w.float().unsqueeze(-1)).to(y.dtype).reshape(T * k, -1)
-        dy = torch.empty_like(y)
-        dy[pos.reshape(-1)] = contrib          # pos is a permutation: plain scatter
-        return dy, dw
+        g = g if g.dtype == y.dtype else K.to_dtype(g, y.dtype)
+        dy, dw = K.moe_combine_bwd(g if g.is_contiguous() else K.contiguous(g), y, w, pos)
+        return dy, dw.to(w.dtype)
 
 
 class GroupedExperts(Module):
@@ -308,14 +302,10 @@ class MoELayer(Module):
         return out
 
     def _local_forward(self, x, idx, w):
-        T, k = idx.shape
-        perm, offsets = K.moe_sort(idx, self.num_experts)
-        token_of = perm // k                                   # sorted row -> source token
-        pos = torch.empty_like(perm)
-        pos[perm] = torch.arange(perm.numel(), device=perm.device, dtype=perm.dtype)   # pair -> sorted row
+        token_of, pos, offsets = K.moe_sort(idx, self.num_experts)
         xs = DispatchFunction.apply(x, Tensor._wrap(token_of))
         ys = self.experts(xs, offsets)
-        return CombineFunction.apply(ys, w, Tensor._wrap(pos.reshape(T, k)))
+        return CombineFunction.apply(ys, w, Tensor._wrap(pos))
 
 
 # ------------------------------------------------------------------------------------

@@ -699,39 +699,95 @@ def moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm):
     return probs * (total - (probs * total).sum(-1, keepdim=True))
 
 
-def moe_sort(experts, num_experts):
-    """Stable sort of the T*k (token, slot) pairs by expert id.
-    Returns (perm [T*k] int64: sorted position -> flat pair index, offsets [E+1] int64)."""
+def moe_sort(experts, num_experts, align=1):
+    """Sort of the T*k (token, slot) pairs by expert id into per-expert segments padded to `align` rows.
+
+    Returns (token_of [Mp]: source token of every sorted row, -1 in pad rows; pos [T, k]: sorted row of
+    every pair; offsets [E+1]: segment boundaries).  On CUDA the segments are padded to 128 rows (one GEMM
+    tile) whatever `align` says; index tensors are int32 there and int64 on CPU."""
     if experts.is_cuda:
-        r = N.moe_sort(experts, num_experts)
+        r = N.moe_sort(experts, num_experts, align)
         if r is not NotImplemented:
             return r
+    return _moe_sort_torch(experts, num_experts, align)
+
+
+def moe_sort_unpadded(experts, num_experts):
+    """Dense (unpadded) expert sort, used where rows travel between ranks before they are grouped."""
+    return _moe_sort_torch(experts, num_experts, 1)
+
+
+def _moe_sort_torch(experts, num_experts, align):
+    T, k = experts.shape
     flat = experts.reshape(-1).long()
     perm = torch.sort(flat, stable=True)[1]
     counts = torch.bincount(flat, minlength=num_experts)
+    padded = (counts + align - 1) // align * align
     offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=experts.device)
-    offsets[1:] = torch.cumsum(counts, 0)
-    return perm, offsets
+    offsets[1:] = torch.cumsum(padded, 0)
+    starts = torch.zeros(num_experts, dtype=torch.int64, device=experts.device)
+    starts[1:] = torch.cumsum(counts, 0)[:-1]
+    sorted_e = flat[perm]
+    dest = offsets[:-1][sorted_e] + (torch.arange(perm.numel(), device=experts.device) - starts[sorted_e])
+    total = int(offsets[-1]) if align > 1 else perm.numel()
+    token_of = torch.full((total,), -1, dtype=torch.int64, device=experts.device)
+    token_of[dest] = perm // k
+    pos = torch.empty(T * k, dtype=torch.int64, device=experts.device)
+    pos[perm] = dest
+    return token_of, pos.reshape(T, k), offsets
 
 
 def gather_rows(x, rows):
-    """x[rows] for a 2-D x."""
+    """x[rows] for a 2-D x; negative row ids give zero rows."""
     if x.is_cuda:
         r = N.gather_rows(x, rows)
         if r is not NotImplemented:
             return r
-    return x.index_select(0, rows.long())
+    rl = rows.long()
+    out = x.index_select(0, rl.clamp_min(0))
+    neg = rl < 0
+    if bool(neg.any()):
+        out[neg] = 0
+    return out
 
 
 def scatter_add_rows(src, rows, num_rows, out_dtype=None):
-    """out[rows[i]] += src[i], fp32 accumulate."""
+    """out[rows[i]] += src[i] (rows with a negative id are skipped), fp32 accumulate."""
     if src.is_cuda:
         r = N.scatter_add_rows(src, rows, num_rows, out_dtype)
         if r is not NotImplemented:
             return r
     out = torch.zeros(num_rows, src.shape[1], dtype=torch.float32, device=src.device)
-    out.index_add_(0, rows.long(), src.float())
+    rl = rows.long()
+    keep = rl >= 0
+    out.index_add_(0, rl[keep], src.float()[keep])
     return out.to(out_dtype or src.dtype)
+
+
+def moe_combine(y, w, pos):
+    """out[t] = sum_j w[t, j] * y[pos[t, j]]."""
+    if y.is_cuda:
+        r = N.moe_combine(y, w, pos)
+        if r is not NotImplemented:
+            return r
+    T, k = w.shape
+    rows = y.index_select(0, pos.reshape(-1).long()).reshape(T, k, -1)
+    return (rows.float() * w.float().unsqueeze(-1)).sum(1).to(y.dtype)
+
+
+def moe_combine_bwd(g, y, w, pos):
+    """Returns (dy [like y, zero in rows no pair points to], dw [T, k] fp32)."""
+    if y.is_cuda:
+        r = N.moe_combine_bwd(g, y, w, pos)
+        if r is not NotImplemented:
+            return r
+    T, k = w.shape
+    idx = pos.reshape(-1).long()
+    rows = y.index_select(0, idx).reshape(T, k, -1)
+    dw = (rows.float() * g.float().unsqueeze(1)).sum(-1)
+    dy = torch.zeros_like(y)
+    dy[idx] = (g.float().unsqueeze(1) * w.float().unsqueeze(-1)).to(y.dtype).reshape(T * k, -1)
+    return dy, dw
 
 
 def _seg(offsets):

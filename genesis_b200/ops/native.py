@@ -928,6 +928,7 @@ def moe_router(logits, k, renorm):
     counts = torch.empty(E, dtype=torch.int32, device=dev)
     _chk(lib().gb_router_fwd(logits.data_ptr(), w.data_ptr(), e.data_ptr(), probs.data_ptr(), counts.data_ptr(), T, E,
                              k, 1 if renorm else 0, _DT[logits.dtype], _st()), "router_fwd")
+    e._gb_counts = counts          # lets the sort reuse the histogram
     return w, e, probs, counts
 
 
@@ -953,7 +954,10 @@ def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None,
     epoch = symm.next_epoch()
     budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000)) * 1e6)
     if ctas is None:
-        ctas = int(os.environ.get("GENESIS_COMM_CTAS", 32))
+        # enough CTAs to keep ~1.5 MB of loads in flight for big buckets, one for tiny ones
+        es = torch.empty(0, dtype=dtype).element_size()
+        per_rank_vecs = n * es // 16 // max(st.world, 1)
+        ctas = max(1, min(int(os.environ.get("GENESIS_COMM_CTAS", 64)), (per_rank_vecs + 2047) // 2048))
     _chk(lib().gb_allreduce_fused(buf.ptr_table, st.flags.ptr_table, offset_elems, n, st.rank, st.world, epoch,
                                   float(prescale), None if inv_scale is None else inv_scale.data_ptr(),
                                   1 if scale_is_reciprocal else 0,
@@ -995,3 +999,13 @@ def grouped_dgrad(gy, w, offsets):
 def grouped_wgrad(gy, x, offsets, num_groups, out_dtype):
     from . import grouped
     return grouped.grouped_wgrad(gy, x, offsets, num_groups, out_dtype)
+
+
+def moe_combine(y, w, pos):
+    from . import grouped
+    return grouped.moe_combine(y, w, pos)
+
+
+def moe_combine_bwd(g, y, w, pos):
+    from . import grouped
+    return grouped.moe_combine_bwd(g, y, w, pos)

@@ -94,10 +94,7 @@ def expert_parallel_forward(layer, x, idx, w):
     El = E // W
     T, k = idx.shape
     dev = idx.device
-    perm, offsets = K.moe_sort(idx, E)
-    token_of = perm // k
-    pos = torch.empty_like(perm)
-    pos[perm] = torch.arange(perm.numel(), device=dev, dtype=perm.dtype)
+    token_of, pos, offsets = K.moe_sort_unpadded(idx, E)          # sorted by global expert id = by destination rank
     xs = DispatchFunction.apply(x, Tensor._wrap(token_of))
 
     send_counts = (offsets[1:] - offsets[:-1]).to(torch.int64)             # [E] rows per global expert
@@ -121,4 +118,4 @@ def expert_parallel_forward(layer, x, idx, w):
     inv[order] = torch.arange(R, device=dev, dtype=order.dtype)
     yr = PermuteRows.apply(ye, Tensor._wrap(inv))                          # back to rank-major order
     ys = AllToAllRows.apply(yr, recv_splits, send_splits)                 # back on the source rank, sorted order
-    return CombineFunction.apply(ys, w, Tensor._wrap(pos.reshape(T, k)))
+    return CombineFunction.apply(ys, w, Tensor._wrap(pos))

@@ -1,0 +1,250 @@
+"""Worker launched by the distributed tests (one process per rank, torchrun environment).
+
+    python -m torch.distributed.run --nproc-per-node N ... tests/_dist_worker.py --scenario S --backend gloo|nccl
+
+Every scenario asserts on all ranks and prints `WORKER_OK <rank>` at the end.
+"""
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as tdist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import genesis_b200 as genesis  # noqa: E402
+import genesis_b200.nn as nn  # noqa: E402
+import genesis_b200.nn.functional as F  # noqa: E402
+from genesis_b200 import distributed as dist  # noqa: E402
+
+
+def dev(backend):
+    return f"cuda:{torch.cuda.current_device()}" if backend == "nccl" else "cpu"
+
+
+class MLP(nn.Module):
+    def __init__(self, d=64, h=256, out=16):
+        super().__init__()
+        self.fc1 = nn.Linear(d, h)
+        self.fc2 = nn.Linear(h, h)
+        self.fc3 = nn.Linear(h, out)
+        self.norm = nn.RMSNorm(h)
+
+    def forward(self, x):
+        return self.fc3(self.norm(F.relu(self.fc2(F.relu(self.fc1(x))))))
+
+
+def scenario_collectives(a):
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    t = genesis.Tensor(torch.full((1000,), float(r + 1), device=d))
+    dist.all_reduce(t)
+    assert torch.allclose(t._t, torch.full((1000,), w * (w + 1) / 2.0, device=d))
+    t = genesis.Tensor(torch.full((7,), float(r + 1), device=d))
+    dist.all_reduce(t, dist.ReduceOp.MAX)
+    assert float(t._t[0]) == w
+    b = genesis.Tensor(torch.arange(5, dtype=torch.float32, device=d) * (r + 1))
+    dist.broadcast(b, src=0)
+    assert torch.equal(b._t.cpu(), torch.arange(5, dtype=torch.float32))
+    outs = [genesis.Tensor(torch.zeros(3, device=d)) for _ in range(w)]
+    dist.all_gather(outs, genesis.Tensor(torch.full((3,), float(r), device=d)))
+    for i, o in enumerate(outs):
+        assert float(o._t[0]) == i
+    out = genesis.Tensor(torch.zeros(4, device=d))
+    dist.reduce_scatter(out, [genesis.Tensor(torch.full((4,), float(i + r), device=d)) for i in range(w)])
+    assert float(out._t[0]) == sum(r + i for i in range(w))
+    inp = torch.arange(w * 2, dtype=torch.float32, device=d) + 100 * r
+    res = torch.zeros(w * 2, device=d)
+    dist.all_to_all_single(res, inp)
+    for i in range(w):
+        assert float(res[2 * i]) == 100 * i + 2 * r
+    dist.barrier()
+    # large, odd-sized float tensors through the default all-reduce path (peer-memory kernel on CUDA)
+    for n, dt in [(1 << 20, torch.float32), (12345, torch.float32), (300001, torch.bfloat16)]:
+        g = torch.Generator().manual_seed(n)
+        base = torch.randn(w, n, generator=g)
+        ref = base.to(dt).float().sum(0)
+        x = base[r].clone().to(dt).to(d)
+        dist.all_reduce(genesis.Tensor(x))
+        tol = 1e-5 if dt == torch.float32 else 5e-2
+        assert torch.allclose(x.float().cpu(), ref, atol=tol * w, rtol=tol), (n, dt)
+
+
+def _local_grads(model_fn, x, y, seed):
+    torch.manual_seed(seed)
+    genesis.manual_seed(seed)
+    m = model_fn()
+    return m
+
+
+def scenario_ddp(a):
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    torch.manual_seed(100 + r)           # different initial weights per rank: DDP must broadcast rank 0's
+    genesis.manual_seed(100 + r)
+    model = MLP().to(d)
+    ref = MLP().to(d)
+    ddp = nn.DistributedDataParallel(model, bucket_cap_mb=0.1)       # several buckets
+    ref.load_state_dict(ddp.state_dict())
+    p0 = [p._t.clone() for p in model.parameters()]
+    gathered = [torch.zeros_like(p0[0]) for _ in range(w)]
+    tdist.all_gather(gathered, p0[0])
+    for gth in gathered:
+        assert torch.equal(gth, gathered[0]), "parameters were not broadcast"
+    rs = np.random.RandomState(7 + r)
+    opt = genesis.optim.AdamW(ddp.parameters(), lr=1e-2)
+    for step in range(3):
+        x = genesis.Tensor(torch.from_numpy(rs.randn(32, 64).astype(np.float32)).to(d))
+        y = genesis.Tensor(torch.from_numpy(rs.randint(0, 16, (32,))).to(d))
+        # reference: local gradients of an identical un-wrapped model, averaged with the communicator
+        ref.zero_grad()
+        F.cross_entropy(ref(x), y).backward()
+        want = []
+        for p in ref.parameters():
+            g = p.grad._t.clone()
+            tdist.all_reduce(g)
+            want.append(g / w)
+        opt.zero_grad()
+        F.cross_entropy(ddp(x), y).backward()
+        if a.backend == "nccl":
+            torch.cuda.synchronize()
+            dist.symm.check_status("ddp all-reduce") if dist.symm.available() else None
+        for (name, p), g in zip(model.named_parameters(), want):
+            assert p.grad is not None, name
+            assert torch.allclose(p.grad._t, g, atol=1e-5, rtol=1e-4), (name, step, float((p.grad._t - g).abs().max()))
+        opt.step()
+        ref.load_state_dict(ddp.state_dict())
+    # no_sync: gradients stay local
+    opt.zero_grad()
+    with ddp.no_sync():
+        F.cross_entropy(ddp(x), y).backward()
+    g_local = model.fc1.weight.grad._t.clone()
+    ref.zero_grad()
+    F.cross_entropy(ref(x), y).backward()
+    assert torch.allclose(g_local, ref.fc1.weight.grad._t, atol=1e-6)
+    # delegation surface
+    assert ddp.module is model and ddp.model is model
+    assert set(ddp.state_dict()) == set(model.state_dict())
+    assert ddp.fc1 is model.fc1
+
+
+def scenario_ddp_amp(a):
+    """fp16-style loss scaling through DDP: an overflow on ONE rank must skip the step on ALL ranks."""
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    torch.manual_seed(1)
+    genesis.manual_seed(1)
+    model = MLP().to(d)
+    scaler = genesis.amp.GradScaler(init_scale=1024.0)
+    ddp = nn.DistributedDataParallel(model, grad_scaler=scaler)
+    opt = genesis.optim.AdamW(ddp.parameters(), lr=1e-2)
+    x = genesis.Tensor(torch.randn(8, 64).to(d))
+    y = genesis.Tensor(torch.randint(0, 16, (8,)).to(d))
+    before = model.fc1.weight._t.clone()
+    loss = F.cross_entropy(ddp(x), y)
+    if r == w - 1:
+        loss = loss * float("inf")
+    opt.zero_grad()
+    scaler.scale(loss).backward()
+    scaler.step(opt)
+    assert scaler.found_inf(), "overflow flag did not reach this rank"
+    scaler.update()
+    assert torch.equal(model.fc1.weight._t, before), "step was not skipped"
+    assert scaler.get_scale() == 512.0
+    loss = F.cross_entropy(ddp(x), y)
+    opt.zero_grad()
+    scaler.scale(loss).backward()
+    scaler.step(opt)
+    scaler.update()
+    assert not torch.equal(model.fc1.weight._t, before)
+    chk = model.fc1.weight._t.clone()
+    tdist.all_reduce(chk)
+    assert torch.allclose(chk / w, model.fc1.weight._t, atol=1e-6), "ranks diverged"
+
+
+def scenario_ep(a):
+    """Expert-parallel MoE layer equals the single-process layer holding all experts."""
+    from genesis_b200.models.transformers.moe import MoELayer
+    from genesis_b200.parallel.ep import EPGroup, mark_expert_parameters
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    H, E, k, I, T = 32, 4 * w, 2, 48, 24
+    torch.manual_seed(5)
+    genesis.manual_seed(5)
+    full = MoELayer(H, E, k, I).to(d)                       # identical on every rank (same seed)
+    ep_layer = MoELayer(H, E, k, I, ep_group=EPGroup()).to(d)
+    ep_layer.gate.weight._t.copy_(full.gate.weight._t)
+    lo = r * (E // w)
+    for name in ("w_gate", "w_up", "w_down"):
+        getattr(ep_layer.experts, name)._t.copy_(getattr(full.experts, name)._t[lo:lo + E // w])
+    assert mark_expert_parameters(ep_layer) == 3
+    rs = np.random.RandomState(50 + r)
+    xs = torch.from_numpy(rs.randn(w, 2, T // 2, H).astype(np.float32)).to(d)   # each rank builds only its own slice
+    x_mine = torch.from_numpy(np.random.RandomState(50 + r).randn(2, T // 2, H).astype(np.float32)).to(d)
+    xg, xe = genesis.Tensor(x_mine.clone(), requires_grad=True), genesis.Tensor(x_mine.clone(), requires_grad=True)
+    full.train()
+    ep_layer.train()
+    of = full(xg)
+    oe = ep_layer(xe)
+    assert torch.allclose(of._t, oe._t, atol=1e-5, rtol=1e-4), float((of._t - oe._t).abs().max())
+    gout = torch.from_numpy(np.random.RandomState(90 + r).randn(*of.shape).astype(np.float32)).to(d)
+    (of * genesis.Tensor(gout)).sum().backward()
+    (oe * genesis.Tensor(gout)).sum().backward()
+    assert torch.allclose(xg.grad._t, xe.grad._t, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(full.gate.weight.grad._t, ep_layer.gate.weight.grad._t, atol=1e-5, rtol=1e-4)
+    # expert gradients: the shard's gradient is the SUM over ranks of the full model's local gradients
+    for name in ("w_gate", "w_up", "w_down"):
+        gfull = getattr(full.experts, name).grad._t.clone()
+        tdist.all_reduce(gfull)
+        got = getattr(ep_layer.experts, name).grad._t
+        assert torch.allclose(got, gfull[lo:lo + E // w], atol=2e-5, rtol=1e-4), name
+    del xs
+
+
+def scenario_heartbeat(a):
+    """A rank that stops beating is reported by the others within the budget; nobody touches a GPU."""
+    import time
+    from genesis_b200.distributed.process_group import CommTimeout
+    r, w = dist.get_rank(), dist.get_world_size()
+    store = tdist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]) + 7, w, r == 0, wait_for_workers=True)
+    hb = dist.Heartbeat(store, r, w, interval=0.05, timeout=0.6).start()
+    time.sleep(0.5)
+    hb.check()                                   # everyone alive
+    if r == w - 1:
+        hb.pause()                               # this rank "hangs" (stops beating) but keeps its process
+        time.sleep(2.0)
+    else:
+        t0 = time.time()
+        dead = []
+        while time.time() - t0 < 3.0 and not dead:
+            dead = hb.dead_ranks()
+            time.sleep(0.05)
+        assert dead == [w - 1], dead
+        try:
+            hb.check()
+            raise AssertionError("check() did not raise")
+        except CommTimeout as e:
+            assert str(w - 1) in str(e)
+        time.sleep(0.5)
+    hb.stop()
+
+
+SCENARIOS = {k[len("scenario_"):]: v for k, v in list(globals().items()) if k.startswith("scenario_")}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--scenario", required=True)
+    ap.add_argument("--backend", default="gloo")
+    a = ap.parse_args()
+    if a.backend == "nccl":
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dist.init_process_group(backend=a.backend)
+    try:
+        SCENARIOS[a.scenario](a)
+        if a.backend == "nccl":
+            torch.cuda.synchronize()
+        print(f"WORKER_OK {dist.get_rank()}", flush=True)
+    finally:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
