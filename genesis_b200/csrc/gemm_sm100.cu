@@ -5,7 +5,8 @@
 // One persistent, warp-specialised kernel:
 //   warp 0    TMA producer   cp.async.bulk.tensor (128-byte swizzle) into a ring of smem stages
 //   warp 1    MMA issuer     one elected thread issues tcgen05.mma (UMMA 128 x BN x 16); TMEM owner
-//   warps 2-5 epilogue       tcgen05.ld of the finished accumulator -> bias/accumulate/convert -> global
+//   warps 2-9 epilogue       tcgen05.ld of the finished accumulator -> bias/accumulate/convert -> global
+//                            (two warps per TMEM lane quarter, each takes half of the tile's columns)
 // Two accumulators live in TMEM (2 x BN columns), so the epilogue of tile i overlaps the main loop of
 // tile i+1.  Every load targets one CTA only: the kernel is safe in multi-GPU jobs.
 //
@@ -41,6 +42,8 @@ struct GemmParams {
   int group_mode;
   int groups;
   int m_fastest;           // tile order
+  int raster_group;        // tiles of the fast dimension swept together (keeps both operand panels in L2)
+  int splits;              // split-K factor (>1: fp32 output, partial sums combined with atomic adds)
   float alpha;
 };
 
@@ -64,7 +67,7 @@ __device__ __forceinline__ int find_group(const int* offs, int groups, int m0) {
 }
 
 template <int BN, int STAGES, int ESIZE, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
             const GemmParams p) {
   using L = SmemLayout<BN, STAGES, ESIZE>;
@@ -88,7 +91,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 8); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmapA);
@@ -108,18 +111,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 
   const int tiles_m = (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int nz = (p.group_mode == GROUP_K) ? p.groups : p.batch;
+  const int nz = (p.group_mode == GROUP_K) ? p.groups : p.batch * p.splits;
   const long long total_tiles = (long long)tiles_m * tiles_n * nz;
+  const int k_iters_per_split = (((p.K + BK - 1) / BK) + p.splits - 1) / p.splits;
 
+  // z carries (batch, split) for plain GEMMs: z = batch * splits + split
   auto decode = [&](long long t, int& mi, int& ni, int& z) {
     z = (int)(t / ((long long)tiles_m * tiles_n));
     int r = (int)(t % ((long long)tiles_m * tiles_n));
-    if (p.m_fastest) { mi = r % tiles_m; ni = r / tiles_m; } else { ni = r % tiles_n; mi = r / tiles_n; }
+    const int g = p.raster_group;
+    if (p.m_fastest) {
+      const int grp = r / (g * tiles_n), rr = r % (g * tiles_n);
+      const int gs = (tiles_m - grp * g) < g ? (tiles_m - grp * g) : g;
+      mi = grp * g + rr % gs; ni = rr / gs;
+    } else {
+      const int grp = r / (g * tiles_m), rr = r % (g * tiles_m);
+      const int gs = (tiles_n - grp * g) < g ? (tiles_n - grp * g) : g;
+      ni = grp * g + rr % gs; mi = rr / gs;
+    }
   };
   // k range of a tile, in elements
   auto krange = [&](int z, int& k_begin, int& k_end) {
     if (p.group_mode == GROUP_K) { k_begin = s_offs[z]; k_end = s_offs[z + 1]; }
-    else { k_begin = 0; k_end = p.K; }
+    else if (p.splits > 1) {
+      const int sp = z % p.splits;
+      k_begin = sp * k_iters_per_split * BK;
+      k_end = k_begin + k_iters_per_split * BK;
+      if (k_end > p.K) k_end = p.K;
+    } else { k_begin = 0; k_end = p.K; }
   };
 
   if (warp == 0) {
@@ -129,7 +148,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
       for (long long t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
         int mi, ni, z; decode(t, mi, ni, z);
         const int m0 = mi * BM, n0 = ni * BN;
-        int za = z, zb = z;
+        int za = z / p.splits, zb = z / p.splits;
         if (p.group_mode == GROUP_M) {
           if (m0 >= s_offs[p.groups]) continue;
           za = 0; zb = find_group(s_offs, p.groups, m0);
@@ -215,6 +234,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
   } else {
     // =========================== epilogue warps ===========================
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;             // which half of the tile's columns this warp stores
+    constexpr int HALF_N = BN / 2;
+    const bool use_atomics = p.splits > 1;
     uint32_t tile_no = 0;
     for (long long t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       int mi, ni, z; decode(t, mi, ni, z);
@@ -229,28 +251,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const long long zoff = (p.group_mode == GROUP_M) ? 0 : (long long)z * p.strideD;
+      const int zd = (p.group_mode == GROUP_K) ? z : z / p.splits;
+      const long long zoff = (p.group_mode == GROUP_M) ? 0 : (long long)zd * p.strideD;
       const size_t row_off = (size_t)zoff + (size_t)row * p.ldd;
+      const int dt = p.out_dtype & 0xff;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c, r);
+      for (int c = half * HALF_N; c < (half + 1) * HALF_N; c += 64) {
+        // 64 accumulator columns per TMEM round trip
+        uint32_t r[2][32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c;
+        tmem_ld_32x32b_x32(taddr, r[0]);
+        tmem_ld_32x32b_x32(taddr + 32, r[1]);
         tmem_ld_wait();
-        const int col0 = n0 + c;
-        if (row_ok && col0 < p.N) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int col0 = n0 + c + hh * 32;
+          if (!(row_ok && col0 < p.N)) continue;
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = empty_k ? 0.f : __uint_as_float(r[j]) * p.alpha;
+          for (int j = 0; j < 32; ++j) v[j] = empty_k ? 0.f : __uint_as_float(r[hh][j]) * p.alpha;
           if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (col0 + j < p.N) v[j] += load_as_float(p.bias, p.bias_dtype, col0 + j);
           }
-          const int dt = p.out_dtype & 0xff;
           const bool full = (col0 + 32 <= p.N);
           if (dt == DT_F32) {
             float* dst = reinterpret_cast<float*>(p.D) + row_off + col0;
-            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+            const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+            if (use_atomics) {
+              if (vec) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+              } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, v[j]);
+              }
+            } else if (vec) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -344,11 +381,11 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     configured = true;
   }
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-  const int nz = (p.group_mode == GROUP_K) ? p.groups : p.batch;
+  const int nz = (p.group_mode == GROUP_K) ? p.groups : p.batch * p.splits;
   long long total = (long long)tiles_m * tiles_n * nz;
   int grid = (int)(total < sms ? total : sms);
   if (grid < 1) grid = 1;
-  kern<<<grid, 192, L::TOTAL + 1024, stream>>>(ta, tb, p);
+  kern<<<grid, 320, L::TOTAL + 1024, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }
 
@@ -372,11 +409,12 @@ extern "C" int gb_gemm(const void* A, const void* B, void* D, const void* bias, 
                        long long lda, long long ldb, int ldd, long long strideA, long long strideB,
                        long long strideD, int a_mn, int b_mn, int in_dtype, int out_dtype, int bias_dtype,
                        int accumulate, float alpha, int group_mode, const int* group_offsets, int groups,
-                       int* status, int sm_count, cudaStream_t stream) {
+                       int splits, int bn_hint, int* status, int sm_count, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   const int es = (in_dtype == DT_F32) ? 4 : 2;
   const int bk = 128 / es;
-  const int bn = (N <= 128) ? 128 : 256;
+  const int bn = (N <= 128 || bn_hint == 128) ? 128 : 256;
+  if (splits < 1 || group_mode != GROUP_NONE || out_dtype != DT_F32) splits = 1;
   CUtensorMap ta, tb;
   int r;
   // A: K-major map dims (K, M); MN-major map dims (M, K); boxes: {bk, 128} resp. {bk(along M), bk rows of K}
@@ -394,9 +432,18 @@ extern "C" int gb_gemm(const void* A, const void* B, void* D, const void* bias, 
   p.out_dtype = out_dtype | ((in_dtype == DT_BF16 ? 1 : 0) << 8);
   p.bias_dtype = bias_dtype; p.accumulate = accumulate; p.group_mode = group_mode; p.groups = groups;
   p.alpha = alpha;
+  p.splits = splits;
   // Sweep the dimension whose operand is smaller fastest, so the larger one streams from HBM once
   // and the smaller one stays in L2.
   p.m_fastest = ((long long)M <= (long long)N) ? 1 : 0;
+  {
+    // If the operand of the fast dimension fits comfortably in L2, sweep it whole (the other operand then
+    // streams from HBM exactly once); otherwise walk 16-tile groups so a wave touches ~16 + ~9 panels.
+    const long long fast_bytes = (long long)(p.m_fastest ? M : N) * K * es;
+    const int fast_tiles = p.m_fastest ? (M + BM - 1) / BM : (N + bn - 1) / bn;
+    p.raster_group = (fast_bytes <= (48ll << 20)) ? fast_tiles : 16;
+    if (p.raster_group < 1) p.raster_group = 1;
+  }
   if (es == 4) {
     if (bn == 128) return dispatch_major<128, 4, 4>(a_mn, b_mn, ta, tb, p, sm_count, stream);
     return dispatch_major<256, 4, 4>(a_mn, b_mn, ta, tb, p, sm_count, stream);

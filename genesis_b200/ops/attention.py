@@ -10,7 +10,7 @@ import torch
 from . import native as N
 
 _SIG_FWD = "ppppp" + "iiiiii" + "i" + "f" + "i" + "pp"
-_SIG_BWD = "pppppppppp" + "iiiiii" + "i" + "f" + "i" + "pp"
+_SIG_BWD = "ppppppppppp" + "iiiiii" + "i" + "f" + "i" + "pp"
 N._SIGS["gb_attn_fwd"] = _SIG_FWD
 N._SIGS["gb_attn_bwd"] = _SIG_BWD
 _bound = False
@@ -59,8 +59,11 @@ def backward(do, q, k, v, o, lse, causal, scale):
     Sk, Hkv = k.shape[1], k.shape[2]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+    # grouped-query attention: the query heads of a group accumulate dK / dV in fp32 scratch
+    ws = torch.empty(2 * k.numel(), dtype=torch.float32, device=q.device) if Hq != Hkv else None
     N._chk(_lib().gb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
-                              delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Sk, Hq, Hkv, D,
+                              delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                              ws.data_ptr() if ws is not None else None, B, S, Sk, Hq, Hkv, D,
                               1 if causal else 0, float(scale), 1 if q.dtype == torch.bfloat16 else 0,
                               N.status_tensor(q.device).data_ptr(), N._st()), "attn_bwd")
     return dq, dk, dv

@@ -54,7 +54,7 @@ def _ok(x, w, offsets):
 def _gemm(a, b, out, M, Nn, Kk, lda, ldb, strideB, strideD, a_mn, b_mn, mode, offsets, groups):
     rc = N.lib().gb_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), None, M, Nn, Kk, 1, lda, ldb, Nn, 0, strideB,
                          strideD, a_mn, b_mn, N._GEMM_DT[a.dtype], N._GEMM_DT[out.dtype], 0, 0, 1.0, mode,
-                         offsets.data_ptr(), groups, N.status_tensor(a.device).data_ptr(), N._sms(a.device), N._st())
+                         offsets.data_ptr(), groups, 1, 0, N.status_tensor(a.device).data_ptr(), N._sms(a.device), N._st())
     N._chk(rc, "grouped gemm")
     return out
 

@@ -44,7 +44,7 @@ _SIGS = {
     "gb_grad_multi": "pilpfppip",
     "gb_router_fwd": "ppppp" + "liiiip", "gb_router_bwd": "pppppp" + "liiiip",
     "gb_moe_sort": "pppppp" + "liiilp", "gb_moe_combine": "pppp" + "liiip", "gb_moe_combine_bwd": "pppppp" + "liiip",
-    "gb_gemm": "pppp" + "iiii" + "ll" + "i" + "lll" + "ii" + "iii" + "i" + "f" + "i" + "p" + "i" + "p" + "i" + "p",
+    "gb_gemm": "pppp" + "iiii" + "ll" + "i" + "lll" + "ii" + "iii" + "i" + "f" + "i" + "p" + "i" + "ii" + "p" + "i" + "p",
     "gb_allreduce_fused": "ppllii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "pp",
     "gb_wait_flag": "pIupp",
 }
@@ -433,6 +433,25 @@ def _operand(t, want_contract_last):
     return buf[:, :c], 0, cp
 
 
+def _plan(M, N, K, es, can_split, sms):
+    """Tile width (256 / 128) and split-K factor that minimise a simple wave model of the persistent kernel:
+    cost = waves x (k-iterations per split x cost per iteration + epilogue)."""
+    k_iters = max(1, -(-K * es // 128))
+    best = None
+    for bn in ((256, 128) if N > 128 else (128,)):
+        tiles = -(-M // 128) * -(-N // bn)
+        per_iter = 1.0 if bn == 256 else 0.58
+        for sp in (range(1, 9) if can_split else (1,)):
+            if sp > 1 and k_iters // sp < 8:
+                break
+            waves = -(-tiles * sp // sms)
+            epi = (3.0 if bn == 256 else 1.5) * (1.6 if sp > 1 else 1.0)
+            cost = waves * (-(-k_iters // sp) * per_iter + epi)
+            if best is None or cost < best[0] * 0.97:
+                best = (cost, bn, sp)
+    return best[1], best[2]
+
+
 def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0):
     """D[M, N] = a[M, K] @ b_t[N, K]^T for 2-D operands in any of the supported layouts.
     `a` / `b_t` may be transposed views (stride(0) == 1); misaligned ones are repacked."""
@@ -459,10 +478,14 @@ def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0):
     b2, b_mn, ldb = _operand(b_t, True)
     if bias is not None and (bias.dtype not in _GEMM_DT or not bias.is_contiguous()):
         return NotImplemented
+    sms = _sms(a.device)
+    bn, splits = _plan(M, N, K, a.element_size(), out.dtype == F32 and bias is None, sms)
+    if splits > 1 and accum is None:
+        out.zero_()
     rc = lib().gb_gemm(a2.data_ptr(), b2.data_ptr(), out.data_ptr(), None if bias is None else bias.data_ptr(),
                        M, N, K, 1, lda, ldb, N, 0, 0, 0, a_mn, b_mn, _GEMM_DT[a.dtype], _GEMM_DT[out.dtype],
                        0 if bias is None else _GEMM_DT[bias.dtype], 0 if accum is None else 1, float(alpha),
-                       0, None, 0, status_tensor(a.device).data_ptr(), _sms(a.device), _st())
+                       0, None, 0, splits, bn, status_tensor(a.device).data_ptr(), sms, _st())
     _chk(rc, "gemm")
     return out
 
@@ -479,7 +502,7 @@ def bgemm(a, b_t, out_dtype=None):
     if out.numel() == 0:
         return out
     rc = lib().gb_gemm(a.data_ptr(), b_t.data_ptr(), out.data_ptr(), None, M, N, K, Bn, K, K, N, M * K, N * K, M * N,
-                       0, 0, _GEMM_DT[a.dtype], _GEMM_DT[out.dtype], 0, 0, 1.0, 0, None, 0,
+                       0, 0, _GEMM_DT[a.dtype], _GEMM_DT[out.dtype], 0, 0, 1.0, 0, None, 0, 1, 0,
                        status_tensor(a.device).data_ptr(), _sms(a.device), _st())
     _chk(rc, "bgemm")
     return out

@@ -101,3 +101,15 @@ def test_large_gemm_many_tiles():
     a, b = rnd(M, K_, dt=torch.bfloat16), rnd(N_, K_, dt=torch.bfloat16, seed=1)
     got = N.gemm(a.to(DEV), b.to(DEV))
     check(got, a.float() @ b.float().t(), torch.bfloat16, K_)
+
+
+@pytest.mark.parametrize("M,N_,K_", [(896, 896, 8192), (128, 896, 16384), (4864, 896, 4096), (300, 520, 6000)])
+def test_weight_gradient_shapes_split_k(M, N_, K_):
+    # small outputs with a long contraction: the planner splits K and combines partial sums with atomics
+    gy, x = rnd(K_, M, dt=torch.bfloat16), rnd(K_, N_, dt=torch.bfloat16, seed=1)
+    ref = gy.float().t() @ x.float()
+    got = K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32)
+    check(got, ref, torch.bfloat16, K_ / 16)
+    acc = torch.full((M, N_), 2.0, device=DEV)
+    K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32, accum=acc)
+    check(acc, ref + 2.0, torch.bfloat16, K_ / 16)
