@@ -164,16 +164,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
       if (j > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (j - 1) & 1, 51))) { ok = false; break; }
       const int col0 = j * BW_C;
       const bool need_mask = (col0 + BW_C > p.Sk) || (p.causal && (col0 + BW_C - 1 > m0 + off)) || (m0 + AT_BM > p.S);
+      if (need_mask) {
+        // masked scores become -inf (probability 0) in a pass of their own: the main loop stays branch-free
+        int lim = p.causal ? row + off : p.Sk - 1;            // last visible column of this row
+        lim = lim < p.Sk - 1 ? lim : p.Sk - 1;
+        if (row >= p.S) lim = -1;
+        lim -= col0;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) rs[c][i] = (c * 32 + i <= lim) ? rs[c][i] : 0xff800000u;
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float pr = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse2));
-          if (need_mask) {
-            const int col = col0 + c * 32 + i;
-            if (!(row < p.S && col < p.Sk && (!p.causal || col <= row + off))) pr = 0.f;
-          }
+          const float pr = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse2));
           ds[i] = pr * (__uint_as_float(rp[c][i]) - dl) * p.scale;
         }
         store_row_chunk(sdS, t, c * 32, ds, p.is_bf16, AT_BM * 128);
@@ -334,17 +341,26 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
       mbar_arrive(sdp_free);
       if (it > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (it - 1) & 1, 71))) { ok = false; break; }
       const bool need_mask = (q0 + BW_C > p.S) || (n0 + AT_BM > p.Sk) || (p.causal && (n0 + AT_BM - 1 > q0 + off));
+      if (need_mask) {
+        // this kv row is visible to query columns first..last of the tile; the rest become -inf
+        int first = p.causal ? kvrow - off - q0 : 0;
+        int last = p.S - 1 - q0;
+        if (kvrow >= p.Sk) last = -1;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int qc = c * 32 + i;
+            rs[c][i] = (qc >= first && qc <= last) ? rs[c][i] : 0xff800000u;
+          }
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float pt[32], dst[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int qc = c * 32 + i;
-          float pr = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse_b[qc]));
-          if (need_mask) {
-            const int qr = q0 + qc;
-            if (!(qr < p.S && kvrow < p.Sk && (!p.causal || kvrow <= qr + off))) pr = 0.f;
-          }
+          const float pr = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse_b[qc]));
           pt[i] = pr;
           dst[i] = pr * (__uint_as_float(rp[c][i]) - dl_b[qc]) * p.scale;
         }

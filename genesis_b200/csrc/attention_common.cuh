@@ -23,20 +23,24 @@ struct AttnParams {
 
 // 32 fp32 values of row `row`, columns c0..c0+31, into a K-major 128-byte-swizzled 16-bit tile whose
 // 64-column chunks are `chunk_stride` bytes apart (the layout TMA SWIZZLE_128B produces).
+template <bool BF16>
+__device__ __forceinline__ void store_row_chunk_t(uint8_t* base, int u0, int row, const float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 w;
+    w.x = pack2c<BF16>(v[i * 8 + 0], v[i * 8 + 1]);
+    w.y = pack2c<BF16>(v[i * 8 + 2], v[i * 8 + 3]);
+    w.z = pack2c<BF16>(v[i * 8 + 4], v[i * 8 + 5]);
+    w.w = pack2c<BF16>(v[i * 8 + 6], v[i * 8 + 7]);
+    *reinterpret_cast<uint4*>(base + (((u0 + i) ^ (row & 7)) << 4)) = w;
+  }
+}
 __device__ __forceinline__ void store_row_chunk(uint8_t* tile, int row, int c0, const float (&v)[32], int is_bf16,
                                                 int chunk_stride) {
   uint8_t* base = tile + (c0 >> 6) * chunk_stride + row * 128;
   const int u0 = (c0 & 63) >> 3;
-  const int dt = is_bf16 ? DT_BF16 : DT_F16;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint4 w;
-    w.x = pack2(v[i * 8 + 0], v[i * 8 + 1], dt);
-    w.y = pack2(v[i * 8 + 2], v[i * 8 + 3], dt);
-    w.z = pack2(v[i * 8 + 4], v[i * 8 + 5], dt);
-    w.w = pack2(v[i * 8 + 6], v[i * 8 + 7], dt);
-    *reinterpret_cast<uint4*>(base + (((u0 + i) ^ (row & 7)) << 4)) = w;
-  }
+  if (is_bf16) store_row_chunk_t<true>(base, u0, row, v);
+  else store_row_chunk_t<false>(base, u0, row, v);
 }
 
 // K-major operand (contraction inside the 128-byte rows): k-step kk of 16 elements

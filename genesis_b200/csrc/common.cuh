@@ -18,8 +18,17 @@ __device__ __forceinline__ uint16_t float_to_half_bits(float v, int dt) {
   if (dt == DT_BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
   return __half_as_ushort(__float2half_rn(v));
 }
+// two floats -> one packed 16-bit pair (a in the low half) with the single packed convert instruction;
+// the scalar converts run on the quarter-rate conversion pipe
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2c(float a, float b) {
+  uint32_t r;
+  if (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b, int dt) {
-  return (uint32_t)float_to_half_bits(a, dt) | ((uint32_t)float_to_half_bits(b, dt) << 16);
+  return dt == DT_BF16 ? pack2c<true>(a, b) : pack2c<false>(a, b);
 }
 __device__ __forceinline__ float load_as_float(const void* p, int dt, size_t i) {
   if (dt == DT_F32) return reinterpret_cast<const float*>(p)[i];
