@@ -3,18 +3,19 @@
 // Both kernels work on 128 x 64 score tiles: 128 row threads (one TMEM lane each) by 64 columns, which
 // keeps S and dP (64 + 64 fp32 registers per thread) in registers after ONE tensor-memory round trip, so
 // the TMEM tile is handed back at once and the next tile's QK^T / dO V^T run while the current tile's
-// exponentials are computed.  Operand tiles arrive through a two-stage TMA ring.
+// exponentials are computed.  Operand tiles arrive through a three-stage TMA ring.
 //   dQ    : CTA = (q tile of 128 rows, head); loop over kv tiles of 64:
 //           S = Q K^T, dP = dO V^T, dS = P o (dP - delta) * scale, dQ += dS K          (K tile reused MN-major)
 //   dK/dV : CTA = (kv tile of 128 rows, query head); loop over q tiles of 64:
 //           S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q                     (dO, Q tiles reused MN-major)
-// With D = 64 a CTA needs 256 TMEM columns and < 113 KB of shared memory: two CTAs share an SM.
+// With D = 64 a CTA needs 256 TMEM columns and 112.1 KB of shared memory: two CTAs share an SM.
 // Reference counterpart: genesis/nn/attention.py:162-406 (Triton, 32 x 32 tiles, Hq == Hkv only).
 #include "attention_common.cuh"
 
 namespace gb {
 
 constexpr int BW_C = 64;    // columns of a backward score tile
+constexpr int BW_ST = 3;    // stages of the ring of streamed operand tiles
 
 __device__ __forceinline__ void store_out_row(uint16_t* dst, uint32_t tsrc, int ncols, bool valid, int dt) {
 #pragma unroll 1
@@ -40,7 +41,7 @@ __device__ __forceinline__ void store_out_row(uint16_t* dst, uint32_t tsrc, int 
 // dQ
 // =====================================================================================================
 template <int D, int NCTA>
-__global__ void __launch_bounds__(160, NCTA)
+__global__ void __maxnreg__(NCTA == 2 ? 168 : 255)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                    const __grid_constant__ CUtensorMap tmv, const __grid_constant__ CUtensorMap tmdo,
                    const AttnParams p) {
@@ -49,23 +50,24 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
   constexpr int DSB = AT_BM * BW_C * 2;      // [128 x 64] 16-bit tile
   constexpr uint32_t TCOLS = 256;            // 64 (S) + 64 (dP) + D (dQ) <= 256
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (status_poisoned(p.status)) return;
   if ((reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {
     if (threadIdx.x == 0) report_error(p.status, GB_ERR_BAD_ARG, 2, 0);
     return;
   }
   uint8_t* sQ = smem_raw;
   uint8_t* sdO = sQ + QT;
-  uint8_t* sK = sdO + QT;            // 2 stages
-  uint8_t* sV = sK + 2 * KT;         // 2 stages
-  uint8_t* sdS = sV + 2 * KT;
+  uint8_t* sK = sdO + QT;            // BW_ST stages
+  uint8_t* sV = sK + BW_ST * KT;     // BW_ST stages
+  uint8_t* sdS = sV + BW_ST * KT;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + DSB);
   uint64_t* qdo_full = bars;
-  uint64_t* kv_full = bars + 1;      // [2]
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* sdp_free = bars + 4;
-  uint64_t* ds_ready = bars + 5;
-  uint64_t* acc_done = bars + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* kv_full = bars + 1;      // [BW_ST]
+  uint64_t* sdp_full = bars + 4;
+  uint64_t* sdp_free = bars + 5;
+  uint64_t* ds_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -82,7 +84,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
   if (n_kv < 1) n_kv = 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1); mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1); mbar_init(sdp_full, 1);
+    mbar_init(qdo_full, 1); mbar_init(sdp_full, 1);
+    for (int i = 0; i < BW_ST; ++i) mbar_init(&kv_full[i], 1);
     mbar_init(sdp_free, 128); mbar_init(ds_ready, 128); mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -101,14 +104,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
       const uint32_t idesc_dq = make_idesc(fmt, 0, 1, AT_BM, D);
       const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS);
       auto load_kv = [&](int j) {
-        const int st = j & 1;
+        const int st = j % BW_ST;
         mbar_expect_tx(&kv_full[st], 2 * KT);
         load_tile<D>(sK + st * KT, &tmk, &kv_full[st], kvh, j * BW_C, b, BW_C);
         load_tile<D>(sV + st * KT, &tmv, &kv_full[st], kvh, j * BW_C, b, BW_C);
       };
       auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!AT_WAIT(&kv_full[st], (j >> 1) & 1, 42)) return false;
+        const int st = j % BW_ST;
+        if (!AT_WAIT(&kv_full[st], (j / BW_ST) & 1, 42)) return false;
         if (j > 0 && !AT_WAIT(sdp_free, (j - 1) & 1, 44)) return false;
         tc_fence_after_sync();
         const uint32_t aK = smem_u32(sK + st * KT), aV = smem_u32(sV + st * KT);
@@ -123,22 +126,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
       mbar_expect_tx(qdo_full, 2 * QT);
       load_tile<D>(sQ, &tmq, qdo_full, h, m0, b, AT_BM);
       load_tile<D>(sdO, &tmdo, qdo_full, h, m0, b, AT_BM);
-      load_kv(0);
-      if (n_kv > 1) load_kv(1);
+      for (int j = 0; j < BW_ST && j < n_kv; ++j) load_kv(j);
       bool ok = AT_WAIT(qdo_full, 0, 41) && issue_s(0);
       for (int j = 0; ok && j < n_kv; ++j) {
         if (j + 1 < n_kv && !issue_s(j + 1)) break;
         if (!AT_WAIT(ds_ready, j & 1, 43)) break;
         tc_fence_after_sync();
-        const uint32_t aK = smem_u32(sK + (j & 1) * KT);
+        const uint32_t aK = smem_u32(sK + (j % BW_ST) * KT);
 #pragma unroll
         for (int kk = 0; kk < BW_C / 16; ++kk)
           umma_f16(tdQ, desc_kmajor(adS, kk, AT_BM), desc_mnmajor(aK, kk, BW_C), idesc_dq, (j > 0 || kk > 0));
         umma_commit(acc_done);
-        if (j + 2 < n_kv) {
-          if (!AT_WAIT(acc_done, j & 1, 40)) break;      // stage (j & 1) is free again
-          load_kv(j + 2);
-        }
+        // tile j - 1 is retired (the row threads waited for it before they signalled ds_ready(j)): refill
+        // its stage with tile j - 1 + BW_ST, a full iteration before anything needs it
+        // (no wait on acc_done here: its phase j - 1 is known complete, and a parity wait issued after the
+        // commit above could alias phase j + 1)
+        if (j >= 1 && j - 1 + BW_ST < n_kv) load_kv(j - 1 + BW_ST);
       }
     }
   } else {
@@ -161,7 +164,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(sdp_free);
-      if (j > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (j - 1) & 1, 51))) { ok = false; break; }
       const int col0 = j * BW_C;
       const bool need_mask = (col0 + BW_C > p.Sk) || (p.causal && (col0 + BW_C - 1 > m0 + off)) || (m0 + AT_BM > p.S);
       if (need_mask) {
@@ -183,8 +185,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
           const float pr = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse2));
           ds[i] = pr * (__uint_as_float(rp[c][i]) - dl) * p.scale;
         }
+        // the dS tile is single-buffered: the previous iteration's dQ MMA has to be done reading it
+        if (c == 0 && j > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (j - 1) & 1, 51))) { ok = false; break; }
         store_row_chunk(sdS, t, c * 32, ds, p.is_bf16, AT_BM * 128);
       }
+      if (!ok) break;
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(ds_ready);
@@ -206,7 +211,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
 // causal triangle balanced; with Hq == Hkv the CTA owns its output rows and stores them directly.
 // =====================================================================================================
 template <int D, int NCTA>
-__global__ void __launch_bounds__(160, NCTA)
+__global__ void __maxnreg__(NCTA == 2 ? 168 : 255)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                      const __grid_constant__ CUtensorMap tmv, const __grid_constant__ CUtensorMap tmdo,
                      const AttnParams p, float* __restrict__ ws) {
@@ -215,26 +220,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
   constexpr int PB = AT_BM * BW_C * 2;       // [128 x 64] 16-bit tile
   constexpr uint32_t TCOLS = (D == 64) ? 256 : 512;   // 64 (S^T) + 64 (dP^T) + D (dV) + D (dK)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (status_poisoned(p.status)) return;
   if ((reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {
     if (threadIdx.x == 0) report_error(p.status, GB_ERR_BAD_ARG, 3, 0);
     return;
   }
   uint8_t* sK = smem_raw;
   uint8_t* sV = sK + KT;
-  uint8_t* sQ = sV + KT;             // 2 stages
-  uint8_t* sdO = sQ + 2 * QT;        // 2 stages
-  uint8_t* sPT = sdO + 2 * QT;
+  uint8_t* sQ = sV + KT;             // BW_ST stages
+  uint8_t* sdO = sQ + BW_ST * QT;    // BW_ST stages
+  uint8_t* sPT = sdO + BW_ST * QT;
   uint8_t* sdST = sPT + PB;
-  float* lse_s = reinterpret_cast<float*>(sdST + PB);     // [4 warps][2][64]: every warp stages its own copy
-  float* dl_s = lse_s + 8 * BW_C;                          // [4 warps][2][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dl_s + 8 * BW_C);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdST + PB);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;     // [2]
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* sdp_free = bars + 4;
-  uint64_t* ds_ready = bars + 5;
-  uint64_t* acc_done = bars + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* qdo_full = bars + 1;     // [BW_ST]
+  uint64_t* sdp_full = bars + 4;
+  uint64_t* sdp_free = bars + 5;
+  uint64_t* ds_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -249,7 +253,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
   const int n_it = nq > i_start ? nq - i_start : 0;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(&qdo_full[0], 1); mbar_init(&qdo_full[1], 1); mbar_init(sdp_full, 1);
+    mbar_init(kv_full, 1); mbar_init(sdp_full, 1);
+    for (int i = 0; i < BW_ST; ++i) mbar_init(&qdo_full[i], 1);
     mbar_init(sdp_free, 128); mbar_init(ds_ready, 128); mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -268,15 +273,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
       const uint32_t idesc_acc = make_idesc(fmt, 0, 1, AT_BM, D);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), adST = smem_u32(sdST);
       auto load_q = [&](int it) {
-        const int st = it & 1;
+        const int st = it % BW_ST;
         const int q0 = (i_start + it) * BW_C;
         mbar_expect_tx(&qdo_full[st], 2 * QT);
         load_tile<D>(sQ + st * QT, &tmq, &qdo_full[st], h, q0, b, BW_C);
         load_tile<D>(sdO + st * QT, &tmdo, &qdo_full[st], h, q0, b, BW_C);
       };
       auto issue_s = [&](int it) -> bool {
-        const int st = it & 1;
-        if (!AT_WAIT(&qdo_full[st], (it >> 1) & 1, 62)) return false;
+        const int st = it % BW_ST;
+        if (!AT_WAIT(&qdo_full[st], (it / BW_ST) & 1, 62)) return false;
         if (it > 0 && !AT_WAIT(sdp_free, (it - 1) & 1, 64)) return false;
         tc_fence_after_sync();
         const uint32_t aQ = smem_u32(sQ + st * QT), adO = smem_u32(sdO + st * QT);
@@ -291,24 +296,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
       mbar_expect_tx(kv_full, 2 * KT);
       load_tile<D>(sK, &tmk, kv_full, kvh, n0, b, AT_BM);
       load_tile<D>(sV, &tmv, kv_full, kvh, n0, b, AT_BM);
-      load_q(0);
-      if (n_it > 1) load_q(1);
+      for (int it = 0; it < BW_ST && it < n_it; ++it) load_q(it);
       bool ok = AT_WAIT(kv_full, 0, 61) && issue_s(0);
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it && !issue_s(it + 1)) break;
         if (!AT_WAIT(ds_ready, it & 1, 63)) break;
         tc_fence_after_sync();
-        const uint32_t aQ = smem_u32(sQ + (it & 1) * QT), adO = smem_u32(sdO + (it & 1) * QT);
+        const uint32_t aQ = smem_u32(sQ + (it % BW_ST) * QT), adO = smem_u32(sdO + (it % BW_ST) * QT);
 #pragma unroll
         for (int kk = 0; kk < BW_C / 16; ++kk) {
           umma_f16(tdV, desc_kmajor(aPT, kk, AT_BM), desc_mnmajor(adO, kk, BW_C), idesc_acc, (it > 0 || kk > 0));
           umma_f16(tdK, desc_kmajor(adST, kk, AT_BM), desc_mnmajor(aQ, kk, BW_C), idesc_acc, (it > 0 || kk > 0));
         }
         umma_commit(acc_done);
-        if (it + 2 < n_it) {
-          if (!AT_WAIT(acc_done, it & 1, 60)) break;     // stage (it & 1) is free again
-          load_q(it + 2);
-        }
+        // tile it - 1 is retired (the row threads saw acc_done(it - 1) before ds_ready(it)): refill its stage
+        if (it >= 1 && it - 1 + BW_ST < n_it) load_q(it - 1 + BW_ST);
       }
     }
   } else {
@@ -320,53 +322,68 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const int q0 = (i_start + it) * BW_C;
-      float* lse_b = lse_s + (warp * 2 + (it & 1)) * BW_C;
-      float* dl_b = dl_s + (warp * 2 + (it & 1)) * BW_C;
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int qc = lane + u * 32, qr = q0 + qc;
-        lse_b[qc] = qr < p.S ? p.lse_in[stat0 + qr] * LOG2E : 0.f;
-        dl_b[qc] = qr < p.S ? p.delta[stat0 + qr] : 0.f;
+      // per-column statistics: every thread reads the same addresses (one broadcast transaction per load);
+      // columns past the end of the sequence are masked below, so their index is only clamped
+      const float* lse_q = p.lse_in + stat0;
+      const float* dl_q = p.delta + stat0;
+      const bool stat_vec = ((stat0 + q0) & 3) == 0 && q0 + BW_C <= p.S;
+      // the next tile's statistics (2 x 256 bytes) are pulled into L1 one iteration ahead
+      if (t < 4 && it + 1 < n_it && q0 + 2 * BW_C <= p.S) {
+        const float* nx = ((t & 2) ? dl_q : lse_q) + q0 + BW_C + (t & 1) * 32;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(nx));
       }
-      __syncwarp();
       if (!__all_sync(0xffffffffu, AT_WAIT(sdp_full, it & 1, 70))) { ok = false; break; }
       tc_fence_after_sync();
-      uint32_t rs[2][32], rp[2][32];
-      tmem_ld_32x32b_x32(tST + lane_base, rs[0]);
-      tmem_ld_32x32b_x32(tST + lane_base + 32, rs[1]);
-      tmem_ld_32x32b_x32(tdPT + lane_base, rp[0]);
-      tmem_ld_32x32b_x32(tdPT + lane_base + 32, rp[1]);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(sdp_free);
-      if (it > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (it - 1) & 1, 71))) { ok = false; break; }
       const bool need_mask = (q0 + BW_C > p.S) || (n0 + AT_BM > p.Sk) || (p.causal && (n0 + AT_BM - 1 > q0 + off));
-      if (need_mask) {
-        // this kv row is visible to query columns first..last of the tile; the rest become -inf
-        int first = p.causal ? kvrow - off - q0 : 0;
-        int last = p.S - 1 - q0;
-        if (kvrow >= p.Sk) last = -1;
+      // this kv row is visible to query columns first..last of the tile
+      const int first = p.causal ? kvrow - off - q0 : 0;
+      const int last = kvrow < p.Sk ? p.S - 1 - q0 : -1;
+      // two half tiles of 32 columns, each read from tensor memory just before its use: 64 live accumulator
+      // registers instead of 128 keep the kernel at two CTAs per SM
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32b_x32(tST + lane_base + c * 32, rs);
+        tmem_ld_32x32b_x32(tdPT + lane_base + c * 32, rp);
+        tmem_ld_wait();
+        if (c == 1) { tc_fence_before_sync(); mbar_arrive(sdp_free); }
+        if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int qc = c * 32 + i;
-            rs[c][i] = (qc >= first && qc <= last) ? rs[c][i] : 0xff800000u;
+            rs[i] = (qc >= first && qc <= last) ? rs[i] : 0xff800000u;      // -inf: probability 0
           }
-      }
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+        }
         float pt[32], dst[32];
+        if (stat_vec) {
+          const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0 + c * 32);
+          const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 l = __ldg(l4 + i), d = __ldg(d4 + i);
+            pt[4 * i] = l.x; pt[4 * i + 1] = l.y; pt[4 * i + 2] = l.z; pt[4 * i + 3] = l.w;
+            dst[4 * i] = d.x; dst[4 * i + 1] = d.y; dst[4 * i + 2] = d.z; dst[4 * i + 3] = d.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            int qr = q0 + c * 32 + i;
+            qr = qr < p.S ? qr : p.S - 1;
+            pt[i] = __ldg(lse_q + qr); dst[i] = __ldg(dl_q + qr);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int qc = c * 32 + i;
-          const float pr = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse_b[qc]));
+          const float pr = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -pt[i] * LOG2E));
           pt[i] = pr;
-          dst[i] = pr * (__uint_as_float(rp[c][i]) - dl_b[qc]) * p.scale;
+          dst[i] = pr * (__uint_as_float(rp[i]) - dst[i]) * p.scale;
         }
+        // the P^T / dS^T tiles are single-buffered: the previous iteration's MMAs have to be done with them
+        if (c == 0 && it > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (it - 1) & 1, 71))) { ok = false; break; }
         store_row_chunk(sPT, t, c * 32, pt, p.is_bf16, AT_BM * 128);
         store_row_chunk(sdST, t, c * 32, dst, p.is_bf16, AT_BM * 128);
       }
+      if (!ok) break;
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(ds_ready);
@@ -471,8 +488,8 @@ static int launch_bwd(const CUtensorMap& tq128, const CUtensorMap& tdo128, const
                       cudaStream_t st) {
   // no alignment pad: shared memory of a CTA starts 1024-aligned (checked in the kernels), and at D = 64 two
   // CTAs have to fit in one SM
-  const int smem_dq = 2 * AT_BM * D * 2 + 4 * BW_C * D * 2 + AT_BM * BW_C * 2 + 128;
-  const int smem_kv = 2 * AT_BM * D * 2 + 4 * BW_C * D * 2 + 2 * AT_BM * BW_C * 2 + 16 * BW_C * 4 + 128;
+  const int smem_dq = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + AT_BM * BW_C * 2 + 128;
+  const int smem_kv = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + 2 * AT_BM * BW_C * 2 + 128;
   static bool cfg = false;
   if (!cfg) {
     int r;

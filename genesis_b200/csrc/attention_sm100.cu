@@ -34,6 +34,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
   constexpr int PB = AT_BM * AT_BN * 2;
   constexpr uint32_t TCOLS = SB == 1 ? 256 : 512;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (status_poisoned(p.status)) return;
   if (SB == 1 && (reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {
     // the two-CTA-per-SM configuration has no room for an alignment pad; refuse rather than overrun
     if (threadIdx.x == 0) report_error(p.status, GB_ERR_BAD_ARG, 1, 0);

@@ -77,6 +77,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
   constexpr uint32_t TMEM_COLS = 2 * BN;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (status_poisoned(p.status)) return;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BARRIER_OFFSET);
   uint64_t* empty_bar = full_bar + STAGES;

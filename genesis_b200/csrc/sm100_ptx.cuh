@@ -28,6 +28,13 @@ __device__ __forceinline__ void report_error(int* status, int code, int site, in
   }
 }
 
+// A kernel that finds an error already recorded does no work: after one expired wait the remaining CTAs of
+// the grid (and later launches, until the host has read and cleared the word) leave at once instead of each
+// spending a wait budget of its own.
+__device__ __forceinline__ bool status_poisoned(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

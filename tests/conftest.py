@@ -18,3 +18,18 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _device_status(request):
+    """After every GPU test, read the status word the native kernels share: a bounded wait that expired fails
+    the test that caused it (and clears the word, so the next test starts clean)."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from genesis_b200.ops import native
+    if native.available():
+        native.check_status()
