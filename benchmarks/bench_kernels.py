@@ -61,10 +61,22 @@ def main():
     ap.add_argument("--torch", action="store_true", help="also time the torch/cuBLAS op for comparison")
     ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D of a single attention case")
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--gemm-shape", default=None, help="M,N,K of a single linear-forward case (y = x @ w^T)")
     a = ap.parse_args()
     hbm, tf, src = peaks()
     what = a.what.split(",")
     dev = "cuda"
+    if a.gemm_shape:
+        m, nn, k = [int(v) for v in a.gemm_shape.split(",")]
+        X = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+        W = torch.randn(nn, k, device=dev, dtype=torch.bfloat16)
+        ms = timeit(lambda: K.linear(X, W), iters=a.iters, warmup=min(3, a.iters))
+        rec = {"kernel": "linear_fwd", "M": m, "N": nn, "K": k, "ms": ms, "tflops": 2 * m * nn * k / ms / 1e9,
+               "frac_of_" + src: 2 * m * nn * k / ms / 1e9 / tf}
+        if a.torch:
+            rec["torch_ms"] = timeit(lambda: torch.matmul(X, W.t()), iters=a.iters, warmup=min(3, a.iters))
+        print(json.dumps(rec), flush=True)
+        return
     if "gemm" in what:
         # (run first, before the large squares heat the part into its power cap)
         # the shapes of the Qwen2.5-0.5B step (M = 16384 tokens)

@@ -5,7 +5,9 @@
 // One persistent, warp-specialised kernel:
 //   warp 0    TMA producer   cp.async.bulk.tensor (128-byte swizzle) into a ring of smem stages
 //   warp 1    MMA issuer     one elected thread issues tcgen05.mma (UMMA 128 x BN x 16); TMEM owner
-//   warps 2-9 epilogue       tcgen05.ld of the finished accumulator -> bias/accumulate/convert -> global
+//   warps 2-9 epilogue       tcgen05.ld of the finished accumulator -> bias/convert -> swizzled smem slab of the
+//                            warp -> TMA store (or TMA add-reduce for fp32 accumulation and split-K); outputs
+//                            whose base or pitch is not 16-byte aligned take plain per-thread stores instead
 //                            (two warps per TMEM lane quarter, each takes half of the tile's columns)
 // Two accumulators live in TMEM (2 x BN columns), so the epilogue of tile i overlaps the main loop of
 // tile i+1.  Every load targets one CTA only: the kernel is safe in multi-GPU jobs.
@@ -43,7 +45,8 @@ struct GemmParams {
   int groups;
   int m_fastest;           // tile order
   int raster_group;        // tiles of the fast dimension swept together (keeps both operand panels in L2)
-  int splits;              // split-K factor (>1: fp32 output, partial sums combined with atomic adds)
+  int splits;              // split-K factor (>1: fp32 output, partial sums combined with adds in memory)
+  int tma_out;             // 0: per-thread stores; 1: TMA store; 2: TMA add-reduce (fp32 output)
   float alpha;
 };
 
@@ -53,7 +56,9 @@ struct SmemLayout {
   static constexpr int B_BYTES = BN * BK_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BARRIER_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BARRIER_OFFSET + 1024;
+  static constexpr int SLAB_OFFSET = BARRIER_OFFSET + 1024;      // 8 epilogue warps x [32 rows x 128 bytes]
+  static constexpr int SLAB_BYTES = 32 * 128;
+  static constexpr int TOTAL = SLAB_OFFSET + 8 * SLAB_BYTES;
 };
 
 // Find the segment that contains row `m0` (offsets ascending, last = total padded rows).
@@ -69,7 +74,7 @@ __device__ __forceinline__ int find_group(const int* offs, int groups, int m0) {
 template <int BN, int STAGES, int ESIZE, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(320, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmapD, const GemmParams p) {
   using L = SmemLayout<BN, STAGES, ESIZE>;
   constexpr int BK = BK_BYTES / ESIZE;              // elements of K per stage
   constexpr int UMMA_K = 32 / ESIZE;                // 16 for 16-bit, 8 for tf32
@@ -97,6 +102,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     mbar_fence_init();
     tma_prefetch_desc(&tmapA);
     tma_prefetch_desc(&tmapB);
+    if (p.tma_out) tma_prefetch_desc(&tmapD);
   }
   if (p.group_mode != GROUP_NONE) {
     for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) s_offs[i] = p.group_offsets[i];
@@ -238,6 +244,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     const int half = (warp - 2) >> 2;             // which half of the tile's columns this warp stores
     constexpr int HALF_N = BN / 2;
     const bool use_atomics = p.splits > 1;
+    uint8_t* slab = smem + L::SLAB_OFFSET + (warp - 2) * L::SLAB_BYTES;
+    uint8_t* slab_row = slab + lane * 128;
     uint32_t tile_no = 0;
     for (long long t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       int mi, ni, z; decode(t, mi, ni, z);
@@ -264,6 +272,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         tmem_ld_32x32b_x32(taddr, r[0]);
         tmem_ld_32x32b_x32(taddr + 32, r[1]);
         tmem_ld_wait();
+        if (p.tma_out) {
+          // the warp's 32 x 128-byte slab (128-byte swizzle, as the tensor map expects) goes out as one box
+          const int zc = (p.group_mode == GROUP_M) ? 0 : zd;
+          const int y0 = m0 + q * 32;
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int col0 = n0 + c + hh * 32;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = empty_k ? 0.f : __uint_as_float(r[hh][j]) * p.alpha;
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += load_as_float(p.bias, p.bias_dtype, col0 + j);
+            }
+            if (dt == DT_F32) {
+              // 32 fp32 columns fill the slab: one box per half batch
+              if (lane == 0) bulk_wait_group_read<0>();
+              __syncwarp();
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                *reinterpret_cast<float4*>(slab_row + ((u ^ (lane & 7)) << 4)) =
+                    make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0 && y0 < p.M && col0 < p.N) {
+                if (p.tma_out == 2) tma_reduce_add_3d(&tmapD, slab, col0, y0, zc);
+                else tma_store_3d(&tmapD, slab, col0, y0, zc);
+                bulk_commit_group();
+              }
+            } else {
+              // 64 16-bit columns fill the slab: this half batch writes units 4*hh .. 4*hh+3 of each row
+              if (hh == 0) {
+                if (lane == 0) bulk_wait_group_read<0>();
+                __syncwarp();
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                uint4 o;
+                o.x = pack2(v[8 * u], v[8 * u + 1], dt); o.y = pack2(v[8 * u + 2], v[8 * u + 3], dt);
+                o.z = pack2(v[8 * u + 4], v[8 * u + 5], dt); o.w = pack2(v[8 * u + 6], v[8 * u + 7], dt);
+                *reinterpret_cast<uint4*>(slab_row + (((4 * hh + u) ^ (lane & 7)) << 4)) = o;
+              }
+              if (hh == 1) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && y0 < p.M && n0 + c < p.N) {
+                  tma_store_3d(&tmapD, slab, n0 + c, y0, zc);
+                  bulk_commit_group();
+                }
+              }
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int col0 = n0 + c + hh * 32;
@@ -322,6 +385,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       ++tile_no;
     }
+    // the slab must outlive the last store's read of it
+    if (lane == 0) bulk_wait_group_read<0>();
+    __syncwarp();
   }
 
   tc_fence_before_sync();
@@ -371,8 +437,8 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, long long inner,
 }
 
 template <int BN, int STAGES, int ESIZE, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
-                       cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p,
+                       int sms, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES, ESIZE>;
   auto kern = gemm_kernel<BN, STAGES, ESIZE, A_MN, B_MN>;
   static bool configured = false;
@@ -386,17 +452,17 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   long long total = (long long)tiles_m * tiles_n * nz;
   int grid = (int)(total < sms ? total : sms);
   if (grid < 1) grid = 1;
-  kern<<<grid, 320, L::TOTAL + 1024, stream>>>(ta, tb, p);
+  kern<<<grid, 320, L::TOTAL + 1024, stream>>>(ta, tb, td, p);
   return (int)cudaGetLastError();
 }
 
 template <int BN, int STAGES, int ESIZE>
-static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-                          int sms, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch_gemm<BN, STAGES, ESIZE, false, false>(ta, tb, p, sms, s);
-  if (!a_mn && b_mn) return launch_gemm<BN, STAGES, ESIZE, false, true>(ta, tb, p, sms, s);
-  if (a_mn && !b_mn) return launch_gemm<BN, STAGES, ESIZE, true, false>(ta, tb, p, sms, s);
-  return launch_gemm<BN, STAGES, ESIZE, true, true>(ta, tb, p, sms, s);
+static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                          const GemmParams& p, int sms, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_gemm<BN, STAGES, ESIZE, false, false>(ta, tb, td, p, sms, s);
+  if (!a_mn && b_mn) return launch_gemm<BN, STAGES, ESIZE, false, true>(ta, tb, td, p, sms, s);
+  if (a_mn && !b_mn) return launch_gemm<BN, STAGES, ESIZE, true, false>(ta, tb, td, p, sms, s);
+  return launch_gemm<BN, STAGES, ESIZE, true, true>(ta, tb, td, p, sms, s);
 }
 
 }  // namespace gb
@@ -434,6 +500,22 @@ extern "C" int gb_gemm(const void* A, const void* B, void* D, const void* bias, 
   p.bias_dtype = bias_dtype; p.accumulate = accumulate; p.group_mode = group_mode; p.groups = groups;
   p.alpha = alpha;
   p.splits = splits;
+  // Output through TMA when the tensor-map rules allow it: 16-byte aligned base, pitch and batch stride.
+  // fp32 accumulation and split-K become add-reductions in memory; 16-bit accumulation keeps the
+  // read-modify-write path (one rounding instead of two).
+  CUtensorMap td = ta;
+  p.tma_out = 0;
+  {
+    const int eso = (out_dtype == DT_F32) ? 4 : 2;
+    const bool adds = accumulate != 0 || splits > 1;
+    const long long d_batches = (group_mode == GROUP_K) ? groups : ((group_mode == GROUP_M) ? 1 : p.batch);
+    const bool aligned = (reinterpret_cast<uintptr_t>(D) & 15) == 0 && ((long long)ldd * eso) % 16 == 0 &&
+                         (d_batches <= 1 || (strideD * eso) % 16 == 0);
+    if (aligned && (!adds || out_dtype == DT_F32)) {
+      r = make_tmap_3d(&td, D, out_dtype, N, M, d_batches, ldd, strideD, 32);
+      if (r == 0) p.tma_out = adds ? 2 : 1;
+    }
+  }
   // Sweep the dimension whose operand is smaller fastest, so the larger one streams from HBM once
   // and the smaller one stays in L2.
   p.m_fastest = ((long long)M <= (long long)N) ? 1 : 0;
@@ -446,9 +528,9 @@ extern "C" int gb_gemm(const void* A, const void* B, void* D, const void* bias, 
     if (p.raster_group < 1) p.raster_group = 1;
   }
   if (es == 4) {
-    if (bn == 128) return dispatch_major<128, 4, 4>(a_mn, b_mn, ta, tb, p, sm_count, stream);
-    return dispatch_major<256, 4, 4>(a_mn, b_mn, ta, tb, p, sm_count, stream);
+    if (bn == 128) return dispatch_major<128, 4, 4>(a_mn, b_mn, ta, tb, td, p, sm_count, stream);
+    return dispatch_major<256, 4, 4>(a_mn, b_mn, ta, tb, td, p, sm_count, stream);
   }
-  if (bn == 128) return dispatch_major<128, 6, 2>(a_mn, b_mn, ta, tb, p, sm_count, stream);
-  return dispatch_major<256, 4, 2>(a_mn, b_mn, ta, tb, p, sm_count, stream);
+  if (bn == 128) return dispatch_major<128, 6, 2>(a_mn, b_mn, ta, tb, td, p, sm_count, stream);
+  return dispatch_major<256, 4, 2>(a_mn, b_mn, ta, tb, td, p, sm_count, stream);
 }
