@@ -14,11 +14,11 @@ def _w(t):
 
 
 def triu(a, k=0):
-    return _w(torch.triu(a._t, diagonal=k))
+    return _w(K.triu_tril(a._t, k, True))
 
 
 def tril(a, k=0):
-    return _w(torch.tril(a._t, diagonal=k))
+    return _w(K.triu_tril(a._t, k, False))
 
 
 def isinf(a):
@@ -34,22 +34,21 @@ def isfinite(a):
 
 
 def argsort(a, dim=-1, descending=False):
-    return _w(torch.argsort(a._t, dim=dim, descending=descending, stable=True))
+    return _w(K.sort(a._t, dim, descending)[1])
 
 
 def sort(a, dim=-1, descending=False):
-    v, i = torch.sort(a._t, dim=dim, descending=descending, stable=True)
+    v, i = K.sort(a._t, dim, descending)
     return _w(v), _w(i)
 
 
 def bincount(a, weights=None, minlength=0):
-    return _w(torch.bincount(a._t.reshape(-1).long(), weights=None if weights is None else _r(weights),
-                             minlength=minlength))
+    return _w(K.bincount(a._t, None if weights is None else _r(weights), minlength))
 
 
 def nonzero(a, as_tuple=False):
-    out = torch.nonzero(a._t, as_tuple=as_tuple)
-    return tuple(_w(o) for o in out) if as_tuple else _w(out)
+    out = K.nonzero(a._t)
+    return tuple(_w(out[:, d]) for d in range(out.shape[1])) if as_tuple else _w(out)
 
 
 def allclose(a, b, rtol=1e-5, atol=1e-8, equal_nan=False):

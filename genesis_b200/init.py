@@ -139,8 +139,7 @@ def arange(start, end=None, step=1, device=None, dtype=None, requires_grad=False
     if dtype is None:
         is_int = all(isinstance(v, (int, np.integer)) for v in (start, end, step))
         dtype = "int64" if is_int else "float32"
-    return _mk(torch.arange(start, end, step, dtype=get_dtype(dtype).torch_dtype,
-                            device=as_torch_device(device)), requires_grad)
+    return _mk(K.arange(start, end, step, get_dtype(dtype).torch_dtype, as_torch_device(device)), requires_grad)
 
 
 def from_numpy(array, device=None, dtype=None, requires_grad=False):

@@ -791,7 +791,7 @@ class ScatterAddFunction(_ViewOp):
 class TopKFunction(_ViewOp):
     @staticmethod
     def forward(ctx, a, k, dim, largest, sorted_):
-        vals, idx = torch.topk(a, k, dim=dim, largest=largest, sorted=sorted_)
+        vals, idx = K.topk(a, k, dim, largest)
         ctx.save_for_backward(idx)
         ctx.meta = (dim, a.shape)
         return vals, idx
@@ -809,7 +809,7 @@ class RepeatInterleaveFunction(_ViewOp):
     @staticmethod
     def forward(ctx, a, repeats, dim):
         ctx.meta = (a.shape, repeats, dim)
-        return torch.repeat_interleave(a, repeats, dim=dim)
+        return K.repeat_interleave(a, repeats, dim)
 
     @staticmethod
     def backward(ctx, g):
@@ -1267,11 +1267,11 @@ def logsumexp(a, axis=None):
 
 
 def argmax(a, dim=None, keepdim=False):
-    return Tensor._wrap(torch.argmax(a._t, dim=dim, keepdim=keepdim))
+    return Tensor._wrap(K.argmax(a._t, dim, keepdim))
 
 
 def argmin(a, dim=None, keepdim=False):
-    return Tensor._wrap(torch.argmin(a._t, dim=dim, keepdim=keepdim))
+    return Tensor._wrap(K.argmax(a._t, dim, keepdim, is_min=True))
 
 
 def matmul(a, b):
@@ -1389,8 +1389,7 @@ def repeat_interleave(input, repeats, dim=None):
 
 
 def one_hot(indices, num_classes, dtype=None):
-    out = torch.nn.functional.one_hot(indices._t.long(), num_classes)
-    return Tensor._wrap(out.to(dtype.torch_dtype if dtype is not None else torch.float32))
+    return Tensor._wrap(K.one_hot(indices._t, num_classes, dtype.torch_dtype if dtype is not None else torch.float32))
 
 
 def embedding(weight, idx):

@@ -14,7 +14,7 @@ def _code(ctype):
     t = re.sub(r"\bconst\b", "", t).strip()
     t = " ".join(t.split()[:-1]) if len(t.split()) > 1 else t     # drop the parameter name
     return {"int": "i", "long long": "l", "float": "f", "unsigned long long": "u", "unsigned int": "I",
-            "size_t": "z", "ssize_t": "l", "int64_t": "l"}[t]
+            "size_t": "z", "ssize_t": "l", "int64_t": "l", "double": "d"}[t]
 
 
 def prototypes():

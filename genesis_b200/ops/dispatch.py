@@ -829,3 +829,113 @@ def grouped_wgrad(gy, x, offsets, num_groups, out_dtype=None):
     for g, s, e in _seg(offsets):
         dw[g] = gy[s:e].float().t() @ x[s:e].float()
     return dw.to(out_dtype or gy.dtype)
+
+
+# =============================== sort / select / index producers ================================
+def _last_dim_call(t, dim, fn):
+    """Runs `fn` on `t` with `dim` moved last (contiguous) and moves the result dims back."""
+    d = dim % t.dim() if t.dim() else 0
+    moved = t if d == t.dim() - 1 else t.movedim(d, -1)
+    out = fn(moved.contiguous())
+    if out is NotImplemented:
+        return out
+    if d == t.dim() - 1:
+        return out
+    return tuple(o.movedim(-1, d) for o in out) if isinstance(out, tuple) else out.movedim(-1, d)
+
+
+def sort(t, dim=-1, descending=False):
+    """Stable sort -> (values, int64 indices)."""
+    if _cuda(t) and t.dim() > 0:
+        out = _last_dim_call(t, dim, lambda x: N.sort_rows(x, x.shape[-1], descending))
+        if out is not NotImplemented:
+            return out
+    return tuple(torch.sort(t, dim=dim, descending=descending, stable=True))
+
+
+def topk(t, k, dim=-1, largest=True):
+    if _cuda(t) and t.dim() > 0:
+        out = _last_dim_call(t, dim, lambda x: N.sort_rows(x, k, largest))
+        if out is not NotImplemented:
+            return out
+    return tuple(torch.topk(t, k, dim=dim, largest=largest, sorted=True))
+
+
+def argmax(t, dim=None, keepdim=False, is_min=False):
+    if _cuda(t) and t.numel() > 0:
+        if dim is None:
+            out = N.argmax_rows(t.contiguous().reshape(-1), is_min)
+            if out is not NotImplemented:
+                return out.reshape([1] * t.dim()) if keepdim else out.reshape(())
+        else:
+            d = dim % t.dim()
+            moved = t if d == t.dim() - 1 else t.movedim(d, -1)
+            out = N.argmax_rows(moved.contiguous(), is_min)
+            if out is not NotImplemented:
+                return out.unsqueeze(d) if keepdim else out
+    fn = torch.argmin if is_min else torch.argmax
+    return fn(t, dim=dim, keepdim=keepdim)
+
+
+def bincount(idx, weights=None, minlength=0):
+    flat = idx.reshape(-1)
+    if _cuda(flat) and flat.numel() > 0 and flat.dtype in (torch.int32, torch.int64):
+        nbins = max(int(flat.max().item()) + 1, int(minlength))
+        w = None if weights is None else weights.reshape(-1)
+        if w is None or w.dtype == torch.float32:
+            out = N.bincount(flat.contiguous(), None if w is None else w.contiguous(), nbins)
+            if out is not NotImplemented:
+                return out
+    return torch.bincount(flat.long(), weights=None if weights is None else weights.reshape(-1), minlength=minlength)
+
+
+def nonzero(t):
+    """[count, ndim] int64 coordinates, row-major order."""
+    if _cuda(t) and t.numel() > 0:
+        flat = N.nonzero_flat(t.contiguous())
+        if flat is not NotImplemented:
+            if t.dim() <= 1:
+                return flat.reshape(-1, max(t.dim(), 0)) if t.dim() == 0 else flat.reshape(-1, 1)
+            coords = []
+            rem = flat
+            for size in reversed(t.shape):
+                coords.append(rem % size)
+                rem = torch.div(rem, size, rounding_mode="floor")
+            return torch.stack(coords[::-1], dim=1)
+    return torch.nonzero(t)
+
+
+def triu_tril(t, diag, upper):
+    if _cuda(t) and t.dim() >= 2:
+        out = N.triu_tril(t.contiguous(), diag, upper)
+        if out is not NotImplemented:
+            return out
+    return torch.triu(t, diagonal=diag) if upper else torch.tril(t, diagonal=diag)
+
+
+def one_hot(idx, classes, dtype=torch.int64):
+    if _cuda(idx):
+        out = N.one_hot(idx.contiguous(), classes, dtype)
+        if out is not NotImplemented:
+            return out
+    return torch.nn.functional.one_hot(idx.long(), classes).to(dtype)
+
+
+def arange(start, end, step, dtype, device):
+    dev = torch.device(device)
+    n = max(0, -(-(end - start) // step)) if all(isinstance(v, int) for v in (start, end, step)) \
+        else max(0, int(math.ceil((end - start) / step)))
+    if dev.type == "cuda" and N.available() and n > 0:
+        out = N.arange(start, step, n, dtype, dev)
+        if out is not NotImplemented:
+            return out
+    return torch.arange(start, end, step, dtype=dtype, device=dev)
+
+
+def repeat_interleave(t, repeats, dim=None):
+    if _cuda(t) and isinstance(repeats, int) and t.numel() > 0:
+        src, d = (t.reshape(-1), 0) if dim is None else (t, dim)
+        out = N.repeat_interleave(src.contiguous(), repeats, d)
+        if out is not NotImplemented:
+            return out
+    return torch.repeat_interleave(t, repeats, dim=dim)

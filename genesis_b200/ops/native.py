@@ -24,7 +24,7 @@ _CMP = {"eq": 0, "ne": 1, "lt": 2, "le": 3, "gt": 4, "ge": 5}
 _RED = {"sum": 0, "mean": 0, "max": 1, "min": 2}
 
 _C = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float,
-      "u": ctypes.c_ulonglong, "I": ctypes.c_uint, "z": ctypes.c_size_t}
+      "u": ctypes.c_ulonglong, "I": ctypes.c_uint, "z": ctypes.c_size_t, "d": ctypes.c_double}
 
 # name -> argument type codes (see _C); the trailing stream is a "p"
 _SIGS = {
@@ -47,6 +47,10 @@ _SIGS = {
     "gb_gemm": "pppp" + "iiii" + "ll" + "i" + "lll" + "ii" + "iii" + "i" + "f" + "i" + "p" + "i" + "ii" + "p" + "i" + "p",
     "gb_allreduce_fused": "ppllii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "pp",
     "gb_wait_flag": "pIupp",
+    "gb_sort_rows": "ppp" + "liiii" + "pp", "gb_argmax_rows": "pp" + "liii" + "p",
+    "gb_bincount": "pippli" + "p", "gb_nonzero_count": "ppli" + "p", "gb_nonzero_write": "pppli" + "p",
+    "gb_triu_tril": "ppl" + "iiiii" + "p", "gb_one_hot": "pip" + "lii" + "p", "gb_arange": "pl" + "dd" + "i" + "p",
+    "gb_repeat_interleave": "pp" + "lll" + "ii" + "p",
 }
 
 _L = None
@@ -1032,3 +1036,108 @@ def moe_combine(y, w, pos):
 def moe_combine_bwd(g, y, w, pos):
     from . import grouped
     return grouped.moe_combine_bwd(g, y, w, pos)
+
+
+# =============================== sort / select / index producers ================================
+_SORTABLE = (F32, F16, BF16, torch.int32)
+
+
+def sort_rows(x, k, descending):
+    """Stable sort along the last dim of a contiguous tensor; returns the first `k` (values, int64 indices)."""
+    if x.dtype not in _SORTABLE or not x.is_contiguous() or x.dim() < 1 or x.numel() == 0:
+        return NotImplemented
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if cols >= (1 << 30) or rows >= (1 << 31):
+        return NotImplemented
+    vals = torch.empty(x.shape[:-1] + (k,), dtype=x.dtype, device=x.device)
+    idx = torch.empty(x.shape[:-1] + (k,), dtype=torch.int64, device=x.device)
+    ws = None
+    if cols > 8192:
+        np2 = 1 << (cols - 1).bit_length()
+        ws = torch.empty(rows * np2, dtype=torch.int64, device=x.device)
+    _chk(lib().gb_sort_rows(x.data_ptr(), vals.data_ptr(), idx.data_ptr(), rows, cols, k, 1 if descending else 0,
+                            _DT[x.dtype], ws.data_ptr() if ws is not None else None, _st()), "sort_rows")
+    return vals, idx
+
+
+def argmax_rows(x, is_min=False):
+    if x.dtype not in _SORTABLE or not x.is_contiguous() or x.dim() < 1 or x.numel() == 0:
+        return NotImplemented
+    cols = x.shape[-1]
+    out = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    _chk(lib().gb_argmax_rows(x.data_ptr(), out.data_ptr(), x.numel() // cols, cols, 1 if is_min else 0,
+                              _DT[x.dtype], _st()), "argmax_rows")
+    return out
+
+
+def bincount(idx, weights, nbins):
+    if idx.dtype not in (torch.int32, torch.int64) or not idx.is_contiguous():
+        return NotImplemented
+    if weights is not None:
+        if weights.dtype != F32 or not weights.is_contiguous():
+            return NotImplemented
+        out = torch.zeros(nbins, dtype=F32, device=idx.device)
+    else:
+        out = torch.zeros(nbins, dtype=torch.int64, device=idx.device)
+    _chk(lib().gb_bincount(idx.data_ptr(), 1 if idx.dtype == torch.int64 else 0,
+                           weights.data_ptr() if weights is not None else None, out.data_ptr(), idx.numel(), nbins,
+                           _st()), "bincount")
+    return out
+
+
+def nonzero_flat(x):
+    """int64 flat indices of the nonzero elements of a contiguous tensor (one host read for the count)."""
+    if x.dtype not in _DT or x.dtype == torch.float64 or not x.is_contiguous():
+        return NotImplemented
+    n = x.numel()
+    nb = (n + 1023) // 1024
+    counts = torch.empty(nb + 1, dtype=torch.int32, device=x.device)
+    L = lib()
+    _chk(L.gb_nonzero_count(x.data_ptr(), counts.data_ptr(), n, _DT[x.dtype], _st()), "nonzero_count")
+    total = int(counts[nb].item())
+    out = torch.empty(total, dtype=torch.int64, device=x.device)
+    if total:
+        _chk(L.gb_nonzero_write(x.data_ptr(), counts.data_ptr(), out.data_ptr(), n, _DT[x.dtype], _st()), "nonzero_write")
+    return out
+
+
+def triu_tril(x, diag, upper):
+    if not x.is_contiguous() or x.dim() < 2 or x.element_size() not in (1, 2, 4, 8) or x.numel() == 0:
+        return NotImplemented
+    out = torch.empty_like(x)
+    _chk(lib().gb_triu_tril(x.data_ptr(), out.data_ptr(), x.numel(), x.shape[-2], x.shape[-1], int(diag),
+                            1 if upper else 0, x.element_size(), _st()), "triu_tril")
+    return out
+
+
+def one_hot(idx, classes, dtype):
+    if idx.dtype not in (torch.int32, torch.int64) or not idx.is_contiguous() or dtype not in _DT \
+            or dtype in (torch.float64, torch.uint8, torch.bool):
+        return NotImplemented
+    out = torch.empty(idx.shape + (classes,), dtype=dtype, device=idx.device)
+    _chk(lib().gb_one_hot(idx.data_ptr(), 1 if idx.dtype == torch.int64 else 0, out.data_ptr(), idx.numel(), classes,
+                          _DT[dtype], _st()), "one_hot")
+    return out
+
+
+def arange(start, step, n, dtype, device):
+    if dtype not in _DT or dtype in (torch.float64, torch.uint8, torch.bool):
+        return NotImplemented
+    out = torch.empty(n, dtype=dtype, device=device)
+    _chk(lib().gb_arange(out.data_ptr(), n, float(start), float(step), _DT[dtype], _st()), "arange")
+    return out
+
+
+def repeat_interleave(x, rep, dim):
+    if not x.is_contiguous() or x.element_size() not in (1, 2, 4, 8):
+        return NotImplemented
+    dim = dim % x.dim()
+    outer = math.prod(x.shape[:dim])
+    inner = math.prod(x.shape[dim + 1:])
+    shape = list(x.shape)
+    shape[dim] *= rep
+    out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    _chk(lib().gb_repeat_interleave(x.data_ptr(), out.data_ptr(), outer, x.shape[dim], inner, rep, x.element_size(),
+                                    _st()), "repeat_interleave")
+    return out
