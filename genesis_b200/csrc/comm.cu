@@ -12,58 +12,9 @@
 // Every wait is bounded (time budget); on expiry the kernel records {code, peer, phase, epoch} in
 // `status` and returns, leaving the context usable.
 // Reference counterpart: ncclAllReduce per parameter + a divide kernel, genesis/nn/parallel.py:108-117.
-#include "common.cuh"
-#include "sm100_ptx.cuh"
+#include "comm_common.cuh"
 
 namespace gb {
-
-constexpr int COMM_MAX_WORLD = 16;
-constexpr int COMM_MAX_CTAS = 64;
-// flag layout inside the symmetric flag page (uint32): [phase(2)][cta(64)][src rank(16)], then the overflow epoch
-constexpr int COMM_FLAG_WORDS = 2 * COMM_MAX_CTAS * COMM_MAX_WORLD;
-constexpr int COMM_FOUND_SLOT = COMM_FLAG_WORDS;
-
-struct PeerTable { void* ptr[COMM_MAX_WORLD]; };
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-
-// Signal every peer and wait for every peer on this CTA's channel of `phase`. Returns false on expiry.
-__device__ __forceinline__ bool peer_barrier(const PeerTable& flags, int rank, int world, int phase, uint32_t epoch,
-                                             unsigned long long budget_ns, int* status, int* s_fail) {
-  __syncthreads();
-  if (threadIdx.x < world) {
-    const int peer = threadIdx.x;
-    const int slot = (phase * COMM_MAX_CTAS + blockIdx.x) * COMM_MAX_WORLD;
-    __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(flags.ptr[peer]) + slot + rank, epoch);
-    const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.ptr[rank]) + slot + peer;
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > budget_ns) {
-        *s_fail = 1;
-        report_error(status, GB_ERR_FLAG_TIMEOUT, peer, phase);
-        if (status != nullptr) status[3] = (int)epoch;
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  return *s_fail == 0;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(512)
@@ -141,6 +92,103 @@ allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Pull-style data movement: all-gather, broadcast and all-to-all are the same kernel.  Every rank has
+// staged what it sends in its symmetric buffer and publishes, per destination rank, where that rank's
+// part starts and how long it is (two tables in its flag page).  After barrier A each rank reads the
+// entries addressed to it and copies the parts out of the peers' buffers into LOCAL memory with plain
+// peer loads; barrier B tells the owners that their buffers may be reused.
+// ------------------------------------------------------------------------------------------------
+constexpr int COMM_META_WORD = COMM_FLAG_WORDS + 64;     // uint32 index of the tables inside the flag page
+
+struct SendTable { long long off[COMM_MAX_WORLD]; long long len[COMM_MAX_WORLD]; };   // bytes, per destination
+struct RecvTable { long long off[COMM_MAX_WORLD]; };                                   // bytes, per source
+
+__device__ __forceinline__ long long ld_volatile_s64(const long long* p) {
+  long long v;
+  asm volatile("ld.volatile.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(512)
+peer_pull_kernel(PeerTable bufs, PeerTable flags, SendTable send, RecvTable recv, uint8_t* __restrict__ out,
+                 int rank, int world, uint32_t epoch, unsigned long long budget_ns, int* __restrict__ status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  // every CTA publishes the same tables before its own signal: whichever channel a peer waits on, the
+  // tables are visible once that channel's flag is
+  long long* my_meta = reinterpret_cast<long long*>(reinterpret_cast<uint32_t*>(flags.ptr[rank]) + COMM_META_WORD);
+  if (threadIdx.x < world) {
+    my_meta[threadIdx.x] = send.off[threadIdx.x];
+    my_meta[COMM_MAX_WORLD + threadIdx.x] = send.len[threadIdx.x];
+  }
+  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) return;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  for (int p = 0; p < world; ++p) {
+    const int src = (rank + p) % world;
+    const long long* meta = reinterpret_cast<const long long*>(reinterpret_cast<const uint32_t*>(flags.ptr[src]) + COMM_META_WORD);
+    const long long off = ld_volatile_s64(meta + rank);
+    const long long len = ld_volatile_s64(meta + COMM_MAX_WORLD + rank);
+    if (len <= 0) continue;
+    const uint8_t* from = reinterpret_cast<const uint8_t*>(bufs.ptr[src]) + off;
+    uint8_t* to = out + recv.off[src];
+    if (((reinterpret_cast<uintptr_t>(from) | reinterpret_cast<uintptr_t>(to) | (uintptr_t)len) & 15) == 0) {
+      const long long nv = len >> 4;
+      constexpr int UNR = 4;
+      for (long long i0 = tid; i0 < nv; i0 += nthreads * UNR) {
+        uint4 v[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u)
+          if (i0 + u * nthreads < nv) v[u] = ld_volatile_v4(from + ((i0 + u * nthreads) << 4));
+#pragma unroll
+        for (int u = 0; u < UNR; ++u)
+          if (i0 + u * nthreads < nv) *reinterpret_cast<uint4*>(to + ((i0 + u * nthreads) << 4)) = v[u];
+      }
+    } else {
+      for (long long i = tid; i < len; i += nthreads) to[i] = *reinterpret_cast<const volatile uint8_t*>(from + i);
+    }
+  }
+  peer_barrier(flags, rank, world, 1, epoch, budget_ns, status, &s_fail);
+}
+
+// Reduce-scatter: every rank staged world x n elements; rank r sums slice r of all peers into local `out`.
+template <typename T>
+__global__ void __launch_bounds__(512)
+peer_reduce_scatter_kernel(PeerTable bufs, PeerTable flags, T* __restrict__ out, long long n, int rank, int world,
+                           uint32_t epoch, float scale, unsigned long long budget_ns, int* __restrict__ status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) return;
+  constexpr int V = Vec16<T>::N;
+  const long long nvec = n / V;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    for (int p = 0; p < world; ++p) {
+      const int src = (rank + p) % world;
+      const uint4 raw = ld_volatile_v4(reinterpret_cast<const T*>(bufs.ptr[src]) + (long long)rank * n + i * V);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(e[j]);
+    }
+    Vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(acc[j] * scale);
+    st16(out + i * V, o);
+  }
+  peer_barrier(flags, rank, world, 1, epoch, budget_ns, status, &s_fail);
+}
+
+__global__ void peer_barrier_kernel(PeerTable flags, int rank, int world, uint32_t epoch,
+                                    unsigned long long budget_ns, int* __restrict__ status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail);
+}
+
 // A wait on a flag nobody sets: used to exercise the timeout path without any peer.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t expect, unsigned long long budget_ns, int* status) {
   const uint64_t t0 = globaltimer_ns();
@@ -198,5 +246,53 @@ extern "C" int gb_allreduce_fused(void* const* bufs, void* const* flags, long lo
 extern "C" int gb_wait_flag(const unsigned int* flag, unsigned int expect, unsigned long long budget_ns, int* status,
                             cudaStream_t st) {
   wait_flag_kernel<<<1, 1, 0, st>>>(flag, expect, budget_ns, status);
+  return (int)cudaGetLastError();
+}
+
+// ---- pull collectives ------------------------------------------------------------------------------
+// send_off / send_len: where in THIS rank's symmetric buffer the part for destination d starts and its length;
+// recv_off: where in `out` (local memory) the part coming from source s goes.  All in bytes.
+extern "C" int gb_peer_pull(void* const* bufs, void* const* flags, const long long* send_off,
+                            const long long* send_len, const long long* recv_off, void* out, int rank, int world,
+                            unsigned int epoch, int ctas, unsigned long long budget_ns, int* status,
+                            cudaStream_t st) {
+  if (world > COMM_MAX_WORLD || world < 1) return -2;
+  if (ctas > COMM_MAX_CTAS) ctas = COMM_MAX_CTAS;
+  if (ctas < 1) ctas = 1;
+  PeerTable tb, tf;
+  SendTable sd;
+  RecvTable rv;
+  for (int i = 0; i < world; ++i) {
+    tb.ptr[i] = bufs[i]; tf.ptr[i] = flags[i];
+    sd.off[i] = send_off[i]; sd.len[i] = send_len[i]; rv.off[i] = recv_off[i];
+  }
+  peer_pull_kernel<<<ctas, 512, 0, st>>>(tb, tf, sd, rv, reinterpret_cast<uint8_t*>(out), rank, world, epoch,
+                                         budget_ns, status);
+  return (int)cudaGetLastError();
+}
+
+// out[n] = scale * sum over ranks of (their buffer)[rank * n .. rank * n + n); n a multiple of 16 bytes.
+extern "C" int gb_peer_reduce_scatter(void* const* bufs, void* const* flags, void* out, long long n, int rank,
+                                      int world, unsigned int epoch, float scale, int dt, int ctas,
+                                      unsigned long long budget_ns, int* status, cudaStream_t st) {
+  if (world > COMM_MAX_WORLD || world < 1) return -2;
+  if (ctas > COMM_MAX_CTAS) ctas = COMM_MAX_CTAS;
+  if (ctas < 1) ctas = 1;
+  PeerTable tb, tf;
+  for (int i = 0; i < world; ++i) { tb.ptr[i] = bufs[i]; tf.ptr[i] = flags[i]; }
+  GB_DISPATCH_FLOAT(dt, T, {
+    if (n % Vec16<T>::N != 0) return -3;
+    peer_reduce_scatter_kernel<T><<<ctas, 512, 0, st>>>(tb, tf, reinterpret_cast<T*>(out), n, rank, world, epoch,
+                                                        scale, budget_ns, status);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_peer_barrier(void* const* flags, int rank, int world, unsigned int epoch,
+                               unsigned long long budget_ns, int* status, cudaStream_t st) {
+  if (world > COMM_MAX_WORLD || world < 1) return -2;
+  PeerTable tf;
+  for (int i = 0; i < world; ++i) tf.ptr[i] = flags[i];
+  peer_barrier_kernel<<<1, 32, 0, st>>>(tf, rank, world, epoch, budget_ns, status);
   return (int)cudaGetLastError();
 }

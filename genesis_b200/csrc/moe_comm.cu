@@ -1,0 +1,254 @@
+// Expert-parallel dispatch and combine over peer memory (NVLink / NVSwitch): the all-to-alls of a
+// mixture-of-experts layer as PULL kernels.  Nothing is packed or sent: the owner of an expert reads the
+// token rows it needs straight out of the source ranks' activation buffers (plain peer loads), and the source
+// rank later reads the expert outputs straight out of the owners' output buffers while it forms the weighted
+// sum over the k slots.  No NCCL call, no host synchronisation, every wait bounded.
+//
+// Symmetric (peer-mapped) buffers per rank: x (token rows), tok (token index of every sorted (token, slot)
+// pair, sorted by global expert id), ws (routing weight of every sorted pair), y (rows in the owner's
+// receive layout) and a float-per-row buffer for the routing-weight gradient.
+//
+// Receive layout of rank r: expert-major over its local experts, inside an expert source-rank-minor, every
+// expert segment padded to a multiple of `align` rows (one GEMM tile), so the grouped GEMMs run on it as is.
+//
+//   ep_layout          (local)  all ranks' per-expert offsets -> segment table, padded expert offsets,
+//                               and for every global expert the row where THIS rank's rows start at its owner
+//   ep_dispatch_pull   barrier, then row (e, p, i) <- x_p[tok_p[off_p[e] + i]]           (forward)
+//                      or      row <- ws_p[..] * g_p[tok_p[..]],  dwr[row] = <g_p[..], y[row]>  (backward of combine)
+//   ep_combine_pull    barrier, then out[t] = sum_j w[t, j] * y_d[row(t, j)]                (forward)
+//                      or      dx[t] = sum_j dxe_d[row(t, j)],   dw[t, j] = dwr_d[row(t, j)] (backward of dispatch)
+//
+// Reference counterpart: none (the reference loops over all experts on one GPU,
+// genesis/models/transformers/moe.py:317-361).
+#include "comm_common.cuh"
+
+namespace gb {
+
+constexpr int EP_MAX_SEGS = 4096;      // local experts x world, held in shared memory for the row search
+
+// all_off [W][E + 1]: offsets of every rank's pair list sorted by global expert.
+__global__ void ep_layout_kernel(const int* __restrict__ all_off, int rank, int world, int E, int align,
+                                 int capacity, int* __restrict__ local_offsets, int* __restrict__ seg_start,
+                                 int* __restrict__ seg_src_off, int* __restrict__ dest_base, int* __restrict__ info,
+                                 int* __restrict__ status) {
+  const int El = E / world;
+  extern __shared__ int sm[];
+  int* padded = sm;                      // [world][El + 1] padded expert offsets of every rank's layout
+  // one thread per destination rank computes that rank's padded expert offsets (El <= a few hundred)
+  for (int d = threadIdx.x; d < world; d += blockDim.x) {
+    int pos = 0;
+    for (int e = 0; e < El; ++e) {
+      padded[d * (El + 1) + e] = pos;
+      int cnt = 0;
+      const int g = d * El + e;
+      for (int p = 0; p < world; ++p) cnt += all_off[p * (E + 1) + g + 1] - all_off[p * (E + 1) + g];
+      pos += (cnt + align - 1) / align * align;
+    }
+    padded[d * (El + 1) + El] = pos;
+  }
+  __syncthreads();
+  // rows of rank `rank` for global expert g start, in the owner's layout, after the rows of lower ranks
+  for (int g = threadIdx.x; g < E; g += blockDim.x) {
+    const int d = g / El, e = g % El;
+    int before = 0;
+    for (int p = 0; p < rank; ++p) before += all_off[p * (E + 1) + g + 1] - all_off[p * (E + 1) + g];
+    dest_base[g] = padded[d * (El + 1) + e] + before;
+  }
+  // my own receive layout
+  for (int e = threadIdx.x; e <= El; e += blockDim.x) local_offsets[e] = padded[rank * (El + 1) + e];
+  for (int s = threadIdx.x; s < El * world; s += blockDim.x) {
+    const int e = s / world, p = s % world;
+    const int g = rank * El + e;
+    int before = 0;
+    for (int q = 0; q < p; ++q) before += all_off[q * (E + 1) + g + 1] - all_off[q * (E + 1) + g];
+    seg_start[s] = padded[rank * (El + 1) + e] + before;
+    seg_src_off[s] = all_off[p * (E + 1) + g];
+  }
+  if (threadIdx.x == 0) {
+    const int total = padded[rank * (El + 1) + El];
+    info[0] = total;
+    if (total > capacity) report_error(status, GB_ERR_BAD_ARG, 900, total);
+  }
+}
+
+// seg_cnt is implied: rows of segment s = off_p[g + 1] - off_p[g], read from all_off.
+template <typename T>
+__global__ void __launch_bounds__(512)
+ep_dispatch_pull_kernel(PeerTable xs, PeerTable toks, PeerTable wss, PeerTable flags, const int* __restrict__ all_off,
+                        const int* __restrict__ local_offsets, const int* __restrict__ seg_start,
+                        const int* __restrict__ seg_src_off, T* __restrict__ out, const T* __restrict__ y_rows,
+                        float* __restrict__ dwr, int H, int rank, int world, int E, int capacity, int mode,
+                        uint32_t epoch, unsigned long long budget_ns, int* __restrict__ status) {
+  __shared__ int s_fail;
+  __shared__ int s_start[EP_MAX_SEGS + 1];
+  if (threadIdx.x == 0) s_fail = 0;
+  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) return;
+  const int El = E / world;
+  const int nseg = El * world;
+  for (int s = threadIdx.x; s < nseg; s += blockDim.x) s_start[s] = seg_start[s];
+  int total = local_offsets[El];
+  if (total > capacity) total = capacity;
+  if (threadIdx.x == 0) s_start[nseg] = total;
+  __syncthreads();
+  constexpr int V = Vec16<T>::N;
+  const int nvec = H / V;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = warp; row < total; row += nwarps) {
+    // last segment whose start is <= row
+    int lo = 0, hi = nseg;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (s_start[mid] <= row) lo = mid; else hi = mid; }
+    // segments of zero rows share a start with their successor: take the last one at this start
+    const int s = lo;
+    const int e = s / world, p = s % world;
+    const int g = rank * El + e;
+    const int cnt = all_off[p * (E + 1) + g + 1] - all_off[p * (E + 1) + g];
+    const int i = row - s_start[s];
+    T* dst = out + (size_t)row * H;
+    if (i >= cnt) {
+      // padding between the end of an expert's rows and the next expert
+      for (int v = lane; v < nvec; v += 32) { Vec16<T> z; for (int j = 0; j < V; ++j) z.v[j] = Cvt<T>::from_f(0.f); st16(dst + v * V, z); }
+      if (mode == 1 && lane == 0) dwr[row] = 0.f;
+      continue;
+    }
+    const int sp = seg_src_off[s] + i;                                   // position in p's sorted pair list
+    const int t = *reinterpret_cast<const volatile int*>(reinterpret_cast<const int*>(toks.ptr[p]) + sp);
+    const T* src = reinterpret_cast<const T*>(xs.ptr[p]) + (size_t)t * H;
+    if (mode == 0) {
+      for (int v0 = lane; v0 < nvec; v0 += 128) {
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (v0 + u * 32 < nvec) r[u] = ld_volatile_v4(src + (v0 + u * 32) * V);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (v0 + u * 32 < nvec) *reinterpret_cast<uint4*>(dst + (v0 + u * 32) * V) = r[u];
+      }
+    } else {
+      const float wgt = *reinterpret_cast<const volatile float*>(reinterpret_cast<const float*>(wss.ptr[p]) + sp);
+      const T* yr = y_rows + (size_t)row * H;
+      float dot = 0.f;
+      for (int v = lane; v < nvec; v += 32) {
+        const uint4 raw = ld_volatile_v4(src + v * V);
+        const T* ge = reinterpret_cast<const T*>(&raw);
+        const Vec16<T> yv = ld16(yr + v * V);
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float gj = Cvt<T>::to_f(ge[j]);
+          dot += gj * Cvt<T>::to_f(yv.v[j]);
+          o.v[j] = Cvt<T>::from_f(gj * wgt);
+        }
+        st16(dst + v * V, o);
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) dwr[row] = dot;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+ep_combine_pull_kernel(PeerTable ys, PeerTable dwrs, PeerTable flags, const int* __restrict__ idx,
+                       const int* __restrict__ pos, const float* __restrict__ w, const int* __restrict__ my_off,
+                       const int* __restrict__ dest_base, T* __restrict__ out, float* __restrict__ dw, int T_tokens,
+                       int k, int H, int rank, int world, int E, int capacity, int mode, uint32_t epoch,
+                       unsigned long long budget_ns, int* __restrict__ status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) return;
+  const int El = E / world;
+  constexpr int V = Vec16<T>::N;
+  const int nvec = H / V;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = warp; t < T_tokens; t += nwarps) {
+    for (int v0 = lane; v0 < nvec; v0 += 32) {
+      float acc[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        const int g = idx[t * k + j];
+        const int d = g / El;
+        const int row = dest_base[g] + pos[t * k + j] - my_off[g];
+        if (row >= capacity) continue;                 // the owner's layout overflowed (reported by ep_layout there)
+        const float wt = mode == 0 ? w[t * k + j] : 1.f;
+        const uint4 raw = ld_volatile_v4(reinterpret_cast<const T*>(ys.ptr[d]) + (size_t)row * H + v0 * V);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int q = 0; q < V; ++q) acc[q] += wt * Cvt<T>::to_f(e[q]);
+      }
+      Vec16<T> o;
+#pragma unroll
+      for (int q = 0; q < V; ++q) o.v[q] = Cvt<T>::from_f(acc[q]);
+      st16(out + (size_t)t * H + v0 * V, o);
+    }
+    if (mode == 1 && lane < k) {
+      const int g = idx[t * k + lane];
+      const int row = dest_base[g] + pos[t * k + lane] - my_off[g];
+      dw[t * k + lane] = row >= capacity ? 0.f : *reinterpret_cast<const volatile float*>(reinterpret_cast<const float*>(dwrs.ptr[g / El]) + row);
+    }
+  }
+}
+
+static void fill_table(PeerTable& t, void* const* ptrs, int world) {
+  for (int i = 0; i < COMM_MAX_WORLD; ++i) t.ptr[i] = (ptrs != nullptr && i < world) ? ptrs[i] : nullptr;
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+// all_off: int32 [world][E + 1] (every rank's offsets, gathered).  Outputs: local_offsets [E / world + 1],
+// seg_start / seg_src_off [E / world * world], dest_base [E], info [1] = rows of this rank's receive layout.
+extern "C" int gb_ep_layout(const int* all_off, int rank, int world, int E, int align, int capacity,
+                            int* local_offsets, int* seg_start, int* seg_src_off, int* dest_base, int* info,
+                            int* status, cudaStream_t st) {
+  if (world < 1 || world > COMM_MAX_WORLD || E % world != 0 || (E / world) * world > EP_MAX_SEGS) return -2;
+  const size_t smem = (size_t)world * (E / world + 1) * sizeof(int);
+  ep_layout_kernel<<<1, 256, smem, st>>>(all_off, rank, world, E, align, capacity, local_offsets, seg_start,
+                                         seg_src_off, dest_base, info, status);
+  return (int)cudaGetLastError();
+}
+
+// mode 0: out[row] = x_p[tok_p[..]];  mode 1: out[row] = ws_p[..] * x_p[tok_p[..]], dwr[row] = <x_p[..], y_rows[row]>.
+extern "C" int gb_ep_dispatch_pull(void* const* xs, void* const* toks, void* const* wss, void* const* flags,
+                                   const int* all_off, const int* local_offsets, const int* seg_start,
+                                   const int* seg_src_off, void* out, const void* y_rows, float* dwr, int H,
+                                   int rank, int world, int E, int capacity, int mode, unsigned int epoch, int dt,
+                                   int ctas, unsigned long long budget_ns, int* status, cudaStream_t st) {
+  if (world < 1 || world > COMM_MAX_WORLD || E % world != 0 || (E / world) * world > EP_MAX_SEGS) return -2;
+  if (dt != DT_BF16 && dt != DT_F16 && dt != DT_F32) return -2;
+  if (ctas > COMM_MAX_CTAS) ctas = COMM_MAX_CTAS;
+  if (ctas < 1) ctas = 1;
+  PeerTable tx, tt, tw, tf;
+  fill_table(tx, xs, world); fill_table(tt, toks, world); fill_table(tw, wss, world); fill_table(tf, flags, world);
+  GB_DISPATCH_FLOAT(dt, T, {
+    if (H % Vec16<T>::N != 0) return -3;
+    ep_dispatch_pull_kernel<T><<<ctas, 512, 0, st>>>(tx, tt, tw, tf, all_off, local_offsets, seg_start, seg_src_off,
+                                                     reinterpret_cast<T*>(out), reinterpret_cast<const T*>(y_rows),
+                                                     dwr, H, rank, world, E, capacity, mode, epoch, budget_ns, status);
+  });
+  return (int)cudaGetLastError();
+}
+
+// mode 0: out[t] = sum_j w[t, j] * y_d[row(t, j)];  mode 1: out[t] = sum_j y_d[row(t, j)], dw[t, j] = dwr_d[row(t, j)].
+extern "C" int gb_ep_combine_pull(void* const* ys, void* const* dwrs, void* const* flags, const int* idx,
+                                  const int* pos, const float* w, const int* my_off, const int* dest_base, void* out,
+                                  float* dw, int tokens, int k, int H, int rank, int world, int E, int capacity,
+                                  int mode, unsigned int epoch, int dt, int ctas, unsigned long long budget_ns, int* status,
+                                  cudaStream_t st) {
+  if (world < 1 || world > COMM_MAX_WORLD || E % world != 0 || k > 32) return -2;
+  if (dt != DT_BF16 && dt != DT_F16 && dt != DT_F32) return -2;
+  if (ctas > COMM_MAX_CTAS) ctas = COMM_MAX_CTAS;
+  if (ctas < 1) ctas = 1;
+  PeerTable ty, td, tf;
+  fill_table(ty, ys, world); fill_table(td, dwrs, world); fill_table(tf, flags, world);
+  GB_DISPATCH_FLOAT(dt, T, {
+    if (H % Vec16<T>::N != 0) return -3;
+    ep_combine_pull_kernel<T><<<ctas, 512, 0, st>>>(ty, td, tf, idx, pos, w, my_off, dest_base,
+                                                    reinterpret_cast<T*>(out), dw, tokens, k, H, rank, world, E, capacity,
+                                                    mode, epoch, budget_ns, status);
+  });
+  return (int)cudaGetLastError();
+}

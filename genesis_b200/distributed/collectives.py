@@ -72,7 +72,12 @@ def broadcast(tensor, src=0, async_op=False):
     pg._check()
     if pg._world_size == 1:
         return None
-    _wrap_errors(tdist.broadcast, _raw(tensor), src=src)
+    t = _raw(tensor)
+    if t.is_cuda and comm_mode() == "p2p":
+        from . import symm
+        if symm.broadcast_(t, src):
+            return None
+    _wrap_errors(tdist.broadcast, t, src=src)
     return None
 
 
@@ -83,6 +88,10 @@ def all_gather(tensor_list, tensor, async_op=False):
     if pg._world_size == 1:
         _raw(tensor_list[0]).copy_(t)
         return None
+    if t.is_cuda and comm_mode() == "p2p":
+        from . import symm
+        if symm.all_gather_([_raw(x) for x in tensor_list], t.contiguous()):
+            return None
     _wrap_errors(tdist.all_gather, [_raw(x) for x in tensor_list], t.contiguous())
     return None
 
@@ -95,6 +104,10 @@ def reduce_scatter(output, input_list, op=ReduceOp.SUM, async_op=False):
         out.copy_(_raw(input_list[0]))
         return None
     ins = [_raw(x).contiguous() for x in input_list]
+    if out.is_cuda and op is ReduceOp.SUM and comm_mode() == "p2p":
+        from . import symm
+        if symm.reduce_scatter_(out, ins):
+            return None
     if pg._backend == "gloo":
         # gloo has no reduce_scatter: reduce the concatenation and keep our slice
         flat = torch.stack(ins)
@@ -125,6 +138,13 @@ def all_to_all_single(output, input, output_split_sizes=None, input_split_sizes=
         for q in reqs:
             q.wait()
     else:
+        if out.is_cuda and comm_mode() == "p2p" and inp.dim() >= 1:
+            from . import symm
+            W = pg._world_size
+            ins = list(input_split_sizes) if input_split_sizes is not None else [inp.shape[0] // W] * W
+            outs = list(output_split_sizes) if output_split_sizes is not None else [out.shape[0] // W] * W
+            if symm.all_to_all_(out, inp.contiguous(), outs, ins):
+                return None
         _wrap_errors(tdist.all_to_all_single, out, inp, output_split_sizes, input_split_sizes)
     return None
 
@@ -133,4 +153,8 @@ def barrier():
     pg._check()
     if pg._world_size == 1:
         return
+    if comm_mode() == "p2p" and pg._backend == "nccl":
+        from . import symm
+        if symm.barrier_():
+            return
     _wrap_errors(tdist.barrier)

@@ -183,3 +183,117 @@ def all_reduce_(t, scale=None):
                       prescale=1.0 if scale is None else scale)
     t.reshape(-1).copy_(stage)
     return True
+
+
+def _staging(nbytes):
+    st = state()
+    cap = int(os.environ.get("GENESIS_SYMM_STAGING_MB", 64)) * 1024 * 1024
+    if st.staging is None:
+        st.staging = st.alloc(cap)
+    return st if nbytes <= cap else None
+
+
+def _stage(st, tensors):
+    """Copies contiguous tensors back to back (16-byte aligned starts) into the staging buffer; returns
+    their byte offsets."""
+    offs, pos = [], 0
+    for t in tensors:
+        nb = t.numel() * t.element_size()
+        if nb:
+            st.staging.bytes[pos:pos + nb].copy_(t.reshape(-1).view(torch.uint8))
+        offs.append(pos)
+        pos += (nb + 15) // 16 * 16
+    return offs
+
+
+def all_gather_(outs, t):
+    """outs[r] <- rank r's `t` (same shape on every rank), through peer loads.  False: not available."""
+    if not available() or not t.is_cuda or not t.is_contiguous():
+        return False
+    nb = t.numel() * t.element_size()
+    st = _staging(nb)
+    if st is None or any((not o.is_contiguous()) or o.numel() * o.element_size() != nb for o in outs):
+        return False
+    from ..ops import native as N
+    _stage(st, [t])
+    W = st.world
+    flat = torch.empty(W * nb, dtype=torch.uint8, device=t.device)
+    N.peer_pull(st, st.staging, [0] * W, [nb] * W, [r * nb for r in range(W)], flat)
+    for r, o in enumerate(outs):
+        o.reshape(-1).view(torch.uint8).copy_(flat[r * nb:(r + 1) * nb])
+    return True
+
+
+def broadcast_(t, src):
+    if not available() or not t.is_cuda or not t.is_contiguous():
+        return False
+    nb = t.numel() * t.element_size()
+    st = _staging(nb)
+    if st is None:
+        return False
+    from ..ops import native as N
+    W = st.world
+    if st.rank == src:
+        _stage(st, [t])
+    send_len = [nb if (st.rank == src and d != src) else 0 for d in range(W)]
+    N.peer_pull(st, st.staging, [0] * W, send_len, [0] * W, t)
+    return True
+
+
+def reduce_scatter_(out, ins):
+    """out <- sum over ranks of their ins[my rank] (float tensors of equal size)."""
+    if not available() or not out.is_cuda or not out.is_contiguous() or out.dtype not in (
+            torch.float32, torch.float16, torch.bfloat16):
+        return False
+    n = out.numel()
+    vec = 16 // out.element_size()
+    n_pad = (n + vec - 1) // vec * vec
+    W = state().world
+    st = _staging(W * n_pad * out.element_size())
+    if st is None or len(ins) != W or any(i.numel() != n or i.dtype != out.dtype for i in ins):
+        return False
+    from ..ops import native as N
+    stage = st.staging.view(out.dtype, 0, W * n_pad).view(W, n_pad)
+    for r, i in enumerate(ins):
+        stage[r, :n].copy_(i.reshape(-1))
+    res = out if n_pad == n else torch.empty(n_pad, dtype=out.dtype, device=out.device)
+    N.peer_reduce_scatter(st, st.staging, res, n_pad)
+    if res is not out:
+        out.reshape(-1).copy_(res[:n])
+    return True
+
+
+def all_to_all_(out, inp, out_rows, in_rows):
+    """Row-wise all-to-all of 2-D (or 1-D) contiguous tensors: `in_rows[d]` rows go to rank d, `out_rows[s]`
+    rows arrive from rank s."""
+    if not available() or not inp.is_cuda or not inp.is_contiguous() or not out.is_contiguous():
+        return False
+    row_b = (inp.numel() // inp.shape[0] if inp.shape[0] else 0) * inp.element_size()
+    if inp.shape[0] == 0:
+        row_b = (out.numel() // out.shape[0] if out.shape[0] else 0) * out.element_size()
+    st = _staging(inp.numel() * inp.element_size())
+    if st is None:
+        # sizes differ between ranks here, so a silent fallback on one rank only would leave the others waiting
+        raise RuntimeError("all-to-all send larger than the symmetric staging buffer: raise GENESIS_SYMM_STAGING_MB "
+                           "(same value on every rank) or set GENESIS_COMM=nccl")
+    from ..ops import native as N
+    _stage(st, [inp])
+    W = st.world
+    send_off, pos = [], 0
+    for d in range(W):
+        send_off.append(pos * row_b)
+        pos += in_rows[d]
+    recv_off, pos = [], 0
+    for s_ in range(W):
+        recv_off.append(pos * row_b)
+        pos += out_rows[s_]
+    N.peer_pull(st, st.staging, send_off, [r * row_b for r in in_rows], recv_off, out)
+    return True
+
+
+def barrier_():
+    if not available():
+        return False
+    from ..ops import native as N
+    N.peer_barrier(state())
+    return True

@@ -714,6 +714,10 @@ def moe_sort(experts, num_experts, align=1):
 
 def moe_sort_unpadded(experts, num_experts):
     """Dense (unpadded) expert sort, used where rows travel between ranks before they are grouped."""
+    if experts.is_cuda:
+        r = N.moe_sort(experts, num_experts, 0)
+        if r is not NotImplemented:
+            return r
     return _moe_sort_torch(experts, num_experts, 1)
 
 

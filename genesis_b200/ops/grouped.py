@@ -18,20 +18,21 @@ def _i32(t):
 
 def moe_sort(experts, num_experts, align):
     """experts [T, k] int32 on CUDA -> (token_of [Mp] int32 with -1 in pad rows, pos [T, k] int32,
-    offsets [E+1] int32), segments padded to `ALIGN` rows."""
+    offsets [E+1] int32), segments padded to `ALIGN` rows (`align` == 0: dense, no padding)."""
     if experts.dtype != torch.int32 or not experts.is_contiguous() or num_experts > 1024:
         return NotImplemented
     T, k = experts.shape
     pairs = T * k
     dev = experts.device
-    max_rows = (pairs + num_experts * (ALIGN - 1) + ALIGN - 1) // ALIGN * ALIGN
+    align = 1 if align == 0 else ALIGN          # 0: dense; anything else: one GEMM tile
+    max_rows = (pairs + num_experts * (align - 1) + align - 1) // align * align
     counts = _counts(experts, num_experts)
     offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
     cursor = torch.empty(num_experts, dtype=torch.int32, device=dev)
     pos = torch.empty(T, k, dtype=torch.int32, device=dev)
     token_of = torch.empty(max_rows, dtype=torch.int32, device=dev)
     N._chk(N.lib().gb_moe_sort(experts.data_ptr(), counts.data_ptr(), offsets.data_ptr(), cursor.data_ptr(),
-                               pos.data_ptr(), token_of.data_ptr(), pairs, k, num_experts, ALIGN, max_rows, N._st()),
+                               pos.data_ptr(), token_of.data_ptr(), pairs, k, num_experts, align, max_rows, N._st()),
            "moe_sort")
     return token_of, pos, offsets
 

@@ -47,6 +47,12 @@ _SIGS = {
     "gb_gemm": "pppp" + "iiii" + "ll" + "i" + "lll" + "ii" + "iii" + "i" + "f" + "i" + "p" + "i" + "ii" + "p" + "i" + "p",
     "gb_allreduce_fused": "ppllii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "pp",
     "gb_wait_flag": "pIupp",
+    "gb_peer_pull": "pppppp" + "ii" + "I" + "i" + "u" + "pp",
+    "gb_peer_reduce_scatter": "ppp" + "lii" + "I" + "f" + "ii" + "u" + "pp",
+    "gb_peer_barrier": "p" + "ii" + "I" + "u" + "pp",
+    "gb_ep_layout": "p" + "iiiii" + "pppppp" + "p",
+    "gb_ep_dispatch_pull": "pppp" + "pppp" + "ppp" + "iiiiii" + "I" + "ii" + "u" + "pp",
+    "gb_ep_combine_pull": "ppp" + "ppppp" + "pp" + "iiiiiiii" + "I" + "ii" + "u" + "pp",
     "gb_sort_rows": "ppp" + "liiii" + "pp", "gb_argmax_rows": "pp" + "liii" + "p",
     "gb_bincount": "pippli" + "p", "gb_nonzero_count": "ppli" + "p", "gb_nonzero_write": "pppli" + "p",
     "gb_triu_tril": "ppl" + "iiiii" + "p", "gb_one_hot": "pip" + "lii" + "p", "gb_arange": "pl" + "dd" + "i" + "p",
@@ -991,6 +997,35 @@ def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None,
                                   None if found_inf is None else found_inf.data_ptr(), _DT[dtype], ctas, budget,
                                   st.status.data_ptr(), _st()), "allreduce_fused")
     return True
+
+
+def _comm_budget():
+    return int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000)) * 1e6)
+
+
+def peer_pull(st, buf, send_off, send_len, recv_off, out, ctas=32):
+    """All-gather / broadcast / all-to-all over peer memory (see csrc/comm.cu).  `send_off` / `send_len`:
+    bytes of this rank's staged part for each destination; `recv_off`: byte offset in `out` for each source.
+    `ctas` must be the same on every rank."""
+    from ..distributed import symm
+    W = st.world
+    arr = ctypes.c_longlong * W
+    _chk(lib().gb_peer_pull(buf.ptr_table, st.flags.ptr_table, arr(*send_off), arr(*send_len), arr(*recv_off),
+                            out.data_ptr(), st.rank, W, symm.next_epoch(), ctas, _comm_budget(),
+                            st.status.data_ptr(), _st()), "peer_pull")
+
+
+def peer_reduce_scatter(st, buf, out, n, scale=1.0, ctas=32):
+    from ..distributed import symm
+    _chk(lib().gb_peer_reduce_scatter(buf.ptr_table, st.flags.ptr_table, out.data_ptr(), n, st.rank, st.world,
+                                      symm.next_epoch(), float(scale), _DT[out.dtype], ctas, _comm_budget(),
+                                      st.status.data_ptr(), _st()), "peer_reduce_scatter")
+
+
+def peer_barrier(st):
+    from ..distributed import symm
+    _chk(lib().gb_peer_barrier(st.flags.ptr_table, st.rank, st.world, symm.next_epoch(), _comm_budget(),
+                               st.status.data_ptr(), _st()), "peer_barrier")
 
 
 if torch.cuda.is_available():

@@ -13,9 +13,10 @@ The reference has no expert parallelism at all (its MoE loops over every expert 
 
 Backward mirrors it through the same two all-to-alls in reverse.  Two transports implement
 the row exchange: the communicator's `all_to_all_single` (NCCL / gloo; needs the split sizes
-on the host), and on CUDA the peer-memory kernels of `csrc/moe_comm.cu`, which write rows
-straight into the owner's receive buffer over NVLink from inside the dispatch kernel and need
-no host synchronisation.  Expert parameters are marked `_no_ddp` so `DistributedDataParallel`
+on the host), and on CUDA (`GENESIS_COMM=p2p`, the default) the peer-memory kernels of
+`csrc/moe_comm.cu`: the owner of an expert pulls the rows it needs straight out of the source
+ranks' activation buffers over NVLink, and the source rank pulls the expert outputs back while it
+forms the weighted sum, with no host synchronisation anywhere in the layer.  Expert parameters are marked `_no_ddp` so `DistributedDataParallel`
 does not all-reduce them; it scales their gradients by 1/world instead (every rank's loss is a
 local mean and the experts see tokens of all ranks).
 """
@@ -86,9 +87,184 @@ def mark_expert_parameters(model):
     return n
 
 
+# ---------------------------------------------------------------------------------------------
+# peer-memory transport
+# ---------------------------------------------------------------------------------------------
+class _Workspace:
+    """Symmetric buffers of the pull kernels, allocated collectively on first use and regrown (on every rank at
+    once: shapes are the same everywhere) when a larger layer shows up."""
+
+    def __init__(self):
+        self.key = None
+
+    def ensure(self, T, k, H, cap, dtype):
+        from ..distributed import symm
+        es = torch.empty(0, dtype=dtype).element_size()
+        key = (T, k, H, cap, es)
+        if self.key is not None and all(a <= b for a, b in zip(key, self.key)):
+            return
+        self.key = key
+        self.x = symm.alloc(T * H * es)          # forward: token rows
+        self.g = symm.alloc(T * H * es)          # backward: gradient of the layer output
+        self.tok = symm.alloc(T * k * 4)
+        self.ws = symm.alloc(T * k * 4)
+        self.y = symm.alloc(cap * H * es)        # forward: expert outputs in the owner's layout
+        self.dx = symm.alloc(cap * H * es)       # backward: gradient of the received rows
+        self.dwr = symm.alloc(cap * 4)
+
+
+_ws = _Workspace()
+p2p_layers_run = 0      # forward passes that took the peer-memory transport (tests assert on it)
+
+
+def _p2p_usable(x):
+    from ..distributed import symm
+    return x.is_cuda and C.comm_mode() == "p2p" and symm.available() and x.dtype in (
+        torch.bfloat16, torch.float16, torch.float32)
+
+
+class EPDispatchPull(Function):
+    """xe[row] = x_p[token] for every (token, slot) pair routed to a local expert, pulled over peer memory into the
+    padded expert-major layout.  `w` rides along so that its gradient, which the owners of the experts compute,
+    can be returned here."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, x, w, idx, shared):
+        from ..distributed import symm
+        from ..ops import native as N
+        from ..ops import grouped
+        st = symm.state()
+        W, E, El = shared["W"], shared["E"], shared["El"]
+        T, k = idx.shape
+        H = x.shape[1]
+        dev = x.device
+        cap = shared["cap"]
+        _ws.ensure(T, k, H, cap, x.dtype)
+        token_of, pos, offsets = K.moe_sort_unpadded(idx, E)      # int32: sorted by global expert = by owner
+        token_of = token_of.to(torch.int32)
+        pos = pos.to(torch.int32).contiguous()
+        offsets = offsets.to(torch.int32).contiguous()
+        _ws.x.view(x.dtype, 0, T * H).copy_(x.reshape(-1))
+        _ws.tok.view(torch.int32, 0, T * k).copy_(token_of.reshape(-1))
+        all_off = [torch.empty(E + 1, dtype=torch.int32, device=dev) for _ in range(W)]
+        if not symm.all_gather_(all_off, offsets):
+            raise RuntimeError("peer-memory all-gather unavailable")
+        all_off = torch.stack(all_off).contiguous()
+        local_offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+        seg_start = torch.empty(El * W, dtype=torch.int32, device=dev)
+        seg_src = torch.empty(El * W, dtype=torch.int32, device=dev)
+        dest_base = torch.empty(E, dtype=torch.int32, device=dev)
+        info = torch.zeros(2, dtype=torch.int32, device=dev)
+        L = N.lib()
+        N._chk(L.gb_ep_layout(all_off.data_ptr(), st.rank, W, E, grouped.ALIGN, cap, local_offsets.data_ptr(),
+                              seg_start.data_ptr(), seg_src.data_ptr(), dest_base.data_ptr(), info.data_ptr(),
+                              st.status.data_ptr(), N._st()), "ep_layout")
+        xe = torch.zeros(cap, H, dtype=x.dtype, device=dev)
+        N._chk(L.gb_ep_dispatch_pull(_ws.x.ptr_table, _ws.tok.ptr_table, None, st.flags.ptr_table, all_off.data_ptr(),
+                                     local_offsets.data_ptr(), seg_start.data_ptr(), seg_src.data_ptr(), xe.data_ptr(),
+                                     None, None, H, st.rank, W, E, cap, 0, symm.next_epoch(), N._DT[x.dtype], 64,
+                                     N._comm_budget(), st.status.data_ptr(), N._st()), "ep_dispatch_pull")
+        shared.update(token_of=token_of, pos=pos, offsets=offsets, all_off=all_off, local_offsets=local_offsets,
+                      seg_start=seg_start, seg_src=seg_src, dest_base=dest_base, T=T, k=k, H=H)
+        ctx.shared = shared
+        ctx.w_dtype = w.dtype
+        return xe
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..distributed import symm
+        from ..ops import native as N
+        sh = ctx.shared
+        st = symm.state()
+        T, k, H, cap = sh["T"], sh["k"], sh["H"], sh["cap"]
+        g = g if g.is_contiguous() else g.contiguous()
+        _ws.dx.view(g.dtype, 0, cap * H).copy_(g.reshape(-1))
+        _ws.dwr.view(torch.float32, 0, cap).copy_(sh["dwr"])
+        dx = torch.empty(T, H, dtype=g.dtype, device=g.device)
+        dw = torch.empty(T, k, dtype=torch.float32, device=g.device)
+        N._chk(N.lib().gb_ep_combine_pull(_ws.dx.ptr_table, _ws.dwr.ptr_table, st.flags.ptr_table,
+                                          sh["idx"].data_ptr(), sh["pos"].data_ptr(), None, sh["offsets"].data_ptr(),
+                                          sh["dest_base"].data_ptr(), dx.data_ptr(), dw.data_ptr(), T, k, H, st.rank,
+                                          sh["W"], sh["E"], cap, 1, symm.next_epoch(), N._DT[g.dtype], 64,
+                                          N._comm_budget(), st.status.data_ptr(), N._st()), "ep_combine_pull(bwd)")
+        return dx, dw.to(ctx.w_dtype)
+
+
+class EPCombinePull(Function):
+    """out[t] = sum_j w[t, j] * ye_owner[row(t, j)], pulled from the owners' output buffers."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, ye, w, shared):
+        from ..distributed import symm
+        from ..ops import native as N
+        sh = shared
+        st = symm.state()
+        T, k, H, cap = sh["T"], sh["k"], sh["H"], sh["cap"]
+        ye = ye if ye.is_contiguous() else ye.contiguous()
+        _ws.y.view(ye.dtype, 0, cap * H).copy_(ye.reshape(-1))
+        wf = w.to(torch.float32).contiguous()
+        out = torch.empty(T, H, dtype=ye.dtype, device=ye.device)
+        N._chk(N.lib().gb_ep_combine_pull(_ws.y.ptr_table, None, st.flags.ptr_table, sh["idx"].data_ptr(),
+                                          sh["pos"].data_ptr(), wf.data_ptr(), sh["offsets"].data_ptr(),
+                                          sh["dest_base"].data_ptr(), out.data_ptr(), None, T, k, H, st.rank, sh["W"],
+                                          sh["E"], cap, 0, symm.next_epoch(), N._DT[ye.dtype], 64, N._comm_budget(),
+                                          st.status.data_ptr(), N._st()), "ep_combine_pull")
+        ctx.shared = sh
+        ctx.save_for_backward(ye, wf)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..distributed import symm
+        from ..ops import native as N
+        sh = ctx.shared
+        ye, wf = ctx.saved_tensors
+        st = symm.state()
+        T, k, H, cap = sh["T"], sh["k"], sh["H"], sh["cap"]
+        g = g if g.dtype == ye.dtype else K.to_dtype(g, ye.dtype)
+        _ws.g.view(g.dtype, 0, T * H).copy_(g.reshape(-1))
+        _ws.tok.view(torch.int32, 0, T * k).copy_(sh["token_of"].reshape(-1))
+        # routing weight of every pair, in sorted-pair order
+        ws_sorted = _ws.ws.view(torch.float32, 0, T * k)
+        ws_sorted[sh["pos"].reshape(-1).long()] = wf.reshape(-1)
+        dye = torch.zeros(cap, H, dtype=ye.dtype, device=ye.device)
+        dwr = torch.zeros(cap, dtype=torch.float32, device=ye.device)
+        N._chk(N.lib().gb_ep_dispatch_pull(_ws.g.ptr_table, _ws.tok.ptr_table, _ws.ws.ptr_table, st.flags.ptr_table,
+                                           sh["all_off"].data_ptr(), sh["local_offsets"].data_ptr(),
+                                           sh["seg_start"].data_ptr(), sh["seg_src"].data_ptr(), dye.data_ptr(),
+                                           ye.data_ptr(), dwr.data_ptr(), H, st.rank, sh["W"], sh["E"], cap, 1,
+                                           symm.next_epoch(), N._DT[ye.dtype], 64, N._comm_budget(),
+                                           st.status.data_ptr(), N._st()), "ep_dispatch_pull(bwd)")
+        sh["dwr"] = dwr
+        return dye, None
+
+
+def _expert_parallel_forward_p2p(layer, x, idx, w):
+    import os
+    from ..ops import grouped
+    global p2p_layers_run
+    p2p_layers_run += 1
+    ep = layer.ep
+    W, E = ep.size, layer.num_experts
+    El = E // W
+    T, k = idx.shape
+    factor = float(os.environ.get("GENESIS_EP_CAPACITY", min(W, 2.0)))
+    cap = (int(factor * T * k) + grouped.ALIGN - 1) // grouped.ALIGN * grouped.ALIGN + El * grouped.ALIGN
+    shared = {"W": W, "E": E, "El": El, "cap": cap, "idx": idx.to(torch.int32).contiguous()}
+    xe = EPDispatchPull.apply(x, w, shared["idx"], shared)
+    ye = layer.experts(xe, shared["local_offsets"])
+    return EPCombinePull.apply(ye, w.detach(), shared)
+
+
 def expert_parallel_forward(layer, x, idx, w):
     """x Tensor [T, H]; idx raw int tensor [T, k] (global expert ids); w Tensor [T, k]."""
     from ..models.transformers.moe import DispatchFunction, CombineFunction
+    if _p2p_usable(x._t):
+        return _expert_parallel_forward_p2p(layer, x, idx, w)
     ep = layer.ep
     W, E = ep.size, layer.num_experts
     El = E // W

@@ -68,6 +68,34 @@ def scenario_collectives(a):
         dist.all_reduce(genesis.Tensor(x))
         tol = 1e-5 if dt == torch.float32 else 5e-2
         assert torch.allclose(x.float().cpu(), ref, atol=tol * w, rtol=tol), (n, dt)
+    # larger / odd-sized gather, broadcast, reduce-scatter and variable-split all-to-all (on CUDA these run
+    # as pull kernels over peer memory)
+    for n, dt in [(70001, torch.float32), (4096, torch.bfloat16), (3, torch.int64)]:
+        mine = (torch.arange(n, device=d) % 251 + 1000 * r).to(dt)
+        outs = [torch.zeros(n, dtype=dt, device=d) for _ in range(w)]
+        dist.all_gather([genesis.Tensor(o) for o in outs], genesis.Tensor(mine))
+        for i, o in enumerate(outs):
+            assert torch.equal(o, (torch.arange(n, device=d) % 251 + 1000 * i).to(dt)), (n, dt, i)
+        bc = mine.clone()
+        dist.broadcast(genesis.Tensor(bc), src=w - 1)
+        assert torch.equal(bc, (torch.arange(n, device=d) % 251 + 1000 * (w - 1)).to(dt)), (n, dt)
+    n = 30011
+    ins = [torch.full((n,), float(r + 10 * i), device=d) + torch.arange(n, device=d) % 7 for i in range(w)]
+    out = torch.zeros(n, device=d)
+    dist.reduce_scatter(genesis.Tensor(out), [genesis.Tensor(i) for i in ins])
+    ref = sum(float(q + 10 * r) for q in range(w)) + w * (torch.arange(n, device=d) % 7).float()
+    assert torch.allclose(out, ref), "reduce_scatter"
+    # rank r sends (d + 1 + r) rows of 24 bf16 values to rank d
+    send_rows = [dd + 1 + r for dd in range(w)]
+    recv_rows = [r + 1 + s_ for s_ in range(w)]
+    inp = torch.cat([torch.full((send_rows[dd], 24), float(100 * r + dd), device=d) for dd in range(w)]).to(torch.bfloat16)
+    res = torch.zeros(sum(recv_rows), 24, dtype=torch.bfloat16, device=d)
+    dist.all_to_all_single(res, inp, recv_rows, send_rows)
+    pos = 0
+    for s_ in range(w):
+        assert torch.all(res[pos:pos + recv_rows[s_]].float() == float(100 * s_ + r)), ("a2a", s_)
+        pos += recv_rows[s_]
+    dist.barrier()
 
 
 def _local_grads(model_fn, x, y, seed):
@@ -196,6 +224,30 @@ def scenario_ep(a):
         got = getattr(ep_layer.experts, name).grad._t
         assert torch.allclose(got, gfull[lo:lo + E // w], atol=2e-5, rtol=1e-4), name
     del xs
+    from genesis_b200.parallel import ep as ep_mod
+    if a.backend == "nccl" and os.environ.get("GENESIS_COMM", "p2p") == "p2p":
+        assert ep_mod.p2p_layers_run >= 1, "the peer-memory transport was not used"
+        # bf16 under autocast at a size where every CTA has work: p2p transport against the NCCL transport
+        H, E, k, I, T = 256, 8 * w, 4, 512, 4096
+        genesis.manual_seed(7)
+        layer = MoELayer(H, E, k, I, ep_group=EPGroup()).to(d)
+        x0 = torch.from_numpy(np.random.RandomState(7 + r).randn(1, T, H).astype(np.float32)).to(d)
+        outs, grads = [], []
+        for mode in ("p2p", "nccl"):
+            os.environ["GENESIS_COMM"] = mode
+            xin = genesis.Tensor(x0.clone(), requires_grad=True)
+            for p_ in layer.parameters():
+                p_.grad = None
+            with genesis.amp.autocast(dtype=genesis.bfloat16):
+                o = layer(xin)
+            (o.float() * o.float()).sum().backward()
+            outs.append(o._t.float().clone())
+            grads.append((xin.grad._t.float().clone(), layer.experts.w_down.grad._t.float().clone(),
+                          layer.gate.weight.grad._t.float().clone()))
+        os.environ["GENESIS_COMM"] = "p2p"
+        assert torch.allclose(outs[0], outs[1], atol=2e-2, rtol=2e-2), float((outs[0] - outs[1]).abs().max())
+        for g0, g1 in zip(grads[0], grads[1]):
+            assert torch.allclose(g0, g1, atol=3e-2, rtol=3e-2), float((g0 - g1).abs().max())
 
 
 def scenario_heartbeat(a):
