@@ -60,6 +60,20 @@ class _SymmState:
         self.flags = self.alloc(64 * 1024)
         self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
         self.staging = None
+        self.channels = {}
+
+    def next_epoch(self):
+        self.epoch += 1
+        return self.epoch
+
+    def channel(self, name):
+        """A flag page and epoch counter of its own (collective on first use).  Kernels that may run at the
+        same time on different streams (the bucket all-reduce on DDP's communication stream, the collectives
+        and expert-parallel kernels on the compute stream) must not share flag slots: with a shared page a
+        slower kernel's older epoch could overwrite the newer one a peer is waiting for."""
+        if name not in self.channels:
+            self.channels[name] = _Channel(self, self.alloc(64 * 1024))
+        return self.channels[name]
 
     def _bind(self):
         L = self.lib
@@ -115,6 +129,18 @@ class _SymmState:
         self.buffers = []
 
 
+class _Channel:
+    """What the communication kernels need from the state, with private flags and epochs."""
+
+    def __init__(self, st, flags):
+        self.rank, self.world, self.device, self.status, self.flags = st.rank, st.world, st.device, st.status, flags
+        self.epoch = 0
+
+    def next_epoch(self):
+        self.epoch += 1
+        return self.epoch
+
+
 def available():
     return (pg.is_initialized() and pg._world_size > 1 and pg._backend == "nccl"
             and torch.cuda.is_available() and _lib.available())
@@ -143,9 +169,11 @@ def alloc(nbytes):
 
 
 def next_epoch():
-    st = state()
-    st.epoch += 1
-    return st.epoch
+    return state().next_epoch()
+
+
+def channel(name):
+    return state().channel(name)
 
 
 def check_status(what="collective"):

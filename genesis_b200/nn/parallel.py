@@ -128,6 +128,8 @@ class DistributedDataParallel(Module):
         self._use_symm = self._on_cuda and comm_mode() == "p2p" and symm.available()
         if self._on_cuda:
             self._comm_stream = torch.cuda.Stream()
+        if self._use_symm:
+            symm.channel("ddp")        # flag page of the communication stream (collective allocation: do it here)
         for b in self._buckets:
             esz = torch.empty(0, dtype=b.dtype).element_size()
             pad = (b.numel + 1023) // 1024 * 1024          # slices stay 16-byte aligned for any world size <= 64
@@ -178,7 +180,7 @@ class DistributedDataParallel(Module):
                     if scaler is not None and scaler.is_enabled():
                         scaler._lazy_init(b.flat.device)
                         inv, found = scaler._scale, scaler._found_inf
-                    N.allreduce_fused(symm.state(), b.symm_buf, 0, b.flat.numel(), b.dtype, b.flat,
+                    N.allreduce_fused(symm.channel("ddp"), b.symm_buf, 0, b.flat.numel(), b.dtype, b.flat,
                                       inv_scale=inv, found_inf=found, prescale=1.0 / self.world_size,
                                       scale_is_reciprocal=True)
                 else:

@@ -983,8 +983,7 @@ def moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm):
 def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None, found_inf=None, prescale=1.0,
                     scale_is_reciprocal=True, ctas=None):
     """In-place fused all-reduce over symmetric buffer `buf` (see csrc/comm.cu)."""
-    from ..distributed import symm
-    epoch = symm.next_epoch()
+    epoch = st.next_epoch()
     budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000)) * 1e6)
     if ctas is None:
         # enough CTAs to keep ~1.5 MB of loads in flight for big buckets, one for tiny ones
@@ -1011,20 +1010,20 @@ def peer_pull(st, buf, send_off, send_len, recv_off, out, ctas=32):
     W = st.world
     arr = ctypes.c_longlong * W
     _chk(lib().gb_peer_pull(buf.ptr_table, st.flags.ptr_table, arr(*send_off), arr(*send_len), arr(*recv_off),
-                            out.data_ptr(), st.rank, W, symm.next_epoch(), ctas, _comm_budget(),
+                            out.data_ptr(), st.rank, W, st.next_epoch(), ctas, _comm_budget(),
                             st.status.data_ptr(), _st()), "peer_pull")
 
 
 def peer_reduce_scatter(st, buf, out, n, scale=1.0, ctas=32):
     from ..distributed import symm
     _chk(lib().gb_peer_reduce_scatter(buf.ptr_table, st.flags.ptr_table, out.data_ptr(), n, st.rank, st.world,
-                                      symm.next_epoch(), float(scale), _DT[out.dtype], ctas, _comm_budget(),
+                                      st.next_epoch(), float(scale), _DT[out.dtype], ctas, _comm_budget(),
                                       st.status.data_ptr(), _st()), "peer_reduce_scatter")
 
 
 def peer_barrier(st):
     from ..distributed import symm
-    _chk(lib().gb_peer_barrier(st.flags.ptr_table, st.rank, st.world, symm.next_epoch(), _comm_budget(),
+    _chk(lib().gb_peer_barrier(st.flags.ptr_table, st.rank, st.world, st.next_epoch(), _comm_budget(),
                                st.status.data_ptr(), _st()), "peer_barrier")
 
 
