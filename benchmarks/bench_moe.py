@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=2)
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--kernels", type=int, default=0, help="also list the N kernels with the most device time of one step")
     args = ap.parse_args()
     os.environ["GENESIS_COMM"] = args.transport
 
@@ -80,6 +81,15 @@ def main():
     ms, last = time_steps(torch, step, args.steps, args.warmup, world)
     clocks = sampler.stop() if rank == 0 else None
     loss = float(last._t.float().cpu())
+    kernels = None
+    if args.kernels:
+        from torch.profiler import profile, ProfilerActivity
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        rows = sorted(((e.device_time_total / 1e3, e.count, e.key[:90]) for e in prof.key_averages()
+                       if e.device_time_total > 0), reverse=True)
+        kernels = [{"ms": round(ms_, 3), "calls": n, "name": k} for ms_, n, k in rows[:args.kernels]]
     native.check_status()
     if world > 1:
         from genesis_b200.distributed import symm
@@ -95,7 +105,7 @@ def main():
         "config": {"model": "qwen3-moe-bench", "layers": args.layers, "experts": args.experts, "top_k": 8,
                    "global_batch": B * world, "seq_len": S, "parallelism": f"ep{world} x dp{world}",
                    "transport": args.transport, "params_per_rank": n_params},
-        "clocks": clocks, "loss": loss, "gpu_launches": native.launch_count // (args.steps + args.warmup) * args.steps,
+        "clocks": clocks, "loss": loss, "kernels": kernels, "gpu_launches": native.launch_count // (args.steps + args.warmup) * args.steps,
     }), flush=True)
 
 

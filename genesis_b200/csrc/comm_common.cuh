@@ -7,8 +7,8 @@
 namespace gb {
 
 constexpr int COMM_MAX_WORLD = 16;
-constexpr int COMM_MAX_CTAS = 64;
-// flag layout inside the symmetric flag page (uint32): [phase(2)][cta(64)][src rank(16)], then the overflow epoch
+constexpr int COMM_MAX_CTAS = 128;
+// flag layout inside the symmetric flag page (uint32): [phase(2)][cta(128)][src rank(16)], then the overflow epoch
 constexpr int COMM_FLAG_WORDS = 2 * COMM_MAX_CTAS * COMM_MAX_WORLD;
 constexpr int COMM_FOUND_SLOT = COMM_FLAG_WORDS;
 

@@ -95,53 +95,75 @@ ep_dispatch_pull_kernel(PeerTable xs, PeerTable toks, PeerTable wss, PeerTable f
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  for (int row = warp; row < total; row += nwarps) {
-    // last segment whose start is <= row
-    int lo = 0, hi = nseg;
-    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (s_start[mid] <= row) lo = mid; else hi = mid; }
-    // segments of zero rows share a start with their successor: take the last one at this start
-    const int s = lo;
-    const int e = s / world, p = s % world;
-    const int g = rank * El + e;
-    const int cnt = all_off[p * (E + 1) + g + 1] - all_off[p * (E + 1) + g];
-    const int i = row - s_start[s];
-    T* dst = out + (size_t)row * H;
-    if (i >= cnt) {
-      // padding between the end of an expert's rows and the next expert
-      for (int v = lane; v < nvec; v += 32) { Vec16<T> z; for (int j = 0; j < V; ++j) z.v[j] = Cvt<T>::from_f(0.f); st16(dst + v * V, z); }
-      if (mode == 1 && lane == 0) dwr[row] = 0.f;
-      continue;
+  // A warp takes 32 consecutive rows of the layout: lane l resolves row base + l (segment search, then ONE peer
+  // load of the token index), after which the rows are copied one by one with all 32 lanes on a row.
+  for (int base = warp * 32; base < total; base += nwarps * 32) {
+    const int my_row = base + lane;
+    int my_p = -1, my_t = 0;
+    float my_w = 0.f;
+    if (my_row < total) {
+      int lo = 0, hi = nseg;                             // last segment whose start is <= row
+      while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (s_start[mid] <= my_row) lo = mid; else hi = mid; }
+      const int e = lo / world, p = lo % world;
+      const int g = rank * El + e;
+      const int cnt = all_off[p * (E + 1) + g + 1] - all_off[p * (E + 1) + g];
+      const int i = my_row - s_start[lo];
+      if (i < cnt) {                                     // else: padding up to the next expert
+        const int sp = seg_src_off[lo] + i;              // position in p's sorted pair list
+        my_p = p;
+        my_t = *reinterpret_cast<const volatile int*>(reinterpret_cast<const int*>(toks.ptr[p]) + sp);
+        if (mode == 1) my_w = *reinterpret_cast<const volatile float*>(reinterpret_cast<const float*>(wss.ptr[p]) + sp);
+      }
     }
-    const int sp = seg_src_off[s] + i;                                   // position in p's sorted pair list
-    const int t = *reinterpret_cast<const volatile int*>(reinterpret_cast<const int*>(toks.ptr[p]) + sp);
-    const T* src = reinterpret_cast<const T*>(xs.ptr[p]) + (size_t)t * H;
-    if (mode == 0) {
-      for (int v0 = lane; v0 < nvec; v0 += 128) {
-        uint4 r[4];
+    const int nrows = total - base < 32 ? total - base : 32;
+    for (int r = 0; r < nrows; ++r) {
+      const int p = __shfl_sync(0xffffffffu, my_p, r);
+      const int t = __shfl_sync(0xffffffffu, my_t, r);
+      const float wgt = __shfl_sync(0xffffffffu, my_w, r);
+      const int row = base + r;
+      T* dst = out + (size_t)row * H;
+      if (p < 0) {
+        Vec16<T> z;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) if (v0 + u * 32 < nvec) r[u] = ld_volatile_v4(src + (v0 + u * 32) * V);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) if (v0 + u * 32 < nvec) *reinterpret_cast<uint4*>(dst + (v0 + u * 32) * V) = r[u];
+        for (int q = 0; q < V; ++q) z.v[q] = Cvt<T>::from_f(0.f);
+        for (int v = lane; v < nvec; v += 32) st16(dst + v * V, z);
+        if (mode == 1 && lane == 0) dwr[row] = 0.f;
+        continue;
       }
-    } else {
-      const float wgt = *reinterpret_cast<const volatile float*>(reinterpret_cast<const float*>(wss.ptr[p]) + sp);
-      const T* yr = y_rows + (size_t)row * H;
-      float dot = 0.f;
-      for (int v = lane; v < nvec; v += 32) {
-        const uint4 raw = ld_volatile_v4(src + v * V);
-        const T* ge = reinterpret_cast<const T*>(&raw);
-        const Vec16<T> yv = ld16(yr + v * V);
-        Vec16<T> o;
+      const T* src = reinterpret_cast<const T*>(xs.ptr[p]) + (size_t)t * H;
+      if (mode == 0) {
+        for (int v0 = lane; v0 < nvec; v0 += 256) {
+          uint4 q[8];
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float gj = Cvt<T>::to_f(ge[j]);
-          dot += gj * Cvt<T>::to_f(yv.v[j]);
-          o.v[j] = Cvt<T>::from_f(gj * wgt);
+          for (int u = 0; u < 8; ++u) if (v0 + u * 32 < nvec) q[u] = ld_volatile_v4(src + (v0 + u * 32) * V);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) if (v0 + u * 32 < nvec) *reinterpret_cast<uint4*>(dst + (v0 + u * 32) * V) = q[u];
         }
-        st16(dst + v * V, o);
+      } else {
+        const T* yr = y_rows + (size_t)row * H;
+        float dot = 0.f;
+        for (int v0 = lane; v0 < nvec; v0 += 128) {
+          uint4 q[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) if (v0 + u * 32 < nvec) q[u] = ld_volatile_v4(src + (v0 + u * 32) * V);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (v0 + u * 32 >= nvec) continue;
+            const T* ge = reinterpret_cast<const T*>(&q[u]);
+            const Vec16<T> yv = ld16(yr + (v0 + u * 32) * V);
+            Vec16<T> o;
+#pragma unroll
+            for (int c = 0; c < V; ++c) {
+              const float gj = Cvt<T>::to_f(ge[c]);
+              dot += gj * Cvt<T>::to_f(yv.v[c]);
+              o.v[c] = Cvt<T>::from_f(gj * wgt);
+            }
+            st16(dst + (v0 + u * 32) * V, o);
+          }
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) dwr[row] = dot;
       }
-      dot = warp_sum(dot);
-      if (lane == 0) dwr[row] = dot;
     }
   }
 }
@@ -163,32 +185,61 @@ ep_combine_pull_kernel(PeerTable ys, PeerTable dwrs, PeerTable flags, const int*
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   for (int t = warp; t < T_tokens; t += nwarps) {
+    // lane j resolves slot j of the token once: owner rank, row in the owner's layout, weight
+    int my_d = 0, my_row = -1;
+    float my_w = 0.f;
+    if (lane < k) {
+      const int g = idx[t * k + lane];
+      my_d = g / El;
+      my_row = dest_base[g] + pos[t * k + lane] - my_off[g];
+      if (my_row >= capacity) my_row = -1;              // the owner's layout overflowed (reported there)
+      my_w = mode == 0 ? w[t * k + lane] : 1.f;
+      if (mode == 1)
+        dw[t * k + lane] = my_row < 0 ? 0.f
+            : *reinterpret_cast<const volatile float*>(reinterpret_cast<const float*>(dwrs.ptr[my_d]) + my_row);
+    }
     for (int v0 = lane; v0 < nvec; v0 += 32) {
       float acc[V];
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] = 0.f;
-      for (int j = 0; j < k; ++j) {
-        const int g = idx[t * k + j];
-        const int d = g / El;
-        const int row = dest_base[g] + pos[t * k + j] - my_off[g];
-        if (row >= capacity) continue;                 // the owner's layout overflowed (reported by ep_layout there)
-        const float wt = mode == 0 ? w[t * k + j] : 1.f;
-        const uint4 raw = ld_volatile_v4(reinterpret_cast<const T*>(ys.ptr[d]) + (size_t)row * H + v0 * V);
-        const T* e = reinterpret_cast<const T*>(&raw);
+      for (int c = 0; c < V; ++c) acc[c] = 0.f;
+      for (int j0 = 0; j0 < k; j0 += 4) {
+        uint4 q[4];
+        float wt[4];
 #pragma unroll
-        for (int q = 0; q < V; ++q) acc[q] += wt * Cvt<T>::to_f(e[q]);
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u < k ? j0 + u : k - 1;
+          const int d = __shfl_sync(0xffffffffu, my_d, j);
+          const int row = __shfl_sync(0xffffffffu, my_row, j);
+          const float wj = __shfl_sync(0xffffffffu, my_w, j);
+          const bool ok = j0 + u < k && row >= 0;       // uniform over the warp
+          wt[u] = ok ? wj : 0.f;
+          q[u] = make_uint4(0, 0, 0, 0);
+          if (ok) q[u] = ld_volatile_v4(reinterpret_cast<const T*>(ys.ptr[d]) + (size_t)row * H + v0 * V);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const T* e = reinterpret_cast<const T*>(&q[u]);
+#pragma unroll
+          for (int c = 0; c < V; ++c) acc[c] += wt[u] * Cvt<T>::to_f(e[c]);
+        }
       }
       Vec16<T> o;
 #pragma unroll
-      for (int q = 0; q < V; ++q) o.v[q] = Cvt<T>::from_f(acc[q]);
+      for (int c = 0; c < V; ++c) o.v[c] = Cvt<T>::from_f(acc[c]);
       st16(out + (size_t)t * H + v0 * V, o);
     }
-    if (mode == 1 && lane < k) {
-      const int g = idx[t * k + lane];
-      const int row = dest_base[g] + pos[t * k + lane] - my_off[g];
-      dw[t * k + lane] = row >= capacity ? 0.f : *reinterpret_cast<const volatile float*>(reinterpret_cast<const float*>(dwrs.ptr[g / El]) + row);
-    }
   }
+}
+
+// Copies the rows of the receive layout that exist (row < local_offsets[El], at most `capacity`) into the
+// symmetric buffer the peers read from; the count lives on the device, so the host never waits for it.
+__global__ void ep_stage_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                     const int* __restrict__ total_rows, long long vec_per_row, int capacity) {
+  int total = *total_rows;
+  if (total > capacity) total = capacity;
+  const long long n = (long long)total * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = src[i];
 }
 
 static void fill_table(PeerTable& t, void* const* ptrs, int world) {
@@ -250,5 +301,14 @@ extern "C" int gb_ep_combine_pull(void* const* ys, void* const* dwrs, void* cons
                                                     reinterpret_cast<T*>(out), dw, tokens, k, H, rank, world, E, capacity,
                                                     mode, epoch, budget_ns, status);
   });
+  return (int)cudaGetLastError();
+}
+
+// dst[0 .. rows) = src[0 .. rows) with rows = min(*total_rows, capacity), rows of row_bytes (multiple of 16).
+extern "C" int gb_ep_stage_rows(const void* src, void* dst, const int* total_rows, long long row_bytes, int capacity,
+                                cudaStream_t st) {
+  if (row_bytes % 16 != 0) return -3;
+  ep_stage_rows_kernel<<<148 * 8, 256, 0, st>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst),
+                                                total_rows, row_bytes / 16, capacity);
   return (int)cudaGetLastError();
 }

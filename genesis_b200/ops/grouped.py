@@ -66,7 +66,8 @@ def grouped_linear(x, w, offsets):
         return NotImplemented
     Mp, Kk = x.shape
     G, Nn, _ = w.shape
-    out = torch.zeros(Mp, Nn, dtype=x.dtype, device=x.device)
+    # every tile below offsets[-1] is written (pad rows are zero on the way in); rows past it stay unwritten
+    out = torch.empty(Mp, Nn, dtype=x.dtype, device=x.device)
     return _gemm(x, w, out, Mp, Nn, Kk, Kk, Kk, Nn * Kk, 0, 0, 0, 1, offsets, G)
 
 
@@ -76,7 +77,7 @@ def grouped_dgrad(gy, w, offsets):
         return NotImplemented
     Mp, Nn = gy.shape
     G, _, Kk = w.shape
-    out = torch.zeros(Mp, Kk, dtype=gy.dtype, device=gy.device)
+    out = torch.empty(Mp, Kk, dtype=gy.dtype, device=gy.device)
     # contraction over N: B operand is w[g] stored [N (contraction), K (output columns)] = MN-major
     return _gemm(gy, w, out, Mp, Kk, Nn, Nn, Kk, Nn * Kk, 0, 0, 1, 1, offsets, G)
 

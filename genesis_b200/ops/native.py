@@ -50,7 +50,7 @@ _SIGS = {
     "gb_peer_pull": "pppppp" + "ii" + "I" + "i" + "u" + "pp",
     "gb_peer_reduce_scatter": "ppp" + "lii" + "I" + "f" + "ii" + "u" + "pp",
     "gb_peer_barrier": "p" + "ii" + "I" + "u" + "pp",
-    "gb_ep_layout": "p" + "iiiii" + "pppppp" + "p",
+    "gb_ep_layout": "p" + "iiiii" + "pppppp" + "p", "gb_ep_stage_rows": "ppp" + "li" + "p",
     "gb_ep_dispatch_pull": "pppp" + "pppp" + "ppp" + "iiiiii" + "I" + "ii" + "u" + "pp",
     "gb_ep_combine_pull": "ppp" + "ppppp" + "pp" + "iiiiiiii" + "I" + "ii" + "u" + "pp",
     "gb_sort_rows": "ppp" + "liiii" + "pp", "gb_argmax_rows": "pp" + "liii" + "p",

@@ -114,6 +114,15 @@ class _Workspace:
 
 
 _ws = _Workspace()
+_CTAS = 128             # CTAs of the pull kernels (the same on every rank: each CTA has its own flag channel)
+
+
+def _stage_rows(rows, buf, sh, H):
+    """Copies the rows of the receive layout that exist into a symmetric buffer (count read on the device)."""
+    from ..ops import native as N
+    N._chk(N.lib().gb_ep_stage_rows(rows.data_ptr(), buf.local_ptr, sh["local_offsets"][sh["El"]:].data_ptr(),
+                                    H * rows.element_size(), sh["cap"], N._st()), "ep_stage_rows")
+
 p2p_layers_run = 0      # forward passes that took the peer-memory transport (tests assert on it)
 
 
@@ -161,10 +170,10 @@ class EPDispatchPull(Function):
         N._chk(L.gb_ep_layout(all_off.data_ptr(), st.rank, W, E, grouped.ALIGN, cap, local_offsets.data_ptr(),
                               seg_start.data_ptr(), seg_src.data_ptr(), dest_base.data_ptr(), info.data_ptr(),
                               st.status.data_ptr(), N._st()), "ep_layout")
-        xe = torch.zeros(cap, H, dtype=x.dtype, device=dev)
+        xe = torch.empty(cap, H, dtype=x.dtype, device=dev)     # rows past the layout's end stay unwritten
         N._chk(L.gb_ep_dispatch_pull(_ws.x.ptr_table, _ws.tok.ptr_table, None, st.flags.ptr_table, all_off.data_ptr(),
                                      local_offsets.data_ptr(), seg_start.data_ptr(), seg_src.data_ptr(), xe.data_ptr(),
-                                     None, None, H, st.rank, W, E, cap, 0, symm.next_epoch(), N._DT[x.dtype], 64,
+                                     None, None, H, st.rank, W, E, cap, 0, symm.next_epoch(), N._DT[x.dtype], _CTAS,
                                      N._comm_budget(), st.status.data_ptr(), N._st()), "ep_dispatch_pull")
         shared.update(token_of=token_of, pos=pos, offsets=offsets, all_off=all_off, local_offsets=local_offsets,
                       seg_start=seg_start, seg_src=seg_src, dest_base=dest_base, T=T, k=k, H=H)
@@ -180,14 +189,14 @@ class EPDispatchPull(Function):
         st = symm.state()
         T, k, H, cap = sh["T"], sh["k"], sh["H"], sh["cap"]
         g = g if g.is_contiguous() else g.contiguous()
-        _ws.dx.view(g.dtype, 0, cap * H).copy_(g.reshape(-1))
+        _stage_rows(g, _ws.dx, sh, H)
         _ws.dwr.view(torch.float32, 0, cap).copy_(sh["dwr"])
         dx = torch.empty(T, H, dtype=g.dtype, device=g.device)
         dw = torch.empty(T, k, dtype=torch.float32, device=g.device)
         N._chk(N.lib().gb_ep_combine_pull(_ws.dx.ptr_table, _ws.dwr.ptr_table, st.flags.ptr_table,
                                           sh["idx"].data_ptr(), sh["pos"].data_ptr(), None, sh["offsets"].data_ptr(),
                                           sh["dest_base"].data_ptr(), dx.data_ptr(), dw.data_ptr(), T, k, H, st.rank,
-                                          sh["W"], sh["E"], cap, 1, symm.next_epoch(), N._DT[g.dtype], 64,
+                                          sh["W"], sh["E"], cap, 1, symm.next_epoch(), N._DT[g.dtype], _CTAS,
                                           N._comm_budget(), st.status.data_ptr(), N._st()), "ep_combine_pull(bwd)")
         return dx, dw.to(ctx.w_dtype)
 
@@ -205,13 +214,13 @@ class EPCombinePull(Function):
         st = symm.state()
         T, k, H, cap = sh["T"], sh["k"], sh["H"], sh["cap"]
         ye = ye if ye.is_contiguous() else ye.contiguous()
-        _ws.y.view(ye.dtype, 0, cap * H).copy_(ye.reshape(-1))
+        _stage_rows(ye, _ws.y, sh, H)
         wf = w.to(torch.float32).contiguous()
         out = torch.empty(T, H, dtype=ye.dtype, device=ye.device)
         N._chk(N.lib().gb_ep_combine_pull(_ws.y.ptr_table, None, st.flags.ptr_table, sh["idx"].data_ptr(),
                                           sh["pos"].data_ptr(), wf.data_ptr(), sh["offsets"].data_ptr(),
                                           sh["dest_base"].data_ptr(), out.data_ptr(), None, T, k, H, st.rank, sh["W"],
-                                          sh["E"], cap, 0, symm.next_epoch(), N._DT[ye.dtype], 64, N._comm_budget(),
+                                          sh["E"], cap, 0, symm.next_epoch(), N._DT[ye.dtype], _CTAS, N._comm_budget(),
                                           st.status.data_ptr(), N._st()), "ep_combine_pull")
         ctx.shared = sh
         ctx.save_for_backward(ye, wf)
@@ -231,13 +240,13 @@ class EPCombinePull(Function):
         # routing weight of every pair, in sorted-pair order
         ws_sorted = _ws.ws.view(torch.float32, 0, T * k)
         ws_sorted[sh["pos"].reshape(-1).long()] = wf.reshape(-1)
-        dye = torch.zeros(cap, H, dtype=ye.dtype, device=ye.device)
+        dye = torch.empty(cap, H, dtype=ye.dtype, device=ye.device)
         dwr = torch.zeros(cap, dtype=torch.float32, device=ye.device)
         N._chk(N.lib().gb_ep_dispatch_pull(_ws.g.ptr_table, _ws.tok.ptr_table, _ws.ws.ptr_table, st.flags.ptr_table,
                                            sh["all_off"].data_ptr(), sh["local_offsets"].data_ptr(),
                                            sh["seg_start"].data_ptr(), sh["seg_src"].data_ptr(), dye.data_ptr(),
                                            ye.data_ptr(), dwr.data_ptr(), H, st.rank, sh["W"], sh["E"], cap, 1,
-                                           symm.next_epoch(), N._DT[ye.dtype], 64, N._comm_budget(),
+                                           symm.next_epoch(), N._DT[ye.dtype], _CTAS, N._comm_budget(),
                                            st.status.data_ptr(), N._st()), "ep_dispatch_pull(bwd)")
         sh["dwr"] = dwr
         return dye, None
