@@ -1,0 +1,53 @@
+"""The nanochat trainer end to end on CPU: synthetic data, text shards with the byte tokenizer, resume."""
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "apps", "nanochat"))
+
+
+def _train(argv):
+    import importlib
+    train = importlib.import_module("train")
+    return train.main(argv)
+
+
+def test_trainer_synthetic_and_resume(tmp_path):
+    out = str(tmp_path / "ck")
+    metrics = str(tmp_path / "m.jsonl")
+    common = ["--model", "tiny", "--data", "synthetic", "--vocab-size", "200", "--batch-size", "2", "--block-size", "16",
+              "--device", "cpu", "--out", out, "--log-interval", "2", "--eval-interval", "4", "--eval-batches", "2",
+              "--save-interval", "4", "--accumulation-steps", "2", "--clip-grad", "1.0", "--warmup-steps", "2"]
+    assert _train(common + ["--max-steps", "4", "--metrics", metrics]) == 4
+    rows = [json.loads(l) for l in open(metrics)]
+    assert [r["step"] for r in rows] == [2, 4] and all(np.isfinite(r["loss"]) for r in rows)
+    ck = os.path.join(out, "checkpoint_4.pth")
+    assert os.path.exists(ck) and os.path.exists(os.path.join(out, "checkpoint_final.pth"))
+    assert _train(common + ["--max-steps", "6", "--resume", ck]) == 6
+
+
+def test_trainer_learns_text_shards(tmp_path):
+    data = tmp_path / "shards"
+    data.mkdir()
+    for i in range(2):
+        (data / f"shard_{i}.txt").write_text("the quick brown fox jumps over the lazy dog\n" * 200)
+    metrics = str(tmp_path / "m.jsonl")
+    _train(["--model", "tiny", "--data", str(data), "--tokenizer", "bytes", "--batch-size", "4", "--block-size", "32",
+            "--device", "cpu", "--out", str(tmp_path / "ck"), "--max-steps", "30", "--log-interval", "10",
+            "--eval-interval", "0", "--save-interval", "0", "--learning-rate", "3e-3", "--metrics", metrics,
+            "--amp", "--dtype", "bf16"])
+    rows = [json.loads(l) for l in open(metrics)]
+    assert rows[-1]["loss"] < rows[0]["loss"] - 0.5, rows
+
+
+def test_batches_shift_targets_by_one():
+    import data as D
+    stream = iter([[1, 2, 3, 4, 5], [6, 7, 8, 9, 10, 11, 12]])
+    x, y = next(D.batches(stream, 2, 3))
+    assert x.tolist() == [[1, 2, 3], [4, 5, 6]] and y.tolist() == [[2, 3, 4], [5, 6, 7]]
+    tok = D.ByteTokenizer()
+    ids = tok.encode_batch(["hé"])[0]
+    assert ids[0] == tok.bos_id and tok.decode(ids) == "hé"
