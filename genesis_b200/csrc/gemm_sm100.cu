@@ -47,6 +47,8 @@ struct GemmParams {
   int raster_group;        // tiles of the fast dimension swept together (keeps both operand panels in L2)
   int splits;              // split-K factor (>1: fp32 output, partial sums combined with adds in memory)
   int tma_out;             // 0: per-thread stores; 1: TMA store; 2: TMA add-reduce (fp32 output)
+  int stream_k;            // 1: every CTA takes an equal, contiguous share of all (tile, k-iteration) units and adds
+                           //    its partial tiles into the fp32 output (needs tma_out == 2)
   float alpha;
 };
 
@@ -137,6 +139,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
       ni = grp * g + rr % gs; mi = rr / gs;
     }
   };
+  // stream-K: this CTA's share of the tiles x k-iterations units
+  const long long k_iters_total = (p.K + BK - 1) / BK;
+  const long long sk_units = total_tiles * k_iters_total;
+  const long long sk_u0 = p.stream_k ? sk_units * blockIdx.x / gridDim.x : 0;
+  const long long sk_u1 = p.stream_k ? sk_units * (blockIdx.x + 1) / gridDim.x : 0;
   // k range of a tile, in elements
   auto krange = [&](int z, int& k_begin, int& k_end) {
     if (p.group_mode == GROUP_K) { k_begin = s_offs[z]; k_end = s_offs[z + 1]; }
@@ -148,19 +155,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     } else { k_begin = 0; k_end = p.K; }
   };
 
+  // Next piece of work of this CTA.  Classic: `cur` walks the tiles (stride gridDim.x), each with its whole k range.
+  // Stream-K: `cur` walks this CTA's units; a piece is the part of one tile's k range that falls inside them.
+  auto advance = [&](long long& cur, int& mi, int& ni, int& z, int& k_begin, int& k_end) -> bool {
+    if (!p.stream_k) {
+      if (cur >= total_tiles) return false;
+      decode(cur, mi, ni, z);
+      krange(z, k_begin, k_end);
+      cur += gridDim.x;
+      return true;
+    }
+    if (cur >= sk_u1) return false;
+    const long long tile = cur / k_iters_total;
+    const long long kb = cur % k_iters_total;
+    long long len = k_iters_total - kb;
+    if (len > sk_u1 - cur) len = sk_u1 - cur;
+    decode(tile, mi, ni, z);
+    k_begin = (int)(kb * BK);
+    k_end = (int)((kb + len) * BK);
+    if (k_end > p.K) k_end = p.K;
+    cur += len;
+    return true;
+  };
+  const long long cur0 = p.stream_k ? sk_u0 : (long long)blockIdx.x;
+
   if (warp == 0) {
     // =========================== TMA producer ===========================
     if (elect_one()) {
       uint32_t it = 0;
-      for (long long t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        int mi, ni, z; decode(t, mi, ni, z);
+      long long cur = cur0;
+      int mi, ni, z, k_begin, k_end;
+      while (!*abort_flag && advance(cur, mi, ni, z, k_begin, k_end)) {
         const int m0 = mi * BM, n0 = ni * BN;
         int za = z / p.splits, zb = z / p.splits;
         if (p.group_mode == GROUP_M) {
           if (m0 >= s_offs[p.groups]) continue;
           za = 0; zb = find_group(s_offs, p.groups, m0);
         } else if (p.group_mode == GROUP_K) { za = 0; zb = 0; }
-        int k_begin, k_end; krange(z, k_begin, k_end);
         for (int k0 = k_begin; k0 < k_end; k0 += BK, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -200,10 +231,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
       const uint32_t fmt = (ESIZE == 4) ? 2u : (uint32_t)(p.out_dtype >> 8);   // operand format rides in bits 8+
       const uint32_t idesc = make_idesc(fmt, A_MN ? 1u : 0u, B_MN ? 1u : 0u, BM, BN);
       uint32_t it = 0, tile_no = 0;
-      for (long long t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        int mi, ni, z; decode(t, mi, ni, z);
+      long long cur = cur0;
+      int mi, ni, z, k_begin, k_end;
+      while (!*abort_flag && advance(cur, mi, ni, z, k_begin, k_end)) {
         if (p.group_mode == GROUP_M && mi * BM >= s_offs[p.groups]) continue;
-        int k_begin, k_end; krange(z, k_begin, k_end);
         const uint32_t acc = tile_no & 1;
         const uint32_t acc_ph = (tile_no >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, 200)) break;
@@ -247,11 +278,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     uint8_t* slab = smem + L::SLAB_OFFSET + (warp - 2) * L::SLAB_BYTES;
     uint8_t* slab_row = slab + lane * 128;
     uint32_t tile_no = 0;
-    for (long long t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-      int mi, ni, z; decode(t, mi, ni, z);
+    long long cur = cur0;
+    int mi, ni, z, k_begin, k_end;
+    while (!*abort_flag && advance(cur, mi, ni, z, k_begin, k_end)) {
       const int m0 = mi * BM, n0 = ni * BN;
       if (p.group_mode == GROUP_M && m0 >= s_offs[p.groups]) continue;
-      int k_begin, k_end; krange(z, k_begin, k_end);
       const uint32_t acc = tile_no & 1;
       const uint32_t acc_ph = (tile_no >> 1) & 1;
       const bool empty_k = (k_end <= k_begin);
@@ -451,6 +482,12 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   const int nz = (p.group_mode == GROUP_K) ? p.groups : p.batch * p.splits;
   long long total = (long long)tiles_m * tiles_n * nz;
   int grid = (int)(total < sms ? total : sms);
+  if (p.stream_k) {
+    // at least 16 k-iterations per CTA, so that a piece's main loop outweighs its 128 KB epilogue
+    const long long units = total * ((p.K + (BK_BYTES / ESIZE) - 1) / (BK_BYTES / ESIZE));
+    long long g = units / 16;
+    grid = (int)(g < sms ? g : sms);
+  }
   if (grid < 1) grid = 1;
   kern<<<grid, 320, L::TOTAL + 1024, stream>>>(ta, tb, td, p);
   return (int)cudaGetLastError();
@@ -481,6 +518,8 @@ extern "C" int gb_gemm(const void* A, const void* B, void* D, const void* bias, 
   const int es = (in_dtype == DT_F32) ? 4 : 2;
   const int bk = 128 / es;
   const int bn = (N <= 128 || bn_hint == 128) ? 128 : 256;
+  // splits < 0 asks for stream-K (see GemmParams::stream_k); it needs what split-K needs, and the TMA add path
+  const bool want_stream_k = splits < 0;
   if (splits < 1 || group_mode != GROUP_NONE || out_dtype != DT_F32) splits = 1;
   CUtensorMap ta, tb;
   int r;
@@ -511,10 +550,14 @@ extern "C" int gb_gemm(const void* A, const void* B, void* D, const void* bias, 
     const long long d_batches = (group_mode == GROUP_K) ? groups : ((group_mode == GROUP_M) ? 1 : p.batch);
     const bool aligned = (reinterpret_cast<uintptr_t>(D) & 15) == 0 && ((long long)ldd * eso) % 16 == 0 &&
                          (d_batches <= 1 || (strideD * eso) % 16 == 0);
+    const bool sk_ok = want_stream_k && group_mode == GROUP_NONE && out_dtype == DT_F32 && p.batch == 1 &&
+                       bias == nullptr;
     if (aligned && (!adds || out_dtype == DT_F32)) {
       r = make_tmap_3d(&td, D, out_dtype, N, M, d_batches, ldd, strideD, 32);
-      if (r == 0) p.tma_out = adds ? 2 : 1;
+      if (r == 0) p.tma_out = (adds || sk_ok) ? 2 : 1;
     }
+    p.stream_k = (sk_ok && p.tma_out == 2) ? 1 : 0;
+    if (want_stream_k && !p.stream_k) return -5;      // the caller zeroed D for adds: refuse rather than overwrite
   }
   // Sweep the dimension whose operand is smaller fastest, so the larger one streams from HBM once
   // and the smaller one stays in L2.

@@ -105,7 +105,8 @@ def test_large_gemm_many_tiles():
 
 @pytest.mark.parametrize("M,N_,K_", [(896, 896, 8192), (128, 896, 16384), (4864, 896, 4096), (300, 520, 6000)])
 def test_weight_gradient_shapes_split_k(M, N_, K_):
-    # small outputs with a long contraction: the planner splits K and combines partial sums with atomics
+    # small outputs with a long contraction: the planner spreads the k range of the tiles over all SMs
+    # (stream-K) and the partial tiles are added into the output by the epilogue
     gy, x = rnd(K_, M, dt=torch.bfloat16), rnd(K_, N_, dt=torch.bfloat16, seed=1)
     ref = gy.float().t() @ x.float()
     got = K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32)
@@ -113,3 +114,20 @@ def test_weight_gradient_shapes_split_k(M, N_, K_):
     acc = torch.full((M, N_), 2.0, device=DEV)
     K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32, accum=acc)
     check(acc, ref + 2.0, torch.bfloat16, K_ / 16)
+
+
+@pytest.mark.parametrize("plan", [(256, -1), (128, -1), (256, 3), (128, 1), (256, 1)])
+@pytest.mark.parametrize("M,N_,K_", [(640, 1000, 2500), (4864, 896, 2048)])
+def test_forced_tile_and_split_plans_agree(plan, M, N_, K_):
+    from genesis_b200.ops import native
+    gy, x = rnd(K_, M, dt=torch.bfloat16), rnd(K_, N_, dt=torch.bfloat16, seed=3)
+    ref = gy.float().t() @ x.float()
+    native.plan_override = plan
+    try:
+        got = K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32)
+        acc = torch.full((M, N_), -1.5, device=DEV)
+        K.linear_wgrad(gy.to(DEV), x.to(DEV), out_dtype=torch.float32, accum=acc)
+    finally:
+        native.plan_override = None
+    check(got, ref, torch.bfloat16, K_ / 16)
+    check(acc, ref - 1.5, torch.bfloat16, K_ / 16)
