@@ -17,7 +17,8 @@ namespace gb {
 constexpr int BW_C = 64;    // columns of a backward score tile
 constexpr int BW_ST = 3;    // stages of the ring of streamed operand tiles
 
-__device__ __forceinline__ void store_out_row(uint16_t* dst, uint32_t tsrc, int ncols, bool valid, int dt) {
+__device__ __forceinline__ void store_out_row(uint16_t* dst, uint32_t tsrc, int ncols, bool valid, int dt,
+                                              float mul = 1.f) {
 #pragma unroll 1
   for (int c = 0; c < ncols; c += 32) {
     uint32_t r[32];
@@ -27,10 +28,10 @@ __device__ __forceinline__ void store_out_row(uint16_t* dst, uint32_t tsrc, int 
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
         uint4 w;
-        w.x = pack2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), dt);
-        w.y = pack2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]), dt);
-        w.z = pack2(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]), dt);
-        w.w = pack2(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]), dt);
+        w.x = pack2(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul, dt);
+        w.y = pack2(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul, dt);
+        w.z = pack2(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul, dt);
+        w.w = pack2(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul, dt);
         *reinterpret_cast<uint4*>(dst + c + i) = w;
       }
     }
@@ -47,8 +48,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
                    const AttnParams p) {
   constexpr int QT = AT_BM * D * 2;          // [128 x D] tile
   constexpr int KT = BW_C * D * 2;           // [64 x D] tile
-  constexpr int DSB = AT_BM * BW_C * 2;      // [128 x 64] 16-bit tile
-  constexpr uint32_t TCOLS = 256;            // 64 (S) + 64 (dP) + D (dQ) <= 256
+  constexpr uint32_t TCOLS = (D == 64) ? 256 : 512;   // 64 (S) + 64 (dP) + D (dQ) + 32 (dS as 16-bit pairs)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   if (status_poisoned(p.status)) return;
   if ((reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {
@@ -59,8 +59,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
   uint8_t* sdO = sQ + QT;
   uint8_t* sK = sdO + QT;            // BW_ST stages
   uint8_t* sV = sK + BW_ST * KT;     // BW_ST stages
-  uint8_t* sdS = sV + BW_ST * KT;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + DSB);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + BW_ST * KT);
   uint64_t* qdo_full = bars;
   uint64_t* kv_full = bars + 1;      // [BW_ST]
   uint64_t* sdp_full = bars + 4;
@@ -95,14 +94,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tdP = tmem + BW_C, tdQ = tmem + 2 * BW_C;
+  const uint32_t tS = tmem, tdP = tmem + BW_C, tdQ = tmem + 2 * BW_C, tdS = tmem + 2 * BW_C + D;
 
   if (warp == 4) {
     if (lane == 0) {   // ---------------- TMA + MMA ----------------
       const uint32_t fmt = p.is_bf16 ? 1u : 0u;
       const uint32_t idesc_s = make_idesc(fmt, 0, 0, AT_BM, BW_C);
       const uint32_t idesc_dq = make_idesc(fmt, 0, 1, AT_BM, D);
-      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO);
       auto load_kv = [&](int j) {
         const int st = j % BW_ST;
         mbar_expect_tx(&kv_full[st], 2 * KT);
@@ -135,7 +134,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
         const uint32_t aK = smem_u32(sK + (j % BW_ST) * KT);
 #pragma unroll
         for (int kk = 0; kk < BW_C / 16; ++kk)
-          umma_f16(tdQ, desc_kmajor(adS, kk, AT_BM), desc_mnmajor(aK, kk, BW_C), idesc_dq, (j > 0 || kk > 0));
+          umma_f16_ts(tdQ, tdS + kk * 8, desc_mnmajor(aK, kk, BW_C), idesc_dq, (j > 0 || kk > 0));
         umma_commit(acc_done);
         // tile j - 1 is retired (the row threads waited for it before they signalled ds_ready(j)): refill
         // its stage with tile j - 1 + BW_ST, a full iteration before anything needs it
@@ -177,27 +176,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constan
 #pragma unroll
           for (int i = 0; i < 32; ++i) rs[c][i] = (c * 32 + i <= lim) ? rs[c][i] : 0xff800000u;
       }
+      // dS = P o (dP - delta) as 16-bit pairs (the softmax scale is applied once, to dQ at the end)
+      uint32_t dsp[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        float ds[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pr = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse2));
-          ds[i] = pr * (__uint_as_float(rp[c][i]) - dl) * p.scale;
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[c][i]), sl2, -lse2));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[c][i + 1]), sl2, -lse2));
+          const float d0 = p0 * (__uint_as_float(rp[c][i]) - dl);
+          const float d1 = p1 * (__uint_as_float(rp[c][i + 1]) - dl);
+          dsp[c * 16 + i / 2] = p.is_bf16 ? pack2c<true>(d0, d1) : pack2c<false>(d0, d1);
         }
-        // the dS tile is single-buffered: the previous iteration's dQ MMA has to be done reading it
-        if (c == 0 && j > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (j - 1) & 1, 51))) { ok = false; break; }
-        store_row_chunk(sdS, t, c * 32, ds, p.is_bf16, AT_BM * 128);
       }
-      if (!ok) break;
+      // dS lives in tensor memory (A operand of the dQ MMA), single-buffered: the previous iteration's MMA has
+      // to be done reading it
+      if (j > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (j - 1) & 1, 51))) { ok = false; break; }
+      tc_fence_after_sync();
+      tmem_st_32x32b_x32(tdS + lane_base, dsp);
+      tmem_st_wait();
       tc_fence_before_sync();
-      fence_proxy_async_smem();
       mbar_arrive(ds_ready);
     }
     if (ok && __all_sync(0xffffffffu, AT_WAIT(acc_done, (n_kv - 1) & 1, 52))) {
       tc_fence_after_sync();
       uint16_t* drow = reinterpret_cast<uint16_t*>(p.dq) + (((size_t)b * p.S + row) * p.Hq + h) * D;
-      store_out_row(drow, tdQ + lane_base, D, row < p.S, p.is_bf16 ? DT_BF16 : DT_F16);
+      store_out_row(drow, tdQ + lane_base, D, row < p.S, p.is_bf16 ? DT_BF16 : DT_F16, p.scale);
     }
   }
   tc_fence_before_sync();
@@ -488,7 +492,7 @@ static int launch_bwd(const CUtensorMap& tq128, const CUtensorMap& tdo128, const
                       cudaStream_t st) {
   // no alignment pad: shared memory of a CTA starts 1024-aligned (checked in the kernels), and at D = 64 two
   // CTAs have to fit in one SM
-  const int smem_dq = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + AT_BM * BW_C * 2 + 128;
+  const int smem_dq = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + 128;
   const int smem_kv = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + 2 * AT_BM * BW_C * 2 + 128;
   static bool cfg = false;
   if (!cfg) {
