@@ -9,6 +9,8 @@ replicated); the MLP uses the fused SwiGLU kernel; `tie_word_embeddings=True` re
 one Parameter between `embed_tokens` and `lm_head`; `QwenForCausalLM(idx, labels=...)` runs the
 fused cross-entropy and returns `(loss, logits)`.
 """
+import torch
+
 from ... import nn
 from ...nn import functional as F
 from ...tensor import Tensor
@@ -119,6 +121,23 @@ class QwenForCausalLM(nn.Module):
         loss = F.cross_entropy(F.reshape(logits, (-1, V)), labels, ignore_index=-100,
                                _inplace_backward=not return_logits)
         return (loss, logits) if return_logits else loss
+
+    def generate(self, input_ids, max_new_tokens=100, temperature=1.0, top_k=None, top_p=None):
+        """Appends `max_new_tokens` sampled tokens to `input_ids` [B, S] (temperature 0: greedy).  The prompt is
+        re-encoded every step (no KV cache in this model class, as in the reference)."""
+        from ... import grad_mode
+        from .sampling import sample_next
+        was_training = self.training
+        self.eval()
+        out = input_ids
+        with grad_mode.no_grad():
+            for _ in range(max_new_tokens):
+                logits = self(out)
+                tok = sample_next(logits._t[:, -1, :], temperature, top_k, top_p)
+                out = Tensor._wrap(torch.cat((out._t, tok.to(out._t.dtype)), dim=1))
+        if was_training:
+            self.train()
+        return out
 
     def load_state_dict(self, state_dict, strict=True):
         sd = dict(state_dict)

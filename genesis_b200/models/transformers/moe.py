@@ -25,6 +25,7 @@ from ...function import Function, AMPPolicy
 from ...nn import functional as F
 from ...nn.modules.module import Module, Parameter
 from ...ops import dispatch as K
+from .sampling import sample_next
 from ...tensor import Tensor
 from ...amp_state import amp_state
 from .components import RotaryEmbedding, apply_rope
@@ -495,20 +496,7 @@ class MoEForCausalLM(MoEPreTrainedModel):
         with grad_mode.no_grad():
             for _ in range(max_new_tokens):
                 logits = self(generated)
-                nxt = logits._t[:, -1, :].float()
-                if temperature != 1.0:
-                    nxt = nxt / temperature
-                if top_k is not None:
-                    v, i = torch.topk(nxt, top_k, dim=-1)
-                    nxt = torch.full_like(nxt, float("-inf")).scatter_(-1, i, v)
-                probs = torch.softmax(nxt, -1)
-                if top_p is not None:
-                    sp, si = torch.sort(probs, descending=True)
-                    keep = (torch.cumsum(sp, -1) - sp) < top_p
-                    sp = sp * keep
-                    probs = torch.zeros_like(probs).scatter_(-1, si, sp)
-                    probs = probs / probs.sum(-1, keepdim=True)
-                tok = torch.multinomial(probs.cpu(), 1).to(probs.device)
+                tok = sample_next(logits._t[:, -1, :], temperature, top_k, top_p)
                 generated = Tensor._wrap(torch.cat((generated._t, tok.to(generated._t.dtype)), dim=1))
         return generated
 
