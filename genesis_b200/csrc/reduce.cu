@@ -66,6 +66,7 @@ __global__ void reduce_mid_kernel(const T* __restrict__ x, O* __restrict__ out, 
   const long long r0 = sp * chunk, r1 = (r0 + chunk < red) ? r0 + chunk : red;
   const T* p = x + o * red * inner + col;
   float acc = red_init(op);
+#pragma unroll 8
   for (long long r = r0; r < r1; ++r) acc = red_comb(op, acc, Cvt<T>::to_f(p[r * inner]));
   out[((long long)sp * outer + o) * inner + col] = Cvt<O>::from_f(splits == 1 ? acc * scale : acc);
 }

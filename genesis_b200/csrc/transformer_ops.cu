@@ -84,6 +84,41 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ out, const 
   }
 }
 
+// Vector form: a thread rotates one 16-byte group of the first half against its partner group of the second
+// half (half % (16 / sizeof(T)) == 0, 16-byte aligned rows).
+template <typename T>
+__global__ void rope_vec_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restrict__ cosb,
+                                const float* __restrict__ sinb, const long long* __restrict__ positions, int B, int S,
+                                int H, int D, int inverse) {
+  constexpr int V = Vec16<T>::N;
+  const int half = D / 2;
+  const int gpr = half / V;                                  // vector groups per half row
+  const long long total = (long long)B * S * H * gpr;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int g = (int)(i % gpr);
+    const long long r = i / gpr;                             // (b, s, h)
+    const long long bs = r / H;
+    const int s = (int)(bs % S);
+    const long long pos = positions ? positions[bs] : s;
+    const float* cp = cosb + pos * D + g * V;
+    const float* sp = sinb + pos * D + g * V;
+    const long long base = r * D + g * V;
+    const Vec16<T> a = ld16(x + base), b2 = ld16(x + base + half);
+    Vec16<T> oa, ob;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float c = cp[j];
+      const float sn = inverse ? -sp[j] : sp[j];
+      const float x1 = Cvt<T>::to_f(a.v[j]), x2 = Cvt<T>::to_f(b2.v[j]);
+      oa.v[j] = Cvt<T>::from_f(x1 * c - x2 * sn);
+      ob.v[j] = Cvt<T>::from_f(x2 * c + x1 * sn);
+    }
+    st16(out + base, oa);
+    st16(out + base + half, ob);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // row gather / scatter
 // ------------------------------------------------------------------------------------------
@@ -226,8 +261,15 @@ extern "C" int gb_rope(const void* x, void* out, const float* cosb, const float*
                        int B, int S, int H, int D, int inverse, int dt, cudaStream_t st) {
   const long long total = (long long)B * S * H * (D / 2);
   if (total == 0) return 0;
-  GB_DISPATCH_FLOAT(dt, T, rope_kernel<T><<<gb_grid(total, 256), 256, 0, st>>>(
-      (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse));
+  const int es = dt == DT_F32 ? 4 : 2;
+  const bool vec = (D / 2) % (16 / es) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (vec) {
+    GB_DISPATCH_FLOAT(dt, T, rope_vec_kernel<T><<<gb_grid(total / Vec16<T>::N, 256), 256, 0, st>>>(
+        (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse));
+  } else {
+    GB_DISPATCH_FLOAT(dt, T, rope_kernel<T><<<gb_grid(total, 256), 256, 0, st>>>(
+        (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse));
+  }
   return (int)cudaGetLastError();
 }
 

@@ -351,8 +351,9 @@ class _HookHandle:
 _adopted = set()   # data pointers adopted as leaf gradients during the current backward pass
 
 
-def _accumulate_leaf(t, g):
-    """Leaf gradient: tensor hooks, accumulation into `.grad`, post-accumulate hooks."""
+def _accumulate_leaf(t, g, fire_post_hooks=True):
+    """Leaf gradient: tensor hooks, accumulation into `.grad`, post-accumulate hooks (`fire_post_hooks=False`
+    while further contributions to the same leaf are still to come in this backward pass)."""
     if t._hooks:
         gw = t.apply_hooks(Tensor._wrap(g))
         g = gw._t
@@ -377,7 +378,7 @@ def _accumulate_leaf(t, g):
             t.grad = Tensor._wrap(g)
     else:
         K.add_(t.grad._t, g)
-    if t._post_hooks:
+    if fire_post_hooks and t._post_hooks:
         for h in t._post_hooks:
             h(t)
 
@@ -411,6 +412,13 @@ def _run_backward(root, g, retain_graph):
     from .ops import dispatch as K
     order = _topo(root.creator)
     pending = {id(root.creator): {root.idx: g}}
+    # A leaf used several times in the graph (tied weights) is accumulated several times; its post-accumulate
+    # hooks (DDP's "gradient is final" signal) must fire once, after the last contribution.
+    uses = {}
+    for node in order:
+        for e in node.edges:
+            if e is not None and e.leaf is not None and e.leaf._post_hooks:
+                uses[id(e.leaf)] = uses.get(id(e.leaf), 0) + 1
     for node in order:
         slot = pending.pop(id(node), None)
         if slot is None:
@@ -449,7 +457,9 @@ def _run_backward(root, g, retain_graph):
             if isinstance(gi, Tensor):
                 gi = gi._t
             if e.leaf is not None:
-                _accumulate_leaf(e.leaf, gi)
+                left = uses.get(id(e.leaf), 1) - 1
+                uses[id(e.leaf)] = left
+                _accumulate_leaf(e.leaf, gi, left <= 0)
             else:
                 d = pending.get(id(e.node))
                 if d is None:

@@ -155,6 +155,38 @@ def scenario_ddp(a):
     assert ddp.fc1 is model.fc1
 
 
+def scenario_ddp_tied(a):
+    """Tied embedding / output weights: the parameter receives two gradient contributions per backward pass; its
+    bucket must be reduced after the second one."""
+    from genesis_b200.models.transformers import TransformerConfig, QwenForCausalLM
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    cfg = TransformerConfig(vocab_size=211, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=32,
+                            tie_word_embeddings=True)
+    genesis.manual_seed(3)
+    ref = QwenForCausalLM(cfg).to(d)
+    genesis.manual_seed(3)
+    model = QwenForCausalLM(cfg).to(d)
+    ddp = nn.DistributedDataParallel(model, bucket_cap_mb=0.05)
+    rs = np.random.RandomState(100 + r)
+    idx = genesis.Tensor(torch.from_numpy(rs.randint(0, 211, (2, 16))).to(d))
+    lab = genesis.Tensor(torch.from_numpy(rs.randint(0, 211, (32,))).to(d))
+    for step in range(2):
+        for m in (ref, model):
+            for p_ in m.parameters():
+                p_.grad = None
+        loss_ref, _ = ref(idx, labels=lab)
+        loss_ref.backward()
+        loss, _ = ddp(idx, labels=lab)
+        loss.backward()
+        if d != "cpu":
+            torch.cuda.synchronize()
+        for (n1, p1), (n2, p2) in zip(ref.named_parameters(), model.named_parameters()):
+            g = p1.grad._t.clone()
+            tdist.all_reduce(g)
+            assert torch.allclose(p2.grad._t, g / w, atol=2e-5, rtol=1e-4), (step, n1, float((p2.grad._t - g / w).abs().max()))
+
+
 def scenario_ddp_amp(a):
     """fp16-style loss scaling through DDP: an overflow on ONE rank must skip the step on ALL ranks."""
     r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)

@@ -335,3 +335,14 @@ def test_tensor_basics():
     genesis.manual_seed(3)
     assert np.array_equal(a, genesis.randn(4).numpy())
     assert genesis.allclose(genesis.ones(3), genesis.ones(3))
+
+
+def test_post_accumulate_hook_fires_once_for_a_tensor_used_twice():
+    import genesis_b200 as genesis
+    w = genesis.Tensor(torch.tensor([1.0, 2.0, 3.0]), requires_grad=True)
+    seen = []
+    w.register_post_accumulate_grad_hook(lambda t: seen.append(t.grad._t.clone()))
+    x = genesis.Tensor(torch.tensor([2.0, 2.0, 2.0]))
+    ((w * x).sum() + (w * w).sum()).backward()
+    assert len(seen) == 1                                       # one call, with the complete gradient
+    assert torch.allclose(seen[0], torch.tensor([2.0 + 2.0, 2.0 + 4.0, 2.0 + 6.0]))

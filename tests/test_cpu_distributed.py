@@ -77,7 +77,7 @@ def test_single_process_group_and_error_strings():
     assert {o.name for o in dist.ReduceOp} >= {"SUM", "PRODUCT", "MAX", "MIN"}
 
 
-@pytest.mark.parametrize("scenario", ["collectives", "ddp", "ddp_amp", "ep", "heartbeat"])
+@pytest.mark.parametrize("scenario", ["collectives", "ddp", "ddp_tied", "ddp_amp", "ep", "heartbeat"])
 def test_two_cpu_ranks(scenario):
     launch(scenario, world=2, backend="gloo")
 

