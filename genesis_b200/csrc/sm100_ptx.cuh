@@ -17,7 +17,7 @@ namespace gb {
 // status word shared by all kernels of the library: status[0] = code (0 ok), [1] = site,
 // [2] = block, [3] = extra.  The host reads it after synchronising.
 // ---------------------------------------------------------------------------------------------
-enum : int { GB_OK = 0, GB_ERR_MBAR_TIMEOUT = 1, GB_ERR_FLAG_TIMEOUT = 2, GB_ERR_BAD_ARG = 3 };
+enum : int { GB_OK = 0, GB_ERR_MBAR_TIMEOUT = 1, GB_ERR_FLAG_TIMEOUT = 2, GB_ERR_BAD_ARG = 3, GB_ERR_BAD_INDEX = 4 };
 
 __device__ __forceinline__ void report_error(int* status, int code, int site, int extra) {
   if (status != nullptr && atomicCAS(status, 0, code) == 0) {

@@ -5,6 +5,7 @@
 //   Philox-4x32-10 uniform / normal / randint / dropout   (reference: LCG kernels, ops/cuda/random_ops.py)
 //   row gather / scatter-add for mixture-of-experts dispatch and combine
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace gb {
 
@@ -122,10 +123,12 @@ __global__ void rope_vec_kernel(const T* __restrict__ x, T* __restrict__ out, co
 // ------------------------------------------------------------------------------------------
 // row gather / scatter
 // ------------------------------------------------------------------------------------------
-// out[i, :] = src[idx[i], :] (zeros when idx[i] < 0); 16-byte vectors, one warp per row chunk
+// out[i, :] = src[idx[i], :] (zeros when idx[i] < 0); 16-byte vectors, one warp per row chunk.
+// An index >= src_rows (a token id outside the table) is never dereferenced: the row reads as zeros and the
+// status word records {GB_ERR_BAD_INDEX, site 1, block, index}.
 template <typename E, typename TI>
 __global__ void gather_rows_kernel(const E* __restrict__ src, const TI* __restrict__ idx, E* __restrict__ out,
-                                   long long nrows, int vec_per_row) {
+                                   long long nrows, int vec_per_row, long long src_rows, int* __restrict__ status) {
   const long long total = nrows * vec_per_row;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -133,7 +136,8 @@ __global__ void gather_rows_kernel(const E* __restrict__ src, const TI* __restri
     const int c = (int)(i % vec_per_row);
     const long long s = (long long)idx[r];
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (s >= 0) v = reinterpret_cast<const uint4*>(src)[s * vec_per_row + c];
+    if (s >= src_rows) { if (c == 0) report_error(status, GB_ERR_BAD_INDEX, 1, (int)s); }
+    else if (s >= 0) v = reinterpret_cast<const uint4*>(src)[s * vec_per_row + c];
     reinterpret_cast<uint4*>(out)[i] = v;
   }
 }
@@ -141,14 +145,16 @@ __global__ void gather_rows_kernel(const E* __restrict__ src, const TI* __restri
 // acc[idx[i], :] += src[i, :] with fp32 atomics (acc fp32)
 template <typename T, typename TI>
 __global__ void scatter_add_rows_kernel(const T* __restrict__ src, const TI* __restrict__ idx,
-                                        float* __restrict__ acc, long long nrows, int cols) {
+                                        float* __restrict__ acc, long long nrows, int cols, long long acc_rows,
+                                        int* __restrict__ status) {
   const long long total = nrows * cols;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const long long r = i / cols;
     const int c = (int)(i % cols);
     const long long d = (long long)idx[r];
-    if (d >= 0) atomicAdd(acc + d * cols + c, Cvt<T>::to_f(src[i]));
+    if (d >= acc_rows) { if (c == 0) report_error(status, GB_ERR_BAD_INDEX, 2, (int)d); }
+    else if (d >= 0) atomicAdd(acc + d * cols + c, Cvt<T>::to_f(src[i]));
   }
 }
 
@@ -275,23 +281,23 @@ extern "C" int gb_rope(const void* x, void* out, const float* cosb, const float*
 
 // rows of `row_bytes` bytes (multiple of 16, 16-byte aligned bases)
 extern "C" int gb_gather_rows(const void* src, const void* idx, void* out, long long nrows, long long row_bytes,
-                              int idx_is_i64, cudaStream_t st) {
+                              int idx_is_i64, long long src_rows, int* status, cudaStream_t st) {
   if (nrows == 0) return 0;
   const int vpr = (int)(row_bytes / 16);
   const int g = gb_grid(nrows * vpr, 256);
-  if (idx_is_i64) gather_rows_kernel<uint4, long long><<<g, 256, 0, st>>>((const uint4*)src, (const long long*)idx, (uint4*)out, nrows, vpr);
-  else gather_rows_kernel<uint4, int><<<g, 256, 0, st>>>((const uint4*)src, (const int*)idx, (uint4*)out, nrows, vpr);
+  if (idx_is_i64) gather_rows_kernel<uint4, long long><<<g, 256, 0, st>>>((const uint4*)src, (const long long*)idx, (uint4*)out, nrows, vpr, src_rows, status);
+  else gather_rows_kernel<uint4, int><<<g, 256, 0, st>>>((const uint4*)src, (const int*)idx, (uint4*)out, nrows, vpr, src_rows, status);
   return (int)cudaGetLastError();
 }
 
 extern "C" int gb_scatter_add_rows(const void* src, const void* idx, float* acc, long long nrows, int cols, int dt,
-                                   int idx_is_i64, cudaStream_t st) {
+                                   int idx_is_i64, long long acc_rows, int* status, cudaStream_t st) {
   if (nrows == 0) return 0;
   const int g = gb_grid(nrows * cols, 256);
   if (idx_is_i64) {
-    GB_DISPATCH_FLOAT(dt, T, scatter_add_rows_kernel<T, long long><<<g, 256, 0, st>>>((const T*)src, (const long long*)idx, acc, nrows, cols));
+    GB_DISPATCH_FLOAT(dt, T, scatter_add_rows_kernel<T, long long><<<g, 256, 0, st>>>((const T*)src, (const long long*)idx, acc, nrows, cols, acc_rows, status));
   } else {
-    GB_DISPATCH_FLOAT(dt, T, scatter_add_rows_kernel<T, int><<<g, 256, 0, st>>>((const T*)src, (const int*)idx, acc, nrows, cols));
+    GB_DISPATCH_FLOAT(dt, T, scatter_add_rows_kernel<T, int><<<g, 256, 0, st>>>((const T*)src, (const int*)idx, acc, nrows, cols, acc_rows, status));
   }
   return (int)cudaGetLastError();
 }

@@ -13,12 +13,17 @@ functions, cast cache for parameters).  Differences by design:
 * leaf gradients run the tensor's hooks and post-accumulate hooks, which is what
   lets `DistributedDataParallel` overlap communication with backward.
 """
+import os
 from enum import Enum
 
 import torch
 
 from . import grad_mode
 from .amp_state import amp_state
+
+
+# GENESIS_NVTX=1: one NVTX range per Function forward (and "<name>.backward" per backward node), for timelines
+_NVTX = os.environ.get("GENESIS_NVTX", "0") == "1" and torch.cuda.is_available()
 
 
 class AMPPolicy(Enum):
@@ -117,6 +122,8 @@ class Function:
 
         prev = grad_on
         grad_mode._set(False)
+        if _NVTX:
+            torch.cuda.nvtx.range_push(cls.__name__)
         try:
             if cls.raw:
                 raw_args = tuple(_unwrap(a) for a in args)
@@ -125,6 +132,8 @@ class Function:
                 out = cls.forward(ctx, *args, **kwargs)
         finally:
             grad_mode._set(prev)
+            if _NVTX:
+                torch.cuda.nvtx.range_pop()
 
         is_tuple = isinstance(out, (tuple, list))
         outs = out if is_tuple else (out,)

@@ -38,7 +38,7 @@ _SIGS = {
     "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
     "gb_ce_fwd": "ppppllliip", "gb_ce_bwd": "ppppplll" + "iip",
     "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip", "gb_rope": "pppppiiiiiip",
-    "gb_gather_rows": "pppllip", "gb_scatter_add_rows": "pppliiip",
+    "gb_gather_rows": "pppllilpp", "gb_scatter_add_rows": "pppliiilpp",
     "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
     "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiippp", "gb_sgd_multi": "pilfffp",
     "gb_grad_multi": "pilpfppip",
@@ -115,6 +115,9 @@ def check_status(dev=None):
     rec = st.tolist()
     if rec[0] != 0:
         st.zero_()
+        if rec[0] == 4:
+            raise IndexError(f"index out of range in a native kernel (site={rec[1]}: 1 row gather / embedding lookup, "
+                             f"2 row scatter-add; block={rec[2]}, index={rec[3]}); the access was skipped")
         raise RuntimeError(f"device-side wait expired: code={rec[0]} site={rec[1]} block={rec[2]} extra={rec[3]}")
 
 
@@ -799,7 +802,8 @@ def gather_rows(x, rows):
         return NotImplemented
     out = torch.empty(rows.numel(), x.shape[1], dtype=x.dtype, device=x.device)
     _chk(lib().gb_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), rows.numel(), rb,
-                              1 if rows.dtype == torch.int64 else 0, _st()), "gather_rows")
+                              1 if rows.dtype == torch.int64 else 0, x.shape[0], status_tensor(x.device).data_ptr(),
+                              _st()), "gather_rows")
     return out
 
 
@@ -820,7 +824,8 @@ def scatter_add_rows(src, rows, num_rows, out_dtype):
         return NotImplemented
     acc = torch.zeros(num_rows, src.shape[1], dtype=F32, device=src.device)
     _chk(lib().gb_scatter_add_rows(src.data_ptr(), rows.data_ptr(), acc.data_ptr(), src.shape[0], src.shape[1],
-                                   _DT[src.dtype], 1 if rows.dtype == torch.int64 else 0, _st()), "scatter_add_rows")
+                                   _DT[src.dtype], 1 if rows.dtype == torch.int64 else 0, num_rows,
+                                   status_tensor(src.device).data_ptr(), _st()), "scatter_add_rows")
     od = out_dtype or src.dtype
     return acc if od == F32 else cast(acc, od)
 

@@ -228,7 +228,14 @@ class Tensor:
         return self._numpy().tolist()
 
     def item(self):
-        return self._t.item()
+        v = self._t.item()
+        if self._t.is_cuda:
+            # the host is synchronised here anyway: surface what the native kernels recorded (an expired
+            # bounded wait, an index that was out of range and skipped) at the point the user reads a result
+            from .ops import native
+            if native._status:
+                native.check_status(self._t.device)
+        return v
 
     def __float__(self):
         return float(self._t.item())
@@ -410,6 +417,7 @@ def _topo(root_node):
 
 def _run_backward(root, g, retain_graph):
     from .ops import dispatch as K
+    from . import function as _fn
     order = _topo(root.creator)
     pending = {id(root.creator): {root.idx: g}}
     # A leaf used several times in the graph (tied weights) is accumulated several times; its post-accumulate
@@ -442,10 +450,14 @@ def _run_backward(root, g, retain_graph):
                             gw = r
                     gl[i] = gw._t
             gouts = tuple(gl)
+        if _fn._NVTX:
+            torch.cuda.nvtx.range_push(cls.__name__ + ".backward")
         if cls.raw:
             res = cls.backward(ctx, *gouts)
         else:
             res = cls.backward(ctx, *[None if x is None else Tensor._wrap(x) for x in gouts])
+        if _fn._NVTX:
+            torch.cuda.nvtx.range_pop()
         if not retain_graph and not cls.keep_ctx:
             ctx.release()
         if not isinstance(res, (tuple, list)):

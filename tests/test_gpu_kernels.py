@@ -309,3 +309,29 @@ def test_moe_router(dt, T, E, k, renorm):
     ref = K.moe_router_bwd(dw, dp, pr, e.cpu(), w.cpu(), renorm)
     got = K.moe_router_bwd(dw.to(DEV), dp.to(DEV), probs, e, w, renorm)
     close(got, ref, torch.float32, scale=50)
+
+
+def test_out_of_range_token_id_is_skipped_and_reported():
+    import genesis_b200 as genesis
+    from genesis_b200.ops import native
+    table = torch.randn(10, 16, device="cuda", dtype=torch.bfloat16)
+    idx = torch.tensor([1, 3, 10, 2, 1 << 20], device="cuda")
+    native.status_tensor(table.device)                       # make sure the word exists
+    out = native.gather_rows(table, idx)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], table[1]) and torch.equal(out[3], table[2])
+    assert float(out[2].abs().sum()) == 0.0 and float(out[4].abs().sum()) == 0.0     # never dereferenced
+    with pytest.raises(IndexError):
+        native.check_status(table.device)
+    native.check_status(table.device)                        # cleared by the raise
+    # the same through the public API: the error surfaces where the loss is read
+    emb = genesis.nn.Embedding(10, 16).cuda()
+    y = emb(genesis.Tensor(torch.tensor([[0, 11]], device="cuda"))).sum()
+    with pytest.raises(IndexError):
+        y.item()
+    g = torch.ones(3, 16, device="cuda", dtype=torch.bfloat16)
+    acc = native.scatter_add_rows(g, torch.tensor([0, 12, 2], device="cuda"), 10, torch.float32)
+    torch.cuda.synchronize()
+    assert float(acc[0].sum()) == 16.0 and float(acc.sum()) == 32.0
+    with pytest.raises(IndexError):
+        native.check_status(table.device)
