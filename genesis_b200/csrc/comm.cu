@@ -16,8 +16,10 @@
 
 namespace gb {
 
+// 256 threads and at most 80 registers: 20 K registers per CTA, which fit beside a resident GEMM CTA (43.5 K of the
+// 64 K), so the reduction runs on SMs that backward keeps busy instead of taking SMs away from it.
 template <typename T>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(256, 3)
 allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, long long n, int rank, int world,
                        uint32_t epoch, float prescale, const float* __restrict__ loss_scale, int scale_is_reciprocal,
                        float* __restrict__ found_inf, unsigned long long budget_ns, int* __restrict__ status) {
@@ -237,7 +239,7 @@ extern "C" int gb_allreduce_fused(void* const* bufs, void* const* flags, long lo
   for (int i = 0; i < world; ++i) { tb.ptr[i] = bufs[i]; tf.ptr[i] = flags[i]; }
   GB_DISPATCH_FLOAT(dt, T, {
     if (n % (world * Vec16<T>::N) != 0) return -3;
-    allreduce_fused_kernel<T><<<ctas, 512, 0, st>>>(tb, tf, offset_elems, n, rank, world, epoch, prescale,
+    allreduce_fused_kernel<T><<<ctas, 256, 0, st>>>(tb, tf, offset_elems, n, rank, world, epoch, prescale,
                                                     loss_scale, scale_is_reciprocal, found_inf, budget_ns, status);
   });
   return (int)cudaGetLastError();

@@ -85,7 +85,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   if (status_poisoned(p.status)) return;
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // No alignment pad: the kernel has no static shared memory, so the dynamic part starts 1024-aligned.  The 2 KB this
+  // leaves free per SM is what lets a communication CTA (no shared memory of its own) share the SM with a GEMM CTA.
+  if ((reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {
+    if (threadIdx.x == 0) report_error(p.status, GB_ERR_BAD_ARG, 4, 0);
+    return;
+  }
+  uint8_t* smem = smem_raw;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BARRIER_OFFSET);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full = empty_bar + STAGES;
@@ -474,7 +480,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   auto kern = gemm_kernel<BN, STAGES, ESIZE, A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL + 1024);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -489,7 +495,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     grid = (int)(g < sms ? g : sms);
   }
   if (grid < 1) grid = 1;
-  kern<<<grid, 320, L::TOTAL + 1024, stream>>>(ta, tb, td, p);
+  kern<<<grid, 320, L::TOTAL, stream>>>(ta, tb, td, p);
   return (int)cudaGetLastError();
 }
 

@@ -24,6 +24,31 @@ __device__ __forceinline__ int load_row(const T* p, long long cols, Vec16<T> (&b
   return cnt;
 }
 
+// V consecutive weights starting at element `base` (16-byte aligned: base is a multiple of V) as floats
+template <typename TW, int V>
+__device__ __forceinline__ void load_weights(const TW* __restrict__ w, int base, float (&out)[V]) {
+  if constexpr (sizeof(TW) == 4) {
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      const float4 f = *reinterpret_cast<const float4*>(w + base + 4 * q);
+      out[4 * q] = f.x; out[4 * q + 1] = f.y; out[4 * q + 2] = f.z; out[4 * q + 3] = f.w;
+    }
+  } else {
+    const Vec16<TW> f = ld16(w + base);
+#pragma unroll
+    for (int j = 0; j < V; ++j) out[j] = Cvt<TW>::to_f(f.v[j]);
+  }
+}
+
+template <typename TW, int V>
+__device__ __forceinline__ void load_weights_or(const TW* __restrict__ w, int base, float fill, float (&out)[V]) {
+  if (w != nullptr) load_weights<TW, V>(w, base, out);
+  else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) out[j] = fill;
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // RMSNorm
 // ------------------------------------------------------------------------------------------
@@ -51,9 +76,10 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restr
       const int i = threadIdx.x + k * NORM_THREADS;
       if (i < nv) {
         Vec16<T> o;
+        float wv[V];
+        load_weights<TW, V>(w, i * V, wv);
 #pragma unroll
-        for (int j = 0; j < V; ++j)
-          o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(buf[k].v[j]) * r * Cvt<TW>::to_f(w[i * V + j]));
+        for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(buf[k].v[j]) * r * wv[j]);
         st16(y + row * cols + (long long)i * V, o);
       }
     }
@@ -83,14 +109,17 @@ rmsnorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* _
 #pragma unroll
     for (int k = 0; k < NORM_MAXV; ++k) {
       const int i = threadIdx.x + k * NORM_THREADS;
-      if (i < nv)
+      if (i < nv) {
+        float wv[V];
+        load_weights<TW, V>(w, i * V, wv);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
           const float gg = Cvt<T>::to_f(gb_[k].v[j]);
-          dot += gg * Cvt<TW>::to_f(w[i * V + j]) * xh;
+          dot += gg * wv[j] * xh;
           dwacc[k][j] += gg * xh;
         }
+      }
     }
     dot = block_sum(dot, sh) / cols;
 #pragma unroll
@@ -98,10 +127,12 @@ rmsnorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* _
       const int i = threadIdx.x + k * NORM_THREADS;
       if (i < nv) {
         Vec16<T> o;
+        float wv[V];
+        load_weights<TW, V>(w, i * V, wv);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
-          const float gw = Cvt<T>::to_f(gb_[k].v[j]) * Cvt<TW>::to_f(w[i * V + j]);
+          const float gw = Cvt<T>::to_f(gb_[k].v[j]) * wv[j];
           o.v[j] = Cvt<T>::from_f(r * (gw - xh * dot));
         }
         st16(dx + row * cols + (long long)i * V, o);
@@ -150,13 +181,12 @@ layernorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW
       const int i = threadIdx.x + k * NORM_THREADS;
       if (i < nv) {
         Vec16<T> o;
+        float wv[V], bv[V];
+        load_weights_or<TW, V>(w, i * V, 1.f, wv);
+        load_weights_or<TW, V>(b, i * V, 0.f, bv);
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          float v = (Cvt<T>::to_f(buf[k].v[j]) - mu) * r;
-          if (w != nullptr) v *= Cvt<TW>::to_f(w[i * V + j]);
-          if (b != nullptr) v += Cvt<TW>::to_f(b[i * V + j]);
-          o.v[j] = Cvt<T>::from_f(v);
-        }
+        for (int j = 0; j < V; ++j)
+          o.v[j] = Cvt<T>::from_f((Cvt<T>::to_f(buf[k].v[j]) - mu) * r * wv[j] + bv[j]);
         st16(y + row * cols + (long long)i * V, o);
       }
     }
@@ -185,17 +215,20 @@ layernorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW*
 #pragma unroll
     for (int k = 0; k < NORM_MAXV; ++k) {
       const int i = threadIdx.x + k * NORM_THREADS;
-      if (i < nv)
+      if (i < nv) {
+        float wv[V];
+        load_weights_or<TW, V>(w, i * V, 1.f, wv);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = (Cvt<T>::to_f(xb[k].v[j]) - mu) * r;
           const float gg = Cvt<T>::to_f(gb_[k].v[j]);
-          const float gw = w != nullptr ? gg * Cvt<TW>::to_f(w[i * V + j]) : gg;
+          const float gw = gg * wv[j];
           s1 += gw;
           s2 += gw * xh;
           dwacc[k][j] += gg * xh;
           dbacc[k][j] += gg;
         }
+      }
     }
     s1 = block_sum(s1, sh) / cols;
     s2 = block_sum(s2, sh) / cols;
@@ -204,11 +237,12 @@ layernorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW*
       const int i = threadIdx.x + k * NORM_THREADS;
       if (i < nv) {
         Vec16<T> o;
+        float wv[V];
+        load_weights_or<TW, V>(w, i * V, 1.f, wv);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = (Cvt<T>::to_f(xb[k].v[j]) - mu) * r;
-          const float gg = Cvt<T>::to_f(gb_[k].v[j]);
-          const float gw = w != nullptr ? gg * Cvt<TW>::to_f(w[i * V + j]) : gg;
+          const float gw = Cvt<T>::to_f(gb_[k].v[j]) * wv[j];
           o.v[j] = Cvt<T>::from_f(r * (gw - s1 - xh * s2));
         }
         st16(dx + row * cols + (long long)i * V, o);

@@ -80,6 +80,97 @@ __global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, l
   }
 }
 
+// Register-resident rows: cols / V <= 256 * MV vectors, 16-byte aligned.  The row is read once (MV 16-byte loads per
+// thread, all in flight together), max and sum are two block reductions over registers, the result is written with
+// 16-byte stores.  HBM traffic = one read + one write of the tensor.
+constexpr int SM_THREADS = 256;
+
+template <typename T, int MV>
+__global__ void __launch_bounds__(SM_THREADS)
+softmax_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int cols, int log_mode) {
+  __shared__ float sh[32];
+  constexpr int V = Vec16<T>::N;
+  const int nv = cols / V;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* p = x + row * cols;
+    Vec16<T> buf[MV];
+#pragma unroll
+    for (int k = 0; k < MV; ++k) {
+      const int i = threadIdx.x + k * SM_THREADS;
+      if (i < nv) buf[k] = ld16(p + (long long)i * V);
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < MV; ++k)
+      if (threadIdx.x + k * SM_THREADS < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) mx = fmaxf(mx, Cvt<T>::to_f(buf[k].v[j]));
+    mx = block_max(mx, sh);
+    const float m = mx == -INFINITY ? 0.f : mx;            // a row of -inf gives zeros, not NaN
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < MV; ++k)
+      if (threadIdx.x + k * SM_THREADS < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) sum += __expf(Cvt<T>::to_f(buf[k].v[j]) - m);
+    sum = block_sum(sum, sh);
+    const float inv = 1.f / sum, lse = m + __logf(sum);
+#pragma unroll
+    for (int k = 0; k < MV; ++k) {
+      const int i = threadIdx.x + k * SM_THREADS;
+      if (i < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float v = Cvt<T>::to_f(buf[k].v[j]);
+          o.v[j] = Cvt<T>::from_f(log_mode ? v - lse : __expf(v - m) * inv);
+        }
+        st16(y + row * cols + (long long)i * V, o);
+      }
+    }
+  }
+}
+
+template <typename T, int MV>
+__global__ void __launch_bounds__(SM_THREADS)
+softmax_bwd_reg_kernel(const T* __restrict__ g, const T* __restrict__ y, T* __restrict__ dx, long long rows, int cols,
+                       int log_mode) {
+  __shared__ float sh[32];
+  constexpr int V = Vec16<T>::N;
+  const int nv = cols / V;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    Vec16<T> gb_[MV], yb[MV];
+#pragma unroll
+    for (int k = 0; k < MV; ++k) {
+      const int i = threadIdx.x + k * SM_THREADS;
+      if (i < nv) { gb_[k] = ld16(g + row * cols + (long long)i * V); yb[k] = ld16(y + row * cols + (long long)i * V); }
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < MV; ++k)
+      if (threadIdx.x + k * SM_THREADS < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float gg = Cvt<T>::to_f(gb_[k].v[j]);
+          acc += log_mode ? gg : gg * Cvt<T>::to_f(yb[k].v[j]);
+        }
+    acc = block_sum(acc, sh);
+#pragma unroll
+    for (int k = 0; k < MV; ++k) {
+      const int i = threadIdx.x + k * SM_THREADS;
+      if (i < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float gg = Cvt<T>::to_f(gb_[k].v[j]), yy = Cvt<T>::to_f(yb[k].v[j]);
+          o.v[j] = Cvt<T>::from_f(log_mode ? gg - __expf(yy) * acc : yy * (gg - acc));
+        }
+        st16(dx + row * cols + (long long)i * V, o);
+      }
+    }
+  }
+}
+
 // softmax: dx = y * (g - sum(g*y));  log-softmax: dx = g - exp(y) * sum(g)
 template <typename T>
 __global__ void softmax_bwd_kernel(const T* __restrict__ g, const T* __restrict__ y, T* __restrict__ dx,
@@ -164,6 +255,19 @@ extern "C" int gb_softmax_fwd(const void* x, void* y, long long rows, long long 
                               cudaStream_t st) {
   if (rows == 0) return 0;
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  const int vlen = dt == DT_F32 ? 4 : 8;
+  const bool reg = cols % vlen == 0 && cols / vlen <= SM_THREADS * 8 && cols < (1ll << 30) &&
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (reg) {
+    const long long nv = cols / vlen;
+#define SM_FWD(MVV) GB_DISPATCH_FLOAT(dt, T, softmax_fwd_reg_kernel<T, MVV><<<grid, SM_THREADS, 0, st>>>((const T*)x, (T*)y, rows, (int)cols, log_mode))
+    if (nv <= SM_THREADS) SM_FWD(1);
+    else if (nv <= 2 * SM_THREADS) SM_FWD(2);
+    else if (nv <= 4 * SM_THREADS) SM_FWD(4);
+    else SM_FWD(8);
+#undef SM_FWD
+    return (int)cudaGetLastError();
+  }
   GB_DISPATCH_FLOAT(dt, T, softmax_fwd_kernel<T><<<grid, row_block(cols), 0, st>>>((const T*)x, (T*)y, rows, cols, log_mode));
   return (int)cudaGetLastError();
 }
@@ -172,6 +276,18 @@ extern "C" int gb_softmax_bwd(const void* g, const void* y, void* dx, long long 
                               int dt, cudaStream_t st) {
   if (rows == 0) return 0;
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  const int vlen = dt == DT_F32 ? 4 : 8;
+  const bool reg = cols % vlen == 0 && cols / vlen <= SM_THREADS * 4 && cols < (1ll << 30) &&
+                   ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
+  if (reg) {
+    const long long nv = cols / vlen;
+#define SM_BWD(MVV) GB_DISPATCH_FLOAT(dt, T, softmax_bwd_reg_kernel<T, MVV><<<grid, SM_THREADS, 0, st>>>((const T*)g, (const T*)y, (T*)dx, rows, (int)cols, log_mode))
+    if (nv <= SM_THREADS) SM_BWD(1);
+    else if (nv <= 2 * SM_THREADS) SM_BWD(2);
+    else SM_BWD(4);
+#undef SM_BWD
+    return (int)cudaGetLastError();
+  }
   GB_DISPATCH_FLOAT(dt, T, softmax_bwd_kernel<T><<<grid, row_block(cols), 0, st>>>((const T*)g, (const T*)y, (T*)dx, rows, cols, log_mode));
   return (int)cudaGetLastError();
 }

@@ -1004,7 +1004,7 @@ def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None,
         # enough CTAs to keep ~1.5 MB of loads in flight for big buckets, one for tiny ones
         es = torch.empty(0, dtype=dtype).element_size()
         per_rank_vecs = n * es // 16 // max(st.world, 1)
-        ctas = max(1, min(int(os.environ.get("GENESIS_COMM_CTAS", 64)), (per_rank_vecs + 2047) // 2048))
+        ctas = max(1, min(int(os.environ.get("GENESIS_COMM_CTAS", 128)), (per_rank_vecs + 1023) // 1024))
     _chk(lib().gb_allreduce_fused(buf.ptr_table, st.flags.ptr_table, offset_elems, n, st.rank, st.world, epoch,
                                   float(prescale), None if inv_scale is None else inv_scale.data_ptr(),
                                   1 if scale_is_reciprocal else 0,
