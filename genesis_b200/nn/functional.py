@@ -1,7 +1,7 @@
 """Differentiable operations (`Function` subclasses) and their functional wrappers.
 
 Parity: reference `genesis/nn/functional.py` (op list, argument names such as
-`sum(a, axis, keepdims)`, AMP policy per op — SURVEY of the reference's policy
+`sum(a, axis, keepdims)`, AMP policy per op — the reference's policy
 table: matmul/relu/gelu/attention run in the autocast dtype; pow/log/exp/sqrt/
 sum/mean/logsumexp/sigmoid/tanh/softmax/layer-norm run in float32; shape, index
 and scalar ops preserve dtypes) plus the fused ops the reference builds from
