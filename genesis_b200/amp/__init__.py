@@ -177,3 +177,36 @@ class GradScaler:
         if self._scale is not None:
             self._scale.fill_(self._init_scale)
             self._growth_tracker.fill_(int(state.get("_growth_tracker", 0)))
+
+
+def get_amp_dtype(policy, *args, **kwargs):
+    """Target dtype of an op under `policy` (None = no cast).  Parity: reference `amp/__init__.py:46-79`."""
+    from .. import dtypes
+    from ..function import AMPPolicy
+    if policy == AMPPolicy.FP16:
+        from ..amp_state import amp_state
+        return dtypes.get_dtype(amp_state.dtype)
+    if policy == AMPPolicy.FP32:
+        return dtypes.float32
+    if policy == AMPPolicy.PRESERVE:
+        return None
+
+    def has(value, names):
+        if hasattr(value, "dtype") and getattr(value.dtype, "name", str(value.dtype)) in names:
+            return True
+        if isinstance(value, dict):
+            return any(has(v, names) for v in value.values())
+        if isinstance(value, (list, tuple)):
+            return any(has(v, names) for v in value)
+        return False
+
+    low = ("float16", "bfloat16")
+    if (has(args, ("float32",)) or has(kwargs, ("float32",))) and (has(args, low) or has(kwargs, low)):
+        return dtypes.float32
+    return None
+
+
+def get_amp_cache():
+    """The per-thread cache of low-precision parameter copies used inside `autocast`."""
+    from ..amp_state import amp_state
+    return amp_state.cache

@@ -307,3 +307,27 @@ def analyze_memory_fragmentation():
 get_fragmentation_stats = analyze_memory_fragmentation
 
 _config = _parse_memory_config()
+
+
+class _MemoryManager:
+    """Handle on the allocator statistics of one device (the reference returns its Python pool object here,
+    `cuda/__init__.py`; this one reads the native pool's counters or torch's allocator)."""
+
+    def __init__(self, device):
+        self.device = device
+
+    def get_stats(self):
+        return memory_stats(self.device)
+
+    def empty_cache(self):
+        return empty_cache()
+
+    def memory_summary(self):
+        return memory_summary(self.device)
+
+
+def get_memory_manager(device=None):
+    return _MemoryManager(current_device() if device is None else device)
+
+
+from ..device import Device  # noqa: E402,F401  (re-exported as in the reference)

@@ -1465,3 +1465,66 @@ def dropout(x, p=0.5, training=True):
     if p >= 1.0:
         return x * 0.0
     return DropoutFunction.apply(x, p)
+
+
+# ---- names the reference exports from this module, kept for drop-in imports ---------------------------------------
+class Norm(Function):
+    """L2 norm of all elements, sqrt(sum(a^2)).  (The reference's class of this name negates its input,
+    `functional.py:2065-2080`; this is the operation the name promises.)"""
+    raw = True
+    amp_policy = AMPPolicy.FP32
+
+    @staticmethod
+    def forward(ctx, a):
+        n = torch.sqrt(K.reduce("sum", K.mul(a, a), None, False))
+        ctx.save_for_backward(a, n)
+        return n
+
+    @staticmethod
+    def backward(ctx, g):
+        a, n = ctx.saved_tensors
+        return a * (g / torch.clamp(n, min=1e-30))
+
+
+def norm(a):
+    return Norm.apply(a)
+
+
+View = Reshape
+GetItemView = GetItem
+GetItemGather = GetItem
+
+
+class _FunctionalAlias:
+    """`X.apply(...)` for operations that are plain functions here (no gradient flows through them)."""
+
+    def __init__(self, fn):
+        self._fn = fn
+
+    def apply(self, *a, **k):
+        return self._fn(*a, **k)
+
+
+Equal = _FunctionalAlias(lambda a, b: eq(a, b))
+Argmax = _FunctionalAlias(lambda a, dim=None, keepdim=False: argmax(a, dim, keepdim))
+Argmin = _FunctionalAlias(lambda a, dim=None, keepdim=False: argmin(a, dim, keepdim))
+
+
+def cast_fp32(x):
+    """Differentiable cast to float32."""
+    from ..function import cast
+    return cast(x, torch.float32)
+
+
+cast_to_fp32 = cast_fp32
+CastFP32 = _FunctionalAlias(cast_fp32)
+
+
+def cast_to_fp16(x):
+    from ..function import cast
+    return cast(x, torch.float16)
+
+
+def sum_to_shape(data, shape):
+    """Sum the broadcast dimensions of `data` so that the result has `shape` (the inverse of broadcasting)."""
+    return Tensor._wrap(K.sum_to_shape(data._t if isinstance(data, Tensor) else data, tuple(shape)))

@@ -346,3 +346,22 @@ def test_post_accumulate_hook_fires_once_for_a_tensor_used_twice():
     ((w * x).sum() + (w * w).sum()).backward()
     assert len(seen) == 1                                       # one call, with the complete gradient
     assert torch.allclose(seen[0], torch.tensor([2.0 + 2.0, 2.0 + 4.0, 2.0 + 6.0]))
+
+
+def test_reference_export_names_exist_and_work():
+    import genesis_b200 as genesis
+    import genesis_b200.nn.functional as F
+    from genesis_b200.function import AMPPolicy
+    x = genesis.Tensor(torch.tensor([3.0, 4.0]), requires_grad=True)
+    n = F.norm(x)
+    n.backward()
+    assert abs(float(n.item()) - 5.0) < 1e-6 and torch.allclose(x.grad._t, torch.tensor([0.6, 0.8]))
+    assert F.View is F.Reshape and F.GetItemView is F.GetItem
+    assert F.Equal.apply(x, x)._t.all() and int(F.Argmax.apply(x)._t) == 1 and int(F.Argmin.apply(x)._t) == 0
+    assert F.cast_to_fp16(x).dtype == genesis.float16 and F.cast_fp32(F.cast_to_fp16(x)).dtype == genesis.float32
+    assert F.sum_to_shape(genesis.Tensor(torch.ones(3, 4)), (1, 4))._t.tolist() == [[3.0] * 4]
+    assert genesis.amp.get_amp_dtype(AMPPolicy.FP32) == genesis.float32
+    assert genesis.amp.get_amp_dtype(AMPPolicy.PRESERVE, x) is None
+    assert genesis.amp.get_amp_dtype(AMPPolicy.PROMOTE, x, F.cast_to_fp16(x)) == genesis.float32
+    assert isinstance(genesis.amp.get_amp_cache(), dict)
+    assert genesis.cuda.get_memory_manager(0).device == 0
