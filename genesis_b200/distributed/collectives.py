@@ -49,7 +49,8 @@ def _wrap_errors(fn, *a, **k):
         return fn(*a, **k)
     except RuntimeError as e:
         msg = str(e)
-        if "imeout" in msg or "timed out" in msg:
+        low = msg.lower()
+        if "timeout" in low or "timed out" in low:
             raise pg.CommTimeout(msg) from e
         raise
 

@@ -282,6 +282,27 @@ def scenario_ep(a):
             assert torch.allclose(g0, g1, atol=3e-2, rtol=3e-2), float((g0 - g1).abs().max())
 
 
+def scenario_skipped_collective(a):
+    """One rank does not enter a collective: the others get `CommTimeout` within the process-group budget instead of
+    hanging (host-made failure, CPU ranks only; `GENESIS_COMM_TIMEOUT_S` is short in this scenario)."""
+    import time
+    from genesis_b200.distributed.process_group import CommTimeout
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    t = genesis.Tensor(torch.ones(8, device=d))
+    dist.all_reduce(t)                                  # everyone takes part: fine
+    assert float(t._t[0]) == w
+    if r == w - 1:
+        time.sleep(6.0)                                 # this rank "forgets" the next collective
+    else:
+        t0 = time.time()
+        try:
+            dist.all_reduce(t)
+            raise AssertionError("all_reduce returned although a rank never joined")
+        except CommTimeout:
+            assert time.time() - t0 < 5.5
+    # no further collective: the group is left as is and every process exits on its own
+
+
 def scenario_heartbeat(a):
     """A rank that stops beating is reported by the others within the budget; nobody touches a GPU."""
     import time

@@ -97,3 +97,7 @@ def test_rank_that_never_joins_times_out():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120,
                        env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
     assert "TIMED_OUT" in r.stdout, r.stdout + r.stderr
+
+
+def test_rank_that_skips_a_collective_gives_timeout_on_the_others():
+    launch("skipped_collective", world=2, backend="gloo", env={"GENESIS_COMM_TIMEOUT_S": "3"}, timeout=120)
