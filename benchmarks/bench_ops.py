@@ -74,7 +74,7 @@ def build_cases(torch, genesis, F, K, dt, categories):
     if "norm" in categories:
         for cols in (1024, 4096, 16384):
             x = rnd(8192, cols)
-            w = torch.ones(cols, device="cuda")
+            w = torch.ones(cols, device="cuda", dtype=dt)
             gx, gw = g(x), g(w)
             nb = 2 * x.numel() * es
             cases += [("norm", "rmsnorm", f"8192x{cols}", lambda gx=gx, gw=gw: F.rms_norm(gx, gw, 1e-6),
@@ -99,7 +99,7 @@ def build_cases(torch, genesis, F, K, dt, categories):
                       lambda table=table, ids=ids: table[ids], 2 * 16384 * 896 * es, 0))
         x = torch.randn(4096, 4096, device="cuda")
         cases += [("index", "topk 8", "4096x4096 fp32", lambda: K.topk(x, 8, -1, True), lambda: torch.topk(x, 8, -1), x.numel() * 4, 0),
-                  ("index", "sort", "4096x4096 fp32", lambda: K.sort(x, -1, False), lambda: torch.sort(x, -1, stable=True), 2 * x.numel() * 4, 0),
+                  ("index", "sort", "4096x4096 fp32", lambda: K.sort(x, -1, False), lambda: torch.sort(x, dim=-1, stable=True), 2 * x.numel() * 4, 0),
                   ("index", "argmax", "4096x4096 fp32", lambda: K.argmax(x, -1), lambda: torch.argmax(x, -1), x.numel() * 4, 0)]
     return cases
 

@@ -149,6 +149,112 @@ rmsnorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* _
 }
 
 // ------------------------------------------------------------------------------------------
+// RMSNorm for narrow rows (cols <= 32 lanes x MVW vectors): one WARP per row, eight rows in flight per CTA, warp
+// shuffles instead of block barriers, the weight row held in registers for the whole kernel.  A row of 896 bf16
+// values keeps only 112 of a CTA's 256 threads busy in the row-per-CTA kernels above and pays two barriers per row.
+// ------------------------------------------------------------------------------------------
+constexpr int NORM_WARPS = NORM_THREADS / 32;
+
+template <typename T, typename TW, int MVW>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restrict__ y, float* __restrict__ rstd,
+                        long long rows, int cols, float eps) {
+  constexpr int V = Vec16<T>::N;
+  const int nv = cols / V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float wv[MVW][V];
+#pragma unroll
+  for (int k = 0; k < MVW; ++k)
+    if (lane + 32 * k < nv) load_weights<TW, V>(w, (lane + 32 * k) * V, wv[k]);
+  for (long long row = (long long)blockIdx.x * NORM_WARPS + warp; row < rows; row += (long long)gridDim.x * NORM_WARPS) {
+    Vec16<T> buf[MVW];
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+      if (lane + 32 * k < nv) buf[k] = ld16(x + row * cols + (long long)(lane + 32 * k) * V);
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+      if (lane + 32 * k < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) { const float v = Cvt<T>::to_f(buf[k].v[j]); ss += v * v; }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / cols + eps);
+    if (lane == 0) rstd[row] = r;
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+      if (lane + 32 * k < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(buf[k].v[j]) * r * wv[k][j]);
+        st16(y + row * cols + (long long)(lane + 32 * k) * V, o);
+      }
+  }
+}
+
+template <typename T, typename TW, int MVW>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_warp_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* __restrict__ w,
+                        const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_partial,
+                        long long rows, int cols) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[NORM_WARPS][32 * MVW * V + 1];
+  const int nv = cols / V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float wv[MVW][V], dwacc[MVW][V];
+#pragma unroll
+  for (int k = 0; k < MVW; ++k) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) { dwacc[k][j] = 0.f; wv[k][j] = 0.f; }
+    if (lane + 32 * k < nv) load_weights<TW, V>(w, (lane + 32 * k) * V, wv[k]);
+  }
+  for (long long row = (long long)blockIdx.x * NORM_WARPS + warp; row < rows; row += (long long)gridDim.x * NORM_WARPS) {
+    Vec16<T> xb[MVW], gb_[MVW];
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+      if (lane + 32 * k < nv) {
+        xb[k] = ld16(x + row * cols + (long long)(lane + 32 * k) * V);
+        gb_[k] = ld16(g + row * cols + (long long)(lane + 32 * k) * V);
+      }
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+      if (lane + 32 * k < nv)
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
+          const float gg = Cvt<T>::to_f(gb_[k].v[j]);
+          dot += gg * wv[k][j] * xh;
+          dwacc[k][j] += gg * xh;
+        }
+    dot = warp_sum(dot) / cols;
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+      if (lane + 32 * k < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
+          o.v[j] = Cvt<T>::from_f(r * (Cvt<T>::to_f(gb_[k].v[j]) * wv[k][j] - xh * dot));
+        }
+        st16(dx + row * cols + (long long)(lane + 32 * k) * V, o);
+      }
+  }
+  // this CTA's partial weight gradient: sum over its warps in a fixed order, one row of the partial buffer
+#pragma unroll
+  for (int k = 0; k < MVW; ++k)
+#pragma unroll
+    for (int j = 0; j < V; ++j) red[warp][(lane + 32 * k) * V + j] = dwacc[k][j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
+    float sacc = 0.f;
+#pragma unroll
+    for (int wq = 0; wq < NORM_WARPS; ++wq) sacc += red[wq][c];
+    dw_partial[(long long)blockIdx.x * cols + c] = sacc;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // LayerNorm
 // ------------------------------------------------------------------------------------------
 template <typename T, typename TW, int NORM_MAXV>
@@ -298,6 +404,16 @@ extern "C" int gb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
   if (rows == 0) return 0;
   if (!norm_cols_ok(cols, dt)) return -2;
   const int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
+  const int nvec = cols / (dt == DT_F32 ? 4 : 8);
+  if (nvec <= 128 && rows >= 64) {
+    // narrow rows: warp per row (MVW = 1, 2 or 4 vectors per lane)
+    const long long want = (rows + NORM_WARPS - 1) / NORM_WARPS;
+    const int wgrid = (int)(want < 148 * 8 ? want : 148 * 8);
+    if (nvec <= 32) { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 1><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps)); }
+    else if (nvec <= 64) { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 2><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps)); }
+    else { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 4><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps)); }
+    return (int)cudaGetLastError();
+  }
   NORM_DISPATCH(dt, wdt, cols, rmsnorm_fwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
       (const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps));
   return (int)cudaGetLastError();
@@ -308,6 +424,14 @@ extern "C" int gb_rmsnorm_bwd(const void* g, const void* x, const void* w, const
   if (rows == 0) return 0;
   if (!norm_cols_ok(cols, dt)) return -2;
   const int grid = gb_norm_bwd_ctas(rows);
+  const int nvec = cols / (dt == DT_F32 ? 4 : 8);
+  if (nvec <= 128 && rows >= 64) {
+    // narrow rows: warp per row; every CTA of the grid writes its row of the partial buffer (zeros if it had no rows)
+    if (nvec <= 32) { NORM_DISPATCH_T(dt, wdt, rmsnorm_bwd_warp_kernel<T, TW, 1><<<grid, NORM_THREADS, 0, st>>>((const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols)); }
+    else if (nvec <= 64) { NORM_DISPATCH_T(dt, wdt, rmsnorm_bwd_warp_kernel<T, TW, 2><<<grid, NORM_THREADS, 0, st>>>((const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols)); }
+    else { NORM_DISPATCH_T(dt, wdt, rmsnorm_bwd_warp_kernel<T, TW, 4><<<grid, NORM_THREADS, 0, st>>>((const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols)); }
+    return (int)cudaGetLastError();
+  }
   NORM_DISPATCH(dt, wdt, cols, rmsnorm_bwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
       (const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols));
   return (int)cudaGetLastError();

@@ -71,6 +71,46 @@ __global__ void reduce_mid_kernel(const T* __restrict__ x, O* __restrict__ out, 
   out[((long long)sp * outer + o) * inner + col] = Cvt<O>::from_f(splits == 1 ? acc * scale : acc);
 }
 
+// Vector form of the column reduction (inner a multiple of 16 bytes, 16-byte aligned base): a CTA is 8 row lanes x 32
+// column lanes, a thread reads 16 bytes of a row (a warp reads 512 contiguous bytes), the row lanes stride over the
+// reduced extent and are combined through shared memory at the end.
+template <typename T, typename O>
+__global__ void __launch_bounds__(256)
+reduce_mid_vec_kernel(const T* __restrict__ x, O* __restrict__ out, long long outer, long long red, long long inner,
+                      int splits, int op, float scale) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float sh[8][32 * V + 1];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long col = ((long long)blockIdx.x * 32 + tx) * V;
+  const long long o = blockIdx.y;
+  const int sp = blockIdx.z;
+  const long long chunk = (red + splits - 1) / splits;
+  const long long r0 = sp * chunk, r1 = (r0 + chunk < red) ? r0 + chunk : red;
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = red_init(op);
+  if (col < inner) {
+    const T* p = x + o * red * inner + col;
+#pragma unroll 4
+    for (long long r = r0 + ty; r < r1; r += 8) {
+      const Vec16<T> a = ld16(p + r * inner);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = red_comb(op, acc[j], Cvt<T>::to_f(a.v[j]));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) sh[ty][tx * V + j] = acc[j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < 32 * V; c += 256) {
+    const long long gc = (long long)blockIdx.x * 32 * V + c;
+    if (gc >= inner) continue;
+    float r = sh[0][c];
+#pragma unroll
+    for (int q = 1; q < 8; ++q) r = red_comb(op, r, sh[q][c]);
+    out[((long long)sp * outer + o) * inner + gc] = Cvt<O>::from_f(splits == 1 ? r * scale : r);
+  }
+}
+
 }  // namespace gb
 
 using namespace gb;
@@ -97,6 +137,15 @@ extern "C" int gb_reduce_rows(int op, const void* x, void* out, long long rows, 
 template <typename T>
 static int mid_out(const void* x, void* out, long long outer, long long red, long long inner, int splits, int op,
                    float scale, int odt, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  if (inner % V == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && red >= 16) {
+    dim3 vgrid((unsigned)((inner + 32 * V - 1) / (32 * V)), (unsigned)outer, (unsigned)splits);
+    if (odt == DT_F32) reduce_mid_vec_kernel<T, float><<<vgrid, 256, 0, st>>>((const T*)x, (float*)out, outer, red, inner, splits, op, scale);
+    else if (odt == DT_F16) reduce_mid_vec_kernel<T, __half><<<vgrid, 256, 0, st>>>((const T*)x, (__half*)out, outer, red, inner, splits, op, scale);
+    else if (odt == DT_BF16) reduce_mid_vec_kernel<T, __nv_bfloat16><<<vgrid, 256, 0, st>>>((const T*)x, (__nv_bfloat16*)out, outer, red, inner, splits, op, scale);
+    else return -2;
+    return (int)cudaGetLastError();
+  }
   dim3 grid((unsigned)((inner + 127) / 128), (unsigned)outer, (unsigned)splits);
   if (odt == DT_F32) reduce_mid_kernel<T, float><<<grid, 128, 0, st>>>((const T*)x, (float*)out, outer, red, inner, splits, op, scale);
   else if (odt == DT_F16) reduce_mid_kernel<T, __half><<<grid, 128, 0, st>>>((const T*)x, (__half*)out, outer, red, inner, splits, op, scale);

@@ -343,8 +343,12 @@ def _reduce3(op, x, outer, red, inner, scale, out_dtype):
     if outer > 65535:
         return None
     splits = 1
-    if outer * inner < 148 * 256 and red >= 512:
-        splits = int(min(64, max(1, red // 128), max(1, (148 * 512) // max(outer * inner, 1))))
+    if red >= 512:
+        # the column kernel covers 32 x (16 bytes) columns per CTA; split the reduced extent until ~4 CTAs per SM exist
+        vec = 16 // x.element_size()
+        ctas = outer * (-(-inner // (32 * vec)))
+        if ctas < 148 * 4:
+            splits = int(min(64, max(1, red // 64), -(-148 * 4 // ctas)))
     if splits == 1:
         _chk(L.gb_reduce_mid(op, x.data_ptr(), out.data_ptr(), outer, red, inner, 1, scale, _DT[x.dtype],
                              _DT[out_dtype], _st()), "reduce_mid")
@@ -513,20 +517,23 @@ def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0):
     return out
 
 
-def bgemm(a, b_t, out_dtype=None):
-    """Batched: a [B, M, K], b_t [B, N, K] (K-major, contiguous) -> [B, M, N]."""
+def bgemm(a, b_t, out_dtype=None, b_is_kn=False):
+    """Batched: a [B, M, K] times b_t [B, N, K] (K-major), or with `b_is_kn` times b [B, K, N] as stored (the
+    tensor cores read it MN-major: no transpose copy; 16-bit types only) -> [B, M, N].  Contiguous operands."""
     Bn, M, K = a.shape
-    N = b_t.shape[1]
+    N = b_t.shape[2] if b_is_kn else b_t.shape[1]
     es = a.element_size()
     if not (a.is_contiguous() and b_t.is_contiguous() and (K * es) % 16 == 0 and a.data_ptr() % 16 == 0
             and b_t.data_ptr() % 16 == 0):
         return NotImplemented
+    if b_is_kn and (es != 2 or (N * es) % 16 != 0):
+        return NotImplemented
     out = torch.empty(Bn, M, N, dtype=out_dtype or a.dtype, device=a.device)
     if out.numel() == 0:
         return out
-    rc = lib().gb_gemm(a.data_ptr(), b_t.data_ptr(), out.data_ptr(), None, M, N, K, Bn, K, K, N, M * K, N * K, M * N,
-                       0, 0, _GEMM_DT[a.dtype], _GEMM_DT[out.dtype], 0, 0, 1.0, 0, None, 0, 1, 0,
-                       status_tensor(a.device).data_ptr(), _sms(a.device), _st())
+    rc = lib().gb_gemm(a.data_ptr(), b_t.data_ptr(), out.data_ptr(), None, M, N, K, Bn, K, N if b_is_kn else K, N,
+                       M * K, N * K, M * N, 0, 1 if b_is_kn else 0, _GEMM_DT[a.dtype], _GEMM_DT[out.dtype], 0, 0, 1.0,
+                       0, None, 0, 1, 0, status_tensor(a.device).data_ptr(), _sms(a.device), _st())
     _chk(rc, "bgemm")
     return out
 
@@ -552,6 +559,16 @@ def matmul(a, b):
         ae = aa.expand(*bshape, *aa.shape[-2:]).reshape(-1, *aa.shape[-2:])
         be = bb.expand(*bshape, *bb.shape[-2:]).reshape(-1, *bb.shape[-2:])
         ae = ae if ae.is_contiguous() else ae.contiguous()
+        if ae.element_size() == 2 and (ae.shape[-1] * 2) % 16 == 0 and (be.shape[-1] * 2) % 16 == 0:
+            # b stays [batch, K, N]: read MN-major by the tensor cores, no transpose copy
+            r = bgemm(ae, be if be.is_contiguous() else be.contiguous(), b_is_kn=True)
+            if r is not NotImplemented:
+                out = r.reshape(*bshape, aa.shape[-2], bb.shape[-1])
+                if a1:
+                    out = out.squeeze(-2)
+                if b1:
+                    out = out.squeeze(-1)
+                return out
         bt = be.transpose(-1, -2)
         bt = bt if bt.is_contiguous() else bt.contiguous()
         K = ae.shape[-1]
