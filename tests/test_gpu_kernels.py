@@ -125,7 +125,8 @@ def test_contiguous(shape, perm, dt):
                                         ((8, 3, 2048), (1,)), ((8, 3, 2048), (2,)), ((2048, 2048), (0,)),
                                         ((2048, 2048), (1,)), ((1024, 1024), None), ((4096, 512), (0,)),
                                         ((512, 4096), (1,)), ((1, 2048), (0,)), ((2048, 1), (1,)),
-                                        ((16, 16, 16), (0, 2)), ((300, 70001), None)])
+                                        ((16, 16, 16), (0, 2)), ((300, 70001), None), ((16384, 896), (0,)),
+                                        ((8, 640, 72), (1,)), ((3, 1000, 256), (1,))])
 def test_reductions(dt, shape, dims):
     a = rnd(*shape, dt=dt)
     ac = a.to(DEV)
