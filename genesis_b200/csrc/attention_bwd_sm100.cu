@@ -3,19 +3,20 @@
 // Both kernels work on 128 x 64 score tiles: 128 row threads (one TMEM lane each) by 64 columns, which
 // keeps S and dP (64 + 64 fp32 registers per thread) in registers after ONE tensor-memory round trip, so
 // the TMEM tile is handed back at once and the next tile's QK^T / dO V^T run while the current tile's
-// exponentials are computed.  Operand tiles arrive through a three-stage TMA ring.
+// exponentials are computed.  Operand tiles arrive through a TMA ring (three stages in dQ, two in dK/dV).
 //   dQ    : CTA = (q tile of 128 rows, head); loop over kv tiles of 64:
 //           S = Q K^T, dP = dO V^T, dS = P o (dP - delta) * scale, dQ += dS K          (K tile reused MN-major)
 //   dK/dV : CTA = (kv tile of 128 rows, query head); loop over q tiles of 64:
 //           S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q                     (dO, Q tiles reused MN-major)
-// With D = 64 a CTA needs 256 TMEM columns and 112.1 KB of shared memory: two CTAs share an SM.
+// With D = 64 a CTA needs 256 TMEM columns and at most 100.1 KB of shared memory: two CTAs share an SM.
 // Reference counterpart: genesis/nn/attention.py:162-406 (Triton, 32 x 32 tiles, Hq == Hkv only).
 #include "attention_common.cuh"
 
 namespace gb {
 
 constexpr int BW_C = 64;    // columns of a backward score tile
-constexpr int BW_ST = 3;    // stages of the ring of streamed operand tiles
+constexpr int BW_ST = 3;    // stages of the ring of streamed operand tiles in the dQ kernel
+constexpr int KV_ST = 2;    // ... and in the dK/dV kernel, which spends the shared memory on per-warp statistics instead
 
 __device__ __forceinline__ void store_out_row(uint16_t* dst, uint32_t tsrc, int ncols, bool valid, int dt,
                                               float mul = 1.f) {
@@ -231,13 +232,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
   }
   uint8_t* sK = smem_raw;
   uint8_t* sV = sK + KT;
-  uint8_t* sQ = sV + KT;             // BW_ST stages
-  uint8_t* sdO = sQ + BW_ST * QT;    // BW_ST stages
-  uint8_t* sPT = sdO + BW_ST * QT;
+  uint8_t* sQ = sV + KT;             // KV_ST stages
+  uint8_t* sdO = sQ + KV_ST * QT;    // KV_ST stages
+  uint8_t* sPT = sdO + KV_ST * QT;
   uint8_t* sdST = sPT + PB;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdST + PB);
+  float* lse_s = reinterpret_cast<float*>(sdST + PB);     // [4 warps][2][64] log2-domain row statistics, a copy per warp
+  float* dl_s = lse_s + 8 * BW_C;                          // [4 warps][2][64] delta
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dl_s + 8 * BW_C);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;     // [BW_ST]
+  uint64_t* qdo_full = bars + 1;     // [KV_ST]
   uint64_t* sdp_full = bars + 4;
   uint64_t* sdp_free = bars + 5;
   uint64_t* ds_ready = bars + 6;
@@ -258,7 +261,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(sdp_full, 1);
-    for (int i = 0; i < BW_ST; ++i) mbar_init(&qdo_full[i], 1);
+    for (int i = 0; i < KV_ST; ++i) mbar_init(&qdo_full[i], 1);
     mbar_init(sdp_free, 128); mbar_init(ds_ready, 128); mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -277,15 +280,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
       const uint32_t idesc_acc = make_idesc(fmt, 0, 1, AT_BM, D);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), adST = smem_u32(sdST);
       auto load_q = [&](int it) {
-        const int st = it % BW_ST;
+        const int st = it % KV_ST;
         const int q0 = (i_start + it) * BW_C;
         mbar_expect_tx(&qdo_full[st], 2 * QT);
         load_tile<D>(sQ + st * QT, &tmq, &qdo_full[st], h, q0, b, BW_C);
         load_tile<D>(sdO + st * QT, &tmdo, &qdo_full[st], h, q0, b, BW_C);
       };
       auto issue_s = [&](int it) -> bool {
-        const int st = it % BW_ST;
-        if (!AT_WAIT(&qdo_full[st], (it / BW_ST) & 1, 62)) return false;
+        const int st = it % KV_ST;
+        if (!AT_WAIT(&qdo_full[st], (it / KV_ST) & 1, 62)) return false;
         if (it > 0 && !AT_WAIT(sdp_free, (it - 1) & 1, 64)) return false;
         tc_fence_after_sync();
         const uint32_t aQ = smem_u32(sQ + st * QT), adO = smem_u32(sdO + st * QT);
@@ -300,21 +303,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
       mbar_expect_tx(kv_full, 2 * KT);
       load_tile<D>(sK, &tmk, kv_full, kvh, n0, b, AT_BM);
       load_tile<D>(sV, &tmv, kv_full, kvh, n0, b, AT_BM);
-      for (int it = 0; it < BW_ST && it < n_it; ++it) load_q(it);
+      for (int it = 0; it < KV_ST && it < n_it; ++it) load_q(it);
       bool ok = AT_WAIT(kv_full, 0, 61) && issue_s(0);
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it && !issue_s(it + 1)) break;
         if (!AT_WAIT(ds_ready, it & 1, 63)) break;
         tc_fence_after_sync();
-        const uint32_t aQ = smem_u32(sQ + (it % BW_ST) * QT), adO = smem_u32(sdO + (it % BW_ST) * QT);
+        const uint32_t aQ = smem_u32(sQ + (it % KV_ST) * QT), adO = smem_u32(sdO + (it % KV_ST) * QT);
 #pragma unroll
         for (int kk = 0; kk < BW_C / 16; ++kk) {
           umma_f16(tdV, desc_kmajor(aPT, kk, AT_BM), desc_mnmajor(adO, kk, BW_C), idesc_acc, (it > 0 || kk > 0));
           umma_f16(tdK, desc_kmajor(adST, kk, AT_BM), desc_mnmajor(aQ, kk, BW_C), idesc_acc, (it > 0 || kk > 0));
         }
         umma_commit(acc_done);
-        // tile it - 1 is retired (the row threads saw acc_done(it - 1) before ds_ready(it)): refill its stage
-        if (it >= 1 && it - 1 + BW_ST < n_it) load_q(it - 1 + BW_ST);
+        // two stages: the stage of tile `it` is free once the MMAs just committed are done (a wait on the phase
+        // that was committed last cannot alias)
+        if (it + KV_ST < n_it) {
+          if (!AT_WAIT(acc_done, it & 1, 60)) break;
+          load_q(it + KV_ST);
+        }
       }
     }
   } else {
@@ -324,18 +331,35 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
     const float sl2 = p.scale * LOG2E;
     const size_t stat0 = ((size_t)b * p.Hq + h) * p.S;
     bool ok = true;
+    // Per-column statistics (log2-domain LSE, delta) of a q tile: each warp keeps its own copy in shared memory,
+    // double-buffered; a lane fetches two columns of the NEXT tile into registers at the top of an iteration and
+    // parks them in the other buffer at its end, so the global latency hides behind the tile's arithmetic.
+    auto fetch_stats = [&](int it, float (&v)[4]) {
+      const int q0n = (i_start + it) * BW_C;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int qr = q0n + lane + u * 32;
+        v[u] = qr < p.S ? p.lse_in[stat0 + qr] * LOG2E : 0.f;
+        v[2 + u] = qr < p.S ? p.delta[stat0 + qr] : 0.f;
+      }
+    };
+    auto park_stats = [&](int it, const float (&v)[4]) {
+      float* lb = lse_s + (warp * 2 + (it & 1)) * BW_C;
+      float* db = dl_s + (warp * 2 + (it & 1)) * BW_C;
+      lb[lane] = v[0]; lb[lane + 32] = v[1]; db[lane] = v[2]; db[lane + 32] = v[3];
+    };
+    if (n_it > 0) {
+      float v0[4];
+      fetch_stats(0, v0);
+      park_stats(0, v0);
+      __syncwarp();
+    }
     for (int it = 0; it < n_it; ++it) {
       const int q0 = (i_start + it) * BW_C;
-      // per-column statistics: every thread reads the same addresses (one broadcast transaction per load);
-      // columns past the end of the sequence are masked below, so their index is only clamped
-      const float* lse_q = p.lse_in + stat0;
-      const float* dl_q = p.delta + stat0;
-      const bool stat_vec = ((stat0 + q0) & 3) == 0 && q0 + BW_C <= p.S;
-      // the next tile's statistics (2 x 256 bytes) are pulled into L1 one iteration ahead
-      if (t < 4 && it + 1 < n_it && q0 + 2 * BW_C <= p.S) {
-        const float* nx = ((t & 2) ? dl_q : lse_q) + q0 + BW_C + (t & 1) * 32;
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(nx));
-      }
+      float nxt[4] = {0.f, 0.f, 0.f, 0.f};
+      if (it + 1 < n_it) fetch_stats(it + 1, nxt);
+      const float* lse_b = lse_s + (warp * 2 + (it & 1)) * BW_C;
+      const float* dl_b = dl_s + (warp * 2 + (it & 1)) * BW_C;
       if (!__all_sync(0xffffffffu, AT_WAIT(sdp_full, it & 1, 70))) { ok = false; break; }
       tc_fence_after_sync();
       const bool need_mask = (q0 + BW_C > p.S) || (n0 + AT_BM > p.Sk) || (p.causal && (n0 + AT_BM - 1 > q0 + off));
@@ -359,28 +383,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
           }
         }
         float pt[32], dst[32];
-        if (stat_vec) {
-          const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0 + c * 32);
-          const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0 + c * 32);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 l = __ldg(l4 + i), d = __ldg(d4 + i);
-            pt[4 * i] = l.x; pt[4 * i + 1] = l.y; pt[4 * i + 2] = l.z; pt[4 * i + 3] = l.w;
-            dst[4 * i] = d.x; dst[4 * i + 1] = d.y; dst[4 * i + 2] = d.z; dst[4 * i + 3] = d.w;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            int qr = q0 + c * 32 + i;
-            qr = qr < p.S ? qr : p.S - 1;
-            pt[i] = __ldg(lse_q + qr); dst[i] = __ldg(dl_q + qr);
-          }
-        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float pr = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -pt[i] * LOG2E));
+          const int qc = c * 32 + i;
+          const float pr = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse_b[qc]));
           pt[i] = pr;
-          dst[i] = pr * (__uint_as_float(rp[i]) - dst[i]) * p.scale;
+          dst[i] = pr * (__uint_as_float(rp[i]) - dl_b[qc]);       // the softmax scale is applied once, to dK at the end
         }
         // the P^T / dS^T tiles are single-buffered: the previous iteration's MMAs have to be done with them
         if (c == 0 && it > 0 && !__all_sync(0xffffffffu, AT_WAIT(acc_done, (it - 1) & 1, 71))) { ok = false; break; }
@@ -391,6 +399,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(ds_ready);
+      if (it + 1 < n_it) park_stats(it + 1, nxt);
+      __syncwarp();
     }
     const size_t orow = (((size_t)b * p.Sk + kvrow) * p.Hkv + kvh) * D;
     const bool valid = kvrow < p.Sk;
@@ -407,7 +417,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
       if (ws == nullptr) {
         const int dt = p.is_bf16 ? DT_BF16 : DT_F16;
         store_out_row(reinterpret_cast<uint16_t*>(p.dv) + orow, tdV + lane_base, D, valid, dt);
-        store_out_row(reinterpret_cast<uint16_t*>(p.dk) + orow, tdK + lane_base, D, valid, dt);
+        store_out_row(reinterpret_cast<uint16_t*>(p.dk) + orow, tdK + lane_base, D, valid, dt, p.scale);
       } else {
         // ws = [2][B, Sk, Hkv, D] fp32: dK first, dV second
         const size_t half = (size_t)p.B * p.Sk * p.Hkv * D;
@@ -415,6 +425,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
         for (int which = 0; which < 2; ++which) {
           float* dst = ws + (which ? half : 0) + orow;
           const uint32_t src = (which ? tdV : tdK) + lane_base;
+          const float mul = which ? 1.f : p.scale;
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             uint32_t r[32];
@@ -424,8 +435,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_const
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
                 atomicAdd(reinterpret_cast<float4*>(dst + c + i),
-                          make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                                      __uint_as_float(r[i + 3])));
+                          make_float4(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul,
+                                      __uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul));
             }
           }
         }
@@ -493,7 +504,7 @@ static int launch_bwd(const CUtensorMap& tq128, const CUtensorMap& tdo128, const
   // no alignment pad: shared memory of a CTA starts 1024-aligned (checked in the kernels), and at D = 64 two
   // CTAs have to fit in one SM
   const int smem_dq = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + 128;
-  const int smem_kv = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + 2 * AT_BM * BW_C * 2 + 128;
+  const int smem_kv = 2 * AT_BM * D * 2 + 2 * KV_ST * BW_C * D * 2 + 2 * AT_BM * BW_C * 2 + 16 * BW_C * 4 + 128;
   static bool cfg = false;
   if (!cfg) {
     int r;
