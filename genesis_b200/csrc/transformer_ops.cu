@@ -65,7 +65,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict_
 template <typename T>
 __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restrict__ cosb,
                             const float* __restrict__ sinb, const long long* __restrict__ positions, int B, int S,
-                            int H, int D, int inverse) {
+                            int H, int D, int inverse, long long xrs, long long ors) {
   const int half = D / 2;
   const long long total = (long long)B * S * H * half;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -78,10 +78,11 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ out, const 
     const float c = cosb[pos * D + d];
     float sn = sinb[pos * D + d];
     if (inverse) sn = -sn;
-    const long long base = r * D;
-    const float x1 = Cvt<T>::to_f(x[base + d]), x2 = Cvt<T>::to_f(x[base + d + half]);
-    out[base + d] = Cvt<T>::from_f(x1 * c - x2 * sn);
-    out[base + d + half] = Cvt<T>::from_f(x2 * c + x1 * sn);
+    const int hh = (int)(r % H);
+    const long long xb = bs * xrs + (long long)hh * D, ob = bs * ors + (long long)hh * D;   // token row strides
+    const float x1 = Cvt<T>::to_f(x[xb + d]), x2 = Cvt<T>::to_f(x[xb + d + half]);
+    out[ob + d] = Cvt<T>::from_f(x1 * c - x2 * sn);
+    out[ob + d + half] = Cvt<T>::from_f(x2 * c + x1 * sn);
   }
 }
 
@@ -90,7 +91,7 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ out, const 
 template <typename T>
 __global__ void rope_vec_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restrict__ cosb,
                                 const float* __restrict__ sinb, const long long* __restrict__ positions, int B, int S,
-                                int H, int D, int inverse) {
+                                int H, int D, int inverse, long long xrs, long long ors) {
   constexpr int V = Vec16<T>::N;
   const int half = D / 2;
   const int gpr = half / V;                                  // vector groups per half row
@@ -104,19 +105,20 @@ __global__ void rope_vec_kernel(const T* __restrict__ x, T* __restrict__ out, co
     const long long pos = positions ? positions[bs] : s;
     const float* cp = cosb + pos * D + g * V;
     const float* sp = sinb + pos * D + g * V;
-    const long long base = r * D + g * V;
-    const Vec16<T> a = ld16(x + base), b2 = ld16(x + base + half);
-    Vec16<T> oa, ob;
+    const int hh = (int)(r % H);
+    const long long xb = bs * xrs + (long long)hh * D + g * V, ob = bs * ors + (long long)hh * D + g * V;
+    const Vec16<T> a = ld16(x + xb), b2 = ld16(x + xb + half);
+    Vec16<T> oa, ob2;
 #pragma unroll
     for (int j = 0; j < V; ++j) {
       const float c = cp[j];
       const float sn = inverse ? -sp[j] : sp[j];
       const float x1 = Cvt<T>::to_f(a.v[j]), x2 = Cvt<T>::to_f(b2.v[j]);
       oa.v[j] = Cvt<T>::from_f(x1 * c - x2 * sn);
-      ob.v[j] = Cvt<T>::from_f(x2 * c + x1 * sn);
+      ob2.v[j] = Cvt<T>::from_f(x2 * c + x1 * sn);
     }
-    st16(out + base, oa);
-    st16(out + base + half, ob);
+    st16(out + ob, oa);
+    st16(out + ob + half, ob2);
   }
 }
 
@@ -263,18 +265,22 @@ extern "C" int gb_swiglu_bwd(const void* dy, const void* gate, const void* up, v
   return (int)cudaGetLastError();
 }
 
+// x_row_stride / out_row_stride: elements between consecutive tokens (H * D when the tensor is contiguous; larger when
+// the heads are a column slice of a wider matrix, e.g. a fused q/k/v projection).
 extern "C" int gb_rope(const void* x, void* out, const float* cosb, const float* sinb, const long long* positions,
-                       int B, int S, int H, int D, int inverse, int dt, cudaStream_t st) {
+                       int B, int S, int H, int D, int inverse, int dt, long long x_row_stride,
+                       long long out_row_stride, cudaStream_t st) {
   const long long total = (long long)B * S * H * (D / 2);
   if (total == 0) return 0;
   const int es = dt == DT_F32 ? 4 : 2;
-  const bool vec = (D / 2) % (16 / es) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const bool vec = (D / 2) % (16 / es) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                   (x_row_stride * es) % 16 == 0 && (out_row_stride * es) % 16 == 0;
   if (vec) {
     GB_DISPATCH_FLOAT(dt, T, rope_vec_kernel<T><<<gb_grid(total / Vec16<T>::N, 256), 256, 0, st>>>(
-        (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse));
+        (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse, x_row_stride, out_row_stride));
   } else {
     GB_DISPATCH_FLOAT(dt, T, rope_kernel<T><<<gb_grid(total, 256), 256, 0, st>>>(
-        (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse));
+        (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse, x_row_stride, out_row_stride));
   }
   return (int)cudaGetLastError();
 }

@@ -38,11 +38,14 @@ class Attention(nn.Module):
 
     def forward(self, x, position_ids=None, mask=None):
         B, S, _ = x.shape
-        q = F.reshape(self.q_proj(x), (B, S, self.num_heads, self.head_dim))
-        k = F.reshape(self.k_proj(x), (B, S, self.num_kv_heads, self.head_dim))
-        v = F.reshape(self.v_proj(x), (B, S, self.num_kv_heads, self.head_dim))
-        q = apply_rope(q, self.rotary_emb, position_ids)
-        k = apply_rope(k, self.rotary_emb, position_ids)
+        # q, k and v projections as one GEMM over the stacked weights; RoPE reads its head slices in place
+        y = F.fused_linear(x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight],
+                           [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
+        rot = self.rotary_emb
+        if S > rot.max_seq_len_cached:
+            rot._build(S)
+        q, k, v = F.qkv_rope(y, rot.cos_cached, rot.sin_cached, position_ids, self.num_heads, self.num_kv_heads,
+                             self.head_dim)
         o = F.flash_attention(q, k, v, causal=True)
         return self.o_proj(F.reshape(o, (B, S, self.num_heads * self.head_dim)))
 

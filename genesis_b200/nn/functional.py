@@ -1440,6 +1440,117 @@ def rope(x, cos, sin, positions=None):
     return RoPEFunction.apply(x, cos, sin, positions)
 
 
+def _fused_params(tensors, dtype):
+    """Rows of several parameter matrices (or several bias vectors) stacked in one tensor of `dtype`, rebuilt only when
+    one of them changed (same cache and lifetime as the per-parameter autocast copies)."""
+    key = ("fused", tuple(t.data_ptr() for t in tensors), tuple(t._version for t in tensors), dtype)
+    hit = amp_state.cache.get(key)
+    if hit is not None and all(a is b for a, b in zip(hit[0], tensors)):
+        return hit[1]
+    rows = builtins.sum(t.shape[0] for t in tensors)
+    out = torch.empty((rows,) + tuple(tensors[0].shape[1:]), dtype=dtype, device=tensors[0].device)
+    o = 0
+    for t in tensors:
+        K.copy_(out[o:o + t.shape[0]], t)
+        o += t.shape[0]
+    if amp_state.enabled:
+        amp_state.cache[key] = (list(tensors), out)
+    return out
+
+
+class FusedLinearFunction(Function):
+    """Several linear layers that read the same input, as ONE GEMM: y = x @ cat(weights)^T + cat(biases).
+    The parameters stay separate tensors (state dict and module tree are unchanged); their rows are stacked into one
+    compute-dtype matrix per step, and backward runs one data-gradient GEMM and one weight-gradient GEMM whose result
+    is handed back as row slices.  Replaces e.g. three projections + two gradient additions of an attention block."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, x, weights, biases, compute_dtype):
+        cd = compute_dtype if compute_dtype is not None else weights[0].dtype
+        W = _fused_params(weights, cd)
+        Bv = _fused_params(biases, cd) if biases else None
+        if x.dtype != cd:
+            x = K.to_dtype(x, cd)
+        ctx.save_for_backward(x, W)
+        ctx.meta = ([w.shape[0] for w in weights], weights[0].dtype, biases[0].dtype if biases else None)
+        return K.linear(x, W, Bv)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, W = ctx.saved_tensors
+        sizes, wd, bd = ctx.meta
+        if g.dtype != x.dtype:
+            g = K.to_dtype(g, x.dtype)
+        g = g if g.is_contiguous() else K.contiguous(g)
+        need = ctx.needs_input_grad
+        gx = K.linear_dgrad(g, W) if need[0] else None
+        gW = K.linear_wgrad(g, x, out_dtype=wd)
+        outs, o = [gx], 0
+        for n in sizes:
+            outs.append(gW[o:o + n])
+            o += n
+        if bd is not None:
+            gb = K.bias_grad(g, bd)
+            o = 0
+            for n in sizes:
+                outs.append(gb[o:o + n])
+                o += n
+        return tuple(outs)
+
+
+def fused_linear(x, weights, biases=None):
+    """[..., sum(out_features)] = x through all of `weights` (a list of [out_i, in] parameters) at once."""
+    cd = amp_state.dtype if amp_state.enabled else None
+    return FusedLinearFunction.apply(x, list(weights), list(biases) if biases else [], cd)
+
+
+class QKVRopeFunction(Function):
+    """y [B, S, (Hq + 2 Hkv) D] from a fused q/k/v projection -> rotated q [B, S, Hq, D], rotated k and v
+    [B, S, Hkv, D].  The rotary kernel reads its head slice of y in place (token-row stride = width of y); backward
+    rotates the gradients back straight into their slices of one [B, S, width] buffer, so the projection's backward
+    is a single pair of GEMMs with no concatenation or addition passes."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, y, cos, sin, positions, Hq, Hkv, D):
+        B, S, Nt = y.shape
+        y = y if y.is_contiguous() else K.contiguous(y)
+        q_in = y[..., :Hq * D].unflatten(-1, (Hq, D))
+        k_in = y[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+        v_in = y[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+        ctx.save_for_backward(cos, sin, positions)
+        ctx.meta = (B, S, Nt, Hq, Hkv, D, y.dtype)
+        q = K.rope_fwd(q_in, cos, sin, positions, False)
+        k = K.rope_fwd(k_in, cos, sin, positions, False)
+        return q, k, K.contiguous(v_in)
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        cos, sin, positions = ctx.saved_tensors
+        B, S, Nt, Hq, Hkv, D, dt = ctx.meta
+        dev = (gq if gq is not None else gk if gk is not None else gv).device
+        dy = torch.empty(B, S, Nt, dtype=dt, device=dev)
+        parts = ((gq, 0, Hq, True), (gk, Hq * D, Hkv, True), (gv, (Hq + Hkv) * D, Hkv, False))
+        for g, off, H, rotate in parts:
+            dst = dy[..., off:off + H * D].unflatten(-1, (H, D))
+            if g is None:
+                dst.zero_()
+                continue
+            g = g if g.dtype == dt else K.to_dtype(g, dt)
+            if rotate:
+                K.rope_fwd(g if g.is_contiguous() else K.contiguous(g), cos, sin, positions, True, out=dst)
+            else:
+                K.copy_(dst, g)
+        return dy
+
+
+def qkv_rope(y, cos, sin, positions, num_heads, num_kv_heads, head_dim):
+    return QKVRopeFunction.apply(y, cos, sin, positions, num_heads, num_kv_heads, head_dim)
+
+
 def flash_attention(q, k, v, causal=True, scale=None):
     """q [B, S, Hq, D]; k, v [B, S, Hkv, D] -> [B, S, Hq, D]."""
     if scale is None:

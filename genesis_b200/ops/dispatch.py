@@ -466,11 +466,12 @@ def swiglu_bwd(g, gate, up):
     return dgate.to(gate.dtype), dup.to(up.dtype)
 
 
-def rope_fwd(x, cos, sin, positions=None, inverse=False):
+def rope_fwd(x, cos, sin, positions=None, inverse=False, out=None):
     """Rotate-half RoPE on x [B, S, H, D]; cos/sin [max_pos, D] (halves duplicated).
-    `inverse=True` applies the transposed rotation (the backward)."""
+    `inverse=True` applies the transposed rotation (the backward).  `x` may be a column slice of a wider matrix
+    (a fused projection's output) and `out` a slice to write into."""
     if x.is_cuda:
-        r = N.rope(x, cos, sin, positions, inverse)
+        r = N.rope(x, cos, sin, positions, inverse, out)
         if r is not NotImplemented:
             return r
     B, S, H, D = x.shape
@@ -484,7 +485,11 @@ def rope_fwd(x, cos, sin, positions=None, inverse=False):
         s = -s
     x1, x2 = xf[..., : D // 2], xf[..., D // 2:]
     rot = torch.cat((-x2, x1), -1)
-    return (xf * c + rot * s).to(x.dtype)
+    res = (xf * c + rot * s).to(x.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
 
 
 def embedding_fwd(weight, idx):

@@ -37,7 +37,7 @@ _SIGS = {
     "gb_layernorm_bwd": "pppppppp" + "liiip", "gb_norm_bwd_ctas": "l",
     "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
     "gb_ce_fwd": "ppppllliip", "gb_ce_bwd": "ppppplll" + "iip",
-    "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip", "gb_rope": "pppppiiiiiip",
+    "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip", "gb_rope": "pppppiiiiiillp",
     "gb_gather_rows": "pppllilpp", "gb_scatter_add_rows": "pppliiilpp",
     "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
     "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiippp", "gb_sgd_multi": "pilfffp",
@@ -791,9 +791,25 @@ def swiglu_bwd(g, gate, up):
     return dg, du
 
 
-def rope(x, cos, sin, positions, inverse):
-    if x.dtype not in _FLOATS or x.dim() != 4 or not x.is_contiguous() or cos.dtype != F32 or sin.dtype != F32 \
+def _token_rows(t):
+    """(row stride in elements, ok) of a [B, S, H, D] tensor whose last two dims are dense and whose (b, s) rows are
+    equally spaced (a contiguous tensor, or a column slice of a wider [B, S, N] matrix)."""
+    B, S, H, D = t.shape
+    if t.stride(3) != 1 or (H > 1 and t.stride(2) != D):
+        return 0, False
+    rs = t.stride(1) if S > 1 else H * D
+    if B > 1 and t.stride(0) != S * rs:
+        return 0, False
+    return rs, True
+
+
+def rope(x, cos, sin, positions, inverse, out=None):
+    """Rotate-half RoPE.  `x` and `out` may be column slices of wider matrices (equal token-row spacing)."""
+    if x.dtype not in _FLOATS or x.dim() != 4 or cos.dtype != F32 or sin.dtype != F32 \
             or not cos.is_contiguous() or not sin.is_contiguous() or x.shape[-1] % 2:
+        return NotImplemented
+    xrs, ok = _token_rows(x)
+    if not ok:
         return NotImplemented
     B, S, H, D = x.shape
     pos_ptr = None
@@ -804,9 +820,13 @@ def rope(x, cos, sin, positions, inverse):
         pos_ptr = positions.data_ptr()
     elif cos.shape[0] < S:
         return NotImplemented
-    out = torch.empty_like(x)
+    if out is None:
+        out = torch.empty(B, S, H, D, dtype=x.dtype, device=x.device)
+    ors, ok = _token_rows(out)
+    if not ok or out.dtype != x.dtype or out.shape != x.shape:
+        return NotImplemented
     _chk(lib().gb_rope(x.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos_ptr, B, S, H, D,
-                       1 if inverse else 0, _DT[x.dtype], _st()), "rope")
+                       1 if inverse else 0, _DT[x.dtype], xrs, ors, _st()), "rope")
     return out
 
 

@@ -365,3 +365,36 @@ def test_reference_export_names_exist_and_work():
     assert genesis.amp.get_amp_dtype(AMPPolicy.PROMOTE, x, F.cast_to_fp16(x)) == genesis.float32
     assert isinstance(genesis.amp.get_amp_cache(), dict)
     assert genesis.cuda.get_memory_manager(0).device == 0
+
+
+def test_fused_qkv_projection_and_rope_match_the_separate_ops():
+    import genesis_b200 as genesis
+    import genesis_b200.nn.functional as F
+    torch.manual_seed(0)
+    B, S, Hd, Hq, Hkv, D = 2, 5, 24, 4, 2, 8
+    def leaf(*shape):
+        return genesis.Tensor(torch.randn(*shape), requires_grad=True)
+    x1, x2 = leaf(B, S, Hd), None
+    x2 = genesis.Tensor(x1._t.clone(), requires_grad=True)
+    ws = [leaf(Hq * D, Hd), leaf(Hkv * D, Hd), leaf(Hkv * D, Hd)]
+    bs = [leaf(Hq * D), leaf(Hkv * D), leaf(Hkv * D)]
+    ws2 = [genesis.Tensor(w._t.clone(), requires_grad=True) for w in ws]
+    bs2 = [genesis.Tensor(b._t.clone(), requires_grad=True) for b in bs]
+    pos = torch.arange(16).float()[:, None] * (1.0 / 10000 ** (torch.arange(0, D, 2).float() / D))[None]
+    cos, sin = torch.cat((pos.cos(), pos.cos()), -1), torch.cat((pos.sin(), pos.sin()), -1)
+    gcos, gsin = genesis.Tensor(cos), genesis.Tensor(sin)
+    # fused path
+    y = F.fused_linear(x1, ws, bs)
+    q, k, v = F.qkv_rope(y, gcos, gsin, None, Hq, Hkv, D)
+    # separate path
+    q2 = F.rope(F.reshape(F.linear(x2, ws2[0], bs2[0]), (B, S, Hq, D)), gcos, gsin)
+    k2 = F.rope(F.reshape(F.linear(x2, ws2[1], bs2[1]), (B, S, Hkv, D)), gcos, gsin)
+    v2 = F.reshape(F.linear(x2, ws2[2], bs2[2]), (B, S, Hkv, D))
+    for a, b in ((q, q2), (k, k2), (v, v2)):
+        assert torch.allclose(a._t, b._t, atol=1e-5)
+    gq, gk, gv = torch.randn_like(q._t), torch.randn_like(k._t), torch.randn_like(v._t)
+    ((q * genesis.Tensor(gq)).sum() + (k * genesis.Tensor(gk)).sum() + (v * genesis.Tensor(gv)).sum()).backward()
+    ((q2 * genesis.Tensor(gq)).sum() + (k2 * genesis.Tensor(gk)).sum() + (v2 * genesis.Tensor(gv)).sum()).backward()
+    assert torch.allclose(x1.grad._t, x2.grad._t, atol=1e-4)
+    for a, b in zip(ws + bs, ws2 + bs2):
+        assert torch.allclose(a.grad._t, b.grad._t, atol=1e-4)

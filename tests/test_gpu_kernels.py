@@ -336,3 +336,22 @@ def test_out_of_range_token_id_is_skipped_and_reported():
     assert float(acc[0].sum()) == 16.0 and float(acc.sum()) == 32.0
     with pytest.raises(IndexError):
         native.check_status(table.device)
+
+
+def test_rope_reads_and_writes_column_slices():
+    B, S, Hq, Hkv, D = 2, 37, 4, 2, 64
+    Nt = (Hq + 2 * Hkv) * D
+    y = torch.randn(B, S, Nt, device="cuda", dtype=torch.bfloat16)
+    pos = torch.arange(64, device="cuda").float()[:, None] * (1.0 / 10000 ** (torch.arange(0, D, 2, device="cuda").float() / D))[None]
+    cos, sin = torch.cat((pos.cos(), pos.cos()), -1).contiguous(), torch.cat((pos.sin(), pos.sin()), -1).contiguous()
+    k_in = y[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    got = N.rope(k_in, cos, sin, None, False)
+    ref = N.rope(k_in.contiguous(), cos, sin, None, False)
+    assert got.is_contiguous() and torch.equal(got, ref)
+    # inverse rotation written into a slice of a wider buffer
+    dy = torch.zeros(B, S, Nt, device="cuda", dtype=torch.bfloat16)
+    dst = dy[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    N.rope(ref, cos, sin, None, True, out=dst)
+    back = N.rope(ref, cos, sin, None, True)
+    assert torch.equal(dst, back) and float(dy[..., :Hq * D].abs().sum()) == 0.0
+    torch.testing.assert_close(back.float(), k_in.float(), atol=3e-2, rtol=3e-2)      # rotation then inverse = identity
