@@ -57,6 +57,51 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict_
   }
 }
 
+// Row-strided forms: gate and up are the two column halves of one [rows, 2 * cols] matrix (a fused gate/up
+// projection), out is [rows, cols]; backward writes dgate | dup into the halves of one [rows, 2 * cols] matrix.
+template <typename T>
+__global__ void swiglu_fwd2d_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int cols) {
+  constexpr int V = Vec16<T>::N;
+  const int cpv = cols / V;
+  const long long total = rows * cpv, stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / cpv;
+    const int c = (int)(i % cpv) * V;
+    const T* g = gu + r * 2 * cols + c;
+    Vec16<T> a = ld16(g), b = ld16(g + cols), o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float x = Cvt<T>::to_f(a.v[j]);
+      o.v[j] = Cvt<T>::from_f(x / (1.f + __expf(-x)) * Cvt<T>::to_f(b.v[j]));
+    }
+    st16(out + r * cols + c, o);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd2d_kernel(const T* __restrict__ dy, const T* __restrict__ gu, T* __restrict__ dgu,
+                                    long long rows, int cols) {
+  constexpr int V = Vec16<T>::N;
+  const int cpv = cols / V;
+  const long long total = rows * cpv, stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / cpv;
+    const int c = (int)(i % cpv) * V;
+    const T* g = gu + r * 2 * cols + c;
+    Vec16<T> d = ld16(dy + r * cols + c), a = ld16(g), b = ld16(g + cols), og, ou;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float x = Cvt<T>::to_f(a.v[j]), u = Cvt<T>::to_f(b.v[j]), dd = Cvt<T>::to_f(d.v[j]);
+      const float sg = 1.f / (1.f + __expf(-x));
+      og.v[j] = Cvt<T>::from_f(dd * u * sg * (1.f + x * (1.f - sg)));
+      ou.v[j] = Cvt<T>::from_f(dd * x * sg);
+    }
+    T* o = dgu + r * 2 * cols + c;
+    st16(o, og);
+    st16(o + cols, ou);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // RoPE (rotate-half): out[..., i] = x[i]*cos[i] - x[i+D/2]*sin[i];  out[..., i+D/2] = x[i+D/2]*cos + x[i]*sin
 // cos/sin: fp32 [max_pos, D] with duplicated halves; positions: optional int64 [B, S].
@@ -262,6 +307,27 @@ extern "C" int gb_swiglu_bwd(const void* dy, const void* gate, const void* up, v
   if (n == 0) return 0;
   GB_DISPATCH_FLOAT(dt, T, swiglu_bwd_kernel<T><<<gb_grid(n / Vec16<T>::N + 1, 256), 256, 0, st>>>(
       (const T*)dy, (const T*)gate, (const T*)up, (T*)dgate, (T*)dup, n));
+  return (int)cudaGetLastError();
+}
+
+// gu [rows, 2 * cols] = gate | up; out [rows, cols].  cols a multiple of 16 bytes, 16-byte aligned bases.
+extern "C" int gb_swiglu_fwd2d(const void* gu, void* out, long long rows, int cols, int dt, cudaStream_t st) {
+  if (rows == 0 || cols == 0) return 0;
+  GB_DISPATCH_FLOAT(dt, T, {
+    if (cols % Vec16<T>::N != 0) return -3;
+    swiglu_fwd2d_kernel<T><<<gb_grid(rows * (cols / Vec16<T>::N), 256), 256, 0, st>>>((const T*)gu, (T*)out, rows, cols);
+  });
+  return (int)cudaGetLastError();
+}
+
+// dy [rows, cols], gu [rows, 2 * cols] -> dgu [rows, 2 * cols] = dgate | dup
+extern "C" int gb_swiglu_bwd2d(const void* dy, const void* gu, void* dgu, long long rows, int cols, int dt,
+                               cudaStream_t st) {
+  if (rows == 0 || cols == 0) return 0;
+  GB_DISPATCH_FLOAT(dt, T, {
+    if (cols % Vec16<T>::N != 0) return -3;
+    swiglu_bwd2d_kernel<T><<<gb_grid(rows * (cols / Vec16<T>::N), 256), 256, 0, st>>>((const T*)dy, (const T*)gu, (T*)dgu, rows, cols);
+  });
   return (int)cudaGetLastError();
 }
 

@@ -58,7 +58,9 @@ class FeedForward(nn.Module):
         self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=config.mlp_bias)
 
     def forward(self, x):
-        return self.down_proj(F.swiglu(self.gate_proj(x), self.up_proj(x)))
+        # gate and up projections as one GEMM over the stacked weights; SwiGLU reads the two halves in place
+        biases = [self.gate_proj.bias, self.up_proj.bias] if self.gate_proj.bias is not None else None
+        return self.down_proj(F.swiglu_fused(F.fused_linear(x, [self.gate_proj.weight, self.up_proj.weight], biases)))
 
 
 class TransformerBlock(nn.Module):

@@ -1547,6 +1547,29 @@ class QKVRopeFunction(Function):
         return dy
 
 
+class SwiGLUFusedFunction(Function):
+    """silu(gate) * up where gate | up are the two column halves of one tensor (a fused gate/up projection); the
+    backward writes d(gate | up) as one tensor, ready for a single pair of projection-gradient GEMMs."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, gu):
+        gu = gu if gu.is_contiguous() else K.contiguous(gu)
+        ctx.save_for_backward(gu)
+        return K.swiglu_fused_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, g):
+        (gu,) = ctx.saved_tensors
+        g = g if g.dtype == gu.dtype else K.to_dtype(g, gu.dtype)
+        return K.swiglu_fused_bwd(g if g.is_contiguous() else K.contiguous(g), gu)
+
+
+def swiglu_fused(gate_up):
+    return SwiGLUFusedFunction.apply(gate_up)
+
+
 def qkv_rope(y, cos, sin, positions, num_heads, num_kv_heads, head_dim):
     return QKVRopeFunction.apply(y, cos, sin, positions, num_heads, num_kv_heads, head_dim)
 

@@ -466,6 +466,29 @@ def swiglu_bwd(g, gate, up):
     return dgate.to(gate.dtype), dup.to(up.dtype)
 
 
+def swiglu_fused_fwd(gu):
+    """gu [..., 2 I] holding gate | up (the output of a fused gate/up projection) -> silu(gate) * up."""
+    if gu.is_cuda:
+        r = N.swiglu_fused_fwd(gu)
+        if r is not NotImplemented:
+            return r
+    I = gu.shape[-1] // 2
+    g, u = gu[..., :I].float(), gu[..., I:].float()
+    return (torch.nn.functional.silu(g) * u).to(gu.dtype)
+
+
+def swiglu_fused_bwd(dy, gu):
+    """-> d(gate | up) [..., 2 I]."""
+    if gu.is_cuda:
+        r = N.swiglu_fused_bwd(dy, gu)
+        if r is not NotImplemented:
+            return r
+    I = gu.shape[-1] // 2
+    g, u, d = gu[..., :I].float(), gu[..., I:].float(), dy.float()
+    sg = torch.sigmoid(g)
+    return torch.cat((d * u * sg * (1 + g * (1 - sg)), d * g * sg), -1).to(gu.dtype)
+
+
 def rope_fwd(x, cos, sin, positions=None, inverse=False, out=None):
     """Rotate-half RoPE on x [B, S, H, D]; cos/sin [max_pos, D] (halves duplicated).
     `inverse=True` applies the transposed rotation (the backward).  `x` may be a column slice of a wider matrix

@@ -37,7 +37,8 @@ _SIGS = {
     "gb_layernorm_bwd": "pppppppp" + "liiip", "gb_norm_bwd_ctas": "l",
     "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
     "gb_ce_fwd": "ppppllliip", "gb_ce_bwd": "ppppplll" + "iip",
-    "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip", "gb_rope": "pppppiiiiiillp",
+    "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip",
+    "gb_swiglu_fwd2d": "ppliip", "gb_swiglu_bwd2d": "pppliip", "gb_rope": "pppppiiiiiillp",
     "gb_gather_rows": "pppllilpp", "gb_scatter_add_rows": "pppliiilpp",
     "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
     "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiippp", "gb_sgd_multi": "pilfffp",
@@ -789,6 +790,30 @@ def swiglu_bwd(g, gate, up):
     _chk(lib().gb_swiglu_bwd(g.data_ptr(), gate.data_ptr(), up.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(),
                              _DT[g.dtype], _st()), "swiglu_bwd")
     return dg, du
+
+
+def swiglu_fused_fwd(gu):
+    """gu [..., 2 I] = gate | up -> silu(gate) * up [..., I]."""
+    I = gu.shape[-1] // 2
+    v = 16 // gu.element_size()
+    if gu.dtype not in _FLOATS or not gu.is_contiguous() or gu.shape[-1] % 2 or I % v or gu.data_ptr() % 16:
+        return NotImplemented
+    out = torch.empty(gu.shape[:-1] + (I,), dtype=gu.dtype, device=gu.device)
+    _chk(lib().gb_swiglu_fwd2d(gu.data_ptr(), out.data_ptr(), gu.numel() // (2 * I), I, _DT[gu.dtype], _st()),
+         "swiglu_fwd2d")
+    return out
+
+
+def swiglu_fused_bwd(dy, gu):
+    I = gu.shape[-1] // 2
+    v = 16 // gu.element_size()
+    if gu.dtype not in _FLOATS or dy.dtype != gu.dtype or not gu.is_contiguous() or not dy.is_contiguous() \
+            or I % v or gu.data_ptr() % 16 or dy.data_ptr() % 16:
+        return NotImplemented
+    dgu = torch.empty_like(gu)
+    _chk(lib().gb_swiglu_bwd2d(dy.data_ptr(), gu.data_ptr(), dgu.data_ptr(), gu.numel() // (2 * I), I, _DT[gu.dtype],
+                               _st()), "swiglu_bwd2d")
+    return dgu
 
 
 def _token_rows(t):

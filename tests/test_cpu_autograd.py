@@ -398,3 +398,21 @@ def test_fused_qkv_projection_and_rope_match_the_separate_ops():
     assert torch.allclose(x1.grad._t, x2.grad._t, atol=1e-4)
     for a, b in zip(ws + bs, ws2 + bs2):
         assert torch.allclose(a.grad._t, b.grad._t, atol=1e-4)
+
+
+def test_fused_gate_up_swiglu_matches_the_separate_ops():
+    import genesis_b200 as genesis
+    import genesis_b200.nn.functional as F
+    torch.manual_seed(1)
+    x1 = genesis.Tensor(torch.randn(3, 7, 16), requires_grad=True)
+    x2 = genesis.Tensor(x1._t.clone(), requires_grad=True)
+    wg, wu = (genesis.Tensor(torch.randn(24, 16) * 0.3, requires_grad=True) for _ in range(2))
+    wg2, wu2 = genesis.Tensor(wg._t.clone(), requires_grad=True), genesis.Tensor(wu._t.clone(), requires_grad=True)
+    h1 = F.swiglu_fused(F.fused_linear(x1, [wg, wu]))
+    h2 = F.swiglu(F.linear(x2, wg2), F.linear(x2, wu2))
+    assert torch.allclose(h1._t, h2._t, atol=1e-5)
+    go = torch.randn_like(h1._t)
+    (h1 * genesis.Tensor(go)).sum().backward()
+    (h2 * genesis.Tensor(go)).sum().backward()
+    assert torch.allclose(x1.grad._t, x2.grad._t, atol=1e-4)
+    assert torch.allclose(wg.grad._t, wg2.grad._t, atol=1e-4) and torch.allclose(wu.grad._t, wu2.grad._t, atol=1e-4)

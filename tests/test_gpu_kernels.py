@@ -355,3 +355,18 @@ def test_rope_reads_and_writes_column_slices():
     back = N.rope(ref, cos, sin, None, True)
     assert torch.equal(dst, back) and float(dy[..., :Hq * D].abs().sum()) == 0.0
     torch.testing.assert_close(back.float(), k_in.float(), atol=3e-2, rtol=3e-2)      # rotation then inverse = identity
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_swiglu_on_column_halves(dt):
+    gu = torch.randn(300, 2 * 4864, device="cuda").to(dt)
+    dy = torch.randn(300, 4864, device="cuda").to(dt)
+    I = 4864
+    ref = (torch.nn.functional.silu(gu[:, :I].float()) * gu[:, I:].float())
+    got = K.swiglu_fused_fwd(gu)
+    torch.testing.assert_close(got.float(), ref, atol=3e-2 if dt != torch.float32 else 1e-5, rtol=2e-2 if dt != torch.float32 else 1e-5)
+    g, u, d = gu[:, :I].float(), gu[:, I:].float(), dy.float()
+    sg = torch.sigmoid(g)
+    refb = torch.cat((d * u * sg * (1 + g * (1 - sg)), d * g * sg), -1)
+    gotb = K.swiglu_fused_bwd(dy, gu)
+    torch.testing.assert_close(gotb.float(), refb, atol=6e-2 if dt != torch.float32 else 1e-5, rtol=3e-2 if dt != torch.float32 else 1e-5)
