@@ -117,6 +117,12 @@ class MoEGate(Module):
 # ------------------------------------------------------------------------------------
 # experts
 # ------------------------------------------------------------------------------------
+def _swiglu_mlp(mod, x):
+    """down(silu(gate(x)) * up(x)) with the gate and up projections as one GEMM over the stacked weights."""
+    biases = [mod.gate_proj.bias, mod.up_proj.bias] if mod.gate_proj.bias is not None else None
+    return mod.down_proj(F.swiglu_fused(F.fused_linear(x, [mod.gate_proj.weight, mod.up_proj.weight], biases)))
+
+
 class MoEExpert(Module):
     """One SwiGLU expert: down(silu(gate(x)) * up(x))."""
 
@@ -127,7 +133,7 @@ class MoEExpert(Module):
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=bias)
 
     def forward(self, x):
-        return self.down_proj(F.swiglu(self.gate_proj(x), self.up_proj(x)))
+        return _swiglu_mlp(self, x)
 
 
 class _ExpertView:
@@ -334,14 +340,18 @@ class MoEAttention(Module):
     def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
                 use_cache=False):
         B, S, _ = hidden_states.shape
-        q = F.reshape(self.q_proj(hidden_states), (B, S, self.num_heads, self.head_dim))
-        k = F.reshape(self.k_proj(hidden_states), (B, S, self.num_key_value_heads, self.head_dim))
-        v = F.reshape(self.v_proj(hidden_states), (B, S, self.num_key_value_heads, self.head_dim))
         past = 0 if past_key_value is None else past_key_value[0].shape[1]
         if position_ids is None and past > 0:
-            position_ids = Tensor._wrap(torch.arange(past, past + S, device=q._t.device).expand(B, S).contiguous())
-        q = apply_rope(q, self.rotary_emb, position_ids)
-        k = apply_rope(k, self.rotary_emb, position_ids)
+            position_ids = Tensor._wrap(torch.arange(past, past + S, device=hidden_states._t.device).expand(B, S).contiguous())
+        # q, k and v projections as one GEMM over the stacked weights; RoPE reads its head slices in place
+        biases = [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias] if self.q_proj.bias is not None else None
+        y = F.fused_linear(hidden_states, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], biases)
+        rot = self.rotary_emb
+        need = S + past if position_ids is None else S + past
+        if need > rot.max_seq_len_cached:
+            rot._build(need)
+        q, k, v = F.qkv_rope(y, rot.cos_cached, rot.sin_cached, position_ids, self.num_heads,
+                             self.num_key_value_heads, self.head_dim)
         if past_key_value is not None:
             k = F.cat((past_key_value[0], k), dim=1)
             v = F.cat((past_key_value[1], v), dim=1)
@@ -372,7 +382,7 @@ class DenseFFN(Module):
 
     def forward(self, x):
         if self.hidden_act == "silu":
-            return self.down_proj(F.swiglu(self.gate_proj(x), self.up_proj(x)))
+            return _swiglu_mlp(self, x)
         act = {"gelu": F.gelu, "relu": F.relu}[self.hidden_act]
         return self.down_proj(act(self.gate_proj(x)) * self.up_proj(x))
 

@@ -163,3 +163,18 @@ def test_moe_generate_and_config_validation():
     except ValueError:
         pass
     assert get_moe_config("qwen3-moe-bench").num_local_experts == 128
+
+
+def test_moe_kv_cache_matches_full_recompute():
+    """Prefill + one cached decode step gives the hidden state of a full forward over the longer sequence (the
+    fused q/k/v projection rotates the new token at its absolute position)."""
+    genesis.manual_seed(11)
+    m = MoEForCausalLM(_moe_cfg(attention_bias=True))
+    m.eval()
+    ids = torch.randint(0, 89, (2, 6))
+    with genesis.no_grad():
+        full, _ = m.model(genesis.Tensor(ids), None, None, None, False)
+        h0, cache = m.model(genesis.Tensor(ids[:, :5]), None, None, None, True)
+        h1, _ = m.model(genesis.Tensor(ids[:, 5:]), None, None, cache, True)
+    assert torch.allclose(h0._t, full._t[:, :5], atol=1e-5)
+    assert torch.allclose(h1._t, full._t[:, 5:], atol=1e-5)
