@@ -54,6 +54,10 @@ def parse_args(argv=None):
     ap.add_argument("--device", default=None, help="default: cuda when available, else cpu")
     ap.add_argument("--warmup-steps", type=int, default=0, help="linear warm-up, then cosine decay to --max-steps")
     ap.add_argument("--clip-grad", type=float, default=0.0)
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="capture the whole step (forward, backward, clipping, optimizer) as a CUDA graph after three "
+                         "eager steps and replay it; needs CUDA, --accumulation-steps 1 and, with --ddp, the "
+                         "peer-memory transport")
     ap.add_argument("--eval-batches", type=int, default=20)
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)), "checkpoints", "model"))
     ap.add_argument("--resume", default=None, help="checkpoint file to continue from")
@@ -179,10 +183,60 @@ def main(argv=None):
         prof = profile(activities=acts)
         prof.__enter__()
 
+    def graph_step(x, y):
+        """The whole step with no host read, as `GraphedTrainStep` captures it."""
+        opt.zero_grad()
+        loss = loss_of(x._t, y._t)
+        (scaler.scale(loss) if scaler is not None else loss).backward()
+        if args.clip_grad > 0:
+            if scaler is not None:
+                scaler.unscale_(opt)
+            nn.utils.clip_grad_norm_(model.parameters(), args.clip_grad, sync=False)
+        if scaler is not None:
+            scaler.step(opt)
+            scaler.update()
+        else:
+            opt.step()
+        return loss
+
+    graphed = None
+    if args.cuda_graph:
+        if not device.startswith("cuda") or args.accumulation_steps != 1 or (ddp and not getattr(net, "_use_symm", False)):
+            raise SystemExit("--cuda-graph needs CUDA, --accumulation-steps 1 and (with --ddp) the peer-memory transport")
+
     model.train()
     t0, tokens_since, loss_since, micro = time.time(), 0, 0.0, 0
     log("starting training")
     while args.max_steps is None or step < args.max_steps:
+        if args.cuda_graph:
+            if graphed is None:
+                warm = [[genesis.Tensor(b) for b in next(train_loader)] for _ in range(3)]
+                graphed = genesis.cuda.GraphedTrainStep(graph_step, opt, warm[0], warmup=3, warmup_inputs=warm)
+                done = 3
+                step_loss = graphed.static_outputs
+                log("training step captured as a CUDA graph "
+                    f"({graphed.kernels_per_step} kernels per replay) after 3 eager steps")
+            else:
+                x, y = next(train_loader)
+                step_loss = graphed(x, y)
+                done = 1
+            for _ in range(done):
+                if sched is not None:
+                    sched.step()
+                step += 1
+                micro += 1
+            tokens_since += B * T * world * done
+            if step % args.log_interval < done or step == args.max_steps:
+                lv = float(step_loss.item())
+                dt = time.time() - t0
+                log(f"step {step}: loss {lv:.4f}, {tokens_since / dt:,.0f} tokens/s")
+                metrics.log(step=step, loss=lv, tokens_per_s=tokens_since / dt, lr=opt.lr)
+                t0, tokens_since = time.time(), 0
+            if args.eval_interval and step % args.eval_interval < done:
+                log(f"step {step}: validation loss {evaluate():.4f}")
+            if args.save_interval and step % args.save_interval < done:
+                save(step)
+            continue
         opt.zero_grad()
         step_loss = 0.0
         for a in range(args.accumulation_steps):

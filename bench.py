@@ -162,14 +162,30 @@ def run_ours(args):
             opt.step()
         return loss
 
+    # The whole step (forward, backward, bucket all-reduces on their stream, AdamW) is captured once as a CUDA graph
+    # and replayed, which removes the host launch path from the loop.  With data parallelism this needs the
+    # peer-memory all-reduce (its epochs are counted on the device); over NCCL the step stays eager.
+    graphed = None
+    if not args.no_graph and (world == 1 or getattr(net, "_use_symm", False)):
+        try:
+            graphed = genesis.cuda.GraphedTrainStep(lambda t: train_step(t._t), opt,
+                                                    [genesis.Tensor(dev_batches[0])], warmup=3)
+        except Exception as e:                                   # keep the run; the JSON line says which path ran
+            print(f"[bench] CUDA-graph capture failed, running eagerly: {type(e).__name__}: {e}", file=sys.stderr)
+            graphed = None
+
     def step_device():
         counter["i"] += 1
-        return train_step(dev_batches[counter["i"] % pool_n])
+        tokens = dev_batches[counter["i"] % pool_n]
+        return graphed(tokens) if graphed is not None else train_step(tokens)
 
     def step_e2e():
         counter["i"] += 1
-        tokens = host[counter["i"] % pool_n].to("cuda", non_blocking=True)   # H2D from pinned memory
-        loss = train_step(tokens)
+        src = host[counter["i"] % pool_n]
+        if graphed is not None:
+            loss = graphed(src)                                  # H2D from pinned memory into the static batch
+        else:
+            loss = train_step(src.to("cuda", non_blocking=True))
         return float(loss._t.float().cpu())                                  # D2H of the step's loss
 
     sampler = ClockSampler(local)
@@ -178,7 +194,10 @@ def run_ours(args):
         sampler.start()
     ms, last = time_steps(torch, step_device, args.steps, args.warmup, world)
     clocks = sampler.stop() if rank == 0 else None
-    launches = native.launch_count // max(args.steps + args.warmup, 1) * args.steps
+    if graphed is not None:
+        launches = graphed.kernels_per_step * args.steps          # kernels inside each replayed graph
+    else:
+        launches = native.launch_count // max(args.steps + args.warmup, 1) * args.steps
     ms_e2e, last_loss = time_steps(torch, step_e2e, args.steps, max(1, args.warmup // 2), world)
     native.check_status()
     tokens_per_step = B * S * world
@@ -192,7 +211,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": args.dtype, "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "config": {"model": args.model, "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
-                   "optimizer": "AdamW lr 3e-4", "l2_policy": "working set (~20 GB activations+grads per step) >> 126 MB L2; "
+                   "optimizer": "AdamW lr 3e-4", "cuda_graph": graphed is not None, "l2_policy": "working set (~20 GB activations+grads per step) >> 126 MB L2; "
                    "4 distinct input batches rotated"},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -231,6 +250,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.gpus > 1 and world == 1:

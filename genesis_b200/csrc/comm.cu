@@ -18,16 +18,35 @@ namespace gb {
 
 // 256 threads and at most 80 registers: 20 K registers per CTA, which fit beside a resident GEMM CTA (43.5 K of the
 // 64 K), so the reduction runs on SMs that backward keeps busy instead of taking SMs away from it.
+// Epoch kept on the device (`ctr[0]` last finished epoch, `ctr[1]` CTAs of the running launch that are done): every
+// CTA of a launch reads the same value because ctr[0] only moves once all of them have passed through here, and
+// launches on one stream are ordered.  With it the launch takes nothing step-dependent by value, so a CUDA graph
+// that contains the all-reduce can be replayed; all ranks issue the same launches, so their counters agree.
+__device__ __forceinline__ void epoch_publish(uint32_t* ctr, uint32_t epoch) {
+  if (ctr == nullptr || threadIdx.x != 0) return;
+  __threadfence();
+  if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) {
+    ctr[1] = 0;
+    __threadfence();
+    *reinterpret_cast<volatile uint32_t*>(ctr) = epoch;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256, 3)
 allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, long long n, int rank, int world,
                        uint32_t epoch, float prescale, const float* __restrict__ loss_scale, int scale_is_reciprocal,
-                       float* __restrict__ found_inf, unsigned long long budget_ns, int* __restrict__ status) {
+                       float* __restrict__ found_inf, unsigned long long budget_ns, int* __restrict__ status,
+                       uint32_t* __restrict__ epoch_ctr) {
   __shared__ int s_fail;
   __shared__ int s_bad;
   constexpr int V = Vec16<T>::N;
   if (threadIdx.x == 0) { s_fail = 0; s_bad = 0; }
-  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) return;
+  if (epoch_ctr != nullptr) epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ctr) + 1;
+  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) {
+    epoch_publish(epoch_ctr, epoch);
+    return;
+  }
 
   float scale = prescale;
   if (loss_scale != nullptr) scale *= scale_is_reciprocal ? 1.f / *loss_scale : *loss_scale;
@@ -87,11 +106,15 @@ allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, 
     // tell every rank: this epoch overflowed
     st_release_sys(reinterpret_cast<uint32_t*>(flags.ptr[threadIdx.x]) + COMM_FOUND_SLOT, epoch);
   }
-  if (!peer_barrier(flags, rank, world, 1, epoch, budget_ns, status, &s_fail)) return;
+  if (!peer_barrier(flags, rank, world, 1, epoch, budget_ns, status, &s_fail)) {
+    epoch_publish(epoch_ctr, epoch);
+    return;
+  }
   if (found_inf != nullptr && threadIdx.x == 0) {
     if (ld_acquire_sys(reinterpret_cast<const uint32_t*>(flags.ptr[rank]) + COMM_FOUND_SLOT) == epoch)
       *found_inf = 1.f;
   }
+  epoch_publish(epoch_ctr, epoch);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -231,7 +254,8 @@ extern "C" int gb_ipc_close_handle(void* p) { return (int)cudaIpcCloseMemHandle(
 extern "C" int gb_allreduce_fused(void* const* bufs, void* const* flags, long long offset_elems, long long n,
                                   int rank, int world, unsigned int epoch, float prescale, const float* loss_scale,
                                   int scale_is_reciprocal, float* found_inf, int dt, int ctas,
-                                  unsigned long long budget_ns, int* status, cudaStream_t st) {
+                                  unsigned long long budget_ns, int* status, unsigned int* epoch_ctr,
+                                  cudaStream_t st) {
   if (world > COMM_MAX_WORLD || world < 1) return -2;
   if (ctas > COMM_MAX_CTAS) ctas = COMM_MAX_CTAS;
   if (ctas < 1) ctas = 1;
@@ -240,7 +264,8 @@ extern "C" int gb_allreduce_fused(void* const* bufs, void* const* flags, long lo
   GB_DISPATCH_FLOAT(dt, T, {
     if (n % (world * Vec16<T>::N) != 0) return -3;
     allreduce_fused_kernel<T><<<ctas, 256, 0, st>>>(tb, tf, offset_elems, n, rank, world, epoch, prescale,
-                                                    loss_scale, scale_is_reciprocal, found_inf, budget_ns, status);
+                                                    loss_scale, scale_is_reciprocal, found_inf, budget_ns, status,
+                                                    epoch_ctr);
   });
   return (int)cudaGetLastError();
 }

@@ -29,10 +29,28 @@ struct AdamArgs {
   int shadow_dtype;
 };
 
+// Step-dependent scalars kept on the device so that a captured CUDA graph of the step stays valid when replayed:
+// dyn[0] learning rate (written by the host between replays), dyn[1] / dyn[2] bias corrections, dyn[3] step count.
+__global__ void adam_dyn_advance_kernel(float* __restrict__ dyn, float beta1, float beta2) {
+  const double step = (double)dyn[3] + 1.0;
+  dyn[3] = (float)step;
+  dyn[1] = (float)(1.0 - pow((double)beta1, step));
+  dyn[2] = (float)(1.0 - pow((double)beta2, step));
+}
+
+__device__ __forceinline__ void adam_update(float& pi, float& mi, float& vi, float gi, const AdamArgs& a) {
+  if (a.decoupled) pi *= (1.f - a.lr * a.weight_decay);
+  else gi += a.weight_decay * pi;
+  mi = a.beta1 * mi + (1.f - a.beta1) * gi;
+  vi = a.beta2 * vi + (1.f - a.beta2) * gi * gi;
+  pi -= a.lr * (mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps);
+}
+
 __global__ void __launch_bounds__(OPT_THREADS)
 adam_multi_kernel(const long long* __restrict__ meta, int nt, AdamArgs a, const float* __restrict__ grad_scale,
-                  const float* __restrict__ found_inf) {
+                  const float* __restrict__ found_inf, const float* __restrict__ dyn) {
   if (found_inf != nullptr && *found_inf != 0.f) return;
+  if (dyn != nullptr) { a.lr = dyn[0]; a.bc1 = dyn[1]; a.bc2 = dyn[2]; }
   const int t = find_tensor(meta + 6ll * nt, nt, blockIdx.x);
   float* p = reinterpret_cast<float*>(meta[0ll * nt + t]);
   const void* g = reinterpret_cast<const void*>(meta[1ll * nt + t]);
@@ -44,17 +62,35 @@ adam_multi_kernel(const long long* __restrict__ meta, int nt, AdamArgs a, const 
   const long long base = (blockIdx.x - meta[6ll * nt + t]) * OPT_CHUNK;
   const float gs = grad_scale != nullptr ? *grad_scale : 1.f;
   const long long end = (base + OPT_CHUNK < n) ? base + OPT_CHUNK : n;
+  // fp32 gradients, no shadow copy, 16-byte aligned tensors: four elements per thread and access
+  const bool vec = gdt == DT_F32 && sh == nullptr &&
+      (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0;
+  if (vec) {
+    const long long end4 = base + ((end - base) & ~3ll);
+    for (long long i = base + 4ll * threadIdx.x; i < end4; i += 4ll * OPT_THREADS) {
+      float4 g4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g) + i);
+      float4 p4 = *reinterpret_cast<const float4*>(p + i);
+      float4 m4 = *reinterpret_cast<const float4*>(m + i);
+      float4 v4 = *reinterpret_cast<const float4*>(v + i);
+      adam_update(p4.x, m4.x, v4.x, g4.x * gs, a);
+      adam_update(p4.y, m4.y, v4.y, g4.y * gs, a);
+      adam_update(p4.z, m4.z, v4.z, g4.z * gs, a);
+      adam_update(p4.w, m4.w, v4.w, g4.w * gs, a);
+      *reinterpret_cast<float4*>(p + i) = p4;
+      *reinterpret_cast<float4*>(m + i) = m4;
+      *reinterpret_cast<float4*>(v + i) = v4;
+    }
+    for (long long i = end4 + threadIdx.x; i < end; i += OPT_THREADS) {
+      float pi = p[i], mi = m[i], vi = v[i];
+      adam_update(pi, mi, vi, reinterpret_cast<const float*>(g)[i] * gs, a);
+      p[i] = pi; m[i] = mi; v[i] = vi;
+    }
+    return;
+  }
   for (long long i = base + threadIdx.x; i < end; i += OPT_THREADS) {
-    float gi = load_as_float(g, gdt, i) * gs;
-    float pi = p[i];
-    if (a.decoupled) pi *= (1.f - a.lr * a.weight_decay);
-    else gi += a.weight_decay * pi;
-    const float mi = a.beta1 * m[i] + (1.f - a.beta1) * gi;
-    const float vi = a.beta2 * v[i] + (1.f - a.beta2) * gi * gi;
-    m[i] = mi;
-    v[i] = vi;
-    pi -= a.lr * (mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps);
-    p[i] = pi;
+    float pi = p[i], mi = m[i], vi = v[i];
+    adam_update(pi, mi, vi, load_as_float(g, gdt, i) * gs, a);
+    p[i] = pi; m[i] = mi; v[i] = vi;
     if (sh != nullptr) store_from_float(sh, a.shadow_dtype, i, pi);
   }
 }
@@ -114,10 +150,16 @@ extern "C" int gb_opt_chunk() { return OPT_CHUNK; }
 
 extern "C" int gb_adam_multi(const long long* meta, int nt, long long total_chunks, float lr, float beta1,
                              float beta2, float eps, float weight_decay, float bc1, float bc2, int decoupled,
-                             int shadow_dtype, const float* grad_scale, const float* found_inf, cudaStream_t st) {
+                             int shadow_dtype, const float* grad_scale, const float* found_inf, const float* dyn,
+                             cudaStream_t st) {
   if (total_chunks == 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, bc1, bc2, decoupled, shadow_dtype};
-  adam_multi_kernel<<<(unsigned)total_chunks, OPT_THREADS, 0, st>>>(meta, nt, a, grad_scale, found_inf);
+  adam_multi_kernel<<<(unsigned)total_chunks, OPT_THREADS, 0, st>>>(meta, nt, a, grad_scale, found_inf, dyn);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gb_adam_dyn_advance(float* dyn, float beta1, float beta2, cudaStream_t st) {
+  adam_dyn_advance_kernel<<<1, 1, 0, st>>>(dyn, beta1, beta2);
   return (int)cudaGetLastError();
 }
 
@@ -134,4 +176,10 @@ extern "C" int gb_grad_multi(const long long* meta, int nt, long long total_chun
   grad_multi_kernel<<<(unsigned)total_chunks, OPT_THREADS, 0, st>>>(meta, nt, scale, fixed_scale, found_inf,
                                                                     norm_sq, mode);
   return (int)cudaGetLastError();
+}
+
+// Plain asynchronous host-to-device copy on `st` (pointer tables uploaded while a CUDA graph is captured: the node
+// reads the pinned source again on every replay, the caller keeps it alive).
+extern "C" int gb_copy_h2d_async(void* dst, const void* src, long long bytes, cudaStream_t st) {
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, st);
 }

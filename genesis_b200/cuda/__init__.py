@@ -332,4 +332,4 @@ def get_memory_manager(device=None):
 
 from ..device import Device  # noqa: E402,F401  (re-exported as in the reference)
 
-from .graphs import CUDAGraph, graph, make_graphed_callable  # noqa: E402,F401
+from .graphs import CUDAGraph, GraphedCallable, GraphedTrainStep, graph, make_graphed_callable  # noqa: E402,F401

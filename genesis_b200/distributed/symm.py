@@ -135,10 +135,22 @@ class _Channel:
     def __init__(self, st, flags):
         self.rank, self.world, self.device, self.status, self.flags = st.rank, st.world, st.device, st.status, flags
         self.epoch = 0
+        self.epoch_dev = None
 
     def next_epoch(self):
+        if self.epoch_dev is not None:
+            raise RuntimeError("this channel counts its epochs on the device; host epochs cannot be mixed in")
         self.epoch += 1
         return self.epoch
+
+    def use_device_epochs(self):
+        """Count epochs in device memory (advanced by the kernels themselves) instead of passing them by value, so
+        launches on this channel can be captured in a CUDA graph.  Every rank must switch at the same point."""
+        if self.epoch_dev is None:
+            if self.epoch != 0:
+                raise RuntimeError("switch to device epochs before the channel's first collective")
+            self.epoch_dev = torch.zeros(2, dtype=torch.int32, device=self.device)
+        return self
 
 
 def available():
@@ -182,6 +194,9 @@ def check_status(what="collective"):
     rec = st.status.tolist()
     if rec[0] != 0:
         st.status.zero_()
+        if rec[0] == 3 and rec[1] == 900:
+            raise RuntimeError(f"{what}: expert-parallel receive buffer too small: this rank was sent {rec[3]} "
+                               f"(tile-padded) rows; raise GENESIS_EP_CAPACITY (multiple of the balanced share)")
         raise pg.CommTimeout(f"{what}: device-side wait expired (code={rec[0]}, peer={rec[1]}, phase={rec[2]}, "
                              f"epoch={rec[3]})")
 

@@ -129,7 +129,9 @@ class DistributedDataParallel(Module):
         if self._on_cuda:
             self._comm_stream = torch.cuda.Stream()
         if self._use_symm:
-            symm.channel("ddp")        # flag page of the communication stream (collective allocation: do it here)
+            # flag page of the communication stream (collective allocation: do it here); epochs counted on the
+            # device so that a captured training step can be replayed
+            symm.channel("ddp").use_device_epochs()
         for b in self._buckets:
             esz = torch.empty(0, dtype=b.dtype).element_size()
             pad = (b.numel + 1023) // 1024 * 1024          # slices stay 16-byte aligned for any world size <= 64

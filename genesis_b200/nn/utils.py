@@ -6,7 +6,16 @@ import torch
 from ..ops import dispatch as K
 
 
-def clip_grad_norm_(parameters, max_norm, norm_type=2):
+def clip_grad_norm_(parameters, max_norm, norm_type=2, sync=True):
+    """Scale all gradients so that their total norm is at most `max_norm`; returns the norm before clipping.
+
+    `sync=False` (CUDA, 2-norm) keeps everything on the device: the coefficient min(1, max_norm / (norm + 1e-6)) is
+    computed by device arithmetic, applied by one multi-tensor kernel, and the norm comes back as a 0-d `Tensor`;
+    no host read, so the call can sit inside a captured CUDA graph.  The default reads the norm back as a float
+    (the reference's return type) and skips the scaling pass when nothing has to be clipped."""
+    from ..tensor import Tensor
+    if isinstance(parameters, Tensor):
+        parameters = [parameters]
     params = [p for p in parameters if p.grad is not None]
     if not params:
         return 0.0
@@ -14,6 +23,10 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2):
     if norm_type == 2:
         acc = torch.zeros(1, dtype=torch.float32, device=grads[0].device)
         K.grad_norm_sq(grads, acc)
+        if not sync and grads[0].is_cuda:
+            total_t = acc.sqrt()
+            K.scale_grads_(grads, (max_norm / (total_t + 1e-6)).clamp_(max=1.0))
+            return Tensor._wrap(total_t.reshape(()))
         total = float(acc.sqrt().item())
     elif norm_type == float("inf"):
         total = max(float(g.abs().max()) for g in grads)
@@ -21,6 +34,5 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2):
         total = sum(float(g.float().abs().pow(norm_type).sum()) for g in grads) ** (1.0 / norm_type)
     coef = max_norm / (total + 1e-6)
     if coef < 1:
-        for g in grads:
-            K.mul_(g, coef)
+        K.scale_grads_(grads, coef)
     return total

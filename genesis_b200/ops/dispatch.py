@@ -617,7 +617,7 @@ def random_fill(kind, shape, dtype, device, seed, offset, a=0.0, b=1.0):
 
 # ================================== optimisers ===================================
 def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled=True,
-               grad_scale=None, found_inf=None, shadows=None):
+               grad_scale=None, found_inf=None, shadows=None, dyn=None):
     """Multi-tensor Adam/AdamW over lists of tensors, in place.
 
     decoupled=True: p *= 1 - lr*wd, then Adam update (AdamW, reference `optim/adamw.py:9-64`);
@@ -628,9 +628,11 @@ def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step,
     """
     if params and params[0].is_cuda:
         r = N.adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled,
-                         grad_scale, found_inf, shadows)
+                         grad_scale, found_inf, shadows, dyn)
         if r is not NotImplemented:
             return
+    if dyn is not None:
+        raise RuntimeError("capturable optimizer state needs contiguous fp32 CUDA parameters and floating-point gradients")
     if found_inf is not None and float(found_inf.item()) != 0.0:
         return
     bc1 = 1.0 - beta1 ** step
@@ -681,6 +683,16 @@ def unscale_and_check(grads, inv_scale, found_inf):
             bad = True
     if bad:
         found_inf.fill_(1.0)
+
+
+def scale_grads_(grads, scale):
+    """Every gradient *= scale (a float or a 1-elem fp32 device tensor), one multi-tensor launch on CUDA."""
+    if grads and grads[0].is_cuda:
+        r = N._grad_multi(grads, scale, None, None, 1)
+        if r is not NotImplemented:
+            return
+    for g in grads:
+        g.mul_(scale.to(g.dtype) if isinstance(scale, torch.Tensor) else scale)
 
 
 def grad_norm_sq(grads, out):

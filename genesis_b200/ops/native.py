@@ -41,12 +41,12 @@ _SIGS = {
     "gb_swiglu_fwd2d": "ppliip", "gb_swiglu_bwd2d": "pppliip", "gb_rope": "pppppiiiiiillp",
     "gb_gather_rows": "pppllilpp", "gb_scatter_add_rows": "pppliiilpp",
     "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
-    "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiippp", "gb_sgd_multi": "pilfffp",
+    "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiipppp", "gb_adam_dyn_advance": "pffp", "gb_copy_h2d_async": "pplp", "gb_sgd_multi": "pilfffp",
     "gb_grad_multi": "pilpfppip",
     "gb_router_fwd": "ppppp" + "liiiip", "gb_router_bwd": "pppppp" + "liiiip",
     "gb_moe_sort": "pppppp" + "liiilp", "gb_moe_combine": "pppp" + "liiip", "gb_moe_combine_bwd": "pppppp" + "liiip",
     "gb_gemm": "pppp" + "iiii" + "ll" + "i" + "lll" + "ii" + "iii" + "i" + "f" + "i" + "p" + "i" + "ii" + "p" + "i" + "p",
-    "gb_allreduce_fused": "ppllii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "pp",
+    "gb_allreduce_fused": "ppllii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "ppp",
     "gb_wait_flag": "pIupp",
     "gb_peer_pull": "pppppp" + "ii" + "I" + "i" + "u" + "pp",
     "gb_peer_reduce_scatter": "ppp" + "lii" + "I" + "f" + "ii" + "u" + "pp",
@@ -926,15 +926,40 @@ def random_fill(kind, shape, dtype, dev, seed, offset, a, b):
 
 
 # ================================== optimisers ===================================
-_pinned = {}
+# Host side of pointer tables uploaded while a CUDA graph is being captured: the captured copy node reads the host
+# block again on every replay, so the block must stay alive and unchanged.  `begin_capture_arena` reserves pinned
+# memory BEFORE the capture starts (no pinned allocation inside it); tables are carved out of it and never reused.
+_capture_keepalive = []
+_capture_arena = None
+_capture_arena_used = 0
+
+
+def begin_capture_arena(nwords=1 << 20):
+    global _capture_arena, _capture_arena_used
+    _capture_arena = torch.empty(nwords, dtype=torch.int64).pin_memory()
+    _capture_keepalive.append(_capture_arena)
+    _capture_arena_used = 0
+
 
 
 def _meta(rows, nt, dev):
     """Upload the pointer table (rows x nt int64) through a pinned staging buffer."""
     # torch's pinned-host allocator keeps a staging block alive until the async copy that reads it
     # has completed, so a fresh pinned tensor per call is both safe and cheap (blocks are recycled).
-    host = torch.tensor(rows, dtype=torch.int64).reshape(-1).pin_memory()
-    return host.to(dev, non_blocking=True)
+    flat = torch.tensor(rows, dtype=torch.int64).reshape(-1)
+    if torch.cuda.is_current_stream_capturing():
+        global _capture_arena_used
+        n = flat.numel()
+        if _capture_arena is None or _capture_arena_used + n > _capture_arena.numel():
+            raise RuntimeError("pointer-table upload inside a CUDA-graph capture without a reserved pinned arena: "
+                               "capture through genesis_b200.cuda.graph / make_graphed_callable")
+        host = _capture_arena[_capture_arena_used:_capture_arena_used + n]
+        _capture_arena_used += n
+        host.copy_(flat)
+        out = torch.empty(n, dtype=torch.int64, device=dev)
+        _chk(lib().gb_copy_h2d_async(out.data_ptr(), host.data_ptr(), n * 8, _st()), "copy_h2d_async")
+        return out
+    return flat.pin_memory().to(dev, non_blocking=True)
 
 
 def _multi_table(params, grads, s1, s2, shadows):
@@ -969,7 +994,9 @@ def _opt_ok(params, grads, states):
 
 
 def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled, grad_scale, found_inf,
-               shadows):
+               shadows, dyn=None):
+    """`dyn` (device fp32 [4]: lr, bias corrections, step count) moves the step-dependent scalars to the device:
+    the kernel advances the count itself, so the launch sequence can be replayed from a CUDA graph."""
     if not _opt_ok(params, grads, (ms, vs)):
         return NotImplemented
     sdt = 0
@@ -983,9 +1010,13 @@ def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step,
     meta = _meta(rows, nt, dev)
     gs = None if grad_scale is None else grad_scale.data_ptr()
     fi = None if found_inf is None else found_inf.data_ptr()
+    dp = None
+    if dyn is not None:
+        dp = dyn.data_ptr()
+        _chk(lib().gb_adam_dyn_advance(dp, float(beta1), float(beta2), _st()), "adam_dyn_advance")
     _chk(lib().gb_adam_multi(meta.data_ptr(), nt, total, float(lr), float(beta1), float(beta2), float(eps),
                              float(weight_decay), 1.0 - beta1 ** step, 1.0 - beta2 ** step, 1 if decoupled else 0,
-                             sdt, gs, fi, _st()), "adam_multi")
+                             sdt, gs, fi, dp, _st()), "adam_multi")
     return True
 
 
@@ -1059,8 +1090,10 @@ def moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm):
 # ================================ communication ==================================
 def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None, found_inf=None, prescale=1.0,
                     scale_is_reciprocal=True, ctas=None):
-    """In-place fused all-reduce over symmetric buffer `buf` (see csrc/comm.cu)."""
-    epoch = st.next_epoch()
+    """In-place fused all-reduce over symmetric buffer `buf` (see csrc/comm.cu).  A channel with device-resident
+    epochs (`use_device_epochs()`) makes the launch replayable from a CUDA graph."""
+    ctr = getattr(st, "epoch_dev", None)
+    epoch = 0 if ctr is not None else st.next_epoch()
     budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000)) * 1e6)
     if ctas is None:
         # enough CTAs to keep ~1.5 MB of loads in flight for big buckets, one for tiny ones
@@ -1071,7 +1104,8 @@ def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None,
                                   float(prescale), None if inv_scale is None else inv_scale.data_ptr(),
                                   1 if scale_is_reciprocal else 0,
                                   None if found_inf is None else found_inf.data_ptr(), _DT[dtype], ctas, budget,
-                                  st.status.data_ptr(), _st()), "allreduce_fused")
+                                  st.status.data_ptr(), None if ctr is None else ctr.data_ptr(), _st()),
+         "allreduce_fused")
     return True
 
 

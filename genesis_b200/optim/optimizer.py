@@ -103,6 +103,34 @@ class _AdamBase(Optimizer):
         self.t = 0
         self.m, self.v = {}, {}
         self._shadows = None
+        # capturable mode: learning rate, bias corrections and step count live in a device vector that the kernel
+        # advances, so a CUDA graph of the step can be replayed (see `genesis_b200.cuda.graphs.GraphedTrainStep`)
+        self._dyn = None
+        self._dyn_lr = None
+
+    def make_capturable(self):
+        """Move the step-dependent scalars to the device. Idempotent; needs CUDA parameters."""
+        if self._dyn is None:
+            dev = self.params[0]._t.device
+            if dev.type != "cuda":
+                raise RuntimeError("capturable optimizer state needs CUDA parameters")
+            self._dyn = torch.tensor([self.lr, 1.0 - self.beta1 ** max(self.t, 1), 1.0 - self.beta2 ** max(self.t, 1),
+                                      float(self.t)], dtype=torch.float32, device=dev)
+            self._dyn_lr = self.lr
+        return self
+
+    def load_state_dict(self, state):
+        super().load_state_dict(state)
+        if self._dyn is not None:                 # device copy of the step count and learning rate follows the host
+            self._dyn[3:4].fill_(float(self.t))
+            self._dyn[0:1].fill_(float(self.lr))
+            self._dyn_lr = self.lr
+
+    def _sync_lr(self):
+        """Write a changed host learning rate into the device vector (outside a capture)."""
+        if self._dyn is not None and self._dyn_lr != self.lr:
+            self._dyn[0:1].fill_(float(self.lr))
+            self._dyn_lr = self.lr
 
     def step(self):
         idx = self._active()
@@ -114,8 +142,10 @@ class _AdamBase(Optimizer):
         ms = [self._state(self.m, i) for i in idx]
         vs = [self._state(self.v, i) for i in idx]
         sh = None if self._shadows is None else [self._shadows.get(i) for i in idx]
+        if self._dyn is not None and not torch.cuda.is_current_stream_capturing():
+            self._sync_lr()
         K.adamw_step(ps, gs, ms, vs, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.t,
-                     self.decoupled, self._grad_scale, self._found_inf, sh)
+                     self.decoupled, self._grad_scale, self._found_inf, sh, self._dyn)
         for i in idx:
             self.params[i]._version += 1
 

@@ -261,7 +261,9 @@ def _expert_parallel_forward_p2p(layer, x, idx, w):
     W, E = ep.size, layer.num_experts
     El = E // W
     T, k = idx.shape
-    factor = float(os.environ.get("GENESIS_EP_CAPACITY", min(W, 2.0)))
+    # receive buffers are sized for `factor` times the balanced share; a freshly initialised router is skewed (2.1x
+    # was seen on 8 ranks), and rows beyond the buffer raise an error instead of being dropped
+    factor = float(os.environ.get("GENESIS_EP_CAPACITY", min(W, 4.0 if W > 2 else 2.0)))
     cap = (int(factor * T * k) + grouped.ALIGN - 1) // grouped.ALIGN * grouped.ALIGN + El * grouped.ALIGN
     shared = {"W": W, "E": E, "El": El, "cap": cap, "idx": idx.to(torch.int32).contiguous()}
     xe = EPDispatchPull.apply(x, w, shared["idx"], shared)

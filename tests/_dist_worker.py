@@ -187,6 +187,58 @@ def scenario_ddp_tied(a):
             assert torch.allclose(p2.grad._t, g / w, atol=2e-5, rtol=1e-4), (step, n1, float((p2.grad._t - g / w).abs().max()))
 
 
+def scenario_ddp_graph(a):
+    """A data-parallel training step (forward, backward with bucket all-reduces on the communication stream, AdamW)
+    replayed from a CUDA graph follows the eager data-parallel trajectory."""
+    from genesis_b200.models.transformers import TransformerConfig, QwenForCausalLM
+    from genesis_b200.distributed import symm
+    r, d = dist.get_rank(), dev(a.backend)
+    cfg = TransformerConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                            num_attention_heads=2, num_key_value_heads=1, head_dim=64, max_position_embeddings=128,
+                            attention_bias=True)
+
+    def make():
+        genesis.manual_seed(9)
+        m = QwenForCausalLM(cfg).to(d)
+        net = nn.DistributedDataParallel(m, bucket_cap_mb=0.25)
+        opt = genesis.optim.AdamW(m.parameters(), lr=1e-3)
+
+        def step(tokens):
+            idx = genesis.Tensor(tokens._t[:, :-1].contiguous())
+            labels = genesis.Tensor(tokens._t[:, 1:].reshape(-1).contiguous())
+            with genesis.amp.autocast(dtype=genesis.bfloat16):
+                loss = net(idx, labels=labels, return_logits=False)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            return loss
+        return m, net, opt, step
+
+    ma, neta, oa, step_a = make()
+    mb, netb, ob, step_b = make()
+    assert neta._use_symm and netb._use_symm
+    rs = np.random.RandomState(100 + r)
+    batches = [genesis.Tensor(torch.from_numpy(rs.randint(0, 512, (4, 65))).to(d)) for _ in range(6)]
+    graphed = genesis.cuda.GraphedTrainStep(step_b, ob, [batches[0]], warmup=2)
+    for _ in range(2):
+        step_a(batches[0])
+    for i, t in enumerate(batches[1:]):
+        if i == 2:
+            oa.lr = ob.lr = 3e-4
+        la = step_a(t)
+        lb = graphed(t)
+        torch.cuda.synchronize()
+        assert abs(float(la._t) - float(lb._t)) < 2e-3 * max(1.0, abs(float(la._t))), (i, float(la._t), float(lb._t))
+    symm.check_status("graphed ddp")
+    for pa, pb in zip(ma.parameters(), mb.parameters()):
+        assert torch.allclose(pa._t, pb._t, atol=2e-3, rtol=1e-2)
+    # every rank holds the same parameters
+    for pb in mb.parameters():
+        g = pb._t.clone()
+        tdist.broadcast(g, 0)
+        assert torch.equal(g, pb._t)
+
+
 def scenario_ddp_amp(a):
     """fp16-style loss scaling through DDP: an overflow on ONE rank must skip the step on ALL ranks."""
     r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)

@@ -51,3 +51,10 @@ def test_batches_shift_targets_by_one():
     tok = D.ByteTokenizer()
     ids = tok.encode_batch(["hé"])[0]
     assert ids[0] == tok.bos_id and tok.decode(ids) == "hé"
+
+
+def test_cuda_graph_flag_is_refused_without_cuda(tmp_path):
+    import pytest
+    with pytest.raises(SystemExit):
+        _train(["--model", "tiny", "--data", "synthetic", "--vocab-size", "200", "--batch-size", "2", "--block-size", "16",
+                "--device", "cpu", "--out", str(tmp_path / "ck"), "--max-steps", "2", "--cuda-graph"])

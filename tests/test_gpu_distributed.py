@@ -16,7 +16,7 @@ ENV = {"NCCL_NVLS_ENABLE": "0"}
 
 
 @pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("scenario", ["collectives", "ddp", "ddp_tied", "ddp_amp", "ep"])
+@pytest.mark.parametrize("scenario", ["collectives", "ddp", "ddp_tied", "ddp_amp", "ddp_graph", "ep"])
 def test_two_gpu_ranks(scenario):
     launch(scenario, world=2, backend="nccl", env=ENV, timeout=600)
 

@@ -55,3 +55,125 @@ def test_captured_forward_backward_gives_eager_gradients():
     torch.cuda.synchronize()
     for g, p in zip(got, params):
         assert torch.allclose(g, p.grad._t, atol=1e-4, rtol=1e-4)
+
+
+def _tiny_lm(seed):
+    from genesis_b200.models.transformers import TransformerConfig, QwenForCausalLM
+    genesis.manual_seed(seed)
+    cfg = TransformerConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                            num_attention_heads=2, num_key_value_heads=1, head_dim=64, max_position_embeddings=128,
+                            rope_theta=1e4, norm_eps=1e-6, attention_bias=True)
+    return QwenForCausalLM(cfg).cuda()
+
+
+def _lm_step(model, opt):
+    def step(tokens):
+        idx = genesis.Tensor(tokens._t[:, :-1].contiguous())
+        labels = genesis.Tensor(tokens._t[:, 1:].reshape(-1).contiguous())
+        with genesis.amp.autocast(dtype=genesis.bfloat16):
+            loss = model(idx, labels=labels, return_logits=False)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return loss
+    return step
+
+
+def test_capturable_adamw_matches_host_scalars():
+    """Step count, bias corrections and learning rate read from the device vector give the same parameters as the
+    by-value launch arguments, including after a learning-rate change."""
+    a, b = _tiny_lm(3), _tiny_lm(3)
+    oa = genesis.optim.AdamW(a.parameters(), lr=1e-3)
+    ob = genesis.optim.AdamW(b.parameters(), lr=1e-3).make_capturable()
+    sa, sb = _lm_step(a, oa), _lm_step(b, ob)
+    g = torch.Generator("cuda").manual_seed(0)
+    for i in range(5):
+        if i == 3:
+            oa.lr = ob.lr = 3e-4
+        t = genesis.Tensor(torch.randint(0, 512, (4, 65), device="cuda", generator=g))
+        sa(t)
+        sb(t)
+    torch.cuda.synchronize()
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        assert torch.allclose(pa._t, pb._t, atol=1e-6, rtol=1e-5)
+    assert float(ob._dyn[3]) == 5.0
+
+
+def test_graphed_train_step_follows_the_eager_trajectory():
+    """A whole step (forward, backward, AdamW) replayed from a graph tracks eager training on the same batches: same
+    losses and parameters to bf16 round-off, one graph launch per step, learning-rate change honoured."""
+    a, b = _tiny_lm(5), _tiny_lm(5)
+    oa = genesis.optim.AdamW(a.parameters(), lr=1e-3)
+    ob = genesis.optim.AdamW(b.parameters(), lr=1e-3)
+    sa = _lm_step(a, oa)
+    g = torch.Generator("cuda").manual_seed(1)
+    batches = [genesis.Tensor(torch.randint(0, 512, (4, 65), device="cuda", generator=g)) for _ in range(7)]
+    warm = batches[0]
+    graphed = genesis.cuda.GraphedTrainStep(_lm_step(b, ob), ob, [warm], warmup=2)
+    assert graphed.kernels_per_step > 20
+    for _ in range(2):
+        sa(warm)                                                 # the two warm-up steps were real steps on `warm`
+    assert ob.t == 2 and oa.t == 2
+    for i, t in enumerate(batches[1:]):
+        if i == 3:
+            oa.lr = ob.lr = 2e-4
+        la = sa(t)
+        before = native.launch_count
+        lb = graphed(t)
+        assert native.launch_count == before
+        torch.cuda.synchronize()
+        assert abs(float(la._t) - float(lb._t)) < 2e-3 * max(1.0, abs(float(la._t)))
+    assert ob.t == oa.t == 8
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        assert torch.allclose(pa._t, pb._t, atol=2e-3, rtol=1e-2)
+    native.check_status()
+
+
+def test_clip_grad_norm_without_host_read_matches_torch():
+    import genesis_b200.nn as gnn
+    g = torch.Generator("cuda").manual_seed(4)
+    shapes = [(300, 70), (1025,), (64, 64, 3)]
+    for max_norm in (0.5, 1e6):
+        params = []
+        for s in shapes:
+            p = genesis.Tensor(torch.zeros(s, device="cuda"), requires_grad=True)
+            p.grad = genesis.Tensor(torch.randn(s, device="cuda", generator=g))
+            params.append(p)
+        ref = [p.grad._t.clone().requires_grad_(False) for p in params]
+        leaves = [torch.zeros_like(r, requires_grad=True) for r in ref]
+        for leaf, r in zip(leaves, ref):
+            leaf.grad = r.clone()
+        want = torch.nn.utils.clip_grad_norm_(leaves, max_norm)
+        got = gnn.utils.clip_grad_norm_(params, max_norm, sync=False)
+        assert isinstance(got, genesis.Tensor)
+        assert torch.allclose(got._t, want, rtol=1e-5)
+        for p, leaf in zip(params, leaves):
+            assert torch.allclose(p.grad._t, leaf.grad, rtol=1e-5, atol=1e-7)
+        # the reading form gives a float and the same gradients
+        for p, r in zip(params, ref):
+            p.grad = genesis.Tensor(r.clone())
+        total = gnn.utils.clip_grad_norm_(params, max_norm)
+        assert isinstance(total, float) and abs(total - float(want)) < 1e-4 * float(want)
+        for p, leaf in zip(params, leaves):
+            assert torch.allclose(p.grad._t, leaf.grad, rtol=1e-5, atol=1e-7)
+
+
+def test_trainer_app_with_cuda_graph(tmp_path):
+    """The training app with --cuda-graph: three eager steps, capture, replays; logs finite losses and saves."""
+    import importlib
+    import json
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "apps", "nanochat"))
+    train = importlib.import_module("train")
+    metrics = str(tmp_path / "m.jsonl")
+    n = train.main(["--model", "tiny", "--data", "synthetic", "--vocab-size", "512", "--batch-size", "4",
+                    "--block-size", "64", "--device", "cuda", "--out", str(tmp_path / "ck"), "--max-steps", "9",
+                    "--log-interval", "3", "--eval-interval", "0", "--save-interval", "0", "--amp", "--dtype", "bf16",
+                    "--clip-grad", "1.0", "--warmup-steps", "2", "--cuda-graph", "--metrics", metrics])
+    assert n == 9
+    rows = [json.loads(l) for l in open(metrics)]
+    assert [r["step"] for r in rows] == [3, 6, 9]
+    assert all(r["loss"] == r["loss"] and r["loss"] < 10 for r in rows)
+    assert os.path.exists(str(tmp_path / "ck" / "checkpoint_final.pth"))
