@@ -136,6 +136,10 @@ def run_ours(args):
     net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
     opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
     amp_dtype = genesis.bfloat16 if args.dtype == "bf16" else genesis.float16
+    if not args.no_shadows:
+        # the optimizer kernel keeps the compute-dtype copies of the weights current (q/k/v and gate/up stacked), so
+        # autocast converts no parameter during the step
+        opt.enable_shadows(amp_dtype, genesis.nn.utils.fused_parameter_groups(model))
     scaler = genesis.amp.GradScaler(init_scale=2.0 ** 16) if args.dtype == "fp16" else None
     if scaler is not None and world > 1:
         net.set_grad_scaler(scaler)
@@ -211,7 +215,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": args.dtype, "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "config": {"model": args.model, "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
-                   "optimizer": "AdamW lr 3e-4", "cuda_graph": graphed is not None, "l2_policy": "working set (~20 GB activations+grads per step) >> 126 MB L2; "
+                   "optimizer": "AdamW lr 3e-4", "cuda_graph": graphed is not None, "weight_copies": "kept by optimizer" if not args.no_shadows else "cast per step", "l2_policy": "working set (~20 GB activations+grads per step) >> 126 MB L2; "
                    "4 distinct input batches rotated"},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -250,6 +254,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--no-shadows", action="store_true",
+                    help="convert the fp32 weights to the compute dtype every step instead of keeping copies current")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", 1))

@@ -16,4 +16,47 @@ class _AmpState(threading.local):
         self.cache = {}
 
 
+class ShadowEntry:
+    """A persistent low-precision copy of a parameter, kept current by the optimizer kernel (see
+    `optim.Optimizer.enable_shadows`).  `version` is the parameter's `_version` at the last refresh: any in-place
+    change through the Tensor API makes the entry stale and the autocast cast falls back to a conversion."""
+    __slots__ = ("param", "lp", "version", "group")
+
+    def __init__(self, param, lp, group):
+        self.param, self.lp, self.version, self.group = param, lp, param._version, group
+
+    def valid(self, raw, dtype):
+        p = self.param
+        return p._t is raw and self.version == p._version and self.lp.dtype == dtype
+
+
+# fp32 parameter storage address -> ShadowEntry (process-wide: parameters are shared between threads)
+shadows = {}
+
+
+def shadow_of(raw, dtype):
+    """The current low-precision copy of the parameter whose storage is `raw`, or None."""
+    if not shadows:
+        return None
+    e = shadows.get(raw.data_ptr())
+    return e.lp if e is not None and e.valid(raw, dtype) else None
+
+
+def stacked_shadow_of(raws, dtype):
+    """When `raws` are exactly the members of one shadow group, in order, and all current: the group's stacked
+    low-precision buffer (rows of the members one after another).  None otherwise."""
+    if not shadows:
+        return None
+    first = shadows.get(raws[0].data_ptr())
+    if first is None or first.group is None:
+        return None
+    members, buf = first.group
+    if len(members) != len(raws):
+        return None
+    for e, r in zip(members, raws):
+        if not e.valid(r, dtype):
+            return None
+    return buf
+
+
 amp_state = _AmpState()

@@ -31,11 +31,12 @@ struct AdamArgs {
 
 // Step-dependent scalars kept on the device so that a captured CUDA graph of the step stays valid when replayed:
 // dyn[0] learning rate (written by the host between replays), dyn[1] / dyn[2] bias corrections, dyn[3] step count.
-__global__ void adam_dyn_advance_kernel(float* __restrict__ dyn, float beta1, float beta2) {
+// The betas arrive as doubles so that the corrections round to the same floats as the host's 1 - beta ** step.
+__global__ void adam_dyn_advance_kernel(float* __restrict__ dyn, double beta1, double beta2) {
   const double step = (double)dyn[3] + 1.0;
   dyn[3] = (float)step;
-  dyn[1] = (float)(1.0 - pow((double)beta1, step));
-  dyn[2] = (float)(1.0 - pow((double)beta2, step));
+  dyn[1] = (float)(1.0 - pow(beta1, step));
+  dyn[2] = (float)(1.0 - pow(beta2, step));
 }
 
 __device__ __forceinline__ void adam_update(float& pi, float& mi, float& vi, float gi, const AdamArgs& a) {
@@ -62,8 +63,10 @@ adam_multi_kernel(const long long* __restrict__ meta, int nt, AdamArgs a, const 
   const long long base = (blockIdx.x - meta[6ll * nt + t]) * OPT_CHUNK;
   const float gs = grad_scale != nullptr ? *grad_scale : 1.f;
   const long long end = (base + OPT_CHUNK < n) ? base + OPT_CHUNK : n;
-  // fp32 gradients, no shadow copy, 16-byte aligned tensors: four elements per thread and access
-  const bool vec = gdt == DT_F32 && sh == nullptr &&
+  // fp32 gradients, 16-byte aligned tensors (and an 8-byte aligned 16-bit shadow copy, if any): four elements per
+  // thread and access
+  const bool sh16 = a.shadow_dtype == DT_BF16 || a.shadow_dtype == DT_F16;
+  const bool vec = gdt == DT_F32 && (sh == nullptr || (sh16 && ((uintptr_t)sh & 7) == 0)) &&
       (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0;
   if (vec) {
     const long long end4 = base + ((end - base) & ~3ll);
@@ -79,11 +82,18 @@ adam_multi_kernel(const long long* __restrict__ meta, int nt, AdamArgs a, const 
       *reinterpret_cast<float4*>(p + i) = p4;
       *reinterpret_cast<float4*>(m + i) = m4;
       *reinterpret_cast<float4*>(v + i) = v4;
+      if (sh != nullptr) {
+        uint2 o;
+        if (a.shadow_dtype == DT_BF16) { o.x = pack2c<true>(p4.x, p4.y); o.y = pack2c<true>(p4.z, p4.w); }
+        else { o.x = pack2c<false>(p4.x, p4.y); o.y = pack2c<false>(p4.z, p4.w); }
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(sh) + i) = o;
+      }
     }
     for (long long i = end4 + threadIdx.x; i < end; i += OPT_THREADS) {
       float pi = p[i], mi = m[i], vi = v[i];
       adam_update(pi, mi, vi, reinterpret_cast<const float*>(g)[i] * gs, a);
       p[i] = pi; m[i] = mi; v[i] = vi;
+      if (sh != nullptr) store_from_float(sh, a.shadow_dtype, i, pi);
     }
     return;
   }
@@ -158,7 +168,7 @@ extern "C" int gb_adam_multi(const long long* meta, int nt, long long total_chun
   return (int)cudaGetLastError();
 }
 
-extern "C" int gb_adam_dyn_advance(float* dyn, float beta1, float beta2, cudaStream_t st) {
+extern "C" int gb_adam_dyn_advance(float* dyn, double beta1, double beta2, cudaStream_t st) {
   adam_dyn_advance_kernel<<<1, 1, 0, st>>>(dyn, beta1, beta2);
   return (int)cudaGetLastError();
 }

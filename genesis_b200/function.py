@@ -19,7 +19,7 @@ from enum import Enum
 import torch
 
 from . import grad_mode
-from .amp_state import amp_state
+from .amp_state import amp_state, shadow_of
 
 
 # GENESIS_NVTX=1: one NVTX range per Function forward (and "<name>.backward" per backward node), for timelines
@@ -210,9 +210,9 @@ class Cast(Function):
     keep_ctx = True
 
     @staticmethod
-    def forward(ctx, x, dtype):
+    def forward(ctx, x, dtype, current_copy=None):
         ctx.src = x.dtype
-        return _cast_raw(x, dtype)
+        return current_copy if current_copy is not None else _cast_raw(x, dtype)
 
     @staticmethod
     def backward(ctx, g):
@@ -228,7 +228,8 @@ def cast(t, dtype):
         hit = amp_state.cache.get(key)
         if hit is not None and hit[0] is t and hit[2] == t._version:
             return hit[1]
-        out = Cast.apply(t, dtype)
+        # a copy the optimizer keeps current replaces the conversion kernel
+        out = Cast.apply(t, dtype, shadow_of(t._t, dtype))
         amp_state.cache[key] = (t, out, t._version)
         return out
     return Cast.apply(t, dtype)

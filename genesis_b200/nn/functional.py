@@ -17,7 +17,7 @@ import torch
 from ..function import Function, AMPPolicy, cast
 from ..tensor import Tensor
 from ..ops import dispatch as K
-from ..amp_state import amp_state
+from ..amp_state import amp_state, shadow_of, stacked_shadow_of
 from .. import random as _random
 
 _pysum, _pymax, _pymin, _pyabs, _pypow = builtins.sum, builtins.max, builtins.min, builtins.abs, builtins.pow
@@ -512,6 +512,9 @@ class LinearFunction(Function):
 def _cached_param_cast(w, dtype):
     if w.dtype == dtype:
         return w
+    lp = shadow_of(w, dtype)                      # a copy the optimizer keeps current: no conversion kernel
+    if lp is not None:
+        return lp
     key = ("raw", w.data_ptr(), w._version, dtype)
     hit = amp_state.cache.get(key)
     if hit is not None and hit[0] is w:
@@ -1442,7 +1445,11 @@ def rope(x, cos, sin, positions=None):
 
 def _fused_params(tensors, dtype):
     """Rows of several parameter matrices (or several bias vectors) stacked in one tensor of `dtype`, rebuilt only when
-    one of them changed (same cache and lifetime as the per-parameter autocast copies)."""
+    one of them changed (same cache and lifetime as the per-parameter autocast copies).  Parameters whose
+    low-precision copies the optimizer keeps in one stacked buffer need no kernel at all."""
+    lp = stacked_shadow_of(tensors, dtype)
+    if lp is not None:
+        return lp
     key = ("fused", tuple(t.data_ptr() for t in tensors), tuple(t._version for t in tensors), dtype)
     hit = amp_state.cache.get(key)
     if hit is not None and all(a is b for a, b in zip(hit[0], tensors)):

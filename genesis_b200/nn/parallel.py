@@ -107,6 +107,8 @@ class DistributedDataParallel(Module):
                 n = t.numel()
                 t.copy_(flat[off:off + n].reshape(t.shape))
                 off += n
+        for p in model.parameters():
+            p._version += 1            # overwritten in place: cached casts and low-precision copies are stale
 
     def _build_buckets(self, params):
         cur = {}

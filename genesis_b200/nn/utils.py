@@ -36,3 +36,19 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2, sync=True):
     if coef < 1:
         K.scale_grads_(grads, coef)
     return total
+
+
+def fused_parameter_groups(model):
+    """Parameter lists that layers of `model` multiply as one stacked matrix: the q/k/v projections of every attention
+    block and the gate/up projections of every SwiGLU block (weights, and biases where present).  Hand them to
+    `Optimizer.enable_shadows(dtype, groups=...)` so that the low-precision copies of each list live in one buffer."""
+    groups = []
+    for m in model.modules():
+        for names in (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj")):
+            subs = [getattr(m, n, None) for n in names]
+            if any(s is None or getattr(s, "weight", None) is None for s in subs):
+                continue
+            groups.append([s.weight for s in subs])
+            if all(getattr(s, "bias", None) is not None for s in subs):
+                groups.append([s.bias for s in subs])
+    return groups

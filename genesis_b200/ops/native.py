@@ -41,7 +41,7 @@ _SIGS = {
     "gb_swiglu_fwd2d": "ppliip", "gb_swiglu_bwd2d": "pppliip", "gb_rope": "pppppiiiiiillp",
     "gb_gather_rows": "pppllilpp", "gb_scatter_add_rows": "pppliiilpp",
     "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
-    "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiipppp", "gb_adam_dyn_advance": "pffp", "gb_copy_h2d_async": "pplp", "gb_sgd_multi": "pilfffp",
+    "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiipppp", "gb_adam_dyn_advance": "pddp", "gb_copy_h2d_async": "pplp", "gb_sgd_multi": "pilfffp",
     "gb_grad_multi": "pilpfppip",
     "gb_router_fwd": "ppppp" + "liiiip", "gb_router_bwd": "pppppp" + "liiiip",
     "gb_moe_sort": "pppppp" + "liiilp", "gb_moe_combine": "pppp" + "liiip", "gb_moe_combine_bwd": "pppppp" + "liiip",
@@ -273,10 +273,23 @@ def _strided_copy(src, dst):
     nd = src.dim()
     if nd > 6 or nd == 0:
         return False
-    sh = (ctypes.c_longlong * 6)(*src.shape)
-    ss = (ctypes.c_longlong * 6)(*src.stride())
-    ds = (ctypes.c_longlong * 6)(*dst.stride())
-    _chk(lib().gb_copy_strided(src.data_ptr(), dst.data_ptr(), nd, sh, ss, ds, src.element_size(), _st()), "copy")
+    shape, sst, dst_st, es = list(src.shape), list(src.stride()), list(dst.stride()), src.element_size()
+    if sst[-1] == 1 and dst_st[-1] == 1 and es < 8:
+        # rows that are contiguous on both sides move in wider units (up to 8 bytes) when extents, strides and base
+        # addresses allow: fewer, fatter elements for the index arithmetic of the strided kernel
+        for f in (8 // es, 4 // es, 2 // es):
+            wb = es * f
+            if f > 1 and shape[-1] % f == 0 and src.data_ptr() % wb == 0 and dst.data_ptr() % wb == 0 \
+                    and all(v % f == 0 for v in sst[:-1]) and all(v % f == 0 for v in dst_st[:-1]):
+                shape[-1] //= f
+                sst[:-1] = [v // f for v in sst[:-1]]
+                dst_st[:-1] = [v // f for v in dst_st[:-1]]
+                es = wb
+                break
+    sh = (ctypes.c_longlong * 6)(*shape)
+    ss = (ctypes.c_longlong * 6)(*sst)
+    ds = (ctypes.c_longlong * 6)(*dst_st)
+    _chk(lib().gb_copy_strided(src.data_ptr(), dst.data_ptr(), nd, sh, ss, ds, es, _st()), "copy")
     return True
 
 

