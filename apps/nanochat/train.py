@@ -54,6 +54,8 @@ def parse_args(argv=None):
     ap.add_argument("--device", default=None, help="default: cuda when available, else cpu")
     ap.add_argument("--warmup-steps", type=int, default=0, help="linear warm-up, then cosine decay to --max-steps")
     ap.add_argument("--clip-grad", type=float, default=0.0)
+    ap.add_argument("--weight-copies", action="store_true",
+                    help="with --amp on CUDA: let the optimizer keep the bf16 / fp16 copies of the weights current")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="capture the whole step (forward, backward, clipping, optimizer) as a CUDA graph after three "
                          "eager steps and replay it; needs CUDA, --accumulation-steps 1 and, with --ddp, the "
@@ -119,10 +121,13 @@ def main(argv=None):
     if ddp:
         dist.barrier()
     opt = genesis.optim.AdamW(model.parameters(), lr=args.learning_rate)
+    amp_dtype = genesis.float16 if args.dtype == "fp16" else genesis.bfloat16
+    if args.weight_copies and args.amp and device.startswith("cuda"):
+        # the optimizer kernel keeps the compute-dtype copies of the weights current: no per-step conversions
+        opt.enable_shadows(amp_dtype, nn.utils.fused_parameter_groups(model))
     sched = None
     if args.max_steps and (args.warmup_steps or args.max_steps):
         sched = get_cosine_schedule_with_warmup(opt, args.warmup_steps, args.max_steps)
-    amp_dtype = genesis.float16 if args.dtype == "fp16" else genesis.bfloat16
     scaler = genesis.amp.GradScaler() if (args.amp and args.dtype == "fp16") else None
     if scaler is not None and ddp:
         net.set_grad_scaler(scaler)

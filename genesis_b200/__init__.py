@@ -8,7 +8,7 @@ __version__ = "0.1.0"
 from .dtypes import (float32, float16, float64, bfloat16, int32, int64, int16, int8, uint8, bool,  # noqa: A004
                      get_dtype, is_floating_point, is_integer, DType)
 from .amp_state import amp_state as _amp_state
-from .tensor import Tensor, tensor
+from .tensor import Tensor, make_tensor, tensor
 from .init import (rand, randn, randn_like, randint, ones, zeros, full, full_like, empty, empty_like, zeros_like,
                    ones_like, one_hot, eye, arange, outer, from_numpy, multinomial)
 from .serialization import save, load, save_checkpoint, load_checkpoint

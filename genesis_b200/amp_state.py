@@ -5,6 +5,7 @@ The reference keeps these flags as process-global module attributes
 watchdog thread can never observe another thread's autocast region.
 """
 import threading
+import weakref
 
 import torch
 
@@ -20,7 +21,7 @@ class ShadowEntry:
     """A persistent low-precision copy of a parameter, kept current by the optimizer kernel (see
     `optim.Optimizer.enable_shadows`).  `version` is the parameter's `_version` at the last refresh: any in-place
     change through the Tensor API makes the entry stale and the autocast cast falls back to a conversion."""
-    __slots__ = ("param", "lp", "version", "group")
+    __slots__ = ("param", "lp", "version", "group", "__weakref__")
 
     def __init__(self, param, lp, group):
         self.param, self.lp, self.version, self.group = param, lp, param._version, group
@@ -30,8 +31,9 @@ class ShadowEntry:
         return p._t is raw and self.version == p._version and self.lp.dtype == dtype
 
 
-# fp32 parameter storage address -> ShadowEntry (process-wide: parameters are shared between threads)
-shadows = {}
+# fp32 parameter storage address -> ShadowEntry (process-wide: parameters are shared between threads).  The optimizer
+# that maintains the copies owns the entries; they leave this table when it is collected.
+shadows = weakref.WeakValueDictionary()
 
 
 def shadow_of(raw, dtype):

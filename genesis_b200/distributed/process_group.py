@@ -114,3 +114,10 @@ def get_backend():
 
 def is_initialized():
     return _initialized
+
+
+def barrier():
+    """Block until every rank of the group arrives (reference `distributed/process_group.py:118-127`)."""
+    _check()
+    from . import collectives
+    collectives.barrier()

@@ -137,3 +137,9 @@ def infer_dtype_from_data(data):
             return int64
         return get_dtype(arr.dtype)
     return default_dtype
+
+
+# Lists kept for API parity with the reference (`dtypes.py:183-185`).
+all_dtypes = [float32, float16, float64, bfloat16, int32, int64, int16, int8, uint8, bool]
+floating_dtypes = [dt for dt in all_dtypes if dt.is_floating_point]
+integer_dtypes = [dt for dt in all_dtypes if not dt.is_floating_point and dt is not bool]

@@ -252,3 +252,46 @@ class CastToFP32:
     @staticmethod
     def apply(t):
         return cast(t, torch.float32)
+
+
+def cast_to_fp16(a):
+    """Differentiable cast; a tensor that already has the dtype is returned as is (keeps its creator)."""
+    return cast(a, torch.float16)
+
+
+def cast_to_fp32(a):
+    return cast(a, torch.float32)
+
+
+def cast_to_bf16(a):
+    return cast(a, torch.bfloat16)
+
+
+def check_dtype(value, dtype):
+    """True when `value` (a tensor, or dicts / lists / tuples of them) contains a tensor of `dtype`
+    (reference `function.py:130-147`)."""
+    from .tensor import Tensor
+    if isinstance(value, Tensor):
+        return value.dtype == dtype
+    if isinstance(value, dict):
+        return any(check_dtype(k, dtype) or check_dtype(v, dtype) for k, v in value.items())
+    if isinstance(value, (list, tuple)):
+        return any(check_dtype(v, dtype) for v in value)
+    return False
+
+
+class AccumulateGrad:
+    """Gradient sink of a leaf tensor (reference `function.py:16-60`).  The engine here keeps the leaf on the edge
+    itself (`Edge.leaf`) and never builds these nodes; the class exists for code that constructs one by hand:
+    `apply_grad(g)` adds `g` into `tensor.grad` and fires the tensor's hooks, like the engine does."""
+
+    def __init__(self, tensor):
+        import weakref
+        self.variable = weakref.ref(tensor)
+        self.next_functions = []
+
+    def apply_grad(self, grad):
+        t = self.variable()
+        if t is not None:
+            from .tensor import _accumulate_leaf
+            _accumulate_leaf(t, grad._t if hasattr(grad, "_t") else grad, True)

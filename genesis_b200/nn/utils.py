@@ -6,6 +6,15 @@ import torch
 from ..ops import dispatch as K
 
 
+def norm(data, p=2):
+    """p-norm of all elements as a differentiable 0-d tensor (reference `nn/utils.py:3-7`: (sum x**p)**(1/p), no
+    absolute value)."""
+    from .. import nn as _nn
+    F = _nn.functional
+    return F.pow_scalar(F.summation(F.pow_scalar(data, p)), 1.0 / p) if hasattr(F, "pow_scalar") else \
+        (data ** p).sum() ** (1.0 / p)
+
+
 def clip_grad_norm_(parameters, max_norm, norm_type=2, sync=True):
     """Scale all gradients so that their total norm is at most `max_norm`; returns the norm before clipping.
 

@@ -102,3 +102,56 @@ def nvtx_range(name):
             torch.cuda.nvtx.range_pop()
     else:
         yield
+
+
+# ---- names of the reference's module (`utils/profile.py:11-72`) ---------------------------------------------------
+start_time = time.time()
+
+
+class _ProfileView(dict):
+    """Read-only `{name: {"calls": n, "total_time": s}}` view over the accumulated totals."""
+
+    def _sync(self):
+        dict.clear(self)
+        for k, (n, t) in _totals.items():
+            dict.__setitem__(self, k, {"calls": n, "total_time": t})
+        return self
+
+    def __getitem__(self, k):
+        return dict.__getitem__(self._sync(), k)
+
+    def __iter__(self):
+        return dict.__iter__(self._sync())
+
+    def __len__(self):
+        return dict.__len__(self._sync())
+
+    def items(self):
+        return dict.items(self._sync())
+
+    def keys(self):
+        return dict.keys(self._sync())
+
+    def __contains__(self, k):
+        return k in _totals
+
+    def __eq__(self, other):
+        return dict(self._sync()) == other
+
+
+profile_data = _ProfileView()
+
+
+def profile_method(func):
+    """Wrap one function with call counting and wall-clock accumulation."""
+    global _enabled_print
+    _enabled_print = True
+    return _wrap_fn(func, f"{func.__module__}.{func.__qualname__}")
+
+
+def print_profile_data():
+    """Print the totals now (they are also printed at interpreter exit once anything was profiled)."""
+    if _totals:
+        print(f"Program cost {time.time() - start_time:.4f} seconds!")
+        for name, (n, t) in _totals.items():
+            print(f"{name}: {n} calls, {t:.4f} total seconds")

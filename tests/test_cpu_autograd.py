@@ -416,3 +416,37 @@ def test_fused_gate_up_swiglu_matches_the_separate_ops():
     (h2 * genesis.Tensor(go)).sum().backward()
     assert torch.allclose(x1.grad._t, x2.grad._t, atol=1e-4)
     assert torch.allclose(wg.grad._t, wg2.grad._t, atol=1e-4) and torch.allclose(wu.grad._t, wu2.grad._t, atol=1e-4)
+
+
+def test_small_reference_names_exist_and_work():
+    """Helpers the reference exposes beside its main API: dtype lists, cast helpers, `check_dtype`, a hand-built
+    `AccumulateGrad`, `nn.utils.norm`, the profiling table."""
+    import genesis_b200.function as Fn
+    import genesis_b200.nn as gnn
+    from genesis_b200 import dtypes
+    import importlib
+    prof = importlib.import_module("genesis_b200.utils.profile")
+    assert genesis.bfloat16 in dtypes.floating_dtypes and genesis.int64 in dtypes.integer_dtypes
+    assert len(dtypes.all_dtypes) == 10 and dtypes.bool not in dtypes.integer_dtypes
+    x = genesis.tensor([[1.0, -2.0], [3.0, 4.0]], requires_grad=True)
+    h = Fn.cast_to_bf16(x)
+    assert h.dtype == genesis.bfloat16 and Fn.cast_to_bf16(h) is h and Fn.cast_to_fp32(x) is x
+    assert Fn.check_dtype({"a": [h]}, genesis.bfloat16) and not Fn.check_dtype((x,), genesis.float16)
+    n = gnn.utils.norm(x)
+    assert abs(float(n.item()) - 30.0 ** 0.5) < 1e-5
+    n.backward()
+    assert torch.allclose(x.grad._t, x._t / 30.0 ** 0.5, atol=1e-6)
+    leaf = genesis.tensor([1.0, 2.0], requires_grad=True)
+    node = Fn.AccumulateGrad(leaf)
+    node.apply_grad(genesis.tensor([0.5, 0.5]))
+    node.apply_grad(genesis.tensor([0.5, 0.5]))
+    assert leaf.grad._t.tolist() == [1.0, 1.0]
+
+    @prof.profile_method
+    def f(a):
+        return a + 1
+    f(1)
+    f(2)
+    key = [k for k in prof.profile_data if k.endswith("f")][0]
+    assert prof.profile_data[key]["calls"] == 2 and prof.profile_data[key]["total_time"] >= 0.0
+    prof.print_profile_data()

@@ -185,7 +185,8 @@ def test_trainer_app_with_cuda_graph(tmp_path):
     n = train.main(["--model", "tiny", "--data", "synthetic", "--vocab-size", "512", "--batch-size", "4",
                     "--block-size", "64", "--device", "cuda", "--out", str(tmp_path / "ck"), "--max-steps", "9",
                     "--log-interval", "3", "--eval-interval", "0", "--save-interval", "0", "--amp", "--dtype", "bf16",
-                    "--clip-grad", "1.0", "--warmup-steps", "2", "--cuda-graph", "--metrics", metrics])
+                    "--clip-grad", "1.0", "--warmup-steps", "2", "--cuda-graph", "--weight-copies",
+                    "--metrics", metrics])
     assert n == 9
     rows = [json.loads(l) for l in open(metrics)]
     assert [r["step"] for r in rows] == [3, 6, 9]
@@ -217,6 +218,47 @@ def test_adamw_kernel_writes_current_low_precision_copies(lp):
         for i, (x, y) in enumerate(zip(pa, pb)):
             assert torch.equal(x._t, y._t)
             assert torch.equal(ob._shadows[i], y._t.to(td))
+    finally:
+        ob.disable_shadows()
+    native.check_status()
+
+
+def test_graphed_fp16_step_with_grad_scaler_and_weight_copies():
+    """fp16 autocast + GradScaler + optimizer-kept fp16 weight copies inside one captured step: tracks the eager
+    run, the loss scale grows on the device across replays, and an overflow step is skipped in both."""
+    def build():
+        m = _tiny_lm(7)
+        o = genesis.optim.AdamW(m.parameters(), lr=1e-3)
+        sc = genesis.amp.GradScaler(init_scale=2.0 ** 10, growth_interval=3)
+
+        def step(tokens):
+            idx = genesis.Tensor(tokens._t[:, :-1].contiguous())
+            labels = genesis.Tensor(tokens._t[:, 1:].reshape(-1).contiguous())
+            with genesis.amp.autocast(dtype=genesis.float16):
+                loss = m(idx, labels=labels, return_logits=False)
+            o.zero_grad()
+            sc.scale(loss).backward()
+            sc.step(o)
+            sc.update()
+            return loss
+        return m, o, sc, step
+
+    a, oa, sa_, step_a = build()
+    b, ob, sb_, step_b = build()
+    ob.enable_shadows(genesis.float16, genesis.nn.utils.fused_parameter_groups(b))
+    try:
+        g = torch.Generator("cuda").manual_seed(3)
+        batches = [genesis.Tensor(torch.randint(0, 512, (4, 65), device="cuda", generator=g)) for _ in range(8)]
+        graphed = genesis.cuda.GraphedTrainStep(step_b, ob, [batches[0]], warmup=2)
+        for _ in range(2):
+            step_a(batches[0])
+        for t in batches[1:]:
+            la, lb = step_a(t), graphed(t)
+            torch.cuda.synchronize()
+            assert abs(float(la._t) - float(lb._t)) < 2e-3 * max(1.0, abs(float(la._t)))
+        assert sa_.get_scale() == sb_.get_scale() and sb_.get_scale() > 2.0 ** 10      # grew inside the replays
+        gap = max(float((p._t - q._t).abs().mean()) for p, q in zip(a.parameters(), b.parameters()))
+        assert gap < 5e-5, gap
     finally:
         ob.disable_shadows()
     native.check_status()
