@@ -50,18 +50,39 @@ __device__ __forceinline__ void load_weights_or(const TW* __restrict__ w, int ba
 }
 
 // ------------------------------------------------------------------------------------------
-// RMSNorm
+// RMSNorm.  With `res` the forward kernels normalise s = x + res (rounded to T, as a separate addition would leave it)
+// and also store s to `sum_out`: the residual addition of a pre-norm transformer block rides along with the
+// normalisation that follows it.  With `gres` the backward kernels add the gradient that reaches s along the
+// residual path to the one coming back through the normalisation.
 // ------------------------------------------------------------------------------------------
+template <typename T, int NORM_MAXV>
+__device__ __forceinline__ void add_residual_row(const T* __restrict__ res, T* __restrict__ sum_out, int nv,
+                                                 Vec16<T> (&buf)[NORM_MAXV]) {
+  constexpr int V = Vec16<T>::N;
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k) {
+    const int i = threadIdx.x + k * NORM_THREADS;
+    if (i < nv) {
+      const Vec16<T> rb = ld16(res + (long long)i * V);
+#pragma unroll
+      for (int j = 0; j < V; ++j) buf[k].v[j] = Cvt<T>::from_f(Cvt<T>::to_f(buf[k].v[j]) + Cvt<T>::to_f(rb.v[j]));
+      st16(sum_out + (long long)i * V, buf[k]);
+    }
+  }
+}
+
 template <typename T, typename TW, int NORM_MAXV>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restrict__ y, float* __restrict__ rstd,
-                   long long rows, int cols, float eps) {
+                   long long rows, int cols, float eps, const T* __restrict__ res = nullptr,
+                   T* __restrict__ sum_out = nullptr) {
   __shared__ float sh[32];
   constexpr int V = Vec16<T>::N;
   const int nv = cols / V;
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     Vec16<T> buf[NORM_MAXV];
     load_row<T, NORM_MAXV>(x + row * cols, cols, buf);
+    if (res != nullptr) add_residual_row<T, NORM_MAXV>(res + row * cols, sum_out + row * cols, nv, buf);
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < NORM_MAXV; ++k)
@@ -91,7 +112,7 @@ template <typename T, typename TW, int NORM_MAXV>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* __restrict__ w,
                    const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_partial,
-                   long long rows, int cols) {
+                   long long rows, int cols, const T* __restrict__ gres = nullptr) {
   __shared__ float sh[32];
   constexpr int V = Vec16<T>::N;
   const int nv = cols / V;
@@ -126,14 +147,17 @@ rmsnorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* _
     for (int k = 0; k < NORM_MAXV; ++k) {
       const int i = threadIdx.x + k * NORM_THREADS;
       if (i < nv) {
-        Vec16<T> o;
+        Vec16<T> o, gr;
         float wv[V];
         load_weights<TW, V>(w, i * V, wv);
+        if (gres != nullptr) gr = ld16(gres + row * cols + (long long)i * V);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
           const float gw = Cvt<T>::to_f(gb_[k].v[j]) * wv[j];
-          o.v[j] = Cvt<T>::from_f(r * (gw - xh * dot));
+          float d = r * (gw - xh * dot);
+          if (gres != nullptr) d += Cvt<T>::to_f(gr.v[j]);
+          o.v[j] = Cvt<T>::from_f(d);
         }
         st16(dx + row * cols + (long long)i * V, o);
       }
@@ -158,7 +182,8 @@ constexpr int NORM_WARPS = NORM_THREADS / 32;
 template <typename T, typename TW, int MVW>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restrict__ y, float* __restrict__ rstd,
-                        long long rows, int cols, float eps) {
+                        long long rows, int cols, float eps, const T* __restrict__ res = nullptr,
+                        T* __restrict__ sum_out = nullptr) {
   constexpr int V = Vec16<T>::N;
   const int nv = cols / V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -171,6 +196,20 @@ rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __
 #pragma unroll
     for (int k = 0; k < MVW; ++k)
       if (lane + 32 * k < nv) buf[k] = ld16(x + row * cols + (long long)(lane + 32 * k) * V);
+    if (res != nullptr) {
+      Vec16<T> rb[MVW];                       // all loads of the row in flight before the first use
+#pragma unroll
+      for (int k = 0; k < MVW; ++k)
+        if (lane + 32 * k < nv) rb[k] = ld16(res + row * cols + (long long)(lane + 32 * k) * V);
+#pragma unroll
+      for (int k = 0; k < MVW; ++k)
+        if (lane + 32 * k < nv) {
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            buf[k].v[j] = Cvt<T>::from_f(Cvt<T>::to_f(buf[k].v[j]) + Cvt<T>::to_f(rb[k].v[j]));
+          st16(sum_out + row * cols + (long long)(lane + 32 * k) * V, buf[k]);
+        }
+    }
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < MVW; ++k)
@@ -191,67 +230,130 @@ rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __
   }
 }
 
+// Backward for narrow rows.  A row's gradient needs the whole row twice (dot product, then the result), so a warp that
+// loads, reduces and stores one row at a time leaves the memory system idle half of the time.  Here every lane runs a
+// private ring of asynchronous 16-byte copies (cp.async, global -> shared, no registers held): the operands of the
+// next RING-1 rows of its warp are in flight while the current row is reduced.  A lane reads back only the slots it
+// copied itself, so the ring needs no barriers, and cp.async.wait_group is a dependency wait, not a spin.
+// One CTA per SM (the ring takes up to 144 KB), grid = at most 148 CTAs, each writing one row of the dw partials.
+constexpr int NORM_RING = 2;
+constexpr int NORM_BWD_THREADS = 512;                      // 16 warps: enough rows in progress to hide the per-row chain
+constexpr int NORM_BWD_WARPS = NORM_BWD_THREADS / 32;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <typename T, typename TW, int MVW>
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_BWD_THREADS, 1)
 rmsnorm_bwd_warp_kernel(const T* __restrict__ g, const T* __restrict__ x, const TW* __restrict__ w,
                         const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_partial,
-                        long long rows, int cols) {
+                        long long rows, int cols, const T* __restrict__ gres = nullptr) {
   constexpr int V = Vec16<T>::N;
-  __shared__ float red[NORM_WARPS][32 * MVW * V + 1];
+  extern __shared__ __align__(16) unsigned char norm_smem[];
   const int nv = cols / V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float wv[MVW][V], dwacc[MVW][V];
+  const size_t row_bytes = (size_t)cols * sizeof(T);                       // a multiple of 16
+  unsigned char* ring = norm_smem + (size_t)warp * NORM_RING * 3 * row_bytes;   // [stage][x | g | gres][row]
+  const long long stride = (long long)gridDim.x * NORM_BWD_WARPS;
+  const long long first = (long long)blockIdx.x * NORM_BWD_WARPS + warp;
+
+  auto issue = [&](long long row, int stage) {
+    if (row < rows) {
+      unsigned char* base = ring + (size_t)stage * 3 * row_bytes;
 #pragma unroll
-  for (int k = 0; k < MVW; ++k) {
-#pragma unroll
-    for (int j = 0; j < V; ++j) { dwacc[k][j] = 0.f; wv[k][j] = 0.f; }
-    if (lane + 32 * k < nv) load_weights<TW, V>(w, (lane + 32 * k) * V, wv[k]);
-  }
-  for (long long row = (long long)blockIdx.x * NORM_WARPS + warp; row < rows; row += (long long)gridDim.x * NORM_WARPS) {
-    Vec16<T> xb[MVW], gb_[MVW];
-#pragma unroll
-    for (int k = 0; k < MVW; ++k)
-      if (lane + 32 * k < nv) {
-        xb[k] = ld16(x + row * cols + (long long)(lane + 32 * k) * V);
-        gb_[k] = ld16(g + row * cols + (long long)(lane + 32 * k) * V);
+      for (int k = 0; k < MVW; ++k) {
+        const int i = lane + 32 * k;
+        if (i < nv) {
+          const long long off = row * cols + (long long)i * V;
+          cp_async16(base + (size_t)i * 16, x + off);
+          cp_async16(base + row_bytes + (size_t)i * 16, g + off);
+          if (gres != nullptr) cp_async16(base + 2 * row_bytes + (size_t)i * 16, gres + off);
+        }
       }
+    }
+    cp_async_commit();                                   // an empty group keeps the count uniform past the last row
+  };
+
+  float dwacc[MVW][V];
+#pragma unroll
+  for (int k = 0; k < MVW; ++k)
+#pragma unroll
+    for (int j = 0; j < V; ++j) dwacc[k][j] = 0.f;
+#pragma unroll
+  for (int st = 0; st < NORM_RING - 1; ++st) issue(first + st * stride, st);
+  int stage = 0;
+  for (long long row = first; row < rows; row += stride) {
+    // refill the stage that the previous iteration consumed, then wait for this row's group (the oldest)
+    issue(row + (NORM_RING - 1) * stride, (stage + NORM_RING - 1) % NORM_RING);
+    cp_async_wait<NORM_RING - 1>();
+    const unsigned char* base = ring + (size_t)stage * 3 * row_bytes;
+    // both passes read the operands from the ring (shared memory) instead of holding them in registers
     const float r = rstd[row];
     float dot = 0.f;
 #pragma unroll
     for (int k = 0; k < MVW; ++k)
-      if (lane + 32 * k < nv)
+      if (lane + 32 * k < nv) {
+        const Vec16<T> xb = *reinterpret_cast<const Vec16<T>*>(base + (size_t)(lane + 32 * k) * 16);
+        const Vec16<T> gb_ = *reinterpret_cast<const Vec16<T>*>(base + row_bytes + (size_t)(lane + 32 * k) * 16);
+        float wv[V];
+        load_weights<TW, V>(w, (lane + 32 * k) * V, wv);   // 3.5 KB row, resident in L1
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
-          const float gg = Cvt<T>::to_f(gb_[k].v[j]);
-          dot += gg * wv[k][j] * xh;
+          const float xh = Cvt<T>::to_f(xb.v[j]) * r;
+          const float gg = Cvt<T>::to_f(gb_.v[j]);
+          dot += gg * wv[j] * xh;
           dwacc[k][j] += gg * xh;
         }
+      }
     dot = warp_sum(dot) / cols;
 #pragma unroll
     for (int k = 0; k < MVW; ++k)
       if (lane + 32 * k < nv) {
-        Vec16<T> o;
+        const Vec16<T> xb = *reinterpret_cast<const Vec16<T>*>(base + (size_t)(lane + 32 * k) * 16);
+        const Vec16<T> gb_ = *reinterpret_cast<const Vec16<T>*>(base + row_bytes + (size_t)(lane + 32 * k) * 16);
+        Vec16<T> o, gr;
+        float wv[V];
+        load_weights<TW, V>(w, (lane + 32 * k) * V, wv);
+        if (gres != nullptr) gr = *reinterpret_cast<const Vec16<T>*>(base + 2 * row_bytes + (size_t)(lane + 32 * k) * 16);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float xh = Cvt<T>::to_f(xb[k].v[j]) * r;
-          o.v[j] = Cvt<T>::from_f(r * (Cvt<T>::to_f(gb_[k].v[j]) * wv[k][j] - xh * dot));
+          const float xh = Cvt<T>::to_f(xb.v[j]) * r;
+          float d = r * (Cvt<T>::to_f(gb_.v[j]) * wv[j] - xh * dot);
+          if (gres != nullptr) d += Cvt<T>::to_f(gr.v[j]);
+          o.v[j] = Cvt<T>::from_f(d);
         }
         st16(dx + row * cols + (long long)(lane + 32 * k) * V, o);
       }
+    stage = (stage + 1) % NORM_RING;
   }
+  cp_async_wait<0>();
+  __syncthreads();                                       // every warp is done with its ring: reuse it for the reduction
   // this CTA's partial weight gradient: sum over its warps in a fixed order, one row of the partial buffer
+  constexpr int RED_LD = 32 * MVW * V + 1;
+  float* red = reinterpret_cast<float*>(norm_smem);
 #pragma unroll
   for (int k = 0; k < MVW; ++k)
 #pragma unroll
-    for (int j = 0; j < V; ++j) red[warp][(lane + 32 * k) * V + j] = dwacc[k][j];
+    for (int j = 0; j < V; ++j) red[warp * RED_LD + (lane + 32 * k) * V + j] = dwacc[k][j];
   __syncthreads();
-  for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
+  for (int c = threadIdx.x; c < cols; c += NORM_BWD_THREADS) {
     float sacc = 0.f;
 #pragma unroll
-    for (int wq = 0; wq < NORM_WARPS; ++wq) sacc += red[wq][c];
+    for (int wq = 0; wq < NORM_BWD_WARPS; ++wq) sacc += red[wq * RED_LD + c];
     dw_partial[(long long)blockIdx.x * cols + c] = sacc;
   }
+}
+
+// dynamic shared memory of the kernel above: the per-warp rings, or the reduction buffer if that is larger
+static inline size_t rmsnorm_bwd_warp_smem(int cols, int esize, int mvw) {
+  const size_t ring = (size_t)NORM_BWD_WARPS * NORM_RING * 3 * cols * esize;
+  const size_t red = (size_t)NORM_BWD_WARPS * (32 * mvw * (16 / esize) + 1) * sizeof(float);
+  return ring > red ? ring : red;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -399,8 +501,23 @@ static inline bool norm_cols_ok(int cols, int dt) {
 // Number of CTAs the backward kernels use (= rows of the partial buffers).
 extern "C" int gb_norm_bwd_ctas(long long rows) { return (int)(rows < 148 * 4 ? rows : 148 * 4); }
 
+static int rmsnorm_fwd_impl(const void* x, const void* w, void* y, float* rstd, long long rows, int cols, float eps,
+                            int dt, int wdt, const void* res, void* sum_out, cudaStream_t st);
+
 extern "C" int gb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int cols,
                               float eps, int dt, int wdt, cudaStream_t st) {
+  return rmsnorm_fwd_impl(x, w, y, rstd, rows, cols, eps, dt, wdt, nullptr, nullptr, st);
+}
+
+// sum_out = x + res, y = rmsnorm(sum_out) * w, one pass
+extern "C" int gb_add_rmsnorm_fwd(const void* x, const void* res, void* sum_out, const void* w, void* y, float* rstd,
+                                  long long rows, int cols, float eps, int dt, int wdt, cudaStream_t st) {
+  if (res == nullptr || sum_out == nullptr) return -3;
+  return rmsnorm_fwd_impl(x, w, y, rstd, rows, cols, eps, dt, wdt, res, sum_out, st);
+}
+
+static int rmsnorm_fwd_impl(const void* x, const void* w, void* y, float* rstd, long long rows, int cols, float eps,
+                            int dt, int wdt, const void* res, void* sum_out, cudaStream_t st) {
   if (rows == 0) return 0;
   if (!norm_cols_ok(cols, dt)) return -2;
   const int grid = (int)(rows < 148 * 8 ? rows : 148 * 8);
@@ -409,31 +526,77 @@ extern "C" int gb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
     // narrow rows: warp per row (MVW = 1, 2 or 4 vectors per lane)
     const long long want = (rows + NORM_WARPS - 1) / NORM_WARPS;
     const int wgrid = (int)(want < 148 * 8 ? want : 148 * 8);
-    if (nvec <= 32) { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 1><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps)); }
-    else if (nvec <= 64) { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 2><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps)); }
-    else { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 4><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps)); }
+    if (nvec <= 32) { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 1><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps, (const T*)res, (T*)sum_out)); }
+    else if (nvec <= 64) { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 2><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps, (const T*)res, (T*)sum_out)); }
+    else { NORM_DISPATCH_T(dt, wdt, rmsnorm_fwd_warp_kernel<T, TW, 4><<<wgrid, NORM_THREADS, 0, st>>>((const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps, (const T*)res, (T*)sum_out)); }
     return (int)cudaGetLastError();
   }
   NORM_DISPATCH(dt, wdt, cols, rmsnorm_fwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
-      (const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps));
+      (const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps, (const T*)res, (T*)sum_out));
   return (int)cudaGetLastError();
 }
 
+static int rmsnorm_bwd_impl(const void* g, const void* x, const void* w, const float* rstd, void* dx,
+                            float* dw_partial, long long rows, int cols, int dt, int wdt, const void* gres,
+                            cudaStream_t st);
+
 extern "C" int gb_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, void* dx,
                               float* dw_partial, long long rows, int cols, int dt, int wdt, cudaStream_t st) {
+  return rmsnorm_bwd_impl(g, x, w, rstd, dx, dw_partial, rows, cols, dt, wdt, nullptr, st);
+}
+
+// dx = rmsnorm_backward(g) + gres: the gradient of s = x + res with respect to either addend
+extern "C" int gb_add_rmsnorm_bwd(const void* g, const void* gres, const void* x, const void* w, const float* rstd,
+                                  void* dx, float* dw_partial, long long rows, int cols, int dt, int wdt,
+                                  cudaStream_t st) {
+  return rmsnorm_bwd_impl(g, x, w, rstd, dx, dw_partial, rows, cols, dt, wdt, gres, st);
+}
+
+template <typename T, typename TW, int MVW>
+static int launch_rmsnorm_bwd_warp(const void* g, const void* x, const void* w, const float* rstd, void* dx,
+                                   float* dw_partial, long long rows, int cols, const void* gres, int grid,
+                                   cudaStream_t st) {
+  const size_t smem = rmsnorm_bwd_warp_smem(cols, (int)sizeof(T), MVW);
+  static bool configured = false;                        // once per instantiation: opt in to > 48 KB
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<T, TW, MVW>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  rmsnorm_bwd_warp_kernel<T, TW, MVW><<<grid, NORM_BWD_THREADS, smem, st>>>(
+      (const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols, (const T*)gres);
+  return (int)cudaGetLastError();
+}
+
+static inline bool rmsnorm_bwd_uses_warp_kernel(long long rows, int cols, int dt) {
+  return cols / (dt == DT_F32 ? 4 : 8) <= 128 && rows >= 64;
+}
+
+// Number of CTAs gb_rmsnorm_bwd / gb_add_rmsnorm_bwd launch (= rows of dw_partial they write)
+extern "C" int gb_rmsnorm_bwd_ctas(long long rows, int cols, int dt) {
+  if (rmsnorm_bwd_uses_warp_kernel(rows, cols, dt)) {
+    const long long want = (rows + NORM_BWD_WARPS - 1) / NORM_BWD_WARPS;
+    return (int)(want < 148 ? want : 148);
+  }
+  return gb_norm_bwd_ctas(rows);
+}
+
+static int rmsnorm_bwd_impl(const void* g, const void* x, const void* w, const float* rstd, void* dx,
+                            float* dw_partial, long long rows, int cols, int dt, int wdt, const void* gres,
+                            cudaStream_t st) {
   if (rows == 0) return 0;
   if (!norm_cols_ok(cols, dt)) return -2;
-  const int grid = gb_norm_bwd_ctas(rows);
+  const int grid = gb_rmsnorm_bwd_ctas(rows, cols, dt);
   const int nvec = cols / (dt == DT_F32 ? 4 : 8);
-  if (nvec <= 128 && rows >= 64) {
-    // narrow rows: warp per row; every CTA of the grid writes its row of the partial buffer (zeros if it had no rows)
-    if (nvec <= 32) { NORM_DISPATCH_T(dt, wdt, rmsnorm_bwd_warp_kernel<T, TW, 1><<<grid, NORM_THREADS, 0, st>>>((const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols)); }
-    else if (nvec <= 64) { NORM_DISPATCH_T(dt, wdt, rmsnorm_bwd_warp_kernel<T, TW, 2><<<grid, NORM_THREADS, 0, st>>>((const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols)); }
-    else { NORM_DISPATCH_T(dt, wdt, rmsnorm_bwd_warp_kernel<T, TW, 4><<<grid, NORM_THREADS, 0, st>>>((const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols)); }
-    return (int)cudaGetLastError();
+  if (rmsnorm_bwd_uses_warp_kernel(rows, cols, dt)) {
+    // narrow rows: warp per row; every CTA of the grid writes its row of the partial buffer
+    if (nvec <= 32) { NORM_DISPATCH_T(dt, wdt, return (launch_rmsnorm_bwd_warp<T, TW, 1>(g, x, w, rstd, dx, dw_partial, rows, cols, gres, grid, st))); }
+    else if (nvec <= 64) { NORM_DISPATCH_T(dt, wdt, return (launch_rmsnorm_bwd_warp<T, TW, 2>(g, x, w, rstd, dx, dw_partial, rows, cols, gres, grid, st))); }
+    else { NORM_DISPATCH_T(dt, wdt, return (launch_rmsnorm_bwd_warp<T, TW, 4>(g, x, w, rstd, dx, dw_partial, rows, cols, gres, grid, st))); }
   }
   NORM_DISPATCH(dt, wdt, cols, rmsnorm_bwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
-      (const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols));
+      (const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols, (const T*)gres));
   return (int)cudaGetLastError();
 }
 

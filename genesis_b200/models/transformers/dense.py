@@ -75,6 +75,14 @@ class TransformerBlock(nn.Module):
         h = x + self.self_attn(self.input_layernorm(x), position_ids, mask)
         return h + self.mlp(self.post_attention_layernorm(h))
 
+    def forward_deferred(self, stream, branch, position_ids=None, mask=None):
+        """The same block with its residual additions folded into the normalisations: the block's input is
+        `stream + branch` (`branch` None for the first block), and it returns (stream', branch') whose sum is its
+        output, leaving that last addition to whoever normalises next."""
+        x, n = self.input_layernorm.add_forward(stream, branch)
+        h, n2 = self.post_attention_layernorm.add_forward(x, self.self_attn(n, position_ids, mask))
+        return h, self.mlp(n2)
+
 
 class QwenModel(nn.Module):
     def __init__(self, config):
@@ -96,10 +104,10 @@ class QwenModel(nn.Module):
         self.max_batch_size = max_batch_size
 
     def hidden_states(self, idx, position_ids=None):
-        x = self.embed_tokens(idx)
+        x, branch = self.embed_tokens(idx), None
         for layer in self.layers:
-            x = layer(x, position_ids, position_ids, None)
-        return self.norm(x)
+            x, branch = layer.forward_deferred(x, branch, position_ids, None)
+        return self.norm.add_forward(x, branch)[1]
 
     def forward(self, idx, position_ids=None):
         return self.lm_head(self.hidden_states(idx, position_ids))

@@ -419,6 +419,16 @@ class MoEDecoderLayer(Module):
         h = hidden_states + a
         return h + self.mlp(self.post_attention_layernorm(h)), present
 
+    def forward_deferred(self, stream, branch, attention_mask=None, position_ids=None, past_key_value=None,
+                         use_cache=False):
+        """The same layer with its residual additions folded into the normalisations (one fused kernel each way):
+        its input is `stream + branch` (`branch` None for the first layer); returns (stream', branch', present)
+        with stream' + branch' the layer's output."""
+        x, n = self.input_layernorm.add_forward(stream, branch)
+        a, present = self.self_attn(n, attention_mask, position_ids, past_key_value, use_cache)
+        h, n2 = self.post_attention_layernorm.add_forward(x, a)
+        return h, self.mlp(n2), present
+
 
 class MoEPreTrainedModel(Module):
     def __init__(self, config):
@@ -460,12 +470,13 @@ class MoEModel(MoEPreTrainedModel):
             pad = torch.zeros(B, 1, 1, S, device=am.device).masked_fill(am.reshape(B, 1, 1, S) == 0, float("-inf"))
             mask4 = Tensor._wrap(causal.reshape(1, 1, S, S) + pad)
         presents = [] if use_cache else None
+        branch = None
         for i, layer in enumerate(self.layers):
             past = past_key_values[i] if past_key_values is not None else None
-            h, present = layer(h, mask4, position_ids, past, use_cache)
+            h, branch, present = layer.forward_deferred(h, branch, mask4, position_ids, past, use_cache)
             if use_cache:
                 presents.append(present)
-        return self.norm(h), presents
+        return self.norm.add_forward(h, branch)[1], presents
 
 
 class MoEForCausalLM(MoEPreTrainedModel):

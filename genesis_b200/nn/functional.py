@@ -939,6 +939,46 @@ class FusedRMSNormFunction(Function):
         return dx, (dw if dw.dtype == w.dtype else dw.to(w.dtype))
 
 
+class AddRMSNormFunction(Function):
+    """(s, y) = (x + res, rmsnorm(x + res) * w): the residual addition of a pre-norm block and the normalisation
+    that follows it, one kernel forward and one backward (which also folds in the gradient arriving at s along the
+    residual path, so backward has no separate gradient additions either)."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, x, res, w, eps):
+        if res.dtype != x.dtype:
+            res = K.to_dtype(res, x.dtype)
+        x = x if x.is_contiguous() else K.contiguous(x)
+        res = res if res.is_contiguous() else K.contiguous(res)
+        s, y, rstd = K.add_rmsnorm_fwd(x, res, w, eps)
+        ctx.save_for_backward(s, w, rstd)
+        return s, y
+
+    @staticmethod
+    def backward(ctx, gs, gy):
+        s, w, rstd = ctx.saved_tensors
+        if gy is None:                                   # the normalised output was not used
+            return gs, gs, None
+        if gy.dtype != s.dtype:
+            gy = K.to_dtype(gy, s.dtype)
+        gy = gy if gy.is_contiguous() else K.contiguous(gy)
+        if gs is None:
+            dx, dw = K.rmsnorm_bwd(gy, s, w, rstd)
+        else:
+            if gs.dtype != s.dtype:
+                gs = K.to_dtype(gs, s.dtype)
+            gs = gs if gs.is_contiguous() else K.contiguous(gs)
+            dx, dw = K.add_rmsnorm_bwd(gy, gs, s, w, rstd)
+        return dx, dx, (dw if dw.dtype == w.dtype else dw.to(w.dtype))
+
+
+def add_rms_norm(x, residual, weight, eps=1e-6):
+    """(x + residual, rms_norm(x + residual, weight)) from one fused kernel."""
+    return AddRMSNormFunction.apply(x, residual, weight, eps)
+
+
 class FusedLayerNormFunction(Function):
     raw = True
     amp_policy = AMPPolicy.FP32

@@ -54,3 +54,10 @@ class RMSNorm(Module):
 
     def forward(self, x):
         return F.rms_norm(x, self.weight, self.eps)
+
+    def add_forward(self, x, residual=None):
+        """(x + residual, self(x + residual)) from one fused kernel; with `residual=None` simply (x, self(x)).
+        Lets a pre-norm block hand its branch output to the next normalisation instead of adding it itself."""
+        if residual is None:
+            return x, self.forward(x)
+        return F.add_rms_norm(x, residual, self.weight, self.eps)

@@ -361,6 +361,28 @@ def rmsnorm_bwd(g, x, w, rstd):
     return dx.to(x.dtype), dw
 
 
+def add_rmsnorm_fwd(x, res, w, eps):
+    """Returns (s = x + res in x's dtype, rmsnorm(s) * w, rstd[rows] fp32): residual addition and the normalisation
+    that follows it in one pass."""
+    if x.is_cuda:
+        r = N.add_rmsnorm_fwd(x, res, w, eps)
+        if r is not NotImplemented:
+            return r
+    s = add(x, res)
+    y, rstd = rmsnorm_fwd(s, w, eps)
+    return s, y, rstd
+
+
+def add_rmsnorm_bwd(g, gres, x, w, rstd):
+    """Returns (rmsnorm_backward(g) + gres, dw fp32)."""
+    if g.is_cuda:
+        r = N.add_rmsnorm_bwd(g, gres, x, w, rstd)
+        if r is not NotImplemented:
+            return r
+    dx, dw = rmsnorm_bwd(g, x, w, rstd)
+    return add(dx, gres), dw
+
+
 def layernorm_fwd(x, w, b, eps):
     """Returns (y, mean[rows], rstd[rows])."""
     if x.is_cuda:

@@ -33,8 +33,9 @@ _SIGS = {
     "gb_where": "pppffiiplip", "gb_cast": "ppliip", "gb_fill": "plfip", "gb_axpy": "ppfliip",
     "gb_copy_strided": "ppipppip", "gb_transpose": "ppiiilllip",
     "gb_reduce_rows": "ippllfiip", "gb_reduce_mid": "ipplllifiip",
-    "gb_rmsnorm_fwd": "pppplifiip", "gb_rmsnorm_bwd": "pppppplii" + "ip", "gb_layernorm_fwd": "pppppplifiip",
-    "gb_layernorm_bwd": "pppppppp" + "liiip", "gb_norm_bwd_ctas": "l",
+    "gb_rmsnorm_fwd": "pppplifiip", "gb_rmsnorm_bwd": "pppppplii" + "ip",
+    "gb_add_rmsnorm_fwd": "pppppplifiip", "gb_add_rmsnorm_bwd": "ppppppplii" + "ip", "gb_layernorm_fwd": "pppppplifiip",
+    "gb_layernorm_bwd": "pppppppp" + "liiip", "gb_norm_bwd_ctas": "l", "gb_rmsnorm_bwd_ctas": "lii",
     "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
     "gb_ce_fwd": "ppppllliip", "gb_ce_bwd": "ppppplll" + "iip",
     "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip",
@@ -657,6 +658,38 @@ def rmsnorm_fwd(x, w, eps):
     return y, rstd
 
 
+def add_rmsnorm_fwd(x, res, w, eps):
+    """(s = x + res, rmsnorm(s) * w, rstd) in one pass over the rows."""
+    cols = x.shape[-1]
+    if not _norm_ok(x, cols) or not _norm_ok(res, cols) or res.dtype != x.dtype or res.shape != x.shape \
+            or _wdt(x, w) is None or not w.is_contiguous():
+        return NotImplemented
+    rows = x.numel() // cols
+    s, y = torch.empty_like(x), torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=F32, device=x.device)
+    _chk(lib().gb_add_rmsnorm_fwd(x.data_ptr(), res.data_ptr(), s.data_ptr(), w.data_ptr(), y.data_ptr(),
+                                  rstd.data_ptr(), rows, cols, float(eps), _DT[x.dtype], _wdt(x, w), _st()),
+         "add_rmsnorm_fwd")
+    return s, y, rstd
+
+
+def add_rmsnorm_bwd(g, gres, x, w, rstd):
+    """(rmsnorm_backward(g) + gres, dw): the gradient of either addend of the sum that was normalised."""
+    cols = x.shape[-1]
+    if not _norm_ok(x, cols) or not _norm_ok(g, cols) or not _norm_ok(gres, cols) or g.dtype != x.dtype \
+            or gres.dtype != x.dtype or _wdt(x, w) is None:
+        return NotImplemented
+    rows = x.numel() // cols
+    L = lib()
+    nct = L.gb_rmsnorm_bwd_ctas(rows, cols, _DT[x.dtype])
+    dx = torch.empty_like(x)
+    part = torch.empty(nct * cols, dtype=F32, device=x.device)
+    _chk(L.gb_add_rmsnorm_bwd(g.data_ptr(), gres.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                              dx.data_ptr(), part.data_ptr(), rows, cols, _DT[x.dtype], _wdt(x, w), _st()),
+         "add_rmsnorm_bwd")
+    return dx, _colsum(part, nct, cols)
+
+
 def _colsum(partial, nrows, cols):
     return _reduce3(0, partial, 1, nrows, cols, 1.0, F32)
 
@@ -667,7 +700,7 @@ def rmsnorm_bwd(g, x, w, rstd):
         return NotImplemented
     rows = x.numel() // cols
     L = lib()
-    nct = L.gb_norm_bwd_ctas(rows)
+    nct = L.gb_rmsnorm_bwd_ctas(rows, cols, _DT[x.dtype])
     dx = torch.empty_like(x)
     part = torch.empty(nct * cols, dtype=F32, device=x.device)
     _chk(L.gb_rmsnorm_bwd(g.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), part.data_ptr(),

@@ -450,3 +450,47 @@ def test_small_reference_names_exist_and_work():
     key = [k for k in prof.profile_data if k.endswith("f")][0]
     assert prof.profile_data[key]["calls"] == 2 and prof.profile_data[key]["total_time"] >= 0.0
     prof.print_profile_data()
+
+
+def test_add_rms_norm_equals_separate_add_and_norm():
+    """(x + r, rms_norm(x + r)) as one op gives the values and gradients of the two separate ops, also when only
+    one of its outputs is used; a dense block run with deferred additions equals the plain block."""
+    import genesis_b200.nn as gnn
+    import genesis_b200.nn.functional as F
+    g = torch.Generator().manual_seed(0)
+    xv, rv, wv = torch.randn(5, 7, 16, generator=g), torch.randn(5, 7, 16, generator=g), torch.rand(16, generator=g) + 0.5
+    for use in ("both", "sum", "norm"):
+        ts = []
+        for fused in (False, True):
+            x, r = genesis.Tensor(xv.clone(), requires_grad=True), genesis.Tensor(rv.clone(), requires_grad=True)
+            w = genesis.Tensor(wv.clone(), requires_grad=True)
+            if fused:
+                s, y = F.add_rms_norm(x, r, w, 1e-6)
+            else:
+                s = x + r
+                y = F.rms_norm(s, w, 1e-6)
+            loss = 0
+            if use in ("both", "sum"):
+                loss = loss + (s * s).sum()
+            if use in ("both", "norm"):
+                loss = loss + (y * 3.0).sum() + (y * y).sum()
+            loss.backward()
+            ts.append((s._t, y._t, x.grad._t, r.grad._t, None if w.grad is None else w.grad._t))
+        for a, b in zip(*ts):
+            assert (a is None and b is None) or torch.allclose(a, b, atol=1e-5, rtol=1e-5)
+    from genesis_b200.models.transformers import TransformerConfig
+    from genesis_b200.models.transformers.dense import TransformerBlock
+    genesis.manual_seed(1)
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=8, max_position_embeddings=32)
+    blk = TransformerBlock(cfg)
+    x = genesis.Tensor(torch.randn(2, 9, 32, generator=g))
+    b0 = genesis.Tensor(torch.randn(2, 9, 32, generator=g))
+    with genesis.no_grad():
+        want = blk(x + b0)
+        stream, branch = blk.forward_deferred(x, b0)
+        first, fb = blk.forward_deferred(x + b0, None)
+    assert torch.allclose((stream + branch)._t, want._t, atol=1e-5)
+    assert torch.allclose((first + fb)._t, want._t, atol=1e-5)
+    norm = gnn.RMSNorm(32)
+    assert norm.add_forward(x)[0] is x

@@ -46,3 +46,10 @@ def test_device_queries_without_a_gpu_do_not_raise():
     assert str(d) == "cpu" or "cpu" in repr(d)
     x = genesis.randn(2, 3)
     assert x.device == d or "cpu" in str(x.device)
+
+
+def test_ctypes_signatures_match_the_c_prototypes():
+    """Every binding in ops/native.py has the argument list of its `extern "C"` prototype (checked from the sources,
+    no GPU needed)."""
+    from genesis_b200.ops import abi_check
+    assert abi_check.mismatches() == []

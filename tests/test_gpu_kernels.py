@@ -389,3 +389,35 @@ def test_swiglu_on_column_halves(dt):
     refb = torch.cat((d * u * sg * (1 + g * (1 - sg)), d * g * sg), -1)
     gotb = K.swiglu_fused_bwd(dy, gu)
     torch.testing.assert_close(gotb.float(), refb, atol=6e-2 if dt != torch.float32 else 1e-5, rtol=3e-2 if dt != torch.float32 else 1e-5)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(300, 896), (16, 896), (1000, 256), (64, 4096), (40, 8192), (9, 2056),
+                                       (20000, 896), (3001, 512), (1187, 1024), (77, 64)])
+def test_add_rmsnorm_fused(dt, rows, cols):
+    """Residual addition + RMSNorm in one kernel (warp-per-row and row-per-CTA variants) against fp32 PyTorch, and
+    its backward with the residual-path gradient folded in."""
+    g = torch.Generator(DEV).manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device=DEV, generator=g).to(dt)
+    r = torch.randn(rows, cols, device=DEV, generator=g).to(dt)
+    w = (torch.rand(cols, device=DEV, generator=g) + 0.5)
+    out = N.add_rmsnorm_fwd(x, r, w, 1e-6)
+    assert out is not NotImplemented
+    s, y, rstd = out
+    s_ref = (x.float() + r.float()).to(dt)
+    assert torch.equal(s, s_ref)                                   # rounded once, like a separate addition
+    sf = s_ref.float()
+    rstd_ref = torch.rsqrt(sf.pow(2).mean(-1) + 1e-6)
+    close(rstd, rstd_ref, torch.float32)
+    close(y, sf * rstd_ref[:, None] * w, dt)
+    y1, rstd1 = N.rmsnorm_fwd(s, w, 1e-6)
+    assert torch.equal(y, y1) and torch.equal(rstd, rstd1)         # same arithmetic as the unfused kernel
+    gy = torch.randn(rows, cols, device=DEV, generator=g).to(dt)
+    gs = torch.randn(rows, cols, device=DEV, generator=g).to(dt)
+    dx, dw = N.add_rmsnorm_bwd(gy, gs, s, w, rstd)
+    dx0, dw0 = N.rmsnorm_bwd(gy, s, w, rstd)
+    assert torch.equal(dw, dw0)
+    xh = sf * rstd_ref[:, None]
+    gw = gy.float() * w
+    ref = rstd_ref[:, None] * (gw - xh * (gw * xh).mean(-1, keepdim=True)) + gs.float()
+    close(dx, ref, dt, scale=4)
