@@ -843,7 +843,9 @@ class EmbeddingFunction(Function):
     def backward(ctx, g):
         (idx,) = ctx.saved_tensors
         n, dt = ctx.meta
-        return K.embedding_bwd(g, idx, n, dt)
+        # handed to the leaf as (indices, rows): scattered straight into an existing gradient when there is one
+        from ..tensor import RowScatterGrad
+        return RowScatterGrad(g, idx, n, dt)
 
 
 # ============================== softmax / losses ==================================
@@ -1505,6 +1507,14 @@ def _fused_params(tensors, dtype):
     return out
 
 
+def _fresh_slice(buf, start, n):
+    """Rows [start, start + n) of a buffer allocated by the calling backward: a leaf may take the slice as its
+    `.grad` without copying it (nothing else refers to that memory)."""
+    sl = buf[start:start + n]
+    sl._gb_fresh = True
+    return sl
+
+
 class FusedLinearFunction(Function):
     """Several linear layers that read the same input, as ONE GEMM: y = x @ cat(weights)^T + cat(biases).
     The parameters stay separate tensors (state dict and module tree are unchanged); their rows are stacked into one
@@ -1536,13 +1546,13 @@ class FusedLinearFunction(Function):
         gW = K.linear_wgrad(g, x, out_dtype=wd)
         outs, o = [gx], 0
         for n in sizes:
-            outs.append(gW[o:o + n])
+            outs.append(_fresh_slice(gW, o, n))
             o += n
         if bd is not None:
             gb = K.bias_grad(g, bd)
             o = 0
             for n in sizes:
-                outs.append(gb[o:o + n])
+                outs.append(_fresh_slice(gb, o, n))
                 o += n
         return tuple(outs)
 

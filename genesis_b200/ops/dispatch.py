@@ -557,6 +557,21 @@ def embedding_bwd(g, idx, num_rows, out_dtype=None):
     return out.to(out_dtype or g.dtype)
 
 
+def embedding_bwd_into(acc, g, idx):
+    """acc[idx[i]] += g[i] in place: the embedding gradient added to an existing dense gradient (tied weights)
+    without materialising a second [num_rows, D] tensor."""
+    D = g.shape[-1]
+    g2 = g.reshape(-1, D)
+    g2 = g2 if g2.is_contiguous() else g2.contiguous()
+    flat = idx.reshape(-1)
+    flat = flat if flat.is_contiguous() else flat.contiguous()
+    if g.is_cuda:
+        r = N.scatter_add_rows_into(g2, flat, acc)
+        if r is not NotImplemented:
+            return
+    acc.index_add_(0, flat.long(), g2.to(acc.dtype))
+
+
 def attention_fwd(q, k, v, causal, scale):
     """q [B, S, Hq, D], k/v [B, S, Hkv, D] -> (o [B, S, Hq, D], lse [B, Hq, S] fp32, natural log)."""
     if q.is_cuda:

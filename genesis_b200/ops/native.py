@@ -938,6 +938,18 @@ def scatter_add_rows(src, rows, num_rows, out_dtype):
     return acc if od == F32 else cast(acc, od)
 
 
+def scatter_add_rows_into(src, rows, acc):
+    """acc[rows[i]] += src[i] in place (acc fp32 [num_rows, D] contiguous)."""
+    if src.dtype not in _FLOATS or src.dim() != 2 or not src.is_contiguous() or acc.dtype != F32 \
+            or not acc.is_contiguous() or acc.dim() != 2 or acc.shape[1] != src.shape[1] \
+            or rows.dtype not in (torch.int64, torch.int32) or not rows.is_contiguous():
+        return NotImplemented
+    _chk(lib().gb_scatter_add_rows(src.data_ptr(), rows.data_ptr(), acc.data_ptr(), src.shape[0], src.shape[1],
+                                   _DT[src.dtype], 1 if rows.dtype == torch.int64 else 0, acc.shape[0],
+                                   status_tensor(src.device).data_ptr(), _st()), "scatter_add_rows")
+    return True
+
+
 def embedding_bwd(g, idx, num_rows, out_dtype):
     D = g.shape[-1]
     g2 = g.reshape(-1, D)

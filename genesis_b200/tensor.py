@@ -358,9 +358,48 @@ class _HookHandle:
 _adopted = set()   # data pointers adopted as leaf gradients during the current backward pass
 
 
+class RowScatterGrad:
+    """Gradient of a row lookup (embedding) kept as (row indices, row gradients) until it reaches its leaf: added to
+    a gradient that already exists (a tied output projection contributed first, or gradient accumulation) by one
+    scatter-add in place, instead of materialising a zero-filled [num_rows, D] tensor and adding two dense tensors.
+    Anything that needs a dense tensor calls `dense()`."""
+    __slots__ = ("rows", "idx", "num_rows", "dtype")
+
+    def __init__(self, rows, idx, num_rows, dtype):
+        self.rows, self.idx, self.num_rows, self.dtype = rows, idx, num_rows, dtype
+
+    def dense(self):
+        from .ops import dispatch as K
+        return K.embedding_bwd(self.rows, self.idx, self.num_rows, self.dtype)
+
+    def add_into(self, acc):
+        from .ops import dispatch as K
+        if acc.dtype == torch.float32 and acc.is_contiguous() and acc.dim() == 2:
+            K.embedding_bwd_into(acc, self.rows, self.idx)
+        else:
+            K.add_(acc, self.dense().to(acc.dtype).reshape(acc.shape))
+
+
 def _accumulate_leaf(t, g, fire_post_hooks=True):
     """Leaf gradient: tensor hooks, accumulation into `.grad`, post-accumulate hooks (`fire_post_hooks=False`
     while further contributions to the same leaf are still to come in this backward pass)."""
+    if isinstance(g, RowScatterGrad):
+        target = None
+        if not t._hooks and g.num_rows == t._t.shape[0]:
+            if t.grad is not None:
+                target = t.grad._t
+            elif t._grad_buf is not None:                  # preallocated slot (DDP bucket view)
+                target = t._grad_buf
+                target.zero_()
+                t.grad = Tensor._wrap(target)
+        if target is None:
+            g = g.dense()
+        else:
+            g.add_into(target)
+            if fire_post_hooks and t._post_hooks:
+                for h in t._post_hooks:
+                    h(t)
+            return
     if t._hooks:
         gw = t.apply_hooks(Tensor._wrap(g))
         g = gw._t
@@ -377,8 +416,11 @@ def _accumulate_leaf(t, g, fire_post_hooks=True):
         else:
             # `.grad` must own its memory: views / broadcast (stride-0) gradients and a tensor that
             # another leaf already took in this pass are copied, everything else is adopted as is.
+            # (a Function may mark contiguous slices of a buffer it has just allocated as `_gb_fresh`: the row
+            # slices of a fused weight gradient are owned by nobody else and need no copy)
             key = g.data_ptr()
-            if g._base is not None or not g.is_contiguous() or key in _adopted:
+            if (g._base is not None and not getattr(g, "_gb_fresh", False)) or not g.is_contiguous() \
+                    or key in _adopted:
                 g = K.clone(g)
             else:
                 _adopted.add(key)
@@ -473,6 +515,8 @@ def _run_backward(root, g, retain_graph):
                 uses[id(e.leaf)] = left
                 _accumulate_leaf(e.leaf, gi, left <= 0)
             else:
+                if isinstance(gi, RowScatterGrad):
+                    gi = gi.dense()
                 d = pending.get(id(e.node))
                 if d is None:
                     pending[id(e.node)] = {e.idx: gi}

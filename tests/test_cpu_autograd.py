@@ -494,3 +494,37 @@ def test_add_rms_norm_equals_separate_add_and_norm():
     assert torch.allclose((first + fb)._t, want._t, atol=1e-5)
     norm = gnn.RMSNorm(32)
     assert norm.add_forward(x)[0] is x
+
+
+def test_embedding_gradient_scatters_into_existing_gradient():
+    """The embedding gradient reaches its leaf as (indices, rows): alone it becomes a dense tensor, with a tied
+    output projection or across two backward passes it is scattered into the gradient that is already there, and a
+    tensor hook still sees a dense gradient.  All equal to torch's dense result."""
+    import genesis_b200.nn.functional as F
+    g = torch.Generator().manual_seed(2)
+    wv = torch.randn(11, 6, generator=g)
+    idx = torch.tensor([[1, 3, 3], [10, 1, 0]])
+    tw = wv.clone().requires_grad_(True)
+    (torch.nn.functional.embedding(idx, tw).sum(1) @ tw.t()).pow(2).sum().backward()
+    ref_tied = tw.grad.clone()
+    tw.grad = None
+    torch.nn.functional.embedding(idx, tw).pow(2).sum().backward()
+    ref_alone = tw.grad.clone()
+
+    w = genesis.Tensor(wv.clone(), requires_grad=True)
+    (F.embedding(w, genesis.Tensor(idx)) ** 2).sum().backward()
+    assert torch.allclose(w.grad._t, ref_alone, atol=1e-5)
+    # second backward pass accumulates by scattering in place
+    (F.embedding(w, genesis.Tensor(idx)) ** 2).sum().backward()
+    assert torch.allclose(w.grad._t, 2 * ref_alone, atol=1e-5)
+    # tied: lookup and output projection share the weight
+    w2 = genesis.Tensor(wv.clone(), requires_grad=True)
+    seen = []
+    h = F.embedding(w2, genesis.Tensor(idx)).sum(1)
+    ((h @ w2.transpose(0, 1)) ** 2).sum().backward()
+    assert torch.allclose(w2.grad._t, ref_tied, atol=1e-4)
+    # with a hook the gradient contributions arrive dense
+    w3 = genesis.Tensor(wv.clone(), requires_grad=True)
+    w3.register_hook(lambda gr: seen.append(tuple(gr.shape)) or gr)
+    (F.embedding(w3, genesis.Tensor(idx)) ** 2).sum().backward()
+    assert seen == [(11, 6)] and torch.allclose(w3.grad._t, ref_alone, atol=1e-5)
