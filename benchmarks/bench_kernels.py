@@ -3,7 +3,7 @@
 timed iterations by writing a 256 MB buffer.  Prints one JSON line per case with the achieved
 fraction of the measured peaks (MEASURED_PEAKS.json next to the repo root, else the fallback).
 
-    python benchmarks/bench_kernels.py [--what gemm,norm,softmax,adamw,attn] [--quick]
+    python benchmarks/bench_kernels.py [--what gemm,norm,addnorm,softmax,adamw,attn] [--quick]
 """
 import argparse
 import json
@@ -123,6 +123,20 @@ def main():
                 gbs = 2 * x.numel() * 2 / ms / 1e6
                 print(json.dumps({"kernel": "softmax_fwd", "rows": 8192, "cols": cols, "ms": ms, "GBs": gbs,
                                   "frac_of_" + src: gbs / hbm}), flush=True)
+    if "addnorm" in what:
+        # residual addition + RMSNorm at the residual-stream shape of the 0.5B model (16384 tokens x 896)
+        rows, cols = 16384, 896
+        x = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16)
+        r = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(cols, device=dev)
+        s_, y_, rstd = K.add_rmsnorm_fwd(x, r, w, 1e-6)
+        unit = rows * cols * 2
+        ms = timeit(lambda: K.add_rmsnorm_fwd(x, r, w, 1e-6))
+        print(json.dumps({"kernel": "add_rmsnorm_fwd", "rows": rows, "cols": cols, "ms": ms, "GBs": 4 * unit / ms / 1e6,
+                          "frac_of_" + src: 4 * unit / ms / 1e6 / hbm}), flush=True)
+        ms = timeit(lambda: K.add_rmsnorm_bwd(y_, r, s_, w, rstd))
+        print(json.dumps({"kernel": "add_rmsnorm_bwd", "rows": rows, "cols": cols, "ms": ms, "GBs": 4 * unit / ms / 1e6,
+                          "frac_of_" + src: 4 * unit / ms / 1e6 / hbm}), flush=True)
     if "adamw" in what:
         n = 250_000_000 if a.quick else 1_000_000_000
         p = torch.zeros(n, device=dev)

@@ -155,6 +155,7 @@ class Function:
             node.edges = tuple(
                 (Edge(None, 0, t) if t.creator is None else Edge(t.creator, t.idx, None)) if need else None
                 for t, need in zip(tensor_inputs, needs))
+            ctx.edges = node.edges        # lets a backward see whether an input is a leaf with a gradient slot
         else:
             ctx.release()
         return tuple(results) if is_tuple else results[0]

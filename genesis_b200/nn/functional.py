@@ -502,11 +502,61 @@ class LinearFunction(Function):
         if not g.is_contiguous():
             g = K.contiguous(g)
         gx = K.linear_dgrad(g, wc) if need[0] else None
-        gw = K.linear_wgrad(g, x, out_dtype=wd) if need[1] else None
+        gw = None
+        if need[1]:
+            slot = _grad_slot(ctx, 1, wd, wc.shape)
+            if slot is None:
+                gw = K.linear_wgrad(g, x, out_dtype=wd)
+            else:
+                # the weight is a leaf with a preallocated gradient slot (a DDP bucket view): the GEMM writes or
+                # accumulates there, and the engine recognises the slot instead of copying into it
+                buf, accumulate = slot
+                gw = K.linear_wgrad(g, x, out_dtype=wd, accum=buf if accumulate else None,
+                                    out=None if accumulate else buf)
         gb = None
         if bd is not None and len(need) > 2 and need[2]:
             gb = K.bias_grad(g, bd)
         return (gx, gw, gb) if bd is not None else (gx, gw)
+
+
+def _grad_slot(ctx, i, dtype, shape):
+    """(slot, accumulate) when input `i` of the node is a leaf whose gradient has a preallocated home
+    (`Tensor._grad_buf`, set by DistributedDataParallel) that a kernel may target directly: `accumulate` is False
+    when the leaf has no gradient yet (the kernel overwrites the slot) and True when its gradient already lives in
+    the slot (the kernel adds to it).  None in every other case (hooks, foreign gradient tensor, dtype mismatch)."""
+    edges = getattr(ctx, "edges", None)
+    if not edges or i >= len(edges) or edges[i] is None:
+        return None
+    leaf = edges[i].leaf
+    if leaf is None or leaf._grad_buf is None or leaf._hooks:
+        return None
+    buf = leaf._grad_buf
+    if buf.dtype != dtype or not buf.is_contiguous() or tuple(buf.shape) != tuple(shape):
+        return None
+    if leaf.grad is None:
+        return buf, False
+    if leaf.grad._t.data_ptr() == buf.data_ptr():
+        return buf, True
+    return None
+
+
+def _stacked_grad_slot(ctx, first, sizes, dtype, cols):
+    """One [sum(sizes), cols] view over the gradient slots of inputs first .. first + len(sizes) - 1 when each has a
+    slot (`_grad_slot`), all in the same state, lying back to back in memory in that order; (None, False) otherwise."""
+    slots = []
+    for j, n in enumerate(sizes):
+        sl = _grad_slot(ctx, first + j, dtype, (n, cols))
+        if sl is None or (slots and sl[1] != slots[0][1]):
+            return None, False
+        slots.append(sl)
+    es = slots[0][0].element_size()
+    for (a, _), (b, _) in zip(slots, slots[1:]):
+        if a.data_ptr() + a.numel() * es != b.data_ptr() or a.untyped_storage().data_ptr() != b.untyped_storage().data_ptr():
+            return None, False
+    head = slots[0][0]
+    stacked = torch.empty(0, dtype=dtype, device=head.device).set_(
+        head.untyped_storage(), head.storage_offset(), (builtins.sum(sizes), cols), (cols, 1))
+    return stacked, slots[0][1]
 
 
 def _cached_param_cast(w, dtype):
@@ -1543,7 +1593,13 @@ class FusedLinearFunction(Function):
         g = g if g.is_contiguous() else K.contiguous(g)
         need = ctx.needs_input_grad
         gx = K.linear_dgrad(g, W) if need[0] else None
-        gW = K.linear_wgrad(g, x, out_dtype=wd)
+        stacked, accumulate = _stacked_grad_slot(ctx, 1, sizes, wd, W.shape[1])
+        if stacked is not None:
+            # the members' gradient slots (DDP bucket views) are adjacent in stacking order: one store into the bucket
+            gW = K.linear_wgrad(g, x, out_dtype=wd, accum=stacked if accumulate else None,
+                                out=None if accumulate else stacked)
+        else:
+            gW = K.linear_wgrad(g, x, out_dtype=wd)
         outs, o = [gx], 0
         for n in sizes:
             outs.append(_fresh_slice(gW, o, n))

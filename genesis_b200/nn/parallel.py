@@ -110,23 +110,48 @@ class DistributedDataParallel(Module):
         for p in model.parameters():
             p._version += 1            # overwritten in place: cached casts and low-precision copies are stale
 
+    def _bucket_order(self, params):
+        """Parameters in the order they get bucket slots: reverse registration order (roughly the order gradients
+        become ready), except that parameters some layer multiplies as one stacked matrix (q/k/v, gate/up) sit next
+        to each other in stacking order, so the fused weight-gradient GEMM can write all of them with one store
+        straight into the bucket.  Returns a list of units (lists of parameters that must share a bucket)."""
+        from .utils import fused_parameter_groups
+        ids = {id(p) for p in params}
+        group_of = {}
+        for members in fused_parameter_groups(self.module):
+            if all(id(m) in ids for m in members) and not any(id(m) in group_of for m in members) \
+                    and len({m._t.dtype for m in members}) == 1:
+                for m in members:
+                    group_of[id(m)] = members
+        units, done = [], set()
+        for p in reversed(params):
+            if id(p) in done:
+                continue
+            unit = list(group_of.get(id(p), [p]))
+            done.update(id(m) for m in unit)
+            units.append(unit)
+        return units
+
     def _build_buckets(self, params):
         cur = {}
-        for p in reversed(params):
-            dt = p._t.dtype
-            b = cur.get(dt)
-            nbytes = p._t.numel() * p._t.element_size()
-            if b is None or (b.numel * p._t.element_size() + nbytes > self.bucket_cap_bytes and b.numel > 0):
-                b = _Bucket(len(self._buckets), dt)
-                self._buckets.append(b)
-                cur[dt] = b
-            # 16-byte aligned slots so vector loads never straddle parameters
-            align = 16 // p._t.element_size()
-            b.numel = (b.numel + align - 1) // align * align
-            b.offsets.append(b.numel)
-            b.params.append(p)
-            b.numel += p._t.numel()
-            self._param_bucket[id(p)] = b
+        for unit in self._bucket_order(params):
+            unit_bytes = sum(m._t.numel() * m._t.element_size() for m in unit)
+            for j, p in enumerate(unit):
+                dt = p._t.dtype
+                b = cur.get(dt)
+                # a unit is never split across buckets: only its first member may open a new one
+                if b is None or (j == 0 and b.numel > 0
+                                 and b.numel * p._t.element_size() + unit_bytes > self.bucket_cap_bytes):
+                    b = _Bucket(len(self._buckets), dt)
+                    self._buckets.append(b)
+                    cur[dt] = b
+                # 16-byte aligned slots so vector loads never straddle parameters
+                align = 16 // p._t.element_size()
+                b.numel = (b.numel + align - 1) // align * align
+                b.offsets.append(b.numel)
+                b.params.append(p)
+                b.numel += p._t.numel()
+                self._param_bucket[id(p)] = b
         self._use_symm = self._on_cuda and comm_mode() == "p2p" and symm.available()
         if self._on_cuda:
             self._comm_stream = torch.cuda.Stream()

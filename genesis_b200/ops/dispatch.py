@@ -310,10 +310,11 @@ def linear_dgrad(gy, w):
     return torch.matmul(gy, w)
 
 
-def linear_wgrad(gy, x, out_dtype=None, accum=None):
-    """dw = gy^T @ x over all leading dims; optional `accum` (fp32, [N, K]) gets += dw in place."""
+def linear_wgrad(gy, x, out_dtype=None, accum=None, out=None):
+    """dw = gy^T @ x over all leading dims; optional `accum` ([N, K]) gets += dw in place, optional `out` ([N, K])
+    receives dw (a gradient slot that already exists, e.g. a DDP bucket view)."""
     if gy.is_cuda:
-        r = N.linear_wgrad(gy, x, out_dtype, accum)
+        r = N.linear_wgrad(gy, x, out_dtype, accum, out)
         if r is not NotImplemented:
             return r
     g2 = gy.reshape(-1, gy.shape[-1])
@@ -322,6 +323,9 @@ def linear_wgrad(gy, x, out_dtype=None, accum=None):
     if accum is not None:
         accum.add_(dw.to(accum.dtype))
         return accum
+    if out is not None:
+        out.copy_(dw.reshape(out.shape))
+        return out
     return dw.to(out_dtype or gy.dtype)
 
 

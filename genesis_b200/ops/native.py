@@ -490,9 +490,10 @@ def _plan(M, N, K, es, can_split, sms):
     return bn, 1
 
 
-def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0):
+def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0, out=None):
     """D[M, N] = a[M, K] @ b_t[N, K]^T for 2-D operands in any of the supported layouts.
-    `a` / `b_t` may be transposed views (stride(0) == 1); misaligned ones are repacked."""
+    `a` / `b_t` may be transposed views (stride(0) == 1); misaligned ones are repacked.
+    `accum`: D is added into this tensor; `out`: D is written into this (contiguous [M, N]) tensor."""
     if a.dtype not in _GEMM_DT or a.dtype != b_t.dtype:
         return NotImplemented
     M, K = a.shape
@@ -503,6 +504,9 @@ def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0):
     if accum is not None:
         out = accum
         if not out.is_contiguous():
+            return NotImplemented
+    elif out is not None:
+        if not out.is_contiguous() or out.dtype != out_dtype or out.numel() != M * N:
             return NotImplemented
     else:
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
@@ -625,12 +629,12 @@ def linear_dgrad(gy, w):
     return r.reshape(*lead, w.shape[1])
 
 
-def linear_wgrad(gy, x, out_dtype, accum):
+def linear_wgrad(gy, x, out_dtype, accum, out=None):
     if gy.dtype != x.dtype or gy.dtype not in _GEMM_DT:
         return NotImplemented
     g2 = gy.reshape(-1, gy.shape[-1])
     x2 = x.reshape(-1, x.shape[-1])
-    return gemm(g2.t(), x2.t(), out_dtype=out_dtype or gy.dtype, accum=accum)
+    return gemm(g2.t(), x2.t(), out_dtype=out_dtype or gy.dtype, accum=accum, out=out)
 
 
 # ============================ norms / softmax / loss =============================

@@ -408,8 +408,14 @@ def _accumulate_leaf(t, g, fire_post_hooks=True):
     if g.shape != t._t.shape:
         g = g.reshape(t._t.shape) if g.numel() == t._t.numel() else g.sum_to_size(t._t.shape)
     from .ops import dispatch as K
-    if t.grad is None:
-        buf = t._grad_buf
+    buf = t._grad_buf
+    if buf is not None and g.data_ptr() == buf.data_ptr() and g.dtype == buf.dtype:
+        # the producing kernel already wrote (or accumulated) into the preallocated slot
+        if t.grad is None:
+            t.grad = Tensor._wrap(buf)
+        elif t.grad._t.data_ptr() != buf.data_ptr():
+            K.add_(t.grad._t, g)
+    elif t.grad is None:
         if buf is not None:          # preallocated slot (DDP bucket view): write in place
             K.copy_(buf, g)
             t.grad = Tensor._wrap(buf)

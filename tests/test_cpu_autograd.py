@@ -528,3 +528,64 @@ def test_embedding_gradient_scatters_into_existing_gradient():
     w3.register_hook(lambda gr: seen.append(tuple(gr.shape)) or gr)
     (F.embedding(w3, genesis.Tensor(idx)) ** 2).sum().backward()
     assert seen == [(11, 6)] and torch.allclose(w3.grad._t, ref_alone, atol=1e-5)
+
+
+def test_linear_weight_gradient_goes_straight_into_a_preallocated_slot():
+    """A weight with a gradient slot (`_grad_buf`, what DDP hands out) gets its gradient written by the weight-gradient
+    product itself: overwritten when the weight has no gradient yet (stale slot contents do not matter), accumulated
+    when its gradient already lives there, shared use in two layers included; a tensor hook falls back to the copy."""
+    import genesis_b200.nn as gnn
+    import genesis_b200.nn.functional as F
+    g = torch.Generator().manual_seed(4)
+    xv = torch.randn(5, 8, generator=g)
+    lin = gnn.Linear(8, 6, bias=True)
+    ref_w = lin.weight._t.clone().requires_grad_(True)
+    ref_b = lin.bias._t.clone().requires_grad_(True)
+    (torch.nn.functional.linear(xv, ref_w, ref_b) ** 2).sum().backward()
+    want = ref_w.grad.clone()
+    slot = torch.full((6, 8), 123.0)                               # stale values must be overwritten
+    lin.weight._grad_buf = slot
+    (lin(genesis.Tensor(xv)) ** 2).sum().backward()
+    assert lin.weight.grad._t.data_ptr() == slot.data_ptr()
+    assert torch.allclose(slot, want, atol=1e-5)
+    (lin(genesis.Tensor(xv)) ** 2).sum().backward()              # second pass accumulates in the slot
+    assert lin.weight.grad._t.data_ptr() == slot.data_ptr() and torch.allclose(slot, 2 * want, atol=1e-5)
+    # the same weight in two layers of one graph
+    lin.weight.grad = None
+    y = F.linear(F.linear(genesis.Tensor(xv), lin.weight)[:, :6] @ genesis.Tensor(torch.eye(6, 8)), lin.weight)
+    (y ** 2).sum().backward()
+    w2 = lin.weight._t.clone().requires_grad_(True)
+    t = torch.nn.functional.linear(torch.nn.functional.linear(xv, w2)[:, :6] @ torch.eye(6, 8), w2)
+    (t ** 2).sum().backward()
+    assert lin.weight.grad._t.data_ptr() == slot.data_ptr() and torch.allclose(slot, w2.grad, atol=1e-4)
+    # hooks see the gradient first, so it cannot be produced in place
+    lin.weight.grad = None
+    lin.weight.register_hook(lambda gr: gr * 2.0)
+    (lin(genesis.Tensor(xv)) ** 2).sum().backward()
+    assert torch.allclose(lin.weight.grad._t, 2 * want, atol=1e-5)
+
+
+def test_fused_projection_gradient_goes_straight_into_adjacent_slots():
+    """Weights of a fused projection whose gradient slots lie back to back (as DDP lays them out) receive their
+    gradients from one weight-gradient product writing through a stacked view; slots that are not adjacent fall
+    back to the copy."""
+    import genesis_b200.nn.functional as F
+    g = torch.Generator().manual_seed(5)
+    xv = torch.randn(7, 8, generator=g)
+    ws = [torch.randn(n, 8, generator=g) for n in (6, 2, 2)]
+    refs = [w.clone().requires_grad_(True) for w in ws]
+    (torch.cat([torch.nn.functional.linear(xv, r) for r in refs], -1) ** 2).sum().backward()
+    for adjacent in (True, False):
+        flat = torch.full((10 * 8 + 16,), 7.0)
+        offs = (0, 48, 64) if adjacent else (0, 56, 80)
+        params = [genesis.Tensor(w.clone(), requires_grad=True) for w in ws]
+        for p, o in zip(params, offs):
+            p._grad_buf = flat[o:o + p._t.numel()].view(p._t.shape)
+        (F.fused_linear(genesis.Tensor(xv), params) ** 2).sum().backward()
+        for p, r in zip(params, refs):
+            assert p.grad._t.data_ptr() == p._grad_buf.data_ptr()
+            assert torch.allclose(p.grad._t, r.grad, atol=1e-4)
+        # second pass accumulates
+        (F.fused_linear(genesis.Tensor(xv), params) ** 2).sum().backward()
+        for p, r in zip(params, refs):
+            assert torch.allclose(p._grad_buf, 2 * r.grad, atol=1e-4)
