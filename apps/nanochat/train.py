@@ -174,12 +174,15 @@ def main(argv=None):
         return mean
 
     def save(tag):
-        if rank != 0:
-            return
-        path = os.path.join(args.out, f"checkpoint_{tag}.pth")
-        genesis.save_checkpoint(model.state_dict(), opt.state_dict(), path, step=step,
-                                scaler=None if scaler is None else scaler.state_dict())
-        log(f"saved {path}")
+        if rank == 0:
+            path = os.path.join(args.out, f"checkpoint_{tag}.pth")
+            genesis.save_checkpoint(model.state_dict(), opt.state_dict(), path, step=step,
+                                    scaler=None if scaler is None else scaler.state_dict())
+            log(f"saved {path}")
+        if ddp:
+            # the other ranks wait here on the host while rank 0 writes: without this they would already sit inside
+            # the next step's gradient all-reduce, spending its device-side wait budget on a file write
+            dist.barrier()
 
     prof = None
     if args.profile and rank == 0:

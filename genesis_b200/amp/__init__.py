@@ -106,7 +106,9 @@ class GradScaler:
         if id(optimizer) in self._unscaled:
             raise RuntimeError("unscale_() has already been called on this optimizer since the last update().")
         grads = self._grads(optimizer)
-        if grads:
+        if grads and not self._external_unscale:
+            # (with DistributedDataParallel's fused all-reduce the gradients arrive here already divided by the scale
+            # and checked for overflow: only the book-keeping below is left to do)
             self._lazy_init(grads[0].device)
             K.unscale_and_check(grads, 1.0 / self._scale, self._found_inf)
         self._unscaled.add(id(optimizer))

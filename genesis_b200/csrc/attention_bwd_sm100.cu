@@ -505,13 +505,10 @@ static int launch_bwd(const CUtensorMap& tq128, const CUtensorMap& tdo128, const
   // CTAs have to fit in one SM
   const int smem_dq = 2 * AT_BM * D * 2 + 2 * BW_ST * BW_C * D * 2 + 128;
   const int smem_kv = 2 * AT_BM * D * 2 + 2 * KV_ST * BW_C * D * 2 + 2 * AT_BM * BW_C * 2 + 16 * BW_C * 4 + 128;
-  static bool cfg = false;
-  if (!cfg) {
-    int r;
-    if ((r = set_smem(attn_bwd_dq_kernel<D, NCTA>, smem_dq)) != 0) return r;
-    if ((r = set_smem(attn_bwd_dkdv_kernel<D, NCTA>, smem_kv)) != 0) return r;
-    cfg = true;
-  }
+  static unsigned long long cfg_dq = 0, cfg_kv = 0;
+  int r;
+  if ((r = smem_opt_in(attn_bwd_dq_kernel<D, NCTA>, smem_dq, cfg_dq)) != 0) return r;
+  if ((r = smem_opt_in(attn_bwd_dkdv_kernel<D, NCTA>, smem_kv, cfg_kv)) != 0) return r;
   dim3 gq((p.S + AT_BM - 1) / AT_BM, p.Hq, p.B), gk((p.Sk + AT_BM - 1) / AT_BM, p.Hq, p.B);
   attn_bwd_dq_kernel<D, NCTA><<<gq, 160, smem_dq, st>>>(tq128, tk64, tv64, tdo128, p);
   attn_bwd_dkdv_kernel<D, NCTA><<<gk, 160, smem_kv, st>>>(tq64, tk128, tv128, tdo64, p, ws);

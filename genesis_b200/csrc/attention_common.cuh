@@ -101,10 +101,6 @@ static inline int make_tmap_bshd(CUtensorMap* out, const void* base, int is_bf16
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-template <typename KernT>
-static inline int set_smem(KernT kern, int bytes) {
-  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-}
 
 
 }  // namespace gb

@@ -269,12 +269,12 @@ extern "C" int gb_attn_fwd(const void* q, const void* k, const void* v, void* o,
   // D = 64 runs two CTAs per SM: 2 x (114,944 + 1 KB reserved) just fits, an alignment pad would not
   const int smem = 5 * AT_BM * D * 2 + AT_BM * AT_BN * 2 + 256 + (D == 64 ? 0 : 1024);
   if (D == 64) {
-    static bool cfg = false;
-    if (!cfg) { if ((r = set_smem(attn_fwd_kernel<64, 1>, smem)) != 0) return r; cfg = true; }
+    static unsigned long long cfg = 0;
+    if ((r = smem_opt_in(attn_fwd_kernel<64, 1>, smem, cfg)) != 0) return r;
     attn_fwd_kernel<64, 1><<<grid, 192, smem, st>>>(tq, tk, tv, p);
   } else {
-    static bool cfg = false;
-    if (!cfg) { if ((r = set_smem(attn_fwd_kernel<128, 2>, smem)) != 0) return r; cfg = true; }
+    static unsigned long long cfg = 0;
+    if ((r = smem_opt_in(attn_fwd_kernel<128, 2>, smem, cfg)) != 0) return r;
     attn_fwd_kernel<128, 2><<<grid, 192, smem, st>>>(tq, tk, tv, p);
   }
   return (int)cudaGetLastError();

@@ -7,6 +7,21 @@
 
 namespace gb {
 
+// Opt a kernel in to more than 48 KB of dynamic shared memory.  The attribute belongs to the (kernel, device) pair,
+// so `mask` (one static word per kernel instantiation) keeps a bit per device: a process that works on several
+// GPUs configures each of them on its first launch there.
+template <typename KernT>
+static inline int smem_opt_in(KernT kern, int bytes, unsigned long long& mask) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (mask & bit) return 0;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return (int)e;
+  mask |= bit;
+  return 0;
+}
+
 // dtype codes of the C ABI (mirrored in genesis_b200/ops/native.py)
 enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_F64 = 3, DT_I32 = 4, DT_I64 = 5, DT_U8 = 6, DT_BOOL = 7 };
 

@@ -478,12 +478,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
                        int sms, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES, ESIZE>;
   auto kern = gemm_kernel<BN, STAGES, ESIZE, A_MN, B_MN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static unsigned long long configured = 0;
+  if (int e = smem_opt_in(kern, L::TOTAL, configured)) return e;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
   const int nz = (p.group_mode == GROUP_K) ? p.groups : p.batch * p.splits;
   long long total = (long long)tiles_m * tiles_n * nz;

@@ -382,24 +382,14 @@ extern "C" int gb_sort_rows(const void* in, void* vals, long long* idx, long lon
   if (dt != DT_F32 && dt != DT_F16 && dt != DT_BF16 && dt != DT_I32) return -2;
   const int np2 = next_pow2(cols);
   if (cols <= SORT_SMEM_MAX && k <= 16 && k < cols) {
-    static bool cfgk = false;
-    if (!cfgk) {
-      cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           SORT_SMEM_MAX * 8);
-      if (e != cudaSuccess) return (int)e;
-      cfgk = true;
-    }
+    static unsigned long long cfgk = 0;
+    if (int e = smem_opt_in(topk_select_kernel, SORT_SMEM_MAX * 8, cfgk)) return e;
     topk_select_kernel<<<(unsigned)rows, 256, (size_t)cols * 8, st>>>(in, vals, idx, cols, k, descending, dt);
     return (int)cudaGetLastError();
   }
   if (cols <= SORT_SMEM_MAX) {
-    static bool cfg = false;
-    if (!cfg) {
-      cudaError_t e = cudaFuncSetAttribute(sort_rows_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           SORT_SMEM_MAX * 8);
-      if (e != cudaSuccess) return (int)e;
-      cfg = true;
-    }
+    static unsigned long long cfg = 0;
+    if (int e = smem_opt_in(sort_rows_smem_kernel, SORT_SMEM_MAX * 8, cfg)) return e;
     int threads = np2 / 2 < 32 ? 32 : (np2 / 2 > 1024 ? 1024 : np2 / 2);
     sort_rows_smem_kernel<<<(unsigned)rows, threads, np2 * 8, st>>>(in, vals, idx, cols, np2, k, descending, dt);
     return (int)cudaGetLastError();

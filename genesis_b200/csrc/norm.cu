@@ -557,13 +557,8 @@ static int launch_rmsnorm_bwd_warp(const void* g, const void* x, const void* w, 
                                    float* dw_partial, long long rows, int cols, const void* gres, int grid,
                                    cudaStream_t st) {
   const size_t smem = rmsnorm_bwd_warp_smem(cols, (int)sizeof(T), MVW);
-  static bool configured = false;                        // once per instantiation: opt in to > 48 KB
-  if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<T, TW, MVW>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static unsigned long long configured = 0;              // per instantiation and device: opt in to > 48 KB
+  if (int e = smem_opt_in(rmsnorm_bwd_warp_kernel<T, TW, MVW>, 200 * 1024, configured)) return e;
   rmsnorm_bwd_warp_kernel<T, TW, MVW><<<grid, NORM_BWD_THREADS, smem, st>>>(
       (const T*)g, (const T*)x, (const TW*)w, rstd, (T*)dx, dw_partial, rows, cols, (const T*)gres);
   return (int)cudaGetLastError();
@@ -674,7 +669,8 @@ extern "C" int gb_rmsnorm_bwd_noalloc(const void* g, const void* x, const void* 
                                       float* dw, long long rows, int cols, int dt, int wdt, cudaStream_t st) {
   if (cols > gb::NOALLOC_MAX_COLS) return -10;
   if (cols % (dt == DT_F32 ? 4 : 8) != 0 || cols <= 0) return -11;
-  if (rows <= 0) return 0;
+  // no rows: the sum over rows is zero, and `dw` is documented as overwritten
+  if (rows <= 0) return (int)cudaMemsetAsync(dw, 0, (size_t)cols * sizeof(float), st);
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;

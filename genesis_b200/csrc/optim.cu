@@ -32,7 +32,10 @@ struct AdamArgs {
 // Step-dependent scalars kept on the device so that a captured CUDA graph of the step stays valid when replayed:
 // dyn[0] learning rate (written by the host between replays), dyn[1] / dyn[2] bias corrections, dyn[3] step count.
 // The betas arrive as doubles so that the corrections round to the same floats as the host's 1 - beta ** step.
-__global__ void adam_dyn_advance_kernel(float* __restrict__ dyn, double beta1, double beta2) {
+// A step that the overflow flag cancels does not count: the bias corrections follow the updates actually applied.
+__global__ void adam_dyn_advance_kernel(float* __restrict__ dyn, double beta1, double beta2,
+                                        const float* __restrict__ found_inf) {
+  if (found_inf != nullptr && *found_inf != 0.f) return;
   const double step = (double)dyn[3] + 1.0;
   dyn[3] = (float)step;
   dyn[1] = (float)(1.0 - pow(beta1, step));
@@ -168,8 +171,9 @@ extern "C" int gb_adam_multi(const long long* meta, int nt, long long total_chun
   return (int)cudaGetLastError();
 }
 
-extern "C" int gb_adam_dyn_advance(float* dyn, double beta1, double beta2, cudaStream_t st) {
-  adam_dyn_advance_kernel<<<1, 1, 0, st>>>(dyn, beta1, beta2);
+extern "C" int gb_adam_dyn_advance(float* dyn, double beta1, double beta2, const float* found_inf,
+                                   cudaStream_t st) {
+  adam_dyn_advance_kernel<<<1, 1, 0, st>>>(dyn, beta1, beta2, found_inf);
   return (int)cudaGetLastError();
 }
 

@@ -7,6 +7,13 @@
 // Out of memory => every cached block is released and the allocation retried once.  Counters are
 // always on (they are a few relaxed increments under the pool mutex).
 //
+// CUDA graphs: between `gb_pool_begin_capture` and `gb_pool_end_capture` every block handed out becomes the
+// property of that capture.  Blocks of a capture that are freed (while capturing or later) go to the capture's
+// private free list, which only allocations of the same capture may take from, so memory that a recorded kernel
+// reads or writes on every replay is never handed to eager code; `gb_pool_release_capture` (graph destroyed)
+// returns the private list to the common bins.  Allocation order inside a capture is the order of its replay, so
+// reuse within the private list is safe on any stream of the capture.
+//
 // The two entry points `gb_pool_alloc` / `gb_pool_free` have the signature torch's
 // CUDAPluggableAllocator expects, so the pool can back every torch CUDA tensor.
 // Reference counterpart: genesis/backends/cuda_memory.py:30-848 (Python, cuda-python driver calls).
@@ -29,7 +36,10 @@ constexpr int kMaxDevices = 16;
 struct Block {
   void* ptr;
   size_t size;
-  cudaStream_t stream;
+  cudaStream_t stream;   // stream of the last use
+  bool any_stream;       // the event recorded at free time has completed: every stream may take the block
+                         // (a flag of its own: a null `stream` is the handle of the legacy default stream)
+  int capture;           // 0, or the id of the graph capture that owns the block
 };
 struct Pending {
   Block b;
@@ -44,6 +54,9 @@ struct DevicePool {
   int64_t alloc_count = 0, free_count = 0, cache_hits = 0, cuda_alloc_count = 0, pending_checks = 0;
   int64_t allocated = 0, max_allocated = 0, reserved = 0, max_reserved = 0, oom_retries = 0;
   int64_t limit = 0;   // 0 = none
+  int capturing = 0;   // id of the capture in progress on this device (0 = none)
+  int next_capture = 0;
+  std::map<int, std::map<size_t, std::vector<Block>>> priv;   // capture id -> its private free lists
 };
 
 DevicePool g_pools[kMaxDevices];
@@ -71,7 +84,7 @@ void drain_pending(DevicePool& P) {
     if (cudaEventQuery(P.pending[i].ev) == cudaSuccess) {
       cudaEventDestroy(P.pending[i].ev);
       Block b = P.pending[i].b;
-      b.stream = nullptr;   // reusable by any stream now
+      b.any_stream = true;
       P.bins[b.size].push_back(b);
       P.pending[i] = P.pending.back();
       P.pending.pop_back();
@@ -109,16 +122,36 @@ void* gb_pool_alloc(ssize_t size, int device, cudaStream_t stream) {
   const size_t cls = round_size((size_t)size);
   std::lock_guard<std::mutex> lock(P.mu);
   ++P.alloc_count;
-  if (!P.pending.empty() && (P.alloc_count % 16) == 0) drain_pending(P);
+  const int cap = P.capturing;
+  // (event queries are not allowed while a stream of this thread is capturing)
+  if (cap == 0 && !P.pending.empty() && (P.alloc_count % 16) == 0) drain_pending(P);
+  if (cap != 0) {
+    auto pit = P.priv.find(cap);
+    if (pit != P.priv.end()) {
+      auto cit = pit->second.find(cls);
+      if (cit != pit->second.end() && !cit->second.empty()) {
+        Block b = cit->second.back();
+        cit->second.pop_back();
+        b.stream = stream;
+        P.live[b.ptr] = b;
+        ++P.cache_hits;
+        P.allocated += (int64_t)cls;
+        if (P.allocated > P.max_allocated) P.max_allocated = P.allocated;
+        return b.ptr;
+      }
+    }
+  }
   auto it = P.bins.find(cls);
   if (it != P.bins.end()) {
     std::vector<Block>& v = it->second;
     for (size_t i = v.size(); i-- > 0;) {
-      if (v[i].stream == stream || v[i].stream == nullptr) {
+      if (v[i].any_stream || v[i].stream == stream) {
         Block b = v[i];
         v[i] = v.back();
         v.pop_back();
         b.stream = stream;
+        b.any_stream = false;
+        b.capture = cap;
         P.live[b.ptr] = b;
         ++P.cache_hits;
         P.allocated += (int64_t)cls;
@@ -151,7 +184,7 @@ void* gb_pool_alloc(ssize_t size, int device, cudaStream_t stream) {
   if (P.reserved > P.max_reserved) P.max_reserved = P.reserved;
   P.allocated += (int64_t)cls;
   if (P.allocated > P.max_allocated) P.max_allocated = P.allocated;
-  P.live[p] = Block{p, cls, stream};
+  P.live[p] = Block{p, cls, stream, false, cap};
   return p;
 }
 
@@ -165,7 +198,11 @@ void gb_pool_free(void* ptr, ssize_t /*size*/, int device, cudaStream_t stream) 
   P.live.erase(it);
   ++P.free_count;
   P.allocated -= (int64_t)b.size;
-  if (stream != b.stream) {
+  if (b.capture != 0) {
+    P.priv[b.capture][b.size].push_back(b);
+    return;
+  }
+  if (stream != b.stream && P.capturing == 0) {
     // used on a different stream than it was allocated on: park behind an event
     cudaEvent_t ev;
     if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess &&
@@ -210,6 +247,58 @@ int64_t gb_pool_empty_cache(int device) {
   const int64_t freed = release_cached(P);
   if (prev != device) cudaSetDevice(prev);
   return freed;
+}
+
+// Graph capture brackets (see the header comment).  begin returns the id of the new capture, or 0 when another one
+// is already in progress on the device (nested captures share the outer id).
+int gb_pool_begin_capture(int device) {
+  if (device < 0 || device >= kMaxDevices) return 0;
+  DevicePool& P = g_pools[device];
+  std::lock_guard<std::mutex> lock(P.mu);
+  if (P.capturing != 0) return 0;
+  P.capturing = ++P.next_capture;
+  return P.capturing;
+}
+
+void gb_pool_end_capture(int device) {
+  if (device < 0 || device >= kMaxDevices) return;
+  DevicePool& P = g_pools[device];
+  std::lock_guard<std::mutex> lock(P.mu);
+  P.capturing = 0;
+}
+
+// The graph of capture `id` is gone (and the device idle with respect to it): its private blocks join the common
+// bins, live blocks it still owns become ordinary blocks.  Returns the bytes moved to the bins.
+int64_t gb_pool_release_capture(int device, int id) {
+  if (device < 0 || device >= kMaxDevices || id == 0) return 0;
+  DevicePool& P = g_pools[device];
+  std::lock_guard<std::mutex> lock(P.mu);
+  int64_t moved = 0;
+  auto pit = P.priv.find(id);
+  if (pit != P.priv.end()) {
+    for (auto& kv : pit->second)
+      for (Block b : kv.second) {
+        b.capture = 0;
+        b.any_stream = true;
+        P.bins[b.size].push_back(b);
+        moved += (int64_t)b.size;
+      }
+    P.priv.erase(pit);
+  }
+  for (auto& kv : P.live)
+    if (kv.second.capture == id) kv.second.capture = 0;
+  return moved;
+}
+
+// bytes parked in private free lists of captures
+int64_t gb_pool_capture_cached(int device) {
+  if (device < 0 || device >= kMaxDevices) return 0;
+  DevicePool& P = g_pools[device];
+  std::lock_guard<std::mutex> lock(P.mu);
+  int64_t n = 0;
+  for (auto& c : P.priv)
+    for (auto& kv : c.second) n += (int64_t)kv.first * (int64_t)kv.second.size();
+  return n;
 }
 
 void gb_pool_reset_peak(int device) {

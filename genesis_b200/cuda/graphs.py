@@ -26,12 +26,28 @@ class CUDAGraph:
 
     def __init__(self):
         self._g = torch.cuda.CUDAGraph()
+        self._pool_capture = (0, 0)      # (device, id) of the native pool's private block list for this graph
 
     def replay(self):
         self._g.replay()
 
     def reset(self):
         self._g.reset()
+        self._release_pool()
+
+    def _release_pool(self):
+        dev, cid = self._pool_capture
+        if cid:
+            from . import pool
+            torch.cuda.synchronize(dev)
+            pool.release_capture(dev, cid)
+            self._pool_capture = (0, 0)
+
+    def __del__(self):
+        try:
+            self._release_pool()
+        except Exception:
+            pass
 
 
 class graph:
@@ -40,13 +56,23 @@ class graph:
     def __init__(self, cuda_graph, pool=None, stream=None):
         # "relaxed": pinned staging blocks for pointer tables may be allocated while capturing
         self._ctx = torch.cuda.graph(cuda_graph._g, pool=pool, stream=stream, capture_error_mode="relaxed")
+        self._graph = cuda_graph
 
     def __enter__(self):
         from ..ops import native
+        from . import pool as native_pool
         native.begin_capture_arena()          # pinned memory for pointer tables, reserved before the capture starts
-        return self._ctx.__enter__()
+        r = self._ctx.__enter__()
+        # the native pool keeps what is allocated from here on out of eager code's reach for the graph's lifetime
+        self._dev = torch.cuda.current_device()
+        self._cid = native_pool.begin_capture(self._dev)
+        return r
 
     def __exit__(self, *exc):
+        from . import pool as native_pool
+        if self._cid:
+            native_pool.end_capture(self._dev)
+            self._graph._pool_capture = (self._dev, self._cid)
         return self._ctx.__exit__(*exc)
 
 

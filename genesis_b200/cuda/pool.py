@@ -5,7 +5,9 @@ large classes 2 MB .. 1 GB in 2 MB-rounded power-of-two/half steps, direct alloc
 above), stream-aware (a block freed on another stream than it was allocated on is parked
 behind a CUDA event), with always-on counters.  It exports the two C entry points torch's
 `CUDAPluggableAllocator` expects, so `install()` routes every torch CUDA allocation through
-it; it can also be used standalone (`alloc` / `free`) for communication buffers.
+it; it can also be used standalone (`alloc` / `free`) for communication buffers.  It is installed by default when the
+package is imported on a machine with a GPU (`GENESIS_B200_POOL=0` keeps torch's allocator), and it is aware of
+CUDA graph captures made through `genesis_b200.cuda.graph` (`begin_capture` / `end_capture` / `release_capture`).
 Reference counterpart: `genesis/backends/cuda_memory.py:111-576`.
 """
 import ctypes
@@ -38,18 +40,32 @@ def _L():
         lib.gb_pool_set_limit.argtypes = [ctypes.c_int, ctypes.c_int64]
         lib.gb_pool_round_size.argtypes = [ctypes.c_int64]
         lib.gb_pool_round_size.restype = ctypes.c_int64
+        lib.gb_pool_begin_capture.argtypes = [ctypes.c_int]
+        lib.gb_pool_begin_capture.restype = ctypes.c_int
+        lib.gb_pool_end_capture.argtypes = [ctypes.c_int]
+        lib.gb_pool_end_capture.restype = None
+        lib.gb_pool_release_capture.argtypes = [ctypes.c_int, ctypes.c_int]
+        lib.gb_pool_release_capture.restype = ctypes.c_int64
+        lib.gb_pool_capture_cached.argtypes = [ctypes.c_int]
+        lib.gb_pool_capture_cached.restype = ctypes.c_int64
         lib._pool_bound = True
     return lib
 
 
-def install():
-    """Make the pool torch's CUDA allocator. Must run before the first CUDA allocation."""
+def install(strict=True):
+    """Make the pool torch's CUDA allocator.  Must run before the first CUDA allocation of the process: torch refuses
+    to swap an allocator that is already in use (then this raises, or returns False when `strict` is off)."""
     global _installed
     if _installed:
         return True
     _L()
-    alloc = torch.cuda.memory.CUDAPluggableAllocator(_lib.LIB_PATH, "gb_pool_alloc", "gb_pool_free")
-    torch.cuda.memory.change_current_allocator(alloc)
+    try:
+        alloc = torch.cuda.memory.CUDAPluggableAllocator(_lib.LIB_PATH, "gb_pool_alloc", "gb_pool_free")
+        torch.cuda.memory.change_current_allocator(alloc)
+    except RuntimeError:
+        if strict:
+            raise
+        return False
     _installed = True
     return True
 
@@ -90,9 +106,37 @@ def set_limit(device, nbytes):
     _L().gb_pool_set_limit(device, nbytes)
 
 
+def begin_capture(device=0):
+    """A CUDA graph capture starts on `device`: blocks handed out from now on belong to it (see csrc/pool.cpp).
+    Returns the capture id (0: the pool is not in use, or a capture is already open)."""
+    if not (_installed or _standalone):
+        return 0
+    return int(_L().gb_pool_begin_capture(device))
+
+
+def end_capture(device=0):
+    if _installed or _standalone:
+        _L().gb_pool_end_capture(device)
+
+
+def release_capture(device, capture_id):
+    """The graph is destroyed: its private blocks return to the common bins."""
+    if capture_id and (_installed or _standalone):
+        return int(_L().gb_pool_release_capture(device, capture_id))
+    return 0
+
+
+def capture_cached(device=0):
+    return int(_L().gb_pool_capture_cached(device)) if (_installed or _standalone) else 0
+
+
 def round_size(nbytes):
     return int(_L().gb_pool_round_size(nbytes))
 
 
-if os.environ.get("GENESIS_B200_POOL", "0") == "1" and torch.cuda.is_available():
-    install()
+# The pool is the allocator of every CUDA tensor unless GENESIS_B200_POOL=0 asks for torch's own.  A process that
+# made CUDA allocations before importing this package keeps torch's allocator (it cannot be swapped any more);
+# GENESIS_B200_POOL=1 turns that case into an error instead.
+_mode = os.environ.get("GENESIS_B200_POOL", "auto")
+if _mode != "0" and torch.cuda.is_available() and _lib.available():
+    install(strict=(_mode == "1"))

@@ -58,7 +58,10 @@ class _SymmState:
         self._bind()
         # flags: per-(channel, peer) 32-bit epoch counters; status: error record written by kernels
         self.flags = self.alloc(64 * 1024)
-        self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
+        # the status word is the library-wide one: whatever reads a result on the host (`Tensor.item()`,
+        # `native.check_status`, DDP's probe) also sees an expired communication wait
+        from ..ops import native
+        self.status = native.status_tensor(self.device)
         self.staging = None
         self.channels = {}
 
@@ -190,15 +193,8 @@ def channel(name):
 
 def check_status(what="collective"):
     """Raise `CommTimeout` if a kernel recorded a bounded-wait expiry (synchronises the stream)."""
-    st = state()
-    rec = st.status.tolist()
-    if rec[0] != 0:
-        st.status.zero_()
-        if rec[0] == 3 and rec[1] == 900:
-            raise RuntimeError(f"{what}: expert-parallel receive buffer too small: this rank was sent {rec[3]} "
-                               f"(tile-padded) rows; raise GENESIS_EP_CAPACITY (multiple of the balanced share)")
-        raise pg.CommTimeout(f"{what}: device-side wait expired (code={rec[0]}, peer={rec[1]}, phase={rec[2]}, "
-                             f"epoch={rec[3]})")
+    from ..ops import native
+    native.check_status(state().device, what)
 
 
 def all_reduce_(t, scale=None):

@@ -35,8 +35,12 @@ class Heartbeat:
         now = time.monotonic()
         for r in range(self.world):
             self._last[r] = (None, now)
-        self._thread = threading.Thread(target=self._run, name="genesis-heartbeat", daemon=True)
+        # beating and polling run on threads of their own: a store whose `get` blocks on a key that was never set
+        # (torch's TCPStore waits for its whole timeout: the "rank never joined" case) must not stop this rank's beats
+        self._thread = threading.Thread(target=self._run_beat, name="genesis-heartbeat", daemon=True)
+        self._poll_thread = threading.Thread(target=self._run_poll, name="genesis-heartbeat-poll", daemon=True)
         self._thread.start()
+        self._poll_thread.start()
         return self
 
     def pause(self):
@@ -56,8 +60,12 @@ class Heartbeat:
             if r == self.rank:
                 continue
             try:
-                val = self.store.get(self._key(r))
-                val = val.decode() if isinstance(val, bytes) else str(val)
+                check = getattr(self.store, "check", None)       # non-blocking presence test where the store has one
+                if check is not None and not check([self._key(r)]):
+                    val = None
+                else:
+                    val = self.store.get(self._key(r))
+                    val = val.decode() if isinstance(val, bytes) else str(val)
             except Exception:
                 val = None
             prev, t_prev = self._last[r]
@@ -69,11 +77,18 @@ class Heartbeat:
                 with self._lock:
                     self._dead.add(r)
 
-    def _run(self):
+    def _run_beat(self):
         while not self._stop.is_set():
             try:
                 if not self._paused:
                     self._beat()
+            except Exception:
+                pass
+            self._stop.wait(self.interval)
+
+    def _run_poll(self):
+        while not self._stop.is_set():
+            try:
                 self._poll()
             except Exception:
                 pass
@@ -90,6 +105,8 @@ class Heartbeat:
 
     def stop(self):
         self._stop.set()
-        if self._thread is not None:
-            self._thread.join(timeout=2.0)
-            self._thread = None
+        for name in ("_thread", "_poll_thread"):
+            th = getattr(self, name, None)
+            if th is not None:
+                th.join(timeout=2.0)
+                setattr(self, name, None)

@@ -73,6 +73,11 @@ class DistributedDataParallel(Module):
         self._armed = False
         self._comm_stream = None
         self._use_symm = False
+        self._probe = None
+        # Wait budget of the bucket all-reduce.  Ranks legitimately drift apart by whole seconds between two steps
+        # (rank 0 writing a checkpoint or running an evaluation while the others have already launched backward),
+        # so the budget is far longer than that of the blocking collectives; NCCL would wait without any limit.
+        self._budget_ms = float(os.environ.get("GENESIS_DDP_TIMEOUT_MS", 120000))
         all_params = [p for p in model.parameters() if p.requires_grad]
         # expert-parallel shards are not replicated: no all-reduce, only the 1/world factor
         self._sharded = [p for p in all_params if getattr(p, "_no_ddp", False)]
@@ -211,7 +216,7 @@ class DistributedDataParallel(Module):
                         inv, found = scaler._scale, scaler._found_inf
                     N.allreduce_fused(symm.channel("ddp"), b.symm_buf, 0, b.flat.numel(), b.dtype, b.flat,
                                       inv_scale=inv, found_inf=found, prescale=1.0 / self.world_size,
-                                      scale_is_reciprocal=True)
+                                      scale_is_reciprocal=True, budget_ms=self._budget_ms)
                 else:
                     tdist.all_reduce(b.flat)
                     b.flat.mul_(1.0 / self.world_size)
@@ -237,17 +242,40 @@ class DistributedDataParallel(Module):
             b.ready_event = None
             self._reduce_bucket(b)
         self._next_launch = len(self._buckets)
+        fused_unscale = self._use_symm and self._scaler is not None and self._scaler.is_enabled()
         if self._sharded:
             from ..ops import dispatch as K
-            for p in self._sharded:
-                if p.grad is not None:
-                    K.mul_(p.grad._t, 1.0 / self.world_size)
+            grads = [p.grad._t for p in self._sharded if p.grad is not None]
+            if grads and fused_unscale:
+                # expert shards skip the all-reduce, and with it the unscale and the overflow check it carries:
+                # do both here (1/world folded into the factor) so that every gradient reaches step() unscaled
+                sc = self._scaler
+                sc._lazy_init(grads[0].device)
+                K.unscale_and_check(grads, (1.0 / self.world_size) / sc._scale, sc._found_inf)
+            else:
+                for g in grads:
+                    K.mul_(g, 1.0 / self.world_size)
         if self._on_cuda:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
-        if self._use_symm and self._scaler is not None and self._scaler.is_enabled():
+        if fused_unscale:
             self._scaler._external_unscale = True
+        if self._use_symm:
+            # an all-reduce that gave up waiting leaves a record in the status word: fetch it without a host
+            # synchronisation and look at it when the next forward starts (`Tensor.item()` looks at once)
+            if self._probe is None:
+                from ..ops import native as N
+                self._probe = N.StatusProbe(self._buckets[0].flat.device) if self._buckets else None
+            if self._probe is not None:
+                self._probe.arm()
+
+    def check_comm(self, wait=False):
+        """Raise `CommTimeout` if a bucket all-reduce of an earlier step gave up waiting for a peer (its buckets
+        then hold unreduced gradients).  Non-blocking unless `wait`; called by `forward` on every step."""
+        if self._probe is not None:
+            self._probe.poll("DistributedDataParallel gradient all-reduce", wait=wait)
 
     def _arm(self):
+        self.check_comm()
         self._armed = True
         self._next_launch = 0
         for b in self._buckets:

@@ -42,7 +42,7 @@ _SIGS = {
     "gb_swiglu_fwd2d": "ppliip", "gb_swiglu_bwd2d": "pppliip", "gb_rope": "pppppiiiiiillp",
     "gb_gather_rows": "pppllilpp", "gb_scatter_add_rows": "pppliiilpp",
     "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
-    "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiipppp", "gb_adam_dyn_advance": "pddp", "gb_copy_h2d_async": "pplp", "gb_sgd_multi": "pilfffp",
+    "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiipppp", "gb_adam_dyn_advance": "pddpp", "gb_copy_h2d_async": "pplp", "gb_sgd_multi": "pilfffp",
     "gb_grad_multi": "pilpfppip",
     "gb_router_fwd": "ppppp" + "liiiip", "gb_router_bwd": "pppppp" + "liiiip",
     "gb_moe_sort": "pppppp" + "liiilp", "gb_moe_combine": "pppp" + "liiip", "gb_moe_combine_bwd": "pppppp" + "liiip",
@@ -110,17 +110,63 @@ def status_tensor(dev):
     return _status[i]
 
 
-def check_status(dev=None):
-    """Synchronising read of the status word; raises if a kernel gave up waiting."""
+def check_status(dev=None, what="native kernel"):
+    """Synchronising read of the status word shared by every kernel of the library (compute and communication);
+    raises if a kernel gave up waiting (`CommTimeout` when the expired wait was on a peer's flag), skipped an
+    out-of-range index, or was sent more expert-parallel rows than its receive buffer holds."""
     dev = dev or torch.device("cuda", torch.cuda.current_device())
     st = status_tensor(dev)
     rec = st.tolist()
     if rec[0] != 0:
         st.zero_()
-        if rec[0] == 4:
-            raise IndexError(f"index out of range in a native kernel (site={rec[1]}: 1 row gather / embedding lookup, "
-                             f"2 row scatter-add; block={rec[2]}, index={rec[3]}); the access was skipped")
-        raise RuntimeError(f"device-side wait expired: code={rec[0]} site={rec[1]} block={rec[2]} extra={rec[3]}")
+        _raise_status(rec, what)
+
+
+def _raise_status(rec, what="native kernel"):
+    if rec[0] == 4:
+        raise IndexError(f"index out of range in a native kernel (site={rec[1]}: 1 row gather / embedding lookup, "
+                         f"2 row scatter-add, 3 gather along a dim, 4 scatter along a dim, 5 indexed read, "
+                         f"6 indexed write; block={rec[2]}, index={rec[3]}); the access was skipped")
+    if rec[0] == 3 and rec[1] == 900:
+        raise RuntimeError(f"{what}: expert-parallel receive buffer too small: this rank was sent {rec[3]} "
+                           f"(tile-padded) rows; raise GENESIS_EP_CAPACITY (multiple of the balanced share)")
+    if rec[0] == 2:
+        from ..distributed.process_group import CommTimeout
+        raise CommTimeout(f"{what}: device-side wait on a peer expired (code={rec[0]}, peer={rec[1]}, "
+                          f"block={rec[2]}, epoch={rec[3]}); a rank is late, stopped or gone")
+    raise RuntimeError(f"{what}: device-side wait expired: code={rec[0]} site={rec[1]} block={rec[2]} extra={rec[3]}")
+
+
+class StatusProbe:
+    """Sync-free look at the status word: `arm()` enqueues a device-to-host copy into pinned memory on the current
+    stream; `poll()` raises once that copy has landed and shows a record.  DistributedDataParallel arms it at the
+    end of every backward pass and polls at the next forward, so an expired wait of a gradient all-reduce stops
+    training one step later without adding a host synchronisation."""
+
+    def __init__(self, dev):
+        self.dev = dev
+        self.host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        self.event = None
+
+    def arm(self):
+        if torch.cuda.is_current_stream_capturing():
+            return
+        self.host.copy_(status_tensor(self.dev), non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+    def poll(self, what="gradient all-reduce", wait=False):
+        if self.event is None:
+            return
+        if wait:
+            self.event.synchronize()
+        elif not self.event.query():
+            return
+        self.event = None
+        rec = self.host.tolist()
+        if rec[0] != 0:
+            status_tensor(self.dev).zero_()
+            _raise_status(rec, what)
 
 
 def _ok(t):
@@ -1075,7 +1121,7 @@ def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step,
     dp = None
     if dyn is not None:
         dp = dyn.data_ptr()
-        _chk(lib().gb_adam_dyn_advance(dp, float(beta1), float(beta2), _st()), "adam_dyn_advance")
+        _chk(lib().gb_adam_dyn_advance(dp, float(beta1), float(beta2), fi, _st()), "adam_dyn_advance")
     _chk(lib().gb_adam_multi(meta.data_ptr(), nt, total, float(lr), float(beta1), float(beta2), float(eps),
                              float(weight_decay), 1.0 - beta1 ** step, 1.0 - beta2 ** step, 1 if decoupled else 0,
                              sdt, gs, fi, dp, _st()), "adam_multi")
@@ -1151,12 +1197,13 @@ def moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm):
 
 # ================================ communication ==================================
 def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None, found_inf=None, prescale=1.0,
-                    scale_is_reciprocal=True, ctas=None):
+                    scale_is_reciprocal=True, ctas=None, budget_ms=None):
     """In-place fused all-reduce over symmetric buffer `buf` (see csrc/comm.cu).  A channel with device-resident
-    epochs (`use_device_epochs()`) makes the launch replayable from a CUDA graph."""
+    epochs (`use_device_epochs()`) makes the launch replayable from a CUDA graph.  `budget_ms`: how long the kernel
+    waits for a peer before it records an expiry and returns (default `GENESIS_COMM_TIMEOUT_MS`, 10 s)."""
     ctr = getattr(st, "epoch_dev", None)
     epoch = 0 if ctr is not None else st.next_epoch()
-    budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000)) * 1e6)
+    budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000) if budget_ms is None else budget_ms) * 1e6)
     if ctas is None:
         # enough CTAs to keep ~1.5 MB of loads in flight for big buckets, one for tiny ones
         es = torch.empty(0, dtype=dtype).element_size()

@@ -202,10 +202,29 @@ class _AdamBase(Optimizer):
             self._dyn[0:1].fill_(float(self.lr))
             self._dyn_lr = self.lr
 
+    def steps_applied(self):
+        """Number of updates actually applied.  With a GradScaler the steps an overflow cancelled do not count; the
+        exact figure then lives on the device (this reads it back and brings the host's `t` in line)."""
+        if self._dyn is not None:
+            self.t = int(round(float(self._dyn[3].item())))
+        return self.t
+
+    def state_dict(self):
+        if self._dyn is not None and not torch.cuda.is_current_stream_capturing():
+            self.steps_applied()
+        return super().state_dict()
+
     def step(self):
         idx = self._active()
         if not idx:
             return
+        if self._found_inf is not None and self._dyn is None and self.params[idx[0]]._t.is_cuda:
+            # a step the overflow flag may cancel on the device: count steps there too, so that a cancelled step
+            # does not advance the bias corrections (the host cannot know without reading the flag back)
+            self.make_capturable()
+        elif self._found_inf is not None and not self.params[idx[0]]._t.is_cuda \
+                and float(self._found_inf.item()) != 0.0:
+            return                                # cancelled step (host tensors: the flag is read here)
         self.t += 1
         ps = [self.params[i]._t for i in idx]
         gs = [self.params[i].grad._t for i in idx]

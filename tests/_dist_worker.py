@@ -274,6 +274,45 @@ def scenario_ddp_amp(a):
     assert torch.allclose(chk / w, model.fc1.weight._t, atol=1e-6), "ranks diverged"
 
 
+def scenario_ddp_amp_clip(a):
+    """DDP + GradScaler + explicit `unscale_` + gradient clipping: the gradients that reach the optimizer equal the
+    mean of the ranks' true (unscaled) gradients, whether the fused all-reduce or the scaler did the unscaling."""
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    torch.manual_seed(2)
+    genesis.manual_seed(2)
+    model = MLP().to(d)
+    ref = MLP().to(d)
+    scaler = genesis.amp.GradScaler(init_scale=4096.0)
+    ddp = nn.DistributedDataParallel(model, grad_scaler=scaler)
+    ref.load_state_dict(ddp.state_dict())
+    opt = genesis.optim.AdamW(ddp.parameters(), lr=1e-2)
+    rs = np.random.RandomState(31 + r)
+    x = genesis.Tensor(torch.from_numpy(rs.randn(16, 64).astype(np.float32)).to(d))
+    y = genesis.Tensor(torch.from_numpy(rs.randint(0, 16, (16,))).to(d))
+    ref.zero_grad()
+    F.cross_entropy(ref(x), y).backward()
+    want = []
+    for p in ref.parameters():
+        g = p.grad._t.clone()
+        tdist.all_reduce(g)
+        want.append(g / w)
+    opt.zero_grad()
+    scaler.scale(F.cross_entropy(ddp(x), y)).backward()
+    scaler.unscale_(opt)
+    for (name, p), g in zip(model.named_parameters(), want):
+        assert torch.allclose(p.grad._t, g, atol=1e-5, rtol=1e-3), (name, float((p.grad._t - g).abs().max()))
+    total = nn.utils.clip_grad_norm_(model.parameters(), 1e-3)
+    tot = float(total.item()) if hasattr(total, "item") else float(total)
+    ref_norm = float(torch.sqrt(sum((g.float() ** 2).sum() for g in want)))
+    assert abs(tot - ref_norm) < 1e-3 * max(1.0, ref_norm), (tot, ref_norm)
+    after = float(torch.sqrt(sum((p.grad._t.float() ** 2).sum() for p in model.parameters())))
+    assert after <= 1.05e-3, after                     # clipping did trigger on the true gradient scale
+    before = model.fc1.weight._t.clone()
+    scaler.step(opt)
+    scaler.update()
+    assert not torch.equal(model.fc1.weight._t, before)
+
+
 def scenario_ep(a):
     """Expert-parallel MoE layer equals the single-process layer holding all experts."""
     from genesis_b200.models.transformers.moe import MoELayer

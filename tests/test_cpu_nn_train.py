@@ -268,6 +268,39 @@ def test_grad_scaler_skips_and_grows():
     assert sc2.get_scale() == sc.get_scale()
 
 
+def test_unscale_after_an_external_unscale_divides_nothing():
+    """DistributedDataParallel's fused all-reduce hands over gradients that are already divided by the scale; an
+    explicit `unscale_` (before clipping) must then only do the book-keeping."""
+    p = nn.Parameter(genesis.tensor(np.ones(4, np.float32)))
+    o = optim.AdamW([p], lr=0.1)
+    sc = genesis.amp.GradScaler(init_scale=1024.0)
+    o.zero_grad()
+    sc.scale(F.sum(p * 3.0)).backward()
+    p.grad._t.div_(1024.0)                    # what the all-reduce kernel does
+    sc._external_unscale = True
+    sc.unscale_(o)
+    np.testing.assert_allclose(p.grad.numpy(), 3.0, rtol=1e-6)
+    sc.step(o)
+    sc.update()
+    assert not sc._external_unscale
+
+
+def test_adam_does_not_count_a_cancelled_step():
+    p = nn.Parameter(genesis.tensor(np.ones(4, np.float32)))
+    o = optim.AdamW([p], lr=0.1)
+    sc = genesis.amp.GradScaler(init_scale=4.0)
+    o.zero_grad()
+    sc.scale(F.sum(p * float("inf"))).backward()
+    sc.step(o)
+    sc.update()
+    assert o.t == 0 and o.steps_applied() == 0
+    o.zero_grad()
+    sc.scale(F.sum(p)).backward()
+    sc.step(o)
+    sc.update()
+    assert o.t == 1
+
+
 # ------------------------------------------------------------------ serialization
 def test_save_load_roundtrip_and_atomicity(tmp_path):
     sd = {"w": genesis.tensor(arr(3, 4)), "h": genesis.ones(2, dtype=genesis.float16),

@@ -87,3 +87,61 @@ def test_training_step_with_the_pool_installed():
     env = dict(os.environ, GENESIS_B200_POOL="1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "POOL_OK" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_block_freed_on_the_default_stream_is_not_handed_to_a_side_stream():
+    """Stream 0 (the legacy default stream, torch's current stream unless told otherwise) has a null handle: a block
+    it frees must stay its own until an event says otherwise, like the block of any other stream."""
+    from genesis_b200.cuda import pool
+    dev = torch.cuda.current_device()
+    side = torch.cuda.Stream()
+    n = 3 << 20
+    p = pool.alloc(n, dev, 0)
+    pool.free(p, n, dev, 0)                                     # back in the bin, tagged with stream 0
+    q = pool.alloc(n, dev, side.cuda_stream)                    # another stream: must not get that block
+    assert q != p
+    r = pool.alloc(n, dev, 0)                                   # stream 0 itself reuses it at once
+    assert r == p
+    pool.free(q, n, dev, side.cuda_stream)
+    pool.free(r, n, dev, 0)
+
+
+@pytest.mark.gpu
+def test_graph_capture_keeps_its_blocks_private():
+    """Memory that a captured step allocates (and frees) belongs to the graph: eager allocations made afterwards never
+    alias it, so a replay still computes the same thing after the eager code has scribbled over everything it got."""
+    code = (
+        "import torch, genesis_b200 as genesis, genesis_b200.nn as nn\n"
+        "from genesis_b200.cuda import pool\n"
+        "assert pool.is_installed()\n"
+        "dev = torch.cuda.current_device()\n"
+        "genesis.manual_seed(0)\n"
+        "def make():\n"
+        "    genesis.manual_seed(0)\n"
+        "    m = nn.Sequential(nn.Linear(256, 512), nn.ReLU(), nn.Linear(512, 10)).cuda()\n"
+        "    opt = genesis.optim.AdamW(m.parameters(), lr=1e-3)\n"
+        "    def step(x, y):\n"
+        "        opt.zero_grad(); loss = nn.CrossEntropyLoss()(m(x), y); loss.backward(); opt.step(); return loss\n"
+        "    return m, opt, step\n"
+        "x = genesis.randn(64, 256, device='cuda'); y = genesis.Tensor(torch.randint(0, 10, (64,), device='cuda'))\n"
+        "ma, oa, sa = make(); mb, ob, sb = make()\n"
+        "g = genesis.cuda.GraphedTrainStep(sb, ob, [x, y], warmup=2)\n"
+        "assert pool.capture_cached(dev) > 0\n"
+        "for _ in range(2): sa(x, y)\n"
+        "junk = []\n"
+        "for i in range(6):\n"
+        "    la = sa(x, y)\n"
+        "    # eager code grabs blocks of the classes the step uses and fills them with NaN\n"
+        "    junk = [torch.full((64, 512), float('nan'), device='cuda') for _ in range(8)]\n"
+        "    junk += [torch.full((64, 10), float('nan'), device='cuda') for _ in range(8)]\n"
+        "    lb = g(x, y)\n"
+        "    torch.cuda.synchronize()\n"
+        "    assert abs(float(la._t) - float(lb._t)) < 1e-4, (i, float(la._t), float(lb._t))\n"
+        "cached = pool.capture_cached(dev)\n"
+        "g.graph.reset()\n"
+        "assert pool.capture_cached(dev) == 0 and cached > 0\n"
+        "print('CAPTURE_OK', cached)\n")
+    env = dict(os.environ, GENESIS_B200_POOL="1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "CAPTURE_OK" in r.stdout, r.stdout + r.stderr
