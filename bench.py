@@ -124,6 +124,7 @@ def run_ours(args):
     from genesis_b200 import distributed as dist
     from genesis_b200.models.transformers import TransformerConfig, QwenForCausalLM
     from genesis_b200.ops import native
+    from genesis_b200.ops import dispatch as K
 
     rank, world, local = dist_env(args)
     torch.cuda.set_device(local)
@@ -169,6 +170,9 @@ def run_ours(args):
     # The whole step (forward, backward, bucket all-reduces on their stream, AdamW) is captured once as a CUDA graph
     # and replayed, which removes the host launch path from the loop.  With data parallelism this needs the
     # peer-memory all-reduce (its epochs are counted on the device); over NCCL the step stays eager.
+    # every CUDA op that leaves the native kernels from here on (warm-up, capture and timed steps) is counted and
+    # reported as `native_fallbacks`
+    K.reset_fallbacks()
     graphed = None
     if not args.no_graph and (world == 1 or getattr(net, "_use_symm", False)):
         try:
@@ -222,8 +226,84 @@ def run_ours(args):
                 "h2d_bytes_per_step": B * (S + 1) * 8 * world, "d2h_bytes_per_step": 4 * world,
                 "loss": last_loss},
         "gpu_launches": launches,
+        "native_fallbacks": K.fallback_counts(),
+        # time x clock: steadier than ms alone on a part that sits at its power cap
+        "ms_x_ghz": None if not clocks or not clocks.get("sm_mhz") else ms * clocks["sm_mhz"] / 1e3,
+        "allocator": "native pool" if genesis.cuda.pool.is_installed() else "torch",
         "impl": "genesis_b200",
     }
+
+
+def run_torch(args):
+    """Context arm: the same model, data, optimizer and timing in plain PyTorch (see benchmarks/torch_qwen.py).
+    Labelled `"impl": "torch"`; it is not the reference."""
+    import numpy as np
+    import torch
+    import torch.distributed as tdist
+    sys.path.insert(0, ROOT)
+    from benchmarks.torch_qwen import TorchQwen
+    rank, world, local = dist_env(args)
+    torch.cuda.set_device(local)
+    if world > 1:
+        tdist.init_process_group(backend="nccl")
+    torch.manual_seed(1234)
+    c = CONFIGS[args.model]
+    model = TorchQwen(c).cuda()
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
+    amp_dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    scaler = torch.amp.GradScaler("cuda", init_scale=2.0 ** 16) if args.dtype == "fp16" else None
+    B, S = args.micro_batch, args.seq_len
+    rs = np.random.RandomState(1000 + rank)
+    host = [torch.from_numpy(rs.randint(0, c["vocab_size"], (B, S + 1)).astype(np.int64)).pin_memory()
+            for _ in range(4)]
+    dev_batches = [h.cuda() for h in host]
+    counter = {"i": 0}
+
+    def train_step(tokens):
+        with torch.autocast("cuda", dtype=amp_dtype):
+            loss = net(tokens[:, :-1], tokens[:, 1:].reshape(-1))
+        opt.zero_grad(set_to_none=True)
+        if scaler is not None:
+            scaler.scale(loss).backward()
+            scaler.step(opt)
+            scaler.update()
+        else:
+            loss.backward()
+            opt.step()
+        return loss
+
+    def step_device():
+        counter["i"] += 1
+        return train_step(dev_batches[counter["i"] % 4])
+
+    def step_e2e():
+        counter["i"] += 1
+        return float(train_step(host[counter["i"] % 4].to("cuda", non_blocking=True)).float().cpu())
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms, _ = time_steps(torch, step_device, args.steps, args.warmup, world)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, last_loss = time_steps(torch, step_e2e, args.steps, max(1, args.warmup // 2), world)
+    if world > 1:
+        tdist.destroy_process_group()
+    if rank != 0:
+        return None
+    tok = B * S * world
+    return {"metric": METRIC, "value": tok / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.dtype, "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
+            "config": {"model": args.model, "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
+                       "optimizer": "torch.optim.AdamW(fused=True) lr 3e-4",
+                       "stack": "plain PyTorch eager: cuBLAS, SDPA, torch DDP over NCCL",
+                       "l2_policy": "working set >> 126 MB L2; 4 distinct input batches rotated"},
+            "clocks": clocks,
+            "e2e": {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": B * (S + 1) * 8 * world, "d2h_bytes_per_step": 4 * world, "loss": last_loss},
+            "gpu_launches": 0, "impl": "torch",
+            "note": "context only: plain PyTorch on the same box, not the reference and not this framework"}
 
 
 REFERENCE_FAULT = ("reference GPU path closed on this pool: its own Triton kernels raised 'an illegal memory access was "
@@ -249,7 +329,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
     ap.add_argument("--model", default="qwen2.5-0.5b", choices=sorted(CONFIGS))
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=2048)
@@ -265,7 +345,8 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
                os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    out = run_reference(args) if args.impl == "reference" else (run_torch(args) if args.impl == "torch"
+                                                                else run_ours(args))
     if out is not None:
         print(json.dumps(out), flush=True)
 

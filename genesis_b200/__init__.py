@@ -36,6 +36,25 @@ from .nn.functional import (add, sub, mul, div, pow, neg, exp, log, sqrt, sin, c
                             scatter, scatter_add, repeat_interleave, logsumexp, argmax, argmin, var, std, split)
 from . import models  # noqa: E402
 from . import parallel  # noqa: E402
+from . import backends  # noqa: E402
+from . import storage  # noqa: E402
+from .backends import Storage, CPUStorage, CUDAStorage  # noqa: E402,F401
+
+
+def _export_functional():
+    """The reference star-exports its whole functional namespace at top level (`genesis/__init__.py:52-57`:
+    `from .backends import *`, `from .functional import *`, where `functional.py:10` star-imports `nn.functional`):
+    every public function and Function class of `nn.functional` is reachable as `genesis.<name>` too."""
+    import types
+    from .nn import functional as _F
+    g = globals()
+    for name, obj in vars(_F).items():
+        if name.startswith("_") or isinstance(obj, types.ModuleType) or name in g:
+            continue
+        g[name] = obj
+
+
+_export_functional()
 
 use_triton = False   # kept for API parity; there is no Triton path
 

@@ -92,7 +92,8 @@ def bind_nn_functional_methods():
     T.scatter = lambda s, dim, index, src: F.scatter(s, dim, index, src)
 
     def scatter_(s, dim, index, src):
-        s._t.scatter_(dim, index._t.long(), src._t if isinstance(src, Tensor) else src)
+        from .ops import dispatch as K
+        K.scatter_(s._t, dim, index._t, src._t if isinstance(src, Tensor) else src)
         s._version += 1
         return s
     T.scatter_ = scatter_

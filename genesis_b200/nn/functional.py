@@ -686,7 +686,7 @@ class Stack(_ViewOp):
     @staticmethod
     def forward(ctx, tensors, dim):
         ctx.dim = dim
-        return torch.stack(list(tensors), dim)
+        return K.stack(list(tensors), dim)
 
     @staticmethod
     def backward(ctx, g):
@@ -698,7 +698,7 @@ class Cat(_ViewOp):
     def forward(ctx, tensors, dim):
         ctx.dim = dim
         ctx.sizes = [t.shape[dim] for t in tensors]
-        return torch.cat(list(tensors), dim)
+        return K.cat(list(tensors), dim)
 
     @staticmethod
     def backward(ctx, g):
@@ -716,10 +716,12 @@ class Split(_ViewOp):
     def backward(ctx, *gs):
         dim, shape, sizes = ctx.meta
         ref = next(x for x in gs if x is not None)
-        out = torch.zeros(shape, dtype=ref.dtype, device=ref.device)
+        if all(x is not None for x in gs):
+            return K.cat(list(gs), dim)
+        out = K.zeros(shape, ref.dtype, ref.device)
         for gpart, piece in zip(gs, out.split(sizes, dim)):
             if gpart is not None:
-                piece.copy_(gpart)
+                K.copy_(piece, gpart)
         return out
 
 
@@ -728,7 +730,7 @@ def _raw_index(index):
     """Convert Tensors inside an index expression to torch tensors."""
     if isinstance(index, Tensor):
         t = index._t
-        return t if t.dtype in (torch.bool, torch.int64) else t.long()
+        return t if t.dtype in (torch.bool, torch.int64, torch.int32) else t.long()
     if isinstance(index, tuple):
         return tuple(_raw_index(i) for i in index)
     if isinstance(index, list):
@@ -743,35 +745,16 @@ class GetItem(_ViewOp):
     def forward(ctx, a, index):
         ctx.index = index
         ctx.shape = a.shape
-        return a[index]
+        return K.getitem(a, index)
 
     @staticmethod
     def backward(ctx, g):
-        out = torch.zeros(ctx.shape, dtype=g.dtype, device=g.device)
-        idx = ctx.index
-        adv = _has_advanced(idx)
-        if adv:
-            out.index_put_(idx if isinstance(idx, tuple) else (idx,), g, accumulate=True) \
-                if _all_tensor_index(idx) else _accumulate_mixed(out, idx, g)
-        else:
-            out[idx] = g
-        return out
+        return K.getitem_backward(ctx.shape, ctx.index, g)
 
 
-def _has_advanced(idx):
-    items = idx if isinstance(idx, tuple) else (idx,)
-    return any(isinstance(i, (torch.Tensor, list)) for i in items)
-
-
-def _all_tensor_index(idx):
-    items = idx if isinstance(idx, tuple) else (idx,)
-    return all(isinstance(i, torch.Tensor) for i in items)
-
-
-def _accumulate_mixed(out, idx, g):
-    # Mixed advanced/basic indexing: accumulate through a flat index map.
-    lin = torch.arange(out.numel(), device=out.device).reshape(out.shape)[idx]
-    out.reshape(-1).index_add_(0, lin.reshape(-1), g.reshape(-1).to(out.dtype))
+def _int_index(t):
+    """int32 / int64 index tensors are used as they are (the kernels read both); anything else becomes int64."""
+    return t if t.dtype in (torch.int32, torch.int64) else t.long()
 
 
 class SetItem(_ViewOp):
@@ -781,17 +764,17 @@ class SetItem(_ViewOp):
     def forward(ctx, a, value, index):
         ctx.index = index
         ctx.vshape = value.shape if isinstance(value, torch.Tensor) else None
-        out = a.clone()
-        out[index] = value
+        out = K.clone(a)
+        K.setitem_(out, index, value)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        ga = g.clone()
-        ga[ctx.index] = 0
+        ga = K.clone(g)
+        K.setitem_(ga, ctx.index, 0)
         if ctx.vshape is None:
             return (ga,)
-        gv = g[ctx.index]
+        gv = K.getitem(g, ctx.index)
         return ga, K.sum_to_shape(gv, ctx.vshape)
 
 
@@ -800,15 +783,13 @@ class Gather(_ViewOp):
     def forward(ctx, a, dim, index):
         ctx.save_for_backward(index)
         ctx.meta = (dim, a.shape)
-        return torch.gather(a, dim, index)
+        return K.gather(a, dim, index)
 
     @staticmethod
     def backward(ctx, g):
         (index,) = ctx.saved_tensors
         dim, shape = ctx.meta
-        out = torch.zeros(shape, dtype=g.dtype, device=g.device)
-        out.scatter_add_(dim, index, g)
-        return out
+        return K.scatter_add_into_zeros(shape, dim, index, g)
 
 
 class Scatter(_ViewOp):
@@ -817,14 +798,14 @@ class Scatter(_ViewOp):
         ctx.save_for_backward(index)
         ctx.dim = dim
         ctx.src_is_tensor = isinstance(src, torch.Tensor)
-        return a.scatter(dim, index, src)
+        return K.scatter(a, dim, index, src)
 
     @staticmethod
     def backward(ctx, g):
         (index,) = ctx.saved_tensors
-        ga = g.scatter(ctx.dim, index, 0)
+        ga = K.scatter(g, ctx.dim, index, 0)
         if ctx.src_is_tensor:
-            return ga, None, torch.gather(g, ctx.dim, index)
+            return ga, None, K.gather(g, ctx.dim, index)
         return (ga,)
 
 
@@ -833,12 +814,12 @@ class ScatterAddFunction(_ViewOp):
     def forward(ctx, a, dim, index, src):
         ctx.save_for_backward(index)
         ctx.dim = dim
-        return a.scatter_add(dim, index, src)
+        return K.scatter(a, dim, index, src, add=True)
 
     @staticmethod
     def backward(ctx, g):
         (index,) = ctx.saved_tensors
-        return g, None, torch.gather(g, ctx.dim, index)
+        return g, None, K.gather(g, ctx.dim, index)
 
 
 class TopKFunction(_ViewOp):
@@ -853,9 +834,7 @@ class TopKFunction(_ViewOp):
     def backward(ctx, gv, gi=None):
         (idx,) = ctx.saved_tensors
         dim, shape = ctx.meta
-        out = torch.zeros(shape, dtype=gv.dtype, device=gv.device)
-        out.scatter_add_(dim, idx, gv)
-        return out
+        return K.scatter_add_into_zeros(shape, dim, idx, gv)
 
 
 class RepeatInterleaveFunction(_ViewOp):
@@ -1458,21 +1437,21 @@ def setitem(a, index, value):
         out = SetItem.apply(a, value, idx) if _is_t(value) else SetItem.apply(a, value, idx)
         a._t, a.creator, a.idx, a.requires_grad = out._t, out.creator, out.idx, out.requires_grad
     else:
-        a._t[idx] = value._t if _is_t(value) else value
+        K.setitem_(a._t, idx, value._t if _is_t(value) else value)
     a._version += 1
     return a
 
 
 def gather(input, dim, index):
-    return Gather.apply(input, dim, Tensor._wrap(index._t.long()))
+    return Gather.apply(input, dim, Tensor._wrap(_int_index(index._t)))
 
 
 def scatter(input, dim, index, src):
-    return Scatter.apply(input, dim, Tensor._wrap(index._t.long()), src)
+    return Scatter.apply(input, dim, Tensor._wrap(_int_index(index._t)), src)
 
 
 def scatter_add(input, dim, index, src):
-    return ScatterAddFunction.apply(input, dim, Tensor._wrap(index._t.long()), src)
+    return ScatterAddFunction.apply(input, dim, Tensor._wrap(_int_index(index._t)), src)
 
 
 def topk(input, k, dim=-1, largest=True, sorted=True):
@@ -1775,3 +1754,30 @@ def cast_to_fp16(x):
 def sum_to_shape(data, shape):
     """Sum the broadcast dimensions of `data` so that the result has `shape` (the inverse of broadcasting)."""
     return Tensor._wrap(K.sum_to_shape(data._t if isinstance(data, Tensor) else data, tuple(shape)))
+
+
+# ---- the reference's fused-op entry points (its `nn/attention.py`, `nn/layer_norm.py`, `nn/triton_ops/*`) ----------
+def fused_attention(q, k, v):
+    """Causal flash attention on [B, H, S, D] tensors (reference `nn/attention.py:518`); GQA needs no K/V repeat."""
+    return scaled_dot_product_attention(q, k, v, is_causal=True)
+
+
+def fused_layer_norm(x, weight, bias, eps=1e-6):
+    """Reference `nn/layer_norm.py:212` (default eps 1e-6 there, 1e-5 in `triton_ops/layer_norm.py:232`)."""
+    return FusedLayerNormFunction.apply(x, weight, bias, eps)
+
+
+def fused_rmsnorm(x, weight, eps=1e-6):
+    """Reference `nn/triton_ops/rmsnorm.py:242`."""
+    return FusedRMSNormFunction.apply(x, weight, eps)
+
+
+def safe_softmax(x, dim=-1, dtype=None):
+    """Softmax that subtracts the row maximum (all softmax kernels here do); optional output dtype.
+    Reference `nn/triton_ops/softmax.py:142`."""
+    out = SoftmaxFunction.apply(x, dim, False)
+    return out if dtype is None else out.to_dtype(dtype)
+
+
+triton_softmax = safe_softmax
+triton_gelu = gelu

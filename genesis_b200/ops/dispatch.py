@@ -9,7 +9,9 @@ A native wrapper returns `NotImplemented` for a layout/dtype it does not cover
 (e.g. float64 or >4-D strided broadcasting); only then is the generic torch op
 used on CUDA.
 """
+import collections
 import math
+import os
 
 import torch
 
@@ -17,6 +19,58 @@ from . import native as N
 
 _F32 = torch.float32
 _LOW = (torch.float16, torch.bfloat16)
+
+# ---- falling off the native path is counted, and an error in strict mode ---------------------------------------
+# Every op below tries its sm_100a kernel first; when the wrapper answers `NotImplemented` (a dtype / layout the
+# kernel family does not cover) a CUDA tensor is handed to the generic torch op instead.  That is legitimate for
+# rare cases (float64, integer arithmetic) and invisible in a benchmark, so it is counted per op here;
+# `GENESIS_STRICT_NATIVE=1` (or `strict_native(True)`) turns such a fall into an error.  bench.py and the GPU model
+# tests assert that the counter stays at zero on the paths they time.
+fallbacks = collections.Counter()
+_strict = [os.environ.get("GENESIS_STRICT_NATIVE", "0") == "1"]
+
+
+def _fell(op):
+    fallbacks[op] += 1
+    if _strict[0]:
+        raise RuntimeError(f"GENESIS_STRICT_NATIVE: op '{op}' has no native sm_100a path for these arguments and "
+                           f"would have run a library kernel")
+
+
+def _fb(t, op):
+    """Marks a fall to the library op when `t` is a non-empty CUDA tensor (for ops whose native branch is guarded by
+    more than the device test)."""
+    if isinstance(t, torch.Tensor) and t.is_cuda and t.numel() > 0:
+        _fell(op)
+
+
+def fallback_counts():
+    """{op name: times a CUDA call was served by a library kernel instead of a native one} since the last reset."""
+    return dict(fallbacks)
+
+
+def reset_fallbacks():
+    fallbacks.clear()
+
+
+class strict_native:
+    """`with strict_native():` raises on any CUDA op that would leave the native path (also usable as a switch:
+    `strict_native.set(True)`)."""
+
+    def __init__(self, on=True):
+        self.on, self.prev = on, None
+
+    def __enter__(self):
+        self.prev, _strict[0] = _strict[0], self.on
+        return self
+
+    def __exit__(self, *exc):
+        _strict[0] = self.prev
+        return False
+
+    @staticmethod
+    def set(on):
+        _strict[0] = bool(on)
 
 
 def _cuda(t):
@@ -31,6 +85,7 @@ def to_dtype(t, dtype):
         r = N.cast(t, dtype)
         if r is not NotImplemented:
             return r
+        _fell("to_dtype")
     return t.to(dtype)
 
 
@@ -39,6 +94,7 @@ def copy_(dst, src):
         r = N.copy_(dst, src)
         if r is not NotImplemented:
             return dst
+        _fell("copy_")
     dst.copy_(src)
     return dst
 
@@ -50,6 +106,7 @@ def contiguous(t):
         r = N.contiguous(t)
         if r is not NotImplemented:
             return r
+        _fell("contiguous")
     return t.contiguous()
 
 
@@ -66,8 +123,27 @@ def fill_(t, value):
         r = N.fill_(t, value)
         if r is not NotImplemented:
             return t
+        _fell("fill_")
     t.fill_(value)
     return t
+
+
+def zero_(t):
+    return fill_(t, 0)
+
+
+def fill_view_(v, value):
+    """`v[...] = value` for a strided view: contiguous float views take the fill kernel, the rest the strided-copy
+    kernel fed from a one-element tensor broadcast through zero strides."""
+    if not v.is_cuda:
+        v.fill_(value)
+        return v
+    if N.fill_(v, value) is not NotImplemented:
+        return v
+    if v.dim() == 0 or v.dim() > 6 or v.element_size() not in (1, 2, 4, 8) or v.is_complex():
+        return NotImplemented
+    one = torch.tensor([value], dtype=v.dtype).to(v.device, non_blocking=False)
+    return v if N.copy_(v, one.expand(v.shape)) is not NotImplemented else NotImplemented
 
 
 # ================================ elementwise ====================================
@@ -77,6 +153,7 @@ def _binary(name, torch_fn, a, b):
         r = N.binary(name, a, b)
         if r is not NotImplemented:
             return r
+        _fell(name)
     return torch_fn(a, b)
 
 
@@ -110,6 +187,7 @@ def add_(a, b):
         r = N.add_(a, b)
         if r is not NotImplemented:
             return a
+        _fell("add_")
     a.add_(b)
     return a
 
@@ -120,6 +198,7 @@ def axpy_(a, b, alpha):
         r = N.add_(a, b, alpha)
         if r is not NotImplemented:
             return a
+        _fell("axpy_")
     a.add_(b, alpha=alpha)
     return a
 
@@ -129,6 +208,7 @@ def mul_(a, b):
         r = N.mul_(a, b)
         if r is not NotImplemented:
             return a
+        _fell("mul_")
     a.mul_(b)
     return a
 
@@ -148,6 +228,7 @@ def unary(name, t):
         r = N.unary(name, t)
         if r is not NotImplemented:
             return r
+        _fell(name)
     return _UNARY_TORCH[name](t)
 
 
@@ -157,6 +238,7 @@ def unary_bwd(name, g, x, y=None):
         r = N.unary_bwd(name, g, x if x is not None else y, y)
         if r is not NotImplemented:
             return r
+        _fell(name + "_bwd")
     if name == "neg":
         return -g
     if name == "exp":
@@ -196,6 +278,7 @@ def pow_scalar(t, p):
         r = N.scalar_op("pow", t, p)
         if r is not NotImplemented:
             return r
+        _fell("pow_scalar")
     return torch.pow(t, p)
 
 
@@ -204,6 +287,7 @@ def rpow_scalar(t, base):
         r = N.scalar_op("rpow", t, base)
         if r is not NotImplemented:
             return r
+        _fell("rpow_scalar")
     return torch.pow(torch.tensor(base, dtype=t.dtype, device=t.device), t)
 
 
@@ -212,6 +296,7 @@ def clamp(t, lo, hi):
         r = N.clamp(t, lo, hi)
         if r is not NotImplemented:
             return r
+        _fell("clamp")
     return torch.clamp(t, lo, hi)
 
 
@@ -220,6 +305,7 @@ def where(c, a, b):
         r = N.where(c, a, b)
         if r is not NotImplemented:
             return r
+        _fell("where")
     if not isinstance(a, torch.Tensor):
         ref = b if isinstance(b, torch.Tensor) else None
         a = torch.tensor(a, dtype=ref.dtype if ref is not None else torch.float32, device=c.device)
@@ -236,6 +322,7 @@ def compare(name, a, b):
         r = N.compare(name, a, b)
         if r is not NotImplemented:
             return r
+        _fell(name)
     return _CMP_TORCH[name](a, b)
 
 
@@ -255,6 +342,7 @@ def reduce(name, t, dims=None, keepdim=False):
         r = N.reduce(name, t, dims, keepdim)
         if r is not NotImplemented:
             return r
+        _fell("reduce_" + name)
     if name in ("sum", "mean"):
         fn = torch.sum if name == "sum" else torch.mean
         if dims is None:
@@ -288,6 +376,7 @@ def matmul(a, b):
         r = N.matmul(a, b)
         if r is not NotImplemented:
             return r
+        _fell("matmul")
     return torch.matmul(a, b)
 
 
@@ -297,6 +386,7 @@ def linear(x, w, bias=None, out_dtype=None):
         r = N.linear(x, w, bias, out_dtype)
         if r is not NotImplemented:
             return r
+        _fell("linear")
     y = torch.nn.functional.linear(x, w, None if bias is None else bias.to(x.dtype))
     return y if out_dtype is None else y.to(out_dtype)
 
@@ -307,6 +397,7 @@ def linear_dgrad(gy, w):
         r = N.linear_dgrad(gy, w)
         if r is not NotImplemented:
             return r
+        _fell("linear_dgrad")
     return torch.matmul(gy, w)
 
 
@@ -317,6 +408,7 @@ def linear_wgrad(gy, x, out_dtype=None, accum=None, out=None):
         r = N.linear_wgrad(gy, x, out_dtype, accum, out)
         if r is not NotImplemented:
             return r
+        _fell("linear_wgrad")
     g2 = gy.reshape(-1, gy.shape[-1])
     x2 = x.reshape(-1, x.shape[-1])
     dw = torch.matmul(g2.t().float(), x2.float()) if g2.dtype in _LOW else torch.matmul(g2.t(), x2)
@@ -343,6 +435,7 @@ def rmsnorm_fwd(x, w, eps):
         r = N.rmsnorm_fwd(x, w, eps)
         if r is not NotImplemented:
             return r
+        _fell("rmsnorm_fwd")
     xf = x.float()
     rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     y = (xf * rstd * w.float()).to(x.dtype)
@@ -355,6 +448,7 @@ def rmsnorm_bwd(g, x, w, rstd):
         r = N.rmsnorm_bwd(g, x, w, rstd)
         if r is not NotImplemented:
             return r
+        _fell("rmsnorm_bwd")
     n = x.shape[-1]
     xf, gf, wf = x.float(), g.float(), w.float()
     rs = rstd.reshape(*x.shape[:-1], 1)
@@ -372,6 +466,7 @@ def add_rmsnorm_fwd(x, res, w, eps):
         r = N.add_rmsnorm_fwd(x, res, w, eps)
         if r is not NotImplemented:
             return r
+        _fell("add_rmsnorm_fwd")
     s = add(x, res)
     y, rstd = rmsnorm_fwd(s, w, eps)
     return s, y, rstd
@@ -383,6 +478,7 @@ def add_rmsnorm_bwd(g, gres, x, w, rstd):
         r = N.add_rmsnorm_bwd(g, gres, x, w, rstd)
         if r is not NotImplemented:
             return r
+        _fell("add_rmsnorm_bwd")
     dx, dw = rmsnorm_bwd(g, x, w, rstd)
     return add(dx, gres), dw
 
@@ -393,6 +489,7 @@ def layernorm_fwd(x, w, b, eps):
         r = N.layernorm_fwd(x, w, b, eps)
         if r is not NotImplemented:
             return r
+        _fell("layernorm_fwd")
     xf = x.float()
     mean = xf.mean(-1, keepdim=True)
     var = xf.var(-1, unbiased=False, keepdim=True)
@@ -411,6 +508,7 @@ def layernorm_bwd(g, x, w, mean, rstd):
         r = N.layernorm_bwd(g, x, w, mean, rstd)
         if r is not NotImplemented:
             return r
+        _fell("layernorm_bwd")
     n = x.shape[-1]
     xf, gf = x.float(), g.float()
     mu = mean.reshape(*x.shape[:-1], 1)
@@ -428,6 +526,7 @@ def softmax_fwd(x, dim, log=False):
         r = N.softmax_fwd(x, dim, log)
         if r is not NotImplemented:
             return r
+        _fell("softmax_fwd")
     return torch.log_softmax(x, dim) if log else torch.softmax(x, dim)
 
 
@@ -436,6 +535,7 @@ def softmax_bwd(g, y, dim, log=False):
         r = N.softmax_bwd(g, y, dim, log)
         if r is not NotImplemented:
             return r
+        _fell("softmax_bwd")
     if log:
         return g - torch.exp(y) * g.sum(dim, keepdim=True)
     return y * (g - (g * y).sum(dim, keepdim=True))
@@ -447,6 +547,7 @@ def cross_entropy_fwd(logits, target, ignore_index):
         r = N.cross_entropy_fwd(logits, target, ignore_index)
         if r is not NotImplemented:
             return r
+        _fell("cross_entropy_fwd")
     lf = logits.float()
     lse = torch.logsumexp(lf, -1)
     valid = target != ignore_index
@@ -462,6 +563,7 @@ def cross_entropy_bwd(logits, target, lse, grad_rows, ignore_index, inplace=Fals
         r = N.cross_entropy_bwd(logits, target, lse, grad_rows, ignore_index, inplace)
         if r is not NotImplemented:
             return r
+        _fell("cross_entropy_bwd")
     lf = logits.float()
     p = torch.exp(lf - lse.reshape(-1, 1))
     valid = target != ignore_index
@@ -477,6 +579,7 @@ def swiglu_fwd(gate, up):
         r = N.swiglu_fwd(gate, up)
         if r is not NotImplemented:
             return r
+        _fell("swiglu_fwd")
     return (torch.nn.functional.silu(gate.float()) * up.float()).to(gate.dtype)
 
 
@@ -485,6 +588,7 @@ def swiglu_bwd(g, gate, up):
         r = N.swiglu_bwd(g, gate, up)
         if r is not NotImplemented:
             return r
+        _fell("swiglu_bwd")
     gf, a, b = g.float(), gate.float(), up.float()
     s = torch.sigmoid(a)
     dgate = gf * b * s * (1 + a * (1 - s))
@@ -498,6 +602,7 @@ def swiglu_fused_fwd(gu):
         r = N.swiglu_fused_fwd(gu)
         if r is not NotImplemented:
             return r
+        _fell("swiglu_fused_fwd")
     I = gu.shape[-1] // 2
     g, u = gu[..., :I].float(), gu[..., I:].float()
     return (torch.nn.functional.silu(g) * u).to(gu.dtype)
@@ -509,6 +614,7 @@ def swiglu_fused_bwd(dy, gu):
         r = N.swiglu_fused_bwd(dy, gu)
         if r is not NotImplemented:
             return r
+        _fell("swiglu_fused_bwd")
     I = gu.shape[-1] // 2
     g, u, d = gu[..., :I].float(), gu[..., I:].float(), dy.float()
     sg = torch.sigmoid(g)
@@ -523,6 +629,7 @@ def rope_fwd(x, cos, sin, positions=None, inverse=False, out=None):
         r = N.rope(x, cos, sin, positions, inverse, out)
         if r is not NotImplemented:
             return r
+        _fell("rope_fwd")
     B, S, H, D = x.shape
     if positions is None:
         c, s = cos[:S].reshape(1, S, 1, D), sin[:S].reshape(1, S, 1, D)
@@ -546,6 +653,7 @@ def embedding_fwd(weight, idx):
         r = N.embedding_fwd(weight, idx)
         if r is not NotImplemented:
             return r
+        _fell("embedding_fwd")
     return weight[idx.long()]
 
 
@@ -555,6 +663,7 @@ def embedding_bwd(g, idx, num_rows, out_dtype=None):
         r = N.embedding_bwd(g, idx, num_rows, out_dtype)
         if r is not NotImplemented:
             return r
+        _fell("embedding_bwd")
     D = g.shape[-1]
     out = torch.zeros(num_rows, D, dtype=torch.float32, device=g.device)
     out.index_add_(0, idx.reshape(-1).long(), g.reshape(-1, D).float())
@@ -573,6 +682,7 @@ def embedding_bwd_into(acc, g, idx):
         r = N.scatter_add_rows_into(g2, flat, acc)
         if r is not NotImplemented:
             return
+        _fell("embedding_bwd_into")
     acc.index_add_(0, flat.long(), g2.to(acc.dtype))
 
 
@@ -582,6 +692,7 @@ def attention_fwd(q, k, v, causal, scale):
         r = N.attention_fwd(q, k, v, causal, scale)
         if r is not NotImplemented:
             return r
+        _fell("attention_fwd")
     B, S, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     g = Hq // Hkv
@@ -603,6 +714,7 @@ def attention_bwd(do, q, k, v, o, lse, causal, scale):
         r = N.attention_bwd(do, q, k, v, o, lse, causal, scale)
         if r is not NotImplemented:
             return r
+        _fell("attention_bwd")
     B, S, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     g = Hq // Hkv
@@ -636,6 +748,7 @@ def dropout_mask_apply(x, p, seed, offset):
         r = N.dropout_fwd(x, p, seed, offset)
         if r is not NotImplemented:
             return r
+        _fell("dropout_mask_apply")
     # Same draw and arithmetic order as the reference's CPU dropout (`nn/modules/dropout.py:16-22`):
     # u ~ U[0,1), keep where u <= 1-p, y = x * keep / (1-p).
     keep = (torch.rand(x.shape, device=x.device) <= (1.0 - p))
@@ -649,6 +762,7 @@ def random_fill(kind, shape, dtype, device, seed, offset, a=0.0, b=1.0):
         r = N.random_fill(kind, shape, dtype, dev, seed, offset, a, b)
         if r is not NotImplemented:
             return r
+        _fell("random_fill")
     if kind == "uniform":
         return torch.rand(shape, dtype=torch.float32, device=dev).mul_(b - a).add_(a).to(dtype)
     if kind == "normal":
@@ -672,6 +786,7 @@ def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step,
                          grad_scale, found_inf, shadows, dyn)
         if r is not NotImplemented:
             return
+        _fell("adamw_step")
     if dyn is not None:
         raise RuntimeError("capturable optimizer state needs contiguous fp32 CUDA parameters and floating-point gradients")
     if found_inf is not None and float(found_inf.item()) != 0.0:
@@ -702,6 +817,7 @@ def sgd_step(params, grads, bufs, lr, momentum, weight_decay):
         r = N.sgd_step(params, grads, bufs, lr, momentum, weight_decay)
         if r is not NotImplemented:
             return
+        _fell("sgd_step")
     for p, g, u in zip(params, grads, bufs):
         g = g.to(p.dtype)
         if weight_decay != 0:
@@ -716,6 +832,7 @@ def unscale_and_check(grads, inv_scale, found_inf):
         r = N.unscale_and_check(grads, inv_scale, found_inf)
         if r is not NotImplemented:
             return
+        _fell("unscale_and_check")
     bad = False
     for g in grads:
         if inv_scale is not None:
@@ -732,6 +849,7 @@ def scale_grads_(grads, scale):
         r = N._grad_multi(grads, scale, None, None, 1)
         if r is not NotImplemented:
             return
+        _fell("scale_grads_")
     for g in grads:
         g.mul_(scale.to(g.dtype) if isinstance(scale, torch.Tensor) else scale)
 
@@ -742,6 +860,7 @@ def grad_norm_sq(grads, out):
         r = N.grad_norm_sq(grads, out)
         if r is not NotImplemented:
             return
+        _fell("grad_norm_sq")
     tot = sum(float(g.float().pow(2).sum()) for g in grads)
     out.add_(tot)
 
@@ -754,6 +873,7 @@ def moe_router(logits, k, renorm):
         r = N.moe_router(logits, k, renorm)
         if r is not NotImplemented:
             return r
+        _fell("moe_router")
     probs = torch.softmax(logits.float(), -1)
     w, e = torch.topk(probs, k, dim=-1, sorted=False)
     if renorm:
@@ -768,6 +888,7 @@ def moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm):
         r = N.moe_router_bwd(dweights, dprobs, probs, experts, weights, renorm)
         if r is not NotImplemented:
             return r
+        _fell("moe_router_bwd")
     idx = experts.long()
     total = torch.zeros_like(probs) if dprobs is None else dprobs.float().clone()
     if dweights is not None:
@@ -790,6 +911,7 @@ def moe_sort(experts, num_experts, align=1):
         r = N.moe_sort(experts, num_experts, align)
         if r is not NotImplemented:
             return r
+        _fell("moe_sort")
     return _moe_sort_torch(experts, num_experts, align)
 
 
@@ -799,6 +921,7 @@ def moe_sort_unpadded(experts, num_experts):
         r = N.moe_sort(experts, num_experts, 0)
         if r is not NotImplemented:
             return r
+        _fell("moe_sort_unpadded")
     return _moe_sort_torch(experts, num_experts, 1)
 
 
@@ -828,6 +951,7 @@ def gather_rows(x, rows):
         r = N.gather_rows(x, rows)
         if r is not NotImplemented:
             return r
+        _fell("gather_rows")
     rl = rows.long()
     out = x.index_select(0, rl.clamp_min(0))
     neg = rl < 0
@@ -842,6 +966,7 @@ def scatter_add_rows(src, rows, num_rows, out_dtype=None):
         r = N.scatter_add_rows(src, rows, num_rows, out_dtype)
         if r is not NotImplemented:
             return r
+        _fell("scatter_add_rows")
     out = torch.zeros(num_rows, src.shape[1], dtype=torch.float32, device=src.device)
     rl = rows.long()
     keep = rl >= 0
@@ -855,6 +980,7 @@ def moe_combine(y, w, pos):
         r = N.moe_combine(y, w, pos)
         if r is not NotImplemented:
             return r
+        _fell("moe_combine")
     T, k = w.shape
     rows = y.index_select(0, pos.reshape(-1).long()).reshape(T, k, -1)
     return (rows.float() * w.float().unsqueeze(-1)).sum(1).to(y.dtype)
@@ -866,6 +992,7 @@ def moe_combine_bwd(g, y, w, pos):
         r = N.moe_combine_bwd(g, y, w, pos)
         if r is not NotImplemented:
             return r
+        _fell("moe_combine_bwd")
     T, k = w.shape
     idx = pos.reshape(-1).long()
     rows = y.index_select(0, idx).reshape(T, k, -1)
@@ -886,6 +1013,7 @@ def grouped_linear(x, w, offsets):
         r = N.grouped_linear(x, w, offsets)
         if r is not NotImplemented:
             return r
+        _fell("grouped_linear")
     y = torch.zeros(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
     for g, s, e in _seg(offsets):
         y[s:e] = x[s:e] @ w[g].t()
@@ -898,6 +1026,7 @@ def grouped_dgrad(gy, w, offsets):
         r = N.grouped_dgrad(gy, w, offsets)
         if r is not NotImplemented:
             return r
+        _fell("grouped_dgrad")
     dx = torch.zeros(gy.shape[0], w.shape[2], dtype=gy.dtype, device=gy.device)
     for g, s, e in _seg(offsets):
         dx[s:e] = gy[s:e] @ w[g]
@@ -910,6 +1039,7 @@ def grouped_wgrad(gy, x, offsets, num_groups, out_dtype=None):
         r = N.grouped_wgrad(gy, x, offsets, num_groups, out_dtype)
         if r is not NotImplemented:
             return r
+        _fell("grouped_wgrad")
     dw = torch.zeros(num_groups, gy.shape[1], x.shape[1], dtype=torch.float32, device=gy.device)
     for g, s, e in _seg(offsets):
         dw[g] = gy[s:e].float().t() @ x[s:e].float()
@@ -921,7 +1051,7 @@ def _last_dim_call(t, dim, fn):
     """Runs `fn` on `t` with `dim` moved last (contiguous) and moves the result dims back."""
     d = dim % t.dim() if t.dim() else 0
     moved = t if d == t.dim() - 1 else t.movedim(d, -1)
-    out = fn(moved.contiguous())
+    out = fn(contiguous(moved))
     if out is NotImplemented:
         return out
     if d == t.dim() - 1:
@@ -935,6 +1065,7 @@ def sort(t, dim=-1, descending=False):
         out = _last_dim_call(t, dim, lambda x: N.sort_rows(x, x.shape[-1], descending))
         if out is not NotImplemented:
             return out
+    _fb(t, "sort")
     return tuple(torch.sort(t, dim=dim, descending=descending, stable=True))
 
 
@@ -943,21 +1074,23 @@ def topk(t, k, dim=-1, largest=True):
         out = _last_dim_call(t, dim, lambda x: N.sort_rows(x, k, largest))
         if out is not NotImplemented:
             return out
+    _fb(t, "topk")
     return tuple(torch.topk(t, k, dim=dim, largest=largest, sorted=True))
 
 
 def argmax(t, dim=None, keepdim=False, is_min=False):
     if _cuda(t) and t.numel() > 0:
         if dim is None:
-            out = N.argmax_rows(t.contiguous().reshape(-1), is_min)
+            out = N.argmax_rows(contiguous(t).reshape(-1), is_min)
             if out is not NotImplemented:
                 return out.reshape([1] * t.dim()) if keepdim else out.reshape(())
         else:
             d = dim % t.dim()
             moved = t if d == t.dim() - 1 else t.movedim(d, -1)
-            out = N.argmax_rows(moved.contiguous(), is_min)
+            out = N.argmax_rows(contiguous(moved), is_min)
             if out is not NotImplemented:
                 return out.unsqueeze(d) if keepdim else out
+    _fb(t, "argmax")
     fn = torch.argmin if is_min else torch.argmax
     return fn(t, dim=dim, keepdim=keepdim)
 
@@ -968,16 +1101,17 @@ def bincount(idx, weights=None, minlength=0):
         nbins = max(int(flat.max().item()) + 1, int(minlength))
         w = None if weights is None else weights.reshape(-1)
         if w is None or w.dtype == torch.float32:
-            out = N.bincount(flat.contiguous(), None if w is None else w.contiguous(), nbins)
+            out = N.bincount(contiguous(flat), None if w is None else contiguous(w), nbins)
             if out is not NotImplemented:
                 return out
+    _fb(flat, "bincount")
     return torch.bincount(flat.long(), weights=None if weights is None else weights.reshape(-1), minlength=minlength)
 
 
 def nonzero(t):
     """[count, ndim] int64 coordinates, row-major order."""
     if _cuda(t) and t.numel() > 0:
-        flat = N.nonzero_flat(t.contiguous())
+        flat = N.nonzero_flat(contiguous(t))
         if flat is not NotImplemented:
             if t.dim() <= 1:
                 return flat.reshape(-1, max(t.dim(), 0)) if t.dim() == 0 else flat.reshape(-1, 1)
@@ -987,14 +1121,16 @@ def nonzero(t):
                 coords.append(rem % size)
                 rem = torch.div(rem, size, rounding_mode="floor")
             return torch.stack(coords[::-1], dim=1)
+    _fb(t, "nonzero")
     return torch.nonzero(t)
 
 
 def triu_tril(t, diag, upper):
     if _cuda(t) and t.dim() >= 2:
-        out = N.triu_tril(t.contiguous(), diag, upper)
+        out = N.triu_tril(contiguous(t), diag, upper)
         if out is not NotImplemented:
             return out
+    _fb(t, "triu_tril")
     return torch.triu(t, diagonal=diag) if upper else torch.tril(t, diagonal=diag)
 
 
@@ -1003,6 +1139,7 @@ def one_hot(idx, classes, dtype=torch.int64):
         out = N.one_hot(idx.contiguous(), classes, dtype)
         if out is not NotImplemented:
             return out
+    _fb(idx, "one_hot")
     return torch.nn.functional.one_hot(idx.long(), classes).to(dtype)
 
 
@@ -1014,6 +1151,8 @@ def arange(start, end, step, dtype, device):
         out = N.arange(start, step, n, dtype, dev)
         if out is not NotImplemented:
             return out
+    if dev.type == "cuda" and n > 0:
+        _fell("arange")
     return torch.arange(start, end, step, dtype=dtype, device=dev)
 
 
@@ -1023,4 +1162,128 @@ def repeat_interleave(t, repeats, dim=None):
         out = N.repeat_interleave(src.contiguous(), repeats, d)
         if out is not NotImplemented:
             return out
+    _fb(t, "repeat_interleave")
     return torch.repeat_interleave(t, repeats, dim=dim)
+
+
+# ================================== indexing engine ==============================
+def cat(tensors, dim=0):
+    tensors = list(tensors)
+    if tensors and tensors[0].is_cuda:
+        live = [t for t in tensors if not (t.dim() == 1 and t.numel() == 0)]     # torch skips legacy empty tensors
+        if live and all(t.is_cuda and t.dtype == live[0].dtype for t in live):
+            out = N.cat([contiguous(t) for t in live], dim)
+            if out is not NotImplemented:
+                return out
+        _fell("cat")
+    return torch.cat(tensors, dim)
+
+
+def stack(tensors, dim=0):
+    tensors = list(tensors)
+    if tensors and tensors[0].is_cuda and all(t.shape == tensors[0].shape for t in tensors):
+        d = dim % (tensors[0].dim() + 1)
+        out = cat([t.unsqueeze(d) for t in tensors], d)
+        return out
+    return torch.stack(tensors, dim)
+
+
+def _index_tensor(index, device):
+    if index.device != device:
+        index = index.to(device)
+    return index if index.dtype in (torch.int32, torch.int64) else index.long()
+
+
+def gather(a, dim, index):
+    if a.is_cuda:
+        out = N.gather_dim(a, dim, _index_tensor(index, a.device))
+        if out is not NotImplemented:
+            return out
+        _fell("gather")
+    return torch.gather(a, dim, index.long())
+
+
+def scatter(a, dim, index, src, add=False):
+    """Out of place: a copy of `a` with `src` (tensor or scalar) scattered (or scatter-added) along `dim`."""
+    if a.is_cuda:
+        out = clone(a)
+        s = src
+        if isinstance(s, torch.Tensor) and s.dtype != a.dtype:
+            s = to_dtype(s, a.dtype)
+        r = N.scatter_dim_(out, dim, _index_tensor(index, a.device), s, add)
+        if r is not NotImplemented:
+            return out
+        _fell("scatter_add" if add else "scatter")
+    if add:
+        return a.scatter_add(dim, index.long(), src)
+    return a.scatter(dim, index.long(), src)
+
+
+def scatter_(a, dim, index, src):
+    """In place `a.scatter_(dim, index, src)`."""
+    if a.is_cuda:
+        s = src
+        if isinstance(s, torch.Tensor) and s.dtype != a.dtype:
+            s = to_dtype(s, a.dtype)
+        if N.scatter_dim_(a, dim, _index_tensor(index, a.device), s, False) is not NotImplemented:
+            return a
+        _fell("scatter")
+    return a.scatter_(dim, index.long(), src)
+
+
+def scatter_add_into_zeros(shape, dim, index, src):
+    """zeros(shape).scatter_add_(dim, index, src): the gradient of `gather` / `topk`."""
+    if src.is_cuda:
+        out = torch.empty(shape, dtype=src.dtype, device=src.device)
+        zero_(out)
+        r = N.scatter_dim_(out, dim, _index_tensor(index, src.device), src, True)
+        if r is not NotImplemented:
+            return out
+        _fell("scatter_add")
+    out = torch.zeros(shape, dtype=src.dtype, device=src.device)
+    return out.scatter_add_(dim, index.long(), src)
+
+
+def getitem(a, index):
+    if a.is_cuda:
+        from . import indexing
+        out = indexing.getitem(a, index)
+        if out is not NotImplemented:
+            return out
+        _fell("getitem")
+    return a[index]
+
+
+def setitem_(a, index, value):
+    """`a[index] = value` in place."""
+    if a.is_cuda:
+        from . import indexing
+        if indexing.setitem_(a, index, value) is not NotImplemented:
+            return a
+        _fell("setitem")
+    a[index] = value
+    return a
+
+
+def getitem_backward(shape, index, g):
+    if g.is_cuda:
+        from . import indexing
+        out = indexing.getitem_backward(shape, index, g)
+        if out is not NotImplemented:
+            return out
+        _fell("getitem_backward")
+    out = torch.zeros(shape, dtype=g.dtype, device=g.device)
+    items = index if isinstance(index, tuple) else (index,)
+    if not any(isinstance(i, (torch.Tensor, list)) for i in items):
+        out[index] = g
+    elif all(isinstance(i, torch.Tensor) for i in items):
+        out.index_put_(tuple(i if i.dtype == torch.bool else i.long() for i in items), g, accumulate=True)
+    else:
+        lin = torch.arange(out.numel(), device=out.device).reshape(out.shape)[index]
+        out.reshape(-1).index_add_(0, lin.reshape(-1), g.reshape(-1).to(out.dtype))
+    return out
+
+
+def zeros(shape, dtype, device):
+    out = torch.empty(shape, dtype=dtype, device=device)
+    return zero_(out) if out.is_cuda else out.zero_()

@@ -59,6 +59,12 @@ _SIGS = {
     "gb_bincount": "pippli" + "p", "gb_nonzero_count": "ppli" + "p", "gb_nonzero_write": "pppli" + "p",
     "gb_triu_tril": "ppl" + "iiiii" + "p", "gb_one_hot": "pip" + "lii" + "p", "gb_arange": "pl" + "dd" + "i" + "p",
     "gb_repeat_interleave": "pp" + "lll" + "ii" + "p",
+    "gb_cat": "ppp" + "i" + "p" + "ll" + "i" + "p",
+    "gb_gather_dim": "ppp" + "ii" + "ppp" + "l" + "ii" + "pp",
+    "gb_scatter_dim": "ppp" + "d" + "ii" + "ii" + "pppp" + "l" + "ii" + "pp",
+    "gb_index_get": "pp" + "ppp" + "i" + "pp",
+    "gb_index_put": "pp" + "d" + "ii" + "ppp" + "i" + "pp",
+    "gb_masked_fill": "pp" + "d" + "ll" + "i" + "p", "gb_fill_elems": "pldip",
 }
 
 _L = None
@@ -311,6 +317,10 @@ def cast(t, dtype):
 
 def fill_(t, value):
     if not _ok(t):
+        # integers, bool, float64 and unaligned float tensors: the element-wise fill
+        if t.is_contiguous() and t.dtype in _DT:
+            _chk(lib().gb_fill_elems(t.data_ptr(), t.numel(), float(value), _DT[t.dtype], _st()), "fill_elems")
+            return t
         return NotImplemented
     _chk(lib().gb_fill(t.data_ptr(), t.numel(), float(value), _DT[t.dtype], _st()), "fill")
     return t
@@ -1395,3 +1405,175 @@ def repeat_interleave(x, rep, dim):
     _chk(lib().gb_repeat_interleave(x.data_ptr(), out.data_ptr(), outer, x.shape[dim], inner, rep, x.element_size(),
                                     _st()), "repeat_interleave")
     return out
+
+
+# ================================== indexing engine ==============================
+_ELEM_DT = {F32: 0, F16: 1, BF16: 2, torch.float64: 3, torch.int32: 4, torch.int64: 5, torch.uint8: 6, torch.bool: 7}
+_IDX_DT = (torch.int32, torch.int64)
+
+
+def _ll(vals, n):
+    vals = list(vals)
+    return (ctypes.c_longlong * n)(*(vals + [0] * (n - len(vals))))
+
+
+def cat(tensors, dim):
+    """Concatenation of contiguous tensors along `dim` in one launch per 8 inputs (tiled copies, widest element the
+    alignment allows)."""
+    ref = tensors[0]
+    nd = ref.dim()
+    if nd == 0 or any(t.dtype != ref.dtype or t.dim() != nd or not t.is_contiguous() for t in tensors):
+        return NotImplemented
+    dim = dim % nd
+    shape = list(ref.shape)
+    for t in tensors:
+        if any(t.shape[d] != shape[d] for d in range(nd) if d != dim):
+            return NotImplemented
+    shape[dim] = sum(t.shape[dim] for t in tensors)
+    out = torch.empty(shape, dtype=ref.dtype, device=ref.device)
+    if out.numel() == 0:
+        return out
+    outer = 1
+    for s_ in shape[:dim]:
+        outer *= s_
+    tail = 1
+    for s_ in shape[dim + 1:]:
+        tail *= s_
+    es = ref.element_size()
+    inner = [t.shape[dim] * tail for t in tensors]
+    offs, pos = [], 0
+    for n in inner:
+        offs.append(pos)
+        pos += n
+    out_inner = pos
+    # widen the element while every row start stays aligned
+    for wide in (16, 8, 4, 2):
+        if wide <= es or wide % es:
+            continue
+        f = wide // es
+        if all(n % f == 0 for n in inner) and all(o % f == 0 for o in offs) and out_inner % f == 0 \
+                and out.data_ptr() % wide == 0 and all(t.data_ptr() % wide == 0 for t in tensors):
+            inner = [n // f for n in inner]
+            offs = [o // f for o in offs]
+            out_inner //= f
+            es = wide
+            break
+    live = [(t, n, o) for t, n, o in zip(tensors, inner, offs) if n > 0]
+    L = lib()
+    for i in range(0, len(live), 8):
+        chunk = live[i:i + 8]
+        ptrs = (ctypes.c_void_p * len(chunk))(*[t.data_ptr() for t, _, _ in chunk])
+        _chk(L.gb_cat(ptrs, _ll([n for _, n, _ in chunk], 8), _ll([o for _, _, o in chunk], 8), len(chunk),
+                      out.data_ptr(), outer, out_inner, es, _st()), "cat")
+    return out
+
+
+def gather_dim(src, dim, index):
+    nd = src.dim()
+    if nd == 0 or nd > 6 or index.dim() != nd or index.dtype not in _IDX_DT or src.element_size() not in (1, 2, 4, 8):
+        return NotImplemented
+    dim = dim % nd
+    out = torch.empty(index.shape, dtype=src.dtype, device=src.device)
+    if out.numel() == 0:
+        return out
+    _chk(lib().gb_gather_dim(src.data_ptr(), index.data_ptr(), out.data_ptr(), nd, dim, _ll(index.shape, 6),
+                             _ll(src.stride(), 6), _ll(index.stride(), 6), src.shape[dim],
+                             1 if index.dtype == torch.int64 else 0, src.element_size(),
+                             status_tensor(src.device).data_ptr(), _st()), "gather_dim")
+    return out
+
+
+def scatter_dim_(dst, dim, index, src, add):
+    """dst scattered along `dim` in place from tensor or scalar `src`; `add` accumulates (atomics)."""
+    nd = dst.dim()
+    if nd == 0 or nd > 6 or index.dim() != nd or index.dtype not in _IDX_DT or dst.dtype not in _ELEM_DT:
+        return NotImplemented
+    if dst.dtype in (torch.uint8, torch.bool):
+        return NotImplemented
+    dim = dim % nd
+    scalar = not isinstance(src, torch.Tensor)
+    if not scalar and (src.dtype != dst.dtype or src.dim() != nd
+                       or any(src.shape[d] < index.shape[d] for d in range(nd))):
+        return NotImplemented
+    if index.numel() == 0:
+        return dst
+    _chk(lib().gb_scatter_dim(dst.data_ptr(), index.data_ptr(), None if scalar else src.data_ptr(),
+                              float(src) if scalar else 0.0, 1 if scalar else 0, 1 if add else 0, nd, dim,
+                              _ll(index.shape, 6), _ll(dst.stride(), 6), _ll([0] * nd if scalar else src.stride(), 6),
+                              _ll(index.stride(), 6), dst.shape[dim], 1 if index.dtype == torch.int64 else 0,
+                              _ELEM_DT[dst.dtype], status_tensor(dst.device).data_ptr(), _st()), "scatter_dim")
+    return dst
+
+
+def _index_args(data, dims, idx, bshape, pre, post):
+    """ctypes blocks of `gb_index_get / gb_index_put` (see csrc/indexing.cu): `dims` the indexed dims of `data`,
+    `idx` their index tensors (broadcastable to `bshape`), `pre` / `post` the dims of `data` before / after."""
+    nb = len(bshape)
+    meta = (ctypes.c_int * 8)(len(idx), nb, len(pre), len(post), *[1 if t.dtype == torch.int64 else 0 for t in idx])
+    d = [0] * 40
+    for k, (dm, t) in enumerate(zip(dims, idx)):
+        d[k] = data.shape[dm]
+        d[4 + k] = data.stride(dm)
+        te = t.expand(bshape)
+        for b in range(nb):
+            d[24 + 4 * k + b] = te.stride(b)
+    for b, n in enumerate(bshape):
+        d[8 + b] = n
+    for j, dm in enumerate(pre):
+        d[12 + j], d[15 + j] = data.shape[dm], data.stride(dm)
+    for j, dm in enumerate(post):
+        d[18 + j], d[21 + j] = data.shape[dm], data.stride(dm)
+    ptrs = (ctypes.c_void_p * 4)(*([t.data_ptr() for t in idx] + [None] * (4 - len(idx))))
+    return ptrs, meta, (ctypes.c_longlong * 40)(*d)
+
+
+def index_get(data, dims, idx, bshape, pre, post):
+    """out[pre, bshape, post] (contiguous) = data indexed by tensors `idx` on dims `dims`."""
+    if data.element_size() not in (1, 2, 4, 8) or len(idx) > 4 or len(bshape) > 4 or len(pre) > 3 or len(post) > 3 \
+            or any(t.dtype not in _IDX_DT for t in idx):
+        return NotImplemented
+    shape = [data.shape[d] for d in pre] + list(bshape) + [data.shape[d] for d in post]
+    out = torch.empty(shape, dtype=data.dtype, device=data.device)
+    if out.numel() == 0:
+        return out
+    ptrs, meta, dd = _index_args(data, dims, idx, bshape, pre, post)
+    _chk(lib().gb_index_get(data.data_ptr(), out.data_ptr(), ptrs, meta, dd, data.element_size(),
+                            status_tensor(data.device).data_ptr(), _st()), "index_get")
+    return out
+
+
+def index_put_(data, dims, idx, bshape, pre, post, val, add):
+    """data[...] (= | +=) val, where `val` is a scalar or a contiguous tensor of shape [pre, bshape, post]."""
+    if data.dtype not in _ELEM_DT or len(idx) > 4 or len(bshape) > 4 or len(pre) > 3 or len(post) > 3 \
+            or any(t.dtype not in _IDX_DT for t in idx):
+        return NotImplemented
+    if add and data.dtype in (torch.uint8, torch.bool):
+        return NotImplemented
+    scalar = not isinstance(val, torch.Tensor)
+    if not scalar and (val.dtype != data.dtype or not val.is_contiguous()):
+        return NotImplemented
+    n = 1
+    for s_ in [data.shape[d] for d in pre] + list(bshape) + [data.shape[d] for d in post]:
+        n *= s_
+    if n == 0:
+        return data
+    if not scalar and val.numel() != n:
+        return NotImplemented
+    ptrs, meta, dd = _index_args(data, dims, idx, bshape, pre, post)
+    _chk(lib().gb_index_put(data.data_ptr(), None if scalar else val.data_ptr(), float(val) if scalar else 0.0,
+                            1 if scalar else 0, 1 if add else 0, ptrs, meta, dd, _ELEM_DT[data.dtype],
+                            status_tensor(data.device).data_ptr(), _st()), "index_put")
+    return data
+
+
+def masked_fill_(a, mask, value):
+    """a[mask] = value in place; `mask` (bool, contiguous) covers the leading dims of contiguous `a`."""
+    if a.dtype not in _ELEM_DT or not a.is_contiguous() or mask.dtype != torch.bool or not mask.is_contiguous() \
+            or tuple(a.shape[:mask.dim()]) != tuple(mask.shape):
+        return NotImplemented
+    rows = mask.numel()
+    inner = a.numel() // rows if rows else 0
+    if a.numel():
+        _chk(lib().gb_masked_fill(a.data_ptr(), mask.data_ptr(), float(value), rows, inner, _ELEM_DT[a.dtype], _st()),
+             "masked_fill")
+    return a
