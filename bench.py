@@ -209,6 +209,20 @@ def run_ours(args):
     ms_e2e, last_loss = time_steps(torch, step_e2e, args.steps, max(1, args.warmup // 2), world)
     native.check_status()
     tokens_per_step = B * S * world
+    moe = None
+    if args.moe == "on" or (args.moe == "auto" and world == 8 and args.model == "qwen2.5-0.5b"):
+        # second half of the headline metric ("MoE EP tokens/sec"): the Qwen3-MoE-shaped decoder, expert parallel over
+        # all ranks, in the same job; its 24 layers need the expert shards of 8 GPUs (`--moe-layers` for fewer)
+        del graphed, model, net, opt, dev_batches
+        import gc
+        gc.collect()
+        genesis.cuda.empty_cache()
+        from benchmarks import bench_moe
+        from genesis_b200.parallel import ep as ep_mod
+        ep_mod.profile_comm(True)
+        layers = args.moe_layers or (24 if world >= 8 else (6 if world >= 2 else 2))
+        moe = bench_moe.run(bench_moe.parse(["--steps", str(max(3, args.steps // 2)), "--warmup", "3",
+                                             "--layers", str(layers)]), init_group=False)
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -230,6 +244,9 @@ def run_ours(args):
         # time x clock: steadier than ms alone on a part that sits at its power cap
         "ms_x_ghz": None if not clocks or not clocks.get("sm_mhz") else ms * clocks["sm_mhz"] / 1e3,
         "allocator": "native pool" if genesis.cuda.pool.is_installed() else "torch",
+        "moe_ep": None if moe is None else {"value": moe["value"], "unit": "tokens/s", "ms_per_step": moe["ms_per_step"],
+                                            "steps": moe["steps"], "config": moe["config"], "comm": moe["comm"],
+                                            "clocks": moe["clocks"], "loss": moe["loss"]},
         "impl": "genesis_b200",
     }
 
@@ -337,6 +354,10 @@ def main():
     ap.add_argument("--no-shadows", action="store_true",
                     help="convert the fp32 weights to the compute dtype every step instead of keeping copies current")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--moe", default="auto", choices=["auto", "on", "off"],
+                    help="also time the expert-parallel Qwen3-MoE-shaped model and report it as `moe_ep` "
+                         "(auto: on 8 GPUs, where its 24 layers fit)")
+    ap.add_argument("--moe-layers", type=int, default=0, help="layers of the MoE model (default 24 on 8 GPUs)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.gpus > 1 and world == 1:

@@ -19,7 +19,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
-def main():
+def parse(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
@@ -29,7 +29,12 @@ def main():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nccl"])
     ap.add_argument("--kernels", type=int, default=0, help="also list the N kernels with the most device time of one step")
-    args = ap.parse_args()
+    return ap.parse_args(argv)
+
+
+def run(args, init_group=True):
+    """One timed run; returns the result dict on rank 0 (None elsewhere).  `init_group=False`: the caller owns the
+    process group (bench.py runs this after its dense model inside one job)."""
     os.environ["GENESIS_COMM"] = args.transport
 
     import numpy as np
@@ -40,10 +45,11 @@ def main():
     from genesis_b200.models.transformers import MoEForCausalLM, get_moe_config
     from genesis_b200.ops import native
     from genesis_b200.parallel.ep import EPGroup, mark_expert_parameters
+    from genesis_b200.parallel import ep as ep_mod
 
     rank, world, local = dist_env(args)
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and init_group:
         dist.init_process_group(backend="nccl")
     cfg = get_moe_config("qwen3-moe-bench")
     cfg.num_hidden_layers = args.layers
@@ -94,19 +100,28 @@ def main():
     if world > 1:
         from genesis_b200.distributed import symm
         symm.check_status("moe step")
-        dist.destroy_process_group()
+        if init_group:
+            dist.destroy_process_group()
+    comm = ep_mod.comm_profile() if world > 1 else None
     if rank != 0:
-        return
+        return None
     n_params = sum(p._t.numel() for p in model.parameters())
-    print(json.dumps({
+    return {
         "metric": "MoE EP tokens/sec (box, max over ranks)", "value": B * S * world / (ms / 1e3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "config": {"model": "qwen3-moe-bench", "layers": args.layers, "experts": args.experts, "top_k": 8,
                    "global_batch": B * world, "seq_len": S, "parallelism": f"ep{world} x dp{world}",
                    "transport": args.transport, "params_per_rank": n_params},
-        "clocks": clocks, "loss": loss, "kernels": kernels, "gpu_launches": native.launch_count // (args.steps + args.warmup) * args.steps,
-    }), flush=True)
+        "clocks": clocks, "loss": loss, "kernels": kernels, "comm": comm,
+        "gpu_launches": native.launch_count // (args.steps + args.warmup) * args.steps,
+    }
+
+
+def main():
+    out = run(parse())
+    if out is not None:
+        print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":

@@ -52,8 +52,9 @@ def nonzero(a, as_tuple=False):
 
 
 def allclose(a, b, rtol=1e-5, atol=1e-8, equal_nan=False):
-    return bool(torch.allclose(a._t.float(), b._t.float().to(a._t.device), rtol=rtol, atol=atol,
-                               equal_nan=equal_nan))
+    # a 0-d bool tensor, as in the reference (`functional.py:191-216`): `if allclose(..)` and `.item()` both work
+    return _w(torch.tensor(bool(torch.allclose(a._t.float(), b._t.float().to(a._t.device), rtol=rtol, atol=atol,
+                                               equal_nan=equal_nan)), device=a._t.device))
 
 
 def _cmp(name):

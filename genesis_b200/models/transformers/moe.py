@@ -128,6 +128,8 @@ class MoEExpert(Module):
 
     def __init__(self, hidden_size, intermediate_size, bias=False):
         super().__init__()
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.silu = nn.SiLU()
         self.gate_proj = nn.Linear(hidden_size, intermediate_size, bias=bias)
         self.up_proj = nn.Linear(hidden_size, intermediate_size, bias=bias)
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=bias)
@@ -392,7 +394,8 @@ class MoEDecoderLayer(Module):
         super().__init__()
         self.hidden_size, self.layer_idx = config.hidden_size, layer_idx
         self.self_attn = MoEAttention(config, layer_idx)
-        if self._is_moe_layer(layer_idx, config):
+        self.is_moe_layer = self._is_moe_layer(layer_idx, config)
+        if self.is_moe_layer:
             self.mlp = MoELayer(config.hidden_size, config.num_local_experts, config.num_experts_per_tok,
                                 config.moe_intermediate_size, config.num_shared_experts,
                                 config.shared_expert_intermediate_size, config.router_aux_loss_coef,

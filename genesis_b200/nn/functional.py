@@ -1375,6 +1375,8 @@ def permute(a, dims):
 
 
 def transpose(a, dim0=None, dim1=None, axis=None):
+    if isinstance(dim0, (tuple, list)) and dim1 is None and axis is None:     # transpose(x, (d0, d1))
+        axis = tuple(dim0)
     if axis is not None:
         dim0, dim1 = axis
     if dim0 is None:
@@ -1455,6 +1457,7 @@ def scatter_add(input, dim, index, src):
 
 
 def topk(input, k, dim=-1, largest=True, sorted=True):
+    k = builtins.min(int(k), input.shape[dim]) if input.ndim else 1       # never more elements than exist
     return TopKFunction.apply(input, k, dim, largest, sorted)
 
 

@@ -125,6 +125,53 @@ def _stage_rows(rows, buf, sh, H):
 
 p2p_layers_run = 0      # forward passes that took the peer-memory transport (tests assert on it)
 
+# Optional device timing of the pull kernels (CUDA events around every dispatch / combine launch, forward and
+# backward): `profile_comm(True)` switches it on, `comm_profile()` reads it back.
+_prof = {"on": False, "events": []}
+
+
+def profile_comm(on=True):
+    _prof["on"] = bool(on)
+    _prof["events"] = []
+
+
+class _Timed:
+    def __init__(self, kind, nbytes):
+        self.kind, self.nbytes = kind, nbytes
+
+    def __enter__(self):
+        if _prof["on"]:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e1 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _prof["on"]:
+            self.e1.record()
+            _prof["events"].append((self.kind, self.nbytes, self.e0, self.e1))
+        return False
+
+
+def comm_profile(link_gbs=900.0):
+    """Per-call device time of the dispatch / combine pull kernels since `profile_comm(True)`, the bytes each call
+    moves over NVLink into this rank ((W - 1) / W of the rows for a balanced router) and the fraction of the link
+    bound (bytes / `link_gbs`) that time represents.  Synchronises."""
+    if not _prof["events"]:
+        return None
+    torch.cuda.synchronize()
+    out = {}
+    for kind in ("dispatch", "combine"):
+        ev = [(b, e0.elapsed_time(e1)) for k, b, e0, e1 in _prof["events"] if k == kind]
+        if not ev:
+            continue
+        ms = sorted(t for _, t in ev)[len(ev) // 2]
+        nb = ev[0][0]
+        bound_ms = nb / (link_gbs * 1e9) * 1e3
+        out[kind] = {"calls": len(ev), "ms_per_call_median": ms, "nvlink_bytes_per_call": nb,
+                     "bound_ms_at_%d_gbs" % int(link_gbs): bound_ms, "fraction_of_bound": bound_ms / ms if ms else None}
+    return out
+
 
 def _p2p_usable(x):
     from ..distributed import symm
@@ -171,10 +218,14 @@ class EPDispatchPull(Function):
                               seg_start.data_ptr(), seg_src.data_ptr(), dest_base.data_ptr(), info.data_ptr(),
                               st.status.data_ptr(), N._st()), "ep_layout")
         xe = torch.empty(cap, H, dtype=x.dtype, device=dev)     # rows past the layout's end stay unwritten
+        remote = T * k * H * x.element_size() * (W - 1) // W       # bytes a balanced router sends over NVLink
+        sh_timer = _Timed("dispatch", remote)
+        sh_timer.__enter__()
         N._chk(L.gb_ep_dispatch_pull(_ws.x.ptr_table, _ws.tok.ptr_table, None, st.flags.ptr_table, all_off.data_ptr(),
                                      local_offsets.data_ptr(), seg_start.data_ptr(), seg_src.data_ptr(), xe.data_ptr(),
                                      None, None, H, st.rank, W, E, cap, 0, symm.next_epoch(), N._DT[x.dtype], _CTAS,
                                      N._comm_budget(), st.status.data_ptr(), N._st()), "ep_dispatch_pull")
+        sh_timer.__exit__()
         shared.update(token_of=token_of, pos=pos, offsets=offsets, all_off=all_off, local_offsets=local_offsets,
                       seg_start=seg_start, seg_src=seg_src, dest_base=dest_base, T=T, k=k, H=H)
         ctx.shared = shared

@@ -251,11 +251,26 @@ class Tensor:
     def __index__(self):
         return int(self._t.item())
 
-    def all(self):
-        return bool(self._t.all().item())
+    def all(self, dim=None, keepdim=False):
+        """Whether all elements are non-zero: a bool tensor (0-d without `dim`; `bool(x.all())` works).
+        Parity: reference `genesis/tensor.py:565-600`."""
+        t = self._t if self._t.dtype == torch.bool else (self._t != 0)
+        if dim is None:
+            return Tensor._wrap(t.all())
+        dims = (dim,) if isinstance(dim, int) else tuple(dim)
+        for d in sorted((x % t.dim() for x in dims), reverse=True):
+            t = t.all(dim=d, keepdim=keepdim)
+        return Tensor._wrap(t)
 
-    def any(self):
-        return bool(self._t.any().item())
+    def any(self, dim=None, keepdim=False):
+        """Whether any element is non-zero (see `all`).  Parity: reference `genesis/tensor.py:611-635`."""
+        t = self._t if self._t.dtype == torch.bool else (self._t != 0)
+        if dim is None:
+            return Tensor._wrap(t.any())
+        dims = (dim,) if isinstance(dim, int) else tuple(dim)
+        for d in sorted((x % t.dim() for x in dims), reverse=True):
+            t = t.any(dim=d, keepdim=keepdim)
+        return Tensor._wrap(t)
 
     def __hash__(self):
         return id(self)
