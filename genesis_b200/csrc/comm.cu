@@ -117,6 +117,108 @@ allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, 
   epoch_publish(epoch_ctr, epoch);
 }
 
+// Low-precision wire format: the gradients cross NVLink as 16-bit values (half the bytes of the fp32 form) and leave
+// the kernel as float32 master gradients, the bf16/fp16 -> fp32 cast being the kernel's last phase:
+//   barrier A   every rank's 16-bit bucket is complete
+//   reduce      rank r pulls slice r of all W buckets (16-byte loads of 8 values), accumulates in fp32, multiplies by
+//               prescale (1/world; NOT yet by 1/loss_scale, so fp16 values keep their scaled range), checks Inf/NaN,
+//               rounds to 16 bits and stores the result into slice r of every rank's bucket
+//   barrier B   all slices of the local bucket are final
+//   cast        the whole local bucket -> `out` (float32, local memory) times 1/loss_scale
+template <typename T>
+__global__ void __launch_bounds__(256, 3)
+allreduce_wire_kernel(PeerTable bufs, PeerTable flags, long long n, float* __restrict__ out, int rank, int world,
+                      uint32_t epoch, float prescale, const float* __restrict__ loss_scale, int scale_is_reciprocal,
+                      float* __restrict__ found_inf, unsigned long long budget_ns, int* __restrict__ status,
+                      uint32_t* __restrict__ epoch_ctr) {
+  __shared__ int s_fail;
+  __shared__ int s_bad;
+  constexpr int V = Vec16<T>::N;                       // 8 values per 16-byte vector
+  if (threadIdx.x == 0) { s_fail = 0; s_bad = 0; }
+  if (epoch_ctr != nullptr) epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ctr) + 1;
+  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) {
+    epoch_publish(epoch_ctr, epoch);
+    return;
+  }
+  const long long nvec = n / V;                        // n is padded by the caller to world * V
+  const long long per = nvec / world;
+  const long long v0 = (long long)rank * per, v1 = (rank == world - 1) ? nvec : v0 + per;
+  bool bad = false;
+  constexpr int UNR = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * UNR) {
+    float acc[UNR][V];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u)
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[u][j] = 0.f;
+    for (int p = 0; p < world; ++p) {
+      const int src = (rank + p) % world;
+      const T* base = reinterpret_cast<const T*>(bufs.ptr[src]);
+      uint4 raw[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) raw[u] = ld_volatile_v4(base + i * V);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        if (i0 + u * stride < v1) {
+          const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[u][j] += Cvt<T>::to_f(e[j]);
+        }
+      }
+    }
+    Vec16<T> o[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float r = acc[u][j] * prescale;
+        if (!isfinite(r) && (i0 + u * stride < v1)) bad = true;
+        o[u].v[j] = Cvt<T>::from_f(r);
+      }
+    for (int p = 0; p < world; ++p) {
+      const int dst = (rank + p) % world;
+      T* base = reinterpret_cast<T*>(bufs.ptr[dst]);
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) st16(base + i * V, o[u]);
+      }
+    }
+  }
+  if (bad) s_bad = 1;
+  __syncthreads();
+  if (s_bad && threadIdx.x < world && found_inf != nullptr)
+    st_release_sys(reinterpret_cast<uint32_t*>(flags.ptr[threadIdx.x]) + COMM_FOUND_SLOT, epoch);
+  if (!peer_barrier(flags, rank, world, 1, epoch, budget_ns, status, &s_fail)) {
+    epoch_publish(epoch_ctr, epoch);
+    return;
+  }
+  if (found_inf != nullptr && threadIdx.x == 0) {
+    if (ld_acquire_sys(reinterpret_cast<const uint32_t*>(flags.ptr[rank]) + COMM_FOUND_SLOT) == epoch)
+      *found_inf = 1.f;
+  }
+  // cast phase: peers wrote their slices with plain stores that barrier B made visible; read them past L1
+  float inv = 1.f;
+  if (loss_scale != nullptr) inv = scale_is_reciprocal ? 1.f / *loss_scale : *loss_scale;
+  const T* mine = reinterpret_cast<const T*>(bufs.ptr[rank]);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const uint4 raw = ld_volatile_v4(mine + i * V);
+    const T* e = reinterpret_cast<const T*>(&raw);
+    float4 lo, hi;
+    lo.x = Cvt<T>::to_f(e[0]) * inv; lo.y = Cvt<T>::to_f(e[1]) * inv;
+    lo.z = Cvt<T>::to_f(e[2]) * inv; lo.w = Cvt<T>::to_f(e[3]) * inv;
+    hi.x = Cvt<T>::to_f(e[4]) * inv; hi.y = Cvt<T>::to_f(e[5]) * inv;
+    hi.z = Cvt<T>::to_f(e[6]) * inv; hi.w = Cvt<T>::to_f(e[7]) * inv;
+    *reinterpret_cast<float4*>(out + i * V) = lo;
+    *reinterpret_cast<float4*>(out + i * V + 4) = hi;
+  }
+  epoch_publish(epoch_ctr, epoch);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Pull-style data movement: all-gather, broadcast and all-to-all are the same kernel.  Every rank has
 // staged what it sends in its symmetric buffer and publishes, per destination rank, where that rank's
@@ -267,6 +369,30 @@ extern "C" int gb_allreduce_fused(void* const* bufs, void* const* flags, long lo
                                                     loss_scale, scale_is_reciprocal, found_inf, budget_ns, status,
                                                     epoch_ctr);
   });
+  return (int)cudaGetLastError();
+}
+
+// 16-bit wire form: `bufs` are the ranks' 16-bit buckets (n elements from their start, n a multiple of world * 8),
+// `out` this rank's float32 gradient buffer (n elements, 16-byte aligned).  dt: DT_F16 / DT_BF16.
+extern "C" int gb_allreduce_wire(void* const* bufs, void* const* flags, long long n, float* out, int rank, int world,
+                                 unsigned int epoch, float prescale, const float* loss_scale,
+                                 int scale_is_reciprocal, float* found_inf, int dt, int ctas,
+                                 unsigned long long budget_ns, int* status, unsigned int* epoch_ctr,
+                                 cudaStream_t st) {
+  if (world > COMM_MAX_WORLD || world < 1) return -2;
+  if (dt != DT_F16 && dt != DT_BF16) return -4;
+  if (n % (world * 8) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0) return -3;
+  if (ctas > COMM_MAX_CTAS) ctas = COMM_MAX_CTAS;
+  if (ctas < 1) ctas = 1;
+  PeerTable tb, tf;
+  for (int i = 0; i < world; ++i) { tb.ptr[i] = bufs[i]; tf.ptr[i] = flags[i]; }
+  if (dt == DT_BF16)
+    allreduce_wire_kernel<__nv_bfloat16><<<ctas, 256, 0, st>>>(tb, tf, n, out, rank, world, epoch, prescale,
+                                                               loss_scale, scale_is_reciprocal, found_inf, budget_ns,
+                                                               status, epoch_ctr);
+  else
+    allreduce_wire_kernel<__half><<<ctas, 256, 0, st>>>(tb, tf, n, out, rank, world, epoch, prescale, loss_scale,
+                                                        scale_is_reciprocal, found_inf, budget_ns, status, epoch_ctr);
   return (int)cudaGetLastError();
 }
 

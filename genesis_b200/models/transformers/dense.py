@@ -59,7 +59,10 @@ class FeedForward(nn.Module):
 
     def forward(self, x):
         # gate and up projections as one GEMM over the stacked weights; SwiGLU reads the two halves in place
-        biases = [self.gate_proj.bias, self.up_proj.bias] if self.gate_proj.bias is not None else None
+        if self.gate_proj.bias is None:
+            # ... and with no biases the activation rides in that GEMM's epilogue
+            return self.down_proj(F.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight))
+        biases = [self.gate_proj.bias, self.up_proj.bias]
         return self.down_proj(F.swiglu_fused(F.fused_linear(x, [self.gate_proj.weight, self.up_proj.weight], biases)))
 
 

@@ -1665,6 +1665,51 @@ def swiglu_fused(gate_up):
     return SwiGLUFusedFunction.apply(gate_up)
 
 
+class LinearSwiGLUFunction(Function):
+    """h = silu(x @ Wg^T) * (x @ Wu^T) as one node: the gate and up projections run as ONE GEMM over the stacked
+    weights whose epilogue applies the activation (`K.linear_swiglu`), so the [tokens, 2 I] intermediate is written
+    once (kept for backward) and never read back in the forward pass.  Backward: d(gate | up) from one SwiGLU-backward
+    pass, then one data-gradient and one weight-gradient GEMM for both projections.
+    Reference counterparts: `nn/modules/transformer.py` FeedFowardSwiGLU, `nn/triton_ops/silu.py:29-85`."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_up, compute_dtype):
+        cd = compute_dtype if compute_dtype is not None else w_gate.dtype
+        W = _fused_params([w_gate, w_up], cd)
+        if x.dtype != cd:
+            x = K.to_dtype(x, cd)
+        gu, h = K.linear_swiglu(x, W)
+        ctx.save_for_backward(x, W, gu)
+        ctx.meta = ([w_gate.shape[0], w_up.shape[0]], w_gate.dtype)
+        return h
+
+    @staticmethod
+    def backward(ctx, g):
+        x, W, gu = ctx.saved_tensors
+        sizes, wd = ctx.meta
+        if g.dtype != gu.dtype:
+            g = K.to_dtype(g, gu.dtype)
+        g = g if g.is_contiguous() else K.contiguous(g)
+        dgu = K.swiglu_fused_bwd(g, gu if gu.is_contiguous() else K.contiguous(gu))
+        need = ctx.needs_input_grad
+        gx = K.linear_dgrad(dgu, W) if need[0] else None
+        stacked, accumulate = _stacked_grad_slot(ctx, 1, sizes, wd, W.shape[1])
+        if stacked is not None:
+            gW = K.linear_wgrad(dgu, x, out_dtype=wd, accum=stacked if accumulate else None,
+                                out=None if accumulate else stacked)
+        else:
+            gW = K.linear_wgrad(dgu, x, out_dtype=wd)
+        return gx, _fresh_slice(gW, 0, sizes[0]), _fresh_slice(gW, sizes[0], sizes[1])
+
+
+def linear_swiglu(x, w_gate, w_up):
+    """silu(x @ w_gate^T) * (x @ w_up^T) for two bias-free projections of equal width."""
+    cd = amp_state.dtype if amp_state.enabled else None
+    return LinearSwiGLUFunction.apply(x, w_gate, w_up, cd)
+
+
 def qkv_rope(y, cos, sin, positions, num_heads, num_kv_heads, head_dim):
     return QKVRopeFunction.apply(y, cos, sin, positions, num_heads, num_kv_heads, head_dim)
 

@@ -608,6 +608,17 @@ def swiglu_fused_fwd(gu):
     return (torch.nn.functional.silu(g) * u).to(gu.dtype)
 
 
+def linear_swiglu(x, w):
+    """(gu, h) with gu = x @ w^T (w the stacked [2 I, K] gate | up weight) and h = silu(gate) * up: on CUDA one GEMM
+    on CTA pairs whose epilogue applies the activation; elsewhere the GEMM followed by the SwiGLU kernel."""
+    if x.is_cuda:
+        r = N.linear_swiglu(x, w)
+        if r is not NotImplemented:
+            return r
+    gu = linear(x, w)
+    return gu, swiglu_fused_fwd(gu if gu.is_contiguous() else contiguous(gu))
+
+
 def swiglu_fused_bwd(dy, gu):
     """-> d(gate | up) [..., 2 I]."""
     if gu.is_cuda:

@@ -47,7 +47,9 @@ _SIGS = {
     "gb_router_fwd": "ppppp" + "liiiip", "gb_router_bwd": "pppppp" + "liiiip",
     "gb_moe_sort": "pppppp" + "liiilp", "gb_moe_combine": "pppp" + "liiip", "gb_moe_combine_bwd": "pppppp" + "liiip",
     "gb_gemm": "pppp" + "iiii" + "ll" + "i" + "lll" + "ii" + "iii" + "i" + "f" + "i" + "p" + "i" + "ii" + "p" + "i" + "p",
+    "gb_gemm_pair": "ppppp" + "iii" + "ll" + "ii" + "ii" + "iii" + "i" + "f" + "ii" + "pp",
     "gb_allreduce_fused": "ppllii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "ppp",
+    "gb_allreduce_wire": "pplpii" + "I" + "f" + "p" + "i" + "p" + "ii" + "u" + "ppp",
     "gb_wait_flag": "pIupp",
     "gb_peer_pull": "pppppp" + "ii" + "I" + "i" + "u" + "pp",
     "gb_peer_reduce_scatter": "ppp" + "lii" + "I" + "f" + "ii" + "u" + "pp",
@@ -546,6 +548,63 @@ def _plan(M, N, K, es, can_split, sms):
     return bn, 1
 
 
+pair_mode = os.environ.get("GENESIS_GEMM_PAIR", "auto")     # "auto" | "0" (never) | "1" (whenever the kernel applies)
+
+
+def _pair_width(M, N, K, sms, a_mn=0, b_mn=0):
+    """256 when the CTA-pair kernel (256 x 256 tiles on SM pairs) is expected to beat the single-CTA kernel for this
+    problem, else 0.  Measured on the model's shapes: the pair kernel wins by 2-9 % on K-major x K-major products with
+    many tiles (the forward projections, where operand traffic into the SMs bounds the 128 x 256 tile), loses on
+    MN-major operands (data / weight gradients) and on very wide outputs (the vocabulary projection), and narrower
+    pair tiles never pay."""
+    if pair_mode == "0":
+        return 0
+    if pair_mode == "1":
+        return 256
+    if a_mn or b_mn or M < 2048 or N < 768 or N > 32768:
+        return 0
+    tiles = -(-M // 256) * -(-N // 256)
+    return 256 if tiles >= 2 * (sms // 2) else 0
+
+
+def gemm_pair(a2, a_mn, lda, b2, b_mn, ldb, M, N, K, out, bias, accumulate, alpha, bn):
+    """Launch of the CTA-pair kernel on classified operands (see `_operand`).  Returns False when it does not apply."""
+    if a2.element_size() != 2 or out.data_ptr() % 16 or (N * out.element_size()) % 16 or (K * 2) % 16:
+        return False
+    if accumulate and out.dtype != F32:
+        return False
+    if b_mn and bn == 192:
+        bn = 256
+    rc = lib().gb_gemm_pair(a2.data_ptr(), b2.data_ptr(), out.data_ptr(), None,
+                            None if bias is None else bias.data_ptr(), M, N, K, lda, ldb, N, 0, a_mn, b_mn,
+                            _GEMM_DT[a2.dtype], _GEMM_DT[out.dtype], 0 if bias is None else _GEMM_DT[bias.dtype],
+                            1 if accumulate else 0, float(alpha), 0, bn, status_tensor(a2.device).data_ptr(), _st())
+    _chk(rc, "gemm_pair")
+    return True
+
+
+def linear_swiglu(x, w, want_gu=True):
+    """(gu, h): gu = x @ w^T with w the stacked [2 I, K] gate | up weight, h = silu(gu[:, :I]) * gu[:, I:], from ONE
+    GEMM whose epilogue applies the activation (CTA-pair kernel, csrc/gemm2_sm100.cu).  `NotImplemented` when the
+    shape does not fit (I a multiple of 128, 16-bit contiguous operands)."""
+    if x.dtype not in (F16, BF16) or w.dtype != x.dtype or w.dim() != 2 or not w.is_contiguous() or pair_mode == "0":
+        return NotImplemented
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    M, K = x2.shape
+    I2 = w.shape[0]
+    if I2 % 256 or (K * 2) % 16 or not x2.is_contiguous() or x2.data_ptr() % 16 or w.data_ptr() % 16 or M == 0:
+        return NotImplemented
+    I = I2 // 2
+    gu = torch.empty(M, I2, dtype=x.dtype, device=x.device) if want_gu else None
+    h = torch.empty(M, I, dtype=x.dtype, device=x.device)
+    rc = lib().gb_gemm_pair(x2.data_ptr(), w.data_ptr(), None if gu is None else gu.data_ptr(), h.data_ptr(), None,
+                            M, I, K, K, K, I2, I, 0, 0, _GEMM_DT[x.dtype], _GEMM_DT[x.dtype], 0, 0, 1.0, 1, 256,
+                            status_tensor(x.device).data_ptr(), _st())
+    _chk(rc, "gemm_pair(swiglu)")
+    return (None if gu is None else gu.reshape(*lead, I2)), h.reshape(*lead, I)
+
+
 def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0, out=None):
     """D[M, N] = a[M, K] @ b_t[N, K]^T for 2-D operands in any of the supported layouts.
     `a` / `b_t` may be transposed views (stride(0) == 1); misaligned ones are repacked.
@@ -580,6 +639,10 @@ def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0, out=None):
     bn, splits = _plan(M, N, K, a.element_size(), out.dtype == F32 and bias is None, sms)
     if plan_override is not None:
         bn, splits = plan_override
+    elif splits == 1 and a.element_size() == 2:
+        pbn = _pair_width(M, N, K, sms, a_mn, b_mn)
+        if pbn and gemm_pair(a2, a_mn, lda, b2, b_mn, ldb, M, N, K, out, bias, accum is not None, alpha, pbn):
+            return out
     if splits < 0 and (out.data_ptr() % 16 or (N * out.element_size()) % 16):
         splits = 1                     # the add path of the epilogue needs a 16-byte aligned output
     if splits != 1 and accum is None:
@@ -1226,6 +1289,25 @@ def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None,
                                   st.status.data_ptr(), None if ctr is None else ctr.data_ptr(), _st()),
          "allreduce_fused")
     return True
+
+
+def allreduce_wire(st, buf, n, dtype, out, inv_scale=None, found_inf=None, prescale=1.0, scale_is_reciprocal=True,
+                   ctas=None, budget_ms=None):
+    """All-reduce of the ranks' 16-bit buckets `buf` (symmetric, `n` elements of `dtype`) into the float32 tensor
+    `out`: 16-bit values on the wire, fp32 accumulation, `prescale`, overflow check, and the cast to float32 times
+    1/loss-scale as the kernel's last phase (see csrc/comm.cu)."""
+    ctr = getattr(st, "epoch_dev", None)
+    epoch = 0 if ctr is not None else st.next_epoch()
+    budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000) if budget_ms is None else budget_ms) * 1e6)
+    if ctas is None:
+        per_rank_vecs = n * 2 // 16 // max(st.world, 1)
+        ctas = max(1, min(int(os.environ.get("GENESIS_COMM_CTAS", 128)), (per_rank_vecs + 1023) // 1024))
+    _chk(lib().gb_allreduce_wire(buf.ptr_table, st.flags.ptr_table, n, out.data_ptr(), st.rank, st.world, epoch,
+                                 float(prescale), None if inv_scale is None else inv_scale.data_ptr(),
+                                 1 if scale_is_reciprocal else 0,
+                                 None if found_inf is None else found_inf.data_ptr(), _DT[dtype], ctas, budget,
+                                 st.status.data_ptr(), None if ctr is None else ctr.data_ptr(), _st()),
+         "allreduce_wire")
 
 
 def _comm_budget():

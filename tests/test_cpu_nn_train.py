@@ -496,3 +496,18 @@ def test_low_precision_copies_kept_by_the_optimizer_change_nothing_but_the_casts
     finally:
         ob.disable_shadows()
     assert not any(e.param is p for p in mb.parameters() for e in A.shadows.values())
+
+
+def test_linear_swiglu_matches_separate_layers_on_cpu():
+    g = np.random.RandomState(0)
+    x = genesis.tensor(g.randn(6, 8).astype(np.float32), requires_grad=True)
+    wg = genesis.tensor(g.randn(12, 8).astype(np.float32) * 0.3, requires_grad=True)
+    wu = genesis.tensor(g.randn(12, 8).astype(np.float32) * 0.3, requires_grad=True)
+    h = F.linear_swiglu(x, wg, wu)
+    F.sum(h * h).backward()
+    tx, tg, tu = (torch.tensor(t.detach().numpy(), requires_grad=True) for t in (x, wg, wu))
+    th = torch.nn.functional.silu(tx @ tg.t()) * (tx @ tu.t())
+    (th * th).sum().backward()
+    np.testing.assert_allclose(h.detach().numpy(), th.detach().numpy(), rtol=1e-5, atol=1e-6)
+    for a, b in ((x, tx), (wg, tg), (wu, tu)):
+        np.testing.assert_allclose(a.grad.numpy(), b.grad.numpy(), rtol=1e-4, atol=1e-5)

@@ -131,3 +131,91 @@ def test_forced_tile_and_split_plans_agree(plan, M, N_, K_):
         native.plan_override = None
     check(got, ref, torch.bfloat16, K_ / 16)
     check(acc, ref - 1.5, torch.bfloat16, K_ / 16)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CTA-pair kernel (csrc/gemm2_sm100.cu): tcgen05.mma.cta_group::2 on clusters of two CTAs
+# ---------------------------------------------------------------------------------------------------------
+def _pair(a, b_t, out_dtype=None, bias=None, accum=None, bn=256):
+    M, K_ = a.shape
+    a2, a_mn, lda = N._operand(a, True)
+    b2, b_mn, ldb = N._operand(b_t, True)
+    out = accum if accum is not None else torch.empty(M, b_t.shape[0], dtype=out_dtype or a.dtype, device=a.device)
+    assert N.gemm_pair(a2, a_mn, lda, b2, b_mn, ldb, M, b_t.shape[0], K_, out, bias, accum is not None, 1.0, bn)
+    return out
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N_,K_,bn", [(256, 256, 64, 256), (512, 512, 896, 256), (384, 320, 200, 256),
+                                         (1024, 896, 896, 128), (1024, 1152, 896, 192), (300, 136, 72, 128),
+                                         (2048, 4864, 896, 256), (130, 264, 520, 192)])
+def test_pair_gemm_shapes(dt, M, N_, K_, bn):
+    a, b = rnd(M, K_, dt=dt), rnd(N_, K_, dt=dt, seed=1)
+    got = _pair(a.to(DEV), b.to(DEV), bn=bn)
+    check(got, a.float() @ b.float().t(), dt, K_)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 1), (1, 0), (1, 1)])
+def test_pair_gemm_layouts_and_epilogues(a_mn, b_mn):
+    M, N_, K_ = 768, 640, 448
+    a, b, bias = rnd(M, K_, dt=torch.float16), rnd(N_, K_, dt=torch.float16, seed=1), rnd(N_, seed=2)
+    ref = a.float() @ b.float().t()
+    ac = a.to(DEV).t().contiguous().t() if a_mn else a.to(DEV)
+    bc = b.to(DEV).t().contiguous().t() if b_mn else b.to(DEV)
+    check(_pair(ac, bc, bn=128 if b_mn else 192), ref, torch.float16, K_)
+    check(_pair(ac, bc, out_dtype=torch.float32, bias=bias.to(DEV)), ref + bias, torch.float16, K_)
+    acc = torch.ones(M, N_, device=DEV)
+    check(_pair(ac, bc, accum=acc), ref + 1.0, torch.float16, K_)
+
+
+@pytest.mark.parametrize("M,I,K_", [(256, 128, 64), (512, 256, 896), (1000, 384, 200), (2048, 4864, 896)])
+def test_pair_gemm_swiglu_epilogue(M, I, K_):
+    x = rnd(M, K_, dt=torch.bfloat16)
+    w = (rnd(2 * I, K_, seed=1) * 0.2).bfloat16()
+    gu_ref = x.float() @ w.float().t()
+    h_ref = torch.nn.functional.silu(gu_ref[:, :I]) * gu_ref[:, I:]
+    gu, h = N.linear_swiglu(x.to(DEV), w.to(DEV))
+    check(gu, gu_ref, torch.bfloat16, K_)
+    check(h, h_ref, torch.bfloat16, K_)
+    _, h2 = N.linear_swiglu(x.to(DEV), w.to(DEV), want_gu=False)
+    assert torch.equal(h, h2)
+
+
+def test_linear_swiglu_function_matches_the_unfused_layers():
+    import genesis_b200 as genesis
+    import genesis_b200.nn.functional as F
+    T, H, I = 512, 256, 384
+    g = torch.Generator().manual_seed(3)
+    x0 = torch.randn(T, H, generator=g)
+    wg0, wu0 = torch.randn(I, H, generator=g) * 0.1, torch.randn(I, H, generator=g) * 0.1
+    dy = torch.randn(T, I, generator=g).to(DEV)
+
+    def run(fused):
+        x = genesis.Tensor(x0.clone().to(DEV), requires_grad=True)
+        wg = genesis.Tensor(wg0.clone().to(DEV), requires_grad=True)
+        wu = genesis.Tensor(wu0.clone().to(DEV), requires_grad=True)
+        with genesis.amp.autocast(dtype=genesis.bfloat16):
+            h = F.linear_swiglu(x, wg, wu) if fused else F.swiglu(F.linear(x, wg), F.linear(x, wu))
+        (h * genesis.Tensor(dy.to(h._t.dtype))).sum().backward()
+        return h._t.float(), x.grad._t.float(), wg.grad._t.float(), wu.grad._t.float()
+
+    K.reset_fallbacks()
+    with K.strict_native(True):
+        a = run(True)
+    b = run(False)
+    for u, v in zip(a, b):
+        torch.testing.assert_close(u, v, atol=3e-2 * max(1.0, float(v.abs().max())), rtol=3e-2)
+    # fp32 reference for the forward value
+    ref = torch.nn.functional.silu(x0 @ wg0.t()) * (x0 @ wu0.t())
+    torch.testing.assert_close(a[0].cpu(), ref, atol=0.05, rtol=0.05)
+    assert K.fallback_counts() == {}
+
+
+def test_gemm_routes_large_16_bit_shapes_to_the_pair_kernel():
+    before = N.launch_count
+    a, b = rnd(4096, 896, dt=torch.bfloat16).to(DEV), rnd(4864, 896, dt=torch.bfloat16, seed=1).to(DEV)
+    assert N._pair_width(4096, 4864, 896, N._sms(a.device)) == 256
+    assert N._pair_width(4096, 4864, 896, N._sms(a.device), b_mn=1) == 0
+    got = N.gemm(a, b)
+    check(got, a.float().cpu() @ b.float().cpu().t(), torch.bfloat16, 896)
+    assert N.launch_count == before + 1
