@@ -134,9 +134,12 @@ def run_ours(args):
     B, S = args.micro_batch, args.seq_len
     genesis.manual_seed(1234)
     model = QwenForCausalLM(cfg).cuda()
-    net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
-    opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
     amp_dtype = genesis.bfloat16 if args.dtype == "bf16" else genesis.float16
+    # gradients cross NVLink in the compute dtype (accumulated and handed back in float32) unless --grad-wire fp32
+    wire = None if args.grad_wire == "fp32" else amp_dtype
+    net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_dtype=wire) \
+        if world > 1 else model
+    opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
     if not args.no_shadows:
         # the optimizer kernel keeps the compute-dtype copies of the weights current (q/k/v and gate/up stacked), so
         # autocast converts no parameter during the step
@@ -175,12 +178,18 @@ def run_ours(args):
     K.reset_fallbacks()
     graphed = None
     if not args.no_graph and (world == 1 or getattr(net, "_use_symm", False)):
-        try:
-            graphed = genesis.cuda.GraphedTrainStep(lambda t: train_step(t._t), opt,
-                                                    [genesis.Tensor(dev_batches[0])], warmup=3)
-        except Exception as e:                                   # keep the run; the JSON line says which path ran
-            print(f"[bench] CUDA-graph capture failed, running eagerly: {type(e).__name__}: {e}", file=sys.stderr)
-            graphed = None
+        for attempt in range(2):
+            try:
+                graphed = genesis.cuda.GraphedTrainStep(lambda t: train_step(t._t), opt,
+                                                        [genesis.Tensor(dev_batches[0])], warmup=3)
+                break
+            except Exception as e:                               # keep the run; the JSON line says which path ran
+                import traceback
+                traceback.print_exc(file=sys.stderr)
+                print(f"[bench] CUDA-graph capture failed (attempt {attempt + 1}): {type(e).__name__}: {e}",
+                      file=sys.stderr)
+                graphed = None
+                torch.cuda.synchronize()
 
     def step_device():
         counter["i"] += 1
@@ -233,7 +242,8 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": args.dtype, "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "config": {"model": args.model, "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
-                   "optimizer": "AdamW lr 3e-4", "cuda_graph": graphed is not None, "weight_copies": "kept by optimizer" if not args.no_shadows else "cast per step", "l2_policy": "working set (~20 GB activations+grads per step) >> 126 MB L2; "
+                   "optimizer": "AdamW lr 3e-4", "cuda_graph": graphed is not None,
+                   "grad_wire": None if world == 1 else ("fp32" if wire is None else args.dtype), "weight_copies": "kept by optimizer" if not args.no_shadows else "cast per step", "l2_policy": "working set (~20 GB activations+grads per step) >> 126 MB L2; "
                    "4 distinct input batches rotated"},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -354,6 +364,8 @@ def main():
     ap.add_argument("--no-shadows", action="store_true",
                     help="convert the fp32 weights to the compute dtype every step instead of keeping copies current")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--grad-wire", default="16bit", choices=["16bit", "fp32"],
+                    help="format of the gradients on NVLink under data parallelism (float32 results either way)")
     ap.add_argument("--moe", default="auto", choices=["auto", "on", "off"],
                     help="also time the expert-parallel Qwen3-MoE-shaped model and report it as `moe_ep` "
                          "(auto: on 8 GPUs, where its 24 layers fit)")

@@ -117,17 +117,18 @@ allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, 
   epoch_publish(epoch_ctr, epoch);
 }
 
-// Low-precision wire format: the gradients cross NVLink as 16-bit values (half the bytes of the fp32 form) and leave
-// the kernel as float32 master gradients, the bf16/fp16 -> fp32 cast being the kernel's last phase:
-//   barrier A   every rank's 16-bit bucket is complete
-//   reduce      rank r pulls slice r of all W buckets (16-byte loads of 8 values), accumulates in fp32, multiplies by
+// Low-precision wire format: the gradients cross NVLink as 16-bit values (half the bytes of the fp32 form) while the
+// caller keeps float32 gradients; both casts are phases of this kernel:
+//   pack        local float32 bucket `grad` -> this rank's 16-bit symmetric buffer (round to nearest)
+//   barrier A   every rank's 16-bit buffer is complete
+//   reduce      rank r pulls slice r of all W buffers (16-byte loads of 8 values), accumulates in fp32, multiplies by
 //               prescale (1/world; NOT yet by 1/loss_scale, so fp16 values keep their scaled range), checks Inf/NaN,
-//               rounds to 16 bits and stores the result into slice r of every rank's bucket
-//   barrier B   all slices of the local bucket are final
-//   cast        the whole local bucket -> `out` (float32, local memory) times 1/loss_scale
+//               rounds to 16 bits and stores the result into slice r of every rank's buffer
+//   barrier B   all slices of the local buffer are final
+//   cast        the whole local 16-bit buffer -> `grad` (float32, in place) times 1/loss_scale
 template <typename T>
 __global__ void __launch_bounds__(256, 3)
-allreduce_wire_kernel(PeerTable bufs, PeerTable flags, long long n, float* __restrict__ out, int rank, int world,
+allreduce_wire_kernel(PeerTable bufs, PeerTable flags, long long n, float* __restrict__ grad, int rank, int world,
                       uint32_t epoch, float prescale, const float* __restrict__ loss_scale, int scale_is_reciprocal,
                       float* __restrict__ found_inf, unsigned long long budget_ns, int* __restrict__ status,
                       uint32_t* __restrict__ epoch_ctr) {
@@ -136,16 +137,29 @@ allreduce_wire_kernel(PeerTable bufs, PeerTable flags, long long n, float* __res
   constexpr int V = Vec16<T>::N;                       // 8 values per 16-byte vector
   if (threadIdx.x == 0) { s_fail = 0; s_bad = 0; }
   if (epoch_ctr != nullptr) epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ctr) + 1;
+  const long long nvec = n / V;                        // n is padded by the caller to world * V
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  {
+    // pack phase (the barrier's system-scope fence and release publish these stores to the peers)
+    T* mine = reinterpret_cast<T*>(bufs.ptr[rank]);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+      const float4 lo = *reinterpret_cast<const float4*>(grad + i * V);
+      const float4 hi = *reinterpret_cast<const float4*>(grad + i * V + 4);
+      Vec16<T> o;
+      o.v[0] = Cvt<T>::from_f(lo.x); o.v[1] = Cvt<T>::from_f(lo.y); o.v[2] = Cvt<T>::from_f(lo.z);
+      o.v[3] = Cvt<T>::from_f(lo.w); o.v[4] = Cvt<T>::from_f(hi.x); o.v[5] = Cvt<T>::from_f(hi.y);
+      o.v[6] = Cvt<T>::from_f(hi.z); o.v[7] = Cvt<T>::from_f(hi.w);
+      st16(mine + i * V, o);
+    }
+  }
   if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) {
     epoch_publish(epoch_ctr, epoch);
     return;
   }
-  const long long nvec = n / V;                        // n is padded by the caller to world * V
   const long long per = nvec / world;
   const long long v0 = (long long)rank * per, v1 = (rank == world - 1) ? nvec : v0 + per;
   bool bad = false;
   constexpr int UNR = 4;
-  const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * UNR) {
     float acc[UNR][V];
 #pragma unroll
@@ -213,8 +227,8 @@ allreduce_wire_kernel(PeerTable bufs, PeerTable flags, long long n, float* __res
     lo.z = Cvt<T>::to_f(e[2]) * inv; lo.w = Cvt<T>::to_f(e[3]) * inv;
     hi.x = Cvt<T>::to_f(e[4]) * inv; hi.y = Cvt<T>::to_f(e[5]) * inv;
     hi.z = Cvt<T>::to_f(e[6]) * inv; hi.w = Cvt<T>::to_f(e[7]) * inv;
-    *reinterpret_cast<float4*>(out + i * V) = lo;
-    *reinterpret_cast<float4*>(out + i * V + 4) = hi;
+    *reinterpret_cast<float4*>(grad + i * V) = lo;
+    *reinterpret_cast<float4*>(grad + i * V + 4) = hi;
   }
   epoch_publish(epoch_ctr, epoch);
 }
@@ -372,8 +386,8 @@ extern "C" int gb_allreduce_fused(void* const* bufs, void* const* flags, long lo
   return (int)cudaGetLastError();
 }
 
-// 16-bit wire form: `bufs` are the ranks' 16-bit buckets (n elements from their start, n a multiple of world * 8),
-// `out` this rank's float32 gradient buffer (n elements, 16-byte aligned).  dt: DT_F16 / DT_BF16.
+// 16-bit wire form: `out` is this rank's float32 gradient bucket (n elements, 16-byte aligned; reduced in place),
+// `bufs` the ranks' 16-bit symmetric staging buffers of n elements (n a multiple of world * 8).  dt: DT_F16 / DT_BF16.
 extern "C" int gb_allreduce_wire(void* const* bufs, void* const* flags, long long n, float* out, int rank, int world,
                                  unsigned int epoch, float prescale, const float* loss_scale,
                                  int scale_is_reciprocal, float* found_inf, int dt, int ctas,

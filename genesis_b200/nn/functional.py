@@ -511,7 +511,7 @@ class LinearFunction(Function):
                 # the weight is a leaf with a preallocated gradient slot (a DDP bucket view): the GEMM writes or
                 # accumulates there, and the engine recognises the slot instead of copying into it
                 buf, accumulate = slot
-                gw = K.linear_wgrad(g, x, out_dtype=wd, accum=buf if accumulate else None,
+                gw = K.linear_wgrad(g, x, out_dtype=buf.dtype, accum=buf if accumulate else None,
                                     out=None if accumulate else buf)
         gb = None
         if bd is not None and len(need) > 2 and need[2]:
@@ -531,7 +531,8 @@ def _grad_slot(ctx, i, dtype, shape):
     if leaf is None or leaf._grad_buf is None or leaf._hooks:
         return None
     buf = leaf._grad_buf
-    if buf.dtype != dtype or not buf.is_contiguous() or tuple(buf.shape) != tuple(shape):
+    # (the slot may be narrower than the parameter: DDP's 16-bit wire format; the GEMM then writes that dtype)
+    if not buf.dtype.is_floating_point or not buf.is_contiguous() or tuple(buf.shape) != tuple(shape):
         return None
     if leaf.grad is None:
         return buf, False
@@ -550,6 +551,9 @@ def _stacked_grad_slot(ctx, first, sizes, dtype, cols):
             return None, False
         slots.append(sl)
     es = slots[0][0].element_size()
+    if len({sl[0].dtype for sl in slots}) != 1:
+        return None, False
+    dtype = slots[0][0].dtype
     for (a, _), (b, _) in zip(slots, slots[1:]):
         if a.data_ptr() + a.numel() * es != b.data_ptr() or a.untyped_storage().data_ptr() != b.untyped_storage().data_ptr():
             return None, False
@@ -1578,7 +1582,7 @@ class FusedLinearFunction(Function):
         stacked, accumulate = _stacked_grad_slot(ctx, 1, sizes, wd, W.shape[1])
         if stacked is not None:
             # the members' gradient slots (DDP bucket views) are adjacent in stacking order: one store into the bucket
-            gW = K.linear_wgrad(g, x, out_dtype=wd, accum=stacked if accumulate else None,
+            gW = K.linear_wgrad(g, x, out_dtype=stacked.dtype, accum=stacked if accumulate else None,
                                 out=None if accumulate else stacked)
         else:
             gW = K.linear_wgrad(g, x, out_dtype=wd)
@@ -1697,7 +1701,7 @@ class LinearSwiGLUFunction(Function):
         gx = K.linear_dgrad(dgu, W) if need[0] else None
         stacked, accumulate = _stacked_grad_slot(ctx, 1, sizes, wd, W.shape[1])
         if stacked is not None:
-            gW = K.linear_wgrad(dgu, x, out_dtype=wd, accum=stacked if accumulate else None,
+            gW = K.linear_wgrad(dgu, x, out_dtype=stacked.dtype, accum=stacked if accumulate else None,
                                 out=None if accumulate else stacked)
         else:
             gW = K.linear_wgrad(dgu, x, out_dtype=wd)

@@ -34,7 +34,7 @@ from .modules.module import Module
 
 class _Bucket:
     __slots__ = ("index", "params", "offsets", "numel", "dtype", "flat", "symm_buf", "pending", "launched",
-                 "ready_event")
+                 "ready_event", "wire", "wire_dtype")
 
     def __init__(self, index, dtype):
         self.index, self.dtype = index, dtype
@@ -42,6 +42,8 @@ class _Bucket:
         self.numel = 0
         self.flat = None
         self.symm_buf = None
+        self.wire = None            # 16-bit view of the symmetric buffer when gradients cross NVLink in 16 bits
+        self.wire_dtype = None
         self.pending = 0
         self.launched = False
         self.ready_event = None
@@ -50,7 +52,7 @@ class _Bucket:
 class DistributedDataParallel(Module):
     def __init__(self, model, device_ids=None, output_device=None, broadcast_buffers=True,
                  find_unused_parameters=False, gradient_as_bucket_view=False, bucket_cap_mb=None,
-                 grad_scaler=None):
+                 grad_scaler=None, gradient_dtype=None):
         super().__init__()
         if not pg.is_initialized():
             raise RuntimeError("Process group not initialized. Call genesis.distributed.init_process_group() first")
@@ -67,6 +69,19 @@ class DistributedDataParallel(Module):
                                           else os.environ.get("GENESIS_DDP_BUCKET_MB", 25)) * 1024 * 1024)
         self._sync = True
         self._scaler = grad_scaler
+        # 16-bit wire format (`gradient_dtype="bfloat16"` / "float16", or GENESIS_DDP_GRAD_DTYPE): gradients stay
+        # float32 in local buckets; the all-reduce kernel packs them to 16 bits, moves half the bytes over NVLink,
+        # accumulates in float32 and casts the result back into the float32 bucket (both casts are phases of the
+        # kernel).  Needs the peer-memory transport and float32 parameters.
+        gd = gradient_dtype if gradient_dtype is not None else os.environ.get("GENESIS_DDP_GRAD_DTYPE") or None
+        if gd is not None:
+            from ..dtypes import get_dtype
+            gd = get_dtype(gd).torch_dtype
+            if gd == torch.float32:
+                gd = None
+            elif gd not in (torch.bfloat16, torch.float16):
+                raise ValueError("gradient_dtype must be float32, bfloat16 or float16")
+        self._wire_dtype = gd
         self._buckets = []
         self._param_bucket = {}
         self._next_launch = 0
@@ -78,6 +93,9 @@ class DistributedDataParallel(Module):
         # (rank 0 writing a checkpoint or running an evaluation while the others have already launched backward),
         # so the budget is far longer than that of the blocking collectives; NCCL would wait without any limit.
         self._budget_ms = float(os.environ.get("GENESIS_DDP_TIMEOUT_MS", 120000))
+        # measurement switches: "skip" launches no all-reduce at all (compute time of the data-parallel layout; the
+        # ranks diverge), "serial" reduces every bucket after backward (compute + communication with no overlap)
+        self._debug_comm = os.environ.get("GENESIS_DDP_DEBUG_COMM", "")
         all_params = [p for p in model.parameters() if p.requires_grad]
         # expert-parallel shards are not replicated: no all-reduce, only the 1/world factor
         self._sharded = [p for p in all_params if getattr(p, "_no_ddp", False)]
@@ -164,10 +182,18 @@ class DistributedDataParallel(Module):
             # flag page of the communication stream (collective allocation: do it here); epochs counted on the
             # device so that a captured training step can be replayed
             symm.channel("ddp").use_device_epochs()
+        if self._wire_dtype is not None and not self._use_symm:
+            self._wire_dtype = None                     # NCCL / gloo transport: gradients stay in the parameter dtype
         for b in self._buckets:
             esz = torch.empty(0, dtype=b.dtype).element_size()
             pad = (b.numel + 1023) // 1024 * 1024          # slices stay 16-byte aligned for any world size <= 64
-            if self._use_symm:
+            wire = self._wire_dtype if b.dtype == torch.float32 else None
+            if wire is not None:
+                b.wire_dtype = wire
+                b.symm_buf = symm.alloc(pad * 2)
+                b.wire = b.symm_buf.view(wire, 0, pad)
+                b.flat = torch.zeros(pad, dtype=b.dtype, device=b.params[0]._t.device)
+            elif self._use_symm:
                 b.symm_buf = symm.alloc(pad * esz)
                 b.flat = b.symm_buf.view(b.dtype, 0, pad)
             else:
@@ -191,6 +217,8 @@ class DistributedDataParallel(Module):
         return hook
 
     def _launch_ready(self):
+        if self._debug_comm == "serial":
+            return                            # every bucket is reduced at the end of backward (no overlap)
         while self._next_launch < len(self._buckets):
             b = self._buckets[self._next_launch]
             if b.pending != 0:
@@ -201,6 +229,8 @@ class DistributedDataParallel(Module):
     def _reduce_bucket(self, b):
         b.launched = True
         scaler = self._scaler
+        if self._debug_comm == "skip":
+            return
         if self._on_cuda:
             st = self._comm_stream
             if b.ready_event is not None:
@@ -214,9 +244,14 @@ class DistributedDataParallel(Module):
                     if scaler is not None and scaler.is_enabled():
                         scaler._lazy_init(b.flat.device)
                         inv, found = scaler._scale, scaler._found_inf
-                    N.allreduce_fused(symm.channel("ddp"), b.symm_buf, 0, b.flat.numel(), b.dtype, b.flat,
-                                      inv_scale=inv, found_inf=found, prescale=1.0 / self.world_size,
-                                      scale_is_reciprocal=True, budget_ms=self._budget_ms)
+                    if b.wire is not None:
+                        N.allreduce_wire(symm.channel("ddp"), b.symm_buf, b.wire.numel(), b.wire_dtype, b.flat,
+                                         inv_scale=inv, found_inf=found, prescale=1.0 / self.world_size,
+                                         scale_is_reciprocal=True, budget_ms=self._budget_ms)
+                    else:
+                        N.allreduce_fused(symm.channel("ddp"), b.symm_buf, 0, b.flat.numel(), b.dtype, b.flat,
+                                          inv_scale=inv, found_inf=found, prescale=1.0 / self.world_size,
+                                          scale_is_reciprocal=True, budget_ms=self._budget_ms)
                 else:
                     tdist.all_reduce(b.flat)
                     b.flat.mul_(1.0 / self.world_size)

@@ -1295,6 +1295,20 @@ def getitem_backward(shape, index, g):
     return out
 
 
+def index_add_rows_(acc, rows, idx):
+    """acc[idx[i], :] += rows[i, :] in place for any float accumulator dtype (atomic adds).  False: not available."""
+    if not acc.is_cuda:
+        return False
+    flat = idx.reshape(-1)
+    r2 = rows.reshape(-1, acc.shape[1])
+    if r2.dtype != acc.dtype:
+        r2 = to_dtype(r2, acc.dtype)
+    r2 = contiguous(r2)
+    flat = flat if flat.dtype in (torch.int32, torch.int64) else flat.long()
+    r = N.index_put_(acc, [0], [contiguous(flat)], (flat.numel(),), [], [1], r2, add=True)
+    return r is not NotImplemented
+
+
 def zeros(shape, dtype, device):
     out = torch.empty(shape, dtype=dtype, device=device)
     return zero_(out) if out.is_cuda else out.zero_()

@@ -1293,9 +1293,9 @@ def allreduce_fused(st, buf, offset_elems, n, dtype, local_view, inv_scale=None,
 
 def allreduce_wire(st, buf, n, dtype, out, inv_scale=None, found_inf=None, prescale=1.0, scale_is_reciprocal=True,
                    ctas=None, budget_ms=None):
-    """All-reduce of the ranks' 16-bit buckets `buf` (symmetric, `n` elements of `dtype`) into the float32 tensor
-    `out`: 16-bit values on the wire, fp32 accumulation, `prescale`, overflow check, and the cast to float32 times
-    1/loss-scale as the kernel's last phase (see csrc/comm.cu)."""
+    """In-place all-reduce of the float32 bucket `out` with 16-bit values on the wire: the kernel packs `out` into
+    this rank's symmetric 16-bit buffer `buf` (`n` elements of `dtype`), reduces across ranks with fp32 accumulation,
+    `prescale` and the overflow check, and casts the result back into `out` times 1/loss-scale (see csrc/comm.cu)."""
     ctr = getattr(st, "epoch_dev", None)
     epoch = 0 if ctr is not None else st.next_epoch()
     budget = int(float(os.environ.get("GENESIS_COMM_TIMEOUT_MS", 10000) if budget_ms is None else budget_ms) * 1e6)

@@ -391,6 +391,8 @@ class RowScatterGrad:
         from .ops import dispatch as K
         if acc.dtype == torch.float32 and acc.is_contiguous() and acc.dim() == 2:
             K.embedding_bwd_into(acc, self.rows, self.idx)
+        elif acc.is_cuda and acc.is_contiguous() and acc.dim() == 2 and K.index_add_rows_(acc, self.rows, self.idx):
+            pass                                   # 16-bit accumulator (a 16-bit gradient slot): atomic adds in place
         else:
             K.add_(acc, self.dense().to(acc.dtype).reshape(acc.shape))
 
@@ -418,13 +420,18 @@ def _accumulate_leaf(t, g, fire_post_hooks=True):
     if t._hooks:
         gw = t.apply_hooks(Tensor._wrap(g))
         g = gw._t
-    if g.dtype != t._t.dtype:
-        g = g.to(t._t.dtype)
-    if g.shape != t._t.shape:
-        g = g.reshape(t._t.shape) if g.numel() == t._t.numel() else g.sum_to_size(t._t.shape)
     from .ops import dispatch as K
     buf = t._grad_buf
-    if buf is not None and g.data_ptr() == buf.data_ptr() and g.dtype == buf.dtype:
+    in_slot = buf is not None and g.data_ptr() == buf.data_ptr() and g.dtype == buf.dtype \
+        and g.numel() == buf.numel()
+    # a preallocated slot may be narrower than the parameter (DDP's 16-bit wire format): gradients are brought to
+    # the slot's dtype, not the parameter's
+    want = buf.dtype if buf is not None and (t.grad is None or t.grad._t.data_ptr() == buf.data_ptr()) else t._t.dtype
+    if not in_slot and g.dtype != want:
+        g = K.to_dtype(g, want)
+    if g.shape != t._t.shape:
+        g = g.reshape(t._t.shape) if g.numel() == t._t.numel() else g.sum_to_size(t._t.shape)
+    if in_slot:
         # the producing kernel already wrote (or accumulated) into the preallocated slot
         if t.grad is None:
             t.grad = Tensor._wrap(buf)

@@ -313,6 +313,111 @@ def scenario_ddp_amp_clip(a):
     assert not torch.equal(model.fc1.weight._t, before)
 
 
+def scenario_ddp_wire(a):
+    """16-bit gradients on the wire (`gradient_dtype`): weight-gradient GEMMs write bf16 / fp16 into the buckets, the
+    all-reduce accumulates in float32 and returns float32 gradients that match the float32-wire result to 16-bit
+    rounding; overflow on one rank still skips the step on all ranks; a tied embedding adds its rows into the
+    16-bit slot; the step replays from a CUDA graph."""
+    from genesis_b200.models.transformers import TransformerConfig, QwenForCausalLM
+    r, w, d = dist.get_rank(), dist.get_world_size(), dev(a.backend)
+    cfg = TransformerConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                            num_attention_heads=2, num_key_value_heads=1, head_dim=64, max_position_embeddings=128,
+                            tie_word_embeddings=True)
+    rs = np.random.RandomState(100 + r)
+    tokens = torch.from_numpy(rs.randint(0, 512, (4, 65))).to(d)
+
+    def grads(gradient_dtype, amp_dtype, scaler=None):
+        genesis.manual_seed(11)
+        m = QwenForCausalLM(cfg).to(d)
+        net = nn.DistributedDataParallel(m, bucket_cap_mb=0.25, gradient_dtype=gradient_dtype, grad_scaler=scaler)
+        idx = genesis.Tensor(tokens[:, :-1].contiguous())
+        lab = genesis.Tensor(tokens[:, 1:].reshape(-1).contiguous())
+        with genesis.amp.autocast(dtype=amp_dtype):
+            loss = net(idx, labels=lab, return_logits=False)
+        (scaler.scale(loss) if scaler is not None else loss).backward()
+        torch.cuda.synchronize()
+        dist.symm.check_status("ddp wire")
+        return m, net, [p.grad._t.clone() for p in m.parameters()]
+
+    _, net32, g32 = grads(None, genesis.bfloat16)
+    mw, netw, gw = grads("bfloat16", genesis.bfloat16)
+    assert any(b.wire is not None for b in netw._buckets) and not any(b.wire is not None for b in net32._buckets)
+    for (name, p), a32, aw in zip(mw.named_parameters(), g32, gw):
+        assert aw.dtype == torch.float32 and p.grad._t.data_ptr() == p._grad_buf.data_ptr(), name
+        scale = max(float(a32.abs().max()), 1e-6)
+        assert float((a32 - aw).abs().max()) <= 2e-2 * scale + 1e-6, (name, float((a32 - aw).abs().max()), scale)
+    # every rank holds the same result
+    for gth in gw[:3]:
+        chk = gth.clone()
+        tdist.broadcast(chk, 0)
+        assert torch.equal(chk, gth)
+    # fp16 wire with a GradScaler: values travel scaled, leave the kernel unscaled; an overflow reaches all ranks
+    sc = genesis.amp.GradScaler(init_scale=256.0)
+    m16, net16, g16 = grads("float16", genesis.float16, sc)
+    for (name, p), a32, a16 in zip(m16.named_parameters(), g32, g16):
+        scale = max(float(a32.abs().max()), 1e-6)
+        assert float((a32 - a16).abs().max()) <= 3e-2 * scale + 1e-6, (name, float((a32 - a16).abs().max()), scale)
+    assert not sc.found_inf()
+    opt = genesis.optim.AdamW(m16.parameters(), lr=1e-3)
+    sc.step(opt)
+    sc.update()
+    before = m16.model.layers[0].mlp.down_proj.weight._t.clone()
+    opt.zero_grad()
+    idx = genesis.Tensor(tokens[:, :-1].contiguous())
+    lab = genesis.Tensor(tokens[:, 1:].reshape(-1).contiguous())
+    with genesis.amp.autocast(dtype=genesis.float16):
+        loss = net16(idx, labels=lab, return_logits=False)
+    if r == w - 1:
+        loss = loss * float("inf")
+    sc.scale(loss).backward()
+    sc.step(opt)
+    assert sc.found_inf(), "overflow flag did not reach this rank"
+    sc.update()
+    assert torch.equal(m16.model.layers[0].mlp.down_proj.weight._t, before), "step was not skipped"
+    # local accumulation under no_sync() stays in float32; the next synchronised step reduces the sum
+    genesis.manual_seed(11)
+    ma = QwenForCausalLM(cfg).to(d)
+    neta = nn.DistributedDataParallel(ma, bucket_cap_mb=0.25, gradient_dtype="bfloat16")
+    idx = genesis.Tensor(tokens[:, :-1].contiguous())
+    lab = genesis.Tensor(tokens[:, 1:].reshape(-1).contiguous())
+    with neta.no_sync(), genesis.amp.autocast(dtype=genesis.bfloat16):
+        neta(idx, labels=lab, return_logits=False).backward()
+    with genesis.amp.autocast(dtype=genesis.bfloat16):
+        neta(idx, labels=lab, return_logits=False).backward()
+    torch.cuda.synchronize()
+    for (name, p), a32 in zip(ma.named_parameters(), g32):
+        scale = max(float(a32.abs().max()), 1e-6)
+        assert float((2 * a32 - p.grad._t).abs().max()) <= 5e-2 * scale + 1e-6, name
+    # whole step from a CUDA graph, eager twin alongside
+    def make():
+        genesis.manual_seed(9)
+        m = QwenForCausalLM(cfg).to(d)
+        net = nn.DistributedDataParallel(m, bucket_cap_mb=0.25, gradient_dtype="bfloat16")
+        o = genesis.optim.AdamW(m.parameters(), lr=1e-3)
+
+        def step(tok):
+            i_ = genesis.Tensor(tok._t[:, :-1].contiguous())
+            l_ = genesis.Tensor(tok._t[:, 1:].reshape(-1).contiguous())
+            with genesis.amp.autocast(dtype=genesis.bfloat16):
+                ls = net(i_, labels=l_, return_logits=False)
+            o.zero_grad()
+            ls.backward()
+            o.step()
+            return ls
+        return m, o, step
+    ma, oa, step_a = make()
+    mb, ob, step_b = make()
+    batches = [genesis.Tensor(torch.from_numpy(rs.randint(0, 512, (4, 65))).to(d)) for _ in range(5)]
+    graphed = genesis.cuda.GraphedTrainStep(step_b, ob, [batches[0]], warmup=2)
+    for _ in range(2):
+        step_a(batches[0])
+    for i, t in enumerate(batches[1:]):
+        la, lb = step_a(t), graphed(t)
+        torch.cuda.synchronize()
+        assert abs(float(la._t) - float(lb._t)) < 3e-3 * max(1.0, abs(float(la._t))), (i, float(la._t), float(lb._t))
+    dist.symm.check_status("graphed ddp wire")
+
+
 def scenario_ep(a):
     """Expert-parallel MoE layer equals the single-process layer holding all experts."""
     from genesis_b200.models.transformers.moe import MoELayer

@@ -16,7 +16,7 @@ ENV = {"NCCL_NVLS_ENABLE": "0"}
 
 
 @pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("scenario", ["collectives", "ddp", "ddp_tied", "ddp_amp", "ddp_amp_clip", "ddp_graph", "ep"])
+@pytest.mark.parametrize("scenario", ["collectives", "ddp", "ddp_tied", "ddp_amp", "ddp_amp_clip", "ddp_wire", "ddp_graph", "ep"])
 def test_two_gpu_ranks(scenario):
     launch(scenario, world=2, backend="nccl", env=ENV, timeout=600)
 
@@ -27,8 +27,15 @@ def test_two_gpu_ranks_nccl_transport():
 
 
 @pytest.mark.skipif(NGPU < 4, reason="needs 4 GPUs")
-def test_four_gpu_ranks_ddp():
-    launch("ddp", world=4, backend="nccl", env=ENV, timeout=600)
+@pytest.mark.parametrize("scenario", ["ddp", "ddp_tied", "ddp_wire", "ep"])
+def test_four_gpu_ranks(scenario):
+    launch(scenario, world=4, backend="nccl", env=ENV, timeout=600)
+
+
+@pytest.mark.skipif(NGPU < 8, reason="needs 8 GPUs")
+@pytest.mark.parametrize("scenario", ["collectives", "ddp", "ddp_tied", "ddp_amp", "ddp_wire", "ddp_graph", "ep"])
+def test_eight_gpu_ranks(scenario):
+    launch(scenario, world=8, backend="nccl", env=ENV, timeout=900)
 
 
 def test_device_wait_times_out_with_status():
