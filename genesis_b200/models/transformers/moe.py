@@ -146,47 +146,49 @@ class _ExpertView:
 
     def __call__(self, x):
         o, e = self.owner, self.e
-        g = F.linear(x, o.w_gate[e])
-        u = F.linear(x, o.w_up[e])
+        I = o.intermediate_size
+        g = F.linear(x, o.w_gate_up[e][:I])
+        u = F.linear(x, o.w_gate_up[e][I:])
         return F.linear(F.swiglu(g, u), o.w_down[e])
 
 
 class GroupedExpertsFunction(Function):
     """Sorted rows through their expert's SwiGLU MLP via grouped GEMMs.
-    x [M, H] (rows sorted by expert), offsets [E+1]; weights stacked [E, I, H] / [E, H, I]."""
+    x [M, H] (rows sorted by expert), offsets [E+1]; weights stacked per expert: wgu [E, 2 I, H] (gate rows, then up
+    rows) and wd [E, H, I].  Two grouped GEMMs and one activation pass forward; four grouped GEMMs and one activation
+    pass backward (down weight gradient, down data gradient, gate|up weight gradient, gate|up data gradient).
+    `out`: optional buffer for y (the expert-parallel transport hands in its symmetric staging buffer, so the
+    outputs need no copy before the peers pull them)."""
     raw = True
     amp_policy = AMPPolicy.PRESERVE
 
     @staticmethod
-    def forward(ctx, x, wg, wu, wd, offsets, compute_dtype):
-        master = wg.dtype
+    def forward(ctx, x, wgu, wd, offsets, compute_dtype, out=None):
+        master = wgu.dtype
         if compute_dtype is not None:
             x = K.to_dtype(x, compute_dtype)
-            wg_c, wu_c, wd_c = (F._cached_param_cast(w, compute_dtype) for w in (wg, wu, wd))
+            wgu_c, wd_c = (F._cached_param_cast(w, compute_dtype) for w in (wgu, wd))
         else:
-            wg_c, wu_c, wd_c = wg, wu, wd
-        g = K.grouped_linear(x, wg_c, offsets)
-        u = K.grouped_linear(x, wu_c, offsets)
-        h = K.swiglu_fwd(g, u)
-        y = K.grouped_linear(h, wd_c, offsets)
-        ctx.save_for_backward(x, g, u, wg_c, wu_c, wd_c, offsets)
+            wgu_c, wd_c = wgu, wd
+        gu = K.grouped_linear(x, wgu_c, offsets)
+        h = K.swiglu_fused_fwd(gu)
+        y = K.grouped_linear(h, wd_c, offsets, out=out)
+        ctx.save_for_backward(x, gu, h, wgu_c, wd_c, offsets)
         ctx.master = master
         return y
 
     @staticmethod
     def backward(ctx, gy):
-        x, g, u, wg, wu, wd, offsets = ctx.saved_tensors
-        E = wg.shape[0]
+        x, gu, h, wgu, wd, offsets = ctx.saved_tensors
+        E = wgu.shape[0]
         gy = K.to_dtype(gy, x.dtype) if gy.dtype != x.dtype else gy
         gy = gy if gy.is_contiguous() else K.contiguous(gy)
-        h = K.swiglu_fwd(g, u)                              # recomputed, not stored
         dwd = K.grouped_wgrad(gy, h, offsets, E, ctx.master)
         dh = K.grouped_dgrad(gy, wd, offsets)
-        dg, du = K.swiglu_bwd(dh, g, u)
-        dwg = K.grouped_wgrad(dg, x, offsets, E, ctx.master)
-        dwu = K.grouped_wgrad(du, x, offsets, E, ctx.master)
-        dx = K.add(K.grouped_dgrad(dg, wg, offsets), K.grouped_dgrad(du, wu, offsets))
-        return dx, dwg, dwu, dwd
+        dgu = K.swiglu_fused_bwd(dh, gu)
+        dwgu = K.grouped_wgrad(dgu, x, offsets, E, ctx.master)
+        dx = K.grouped_dgrad(dgu, wgu, offsets)
+        return dx, dwgu, dwd
 
 
 class DispatchFunction(Function):
@@ -225,18 +227,26 @@ class CombineFunction(Function):
 
 
 class GroupedExperts(Module):
-    """All experts of a layer as three stacked parameters (optionally only a shard of them)."""
+    """All experts of a layer as two stacked parameters (optionally only a shard of them): `w_gate_up`
+    [E, 2 I, H] holds every expert's gate rows followed by its up rows, so both projections are one grouped GEMM;
+    `w_down` [E, H, I].  `w_gate` / `w_up` are views for reading; the state dict keeps per-expert
+    `{e}.gate_proj / up_proj / down_proj.weight` entries."""
 
     def __init__(self, num_experts, hidden_size, intermediate_size, first_expert=0, total_experts=None):
         super().__init__()
         self.num_experts, self.hidden_size, self.intermediate_size = num_experts, hidden_size, intermediate_size
         self.first_expert = first_expert
         self.total_experts = total_experts if total_experts is not None else num_experts
-        self.w_gate = Parameter(init.randn(num_experts, intermediate_size, hidden_size, std=0.02))
-        self.w_up = Parameter(init.randn(num_experts, intermediate_size, hidden_size, std=0.02))
+        self.w_gate_up = Parameter(init.randn(num_experts, 2 * intermediate_size, hidden_size, std=0.02))
         self.w_down = Parameter(init.randn(num_experts, hidden_size, intermediate_size, std=0.02))
 
-    _NAMES = (("w_gate", "gate_proj"), ("w_up", "up_proj"), ("w_down", "down_proj"))
+    @property
+    def w_gate(self):
+        return Tensor._wrap(self.w_gate_up._t[:, :self.intermediate_size])
+
+    @property
+    def w_up(self):
+        return Tensor._wrap(self.w_gate_up._t[:, self.intermediate_size:])
 
     def __len__(self):
         return self.num_experts
@@ -247,25 +257,38 @@ class GroupedExperts(Module):
     def __iter__(self):
         return (self[e] for e in range(self.num_experts))
 
-    def forward(self, x_sorted, offsets):
+    def forward(self, x_sorted, offsets, out=None):
         cd = amp_state.dtype if amp_state.enabled else None
-        return GroupedExpertsFunction.apply(x_sorted, self.w_gate, self.w_up, self.w_down,
-                                            Tensor._wrap(offsets) if isinstance(offsets, torch.Tensor) else offsets, cd)
+        return GroupedExpertsFunction.apply(x_sorted, self.w_gate_up, self.w_down,
+                                            Tensor._wrap(offsets) if isinstance(offsets, torch.Tensor) else offsets,
+                                            cd, out)
 
     # state dict: experts.{e}.{gate,up,down}_proj.weight, e = global expert id
     def _state_dict_hook(self, sd, prefix):
-        for attr, name in self._NAMES:
-            stacked = sd.pop(prefix + attr)
-            for e in range(self.num_experts):
-                sd[f"{prefix}{self.first_expert + e}.{name}.weight"] = Tensor._wrap(stacked._t[e])
+        I = self.intermediate_size
+        gu = sd.pop(prefix + "w_gate_up")
+        down = sd.pop(prefix + "w_down")
+        for e in range(self.num_experts):
+            base = f"{prefix}{self.first_expert + e}."
+            sd[base + "gate_proj.weight"] = Tensor._wrap(gu._t[e, :I])
+            sd[base + "up_proj.weight"] = Tensor._wrap(gu._t[e, I:])
+            sd[base + "down_proj.weight"] = Tensor._wrap(down._t[e])
 
     def _load_state_dict_pre_hook(self, sd, prefix):
-        for attr, name in self._NAMES:
+        def take(name):
             keys = [f"{prefix}{self.first_expert + e}.{name}.weight" for e in range(self.num_experts)]
-            if all(k in sd for k in keys):
-                parts = [sd.pop(k) for k in keys]
-                raw = [p._t if isinstance(p, Tensor) else torch.as_tensor(p) for p in parts]
-                sd[prefix + attr] = Tensor._wrap(torch.stack(raw))
+            if not all(k in sd for k in keys):
+                return None
+            parts = [sd.pop(k) for k in keys]
+            return torch.stack([p._t if isinstance(p, Tensor) else torch.as_tensor(p) for p in parts])
+        # (older checkpoints of this framework: stacked w_gate / w_up entries)
+        g = sd.pop(prefix + "w_gate")._t if prefix + "w_gate" in sd else take("gate_proj")
+        u = sd.pop(prefix + "w_up")._t if prefix + "w_up" in sd else take("up_proj")
+        if g is not None and u is not None:
+            sd[prefix + "w_gate_up"] = Tensor._wrap(torch.cat((g, u), dim=1))
+        d = take("down_proj")
+        if d is not None:
+            sd[prefix + "w_down"] = Tensor._wrap(d)
 
 
 class MoELayer(Module):

@@ -1018,16 +1018,20 @@ def _seg(offsets):
     return [(e, o[e], o[e + 1]) for e in range(len(o) - 1) if o[e + 1] > o[e]]
 
 
-def grouped_linear(x, w, offsets):
-    """y[s:e] = x[s:e] @ w[g].T for each group g with rows offsets[g]:offsets[g+1]. x [M,K], w [G,N,K]."""
+def grouped_linear(x, w, offsets, out=None):
+    """y[s:e] = x[s:e] @ w[g].T for each group g with rows offsets[g]:offsets[g+1]. x [M,K], w [G,N,K].
+    `out`: optional [M, N] contiguous buffer of x's dtype that receives y."""
     if x.is_cuda:
-        r = N.grouped_linear(x, w, offsets)
+        r = N.grouped_linear(x, w, offsets, out)
         if r is not NotImplemented:
             return r
         _fell("grouped_linear")
     y = torch.zeros(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
     for g, s, e in _seg(offsets):
         y[s:e] = x[s:e] @ w[g].t()
+    if out is not None:
+        out.copy_(y)
+        return out
     return y
 
 

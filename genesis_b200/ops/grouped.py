@@ -60,14 +60,18 @@ def _gemm(a, b, out, M, Nn, Kk, lda, ldb, strideB, strideD, a_mn, b_mn, mode, of
     return out
 
 
-def grouped_linear(x, w, offsets):
-    """y[seg g] = x[seg g] @ w[g]^T.  x [Mp, K], w [G, N, K] -> [Mp, N]."""
+def grouped_linear(x, w, offsets, out=None):
+    """y[seg g] = x[seg g] @ w[g]^T.  x [Mp, K], w [G, N, K] -> [Mp, N] (into `out` when given)."""
     if not _ok(x, w, offsets) or x.shape[1] % 8 or w.shape[1] % 8:
         return NotImplemented
     Mp, Kk = x.shape
     G, Nn, _ = w.shape
+    if out is not None and (out.dtype != x.dtype or not out.is_contiguous() or tuple(out.shape) != (Mp, Nn)
+                            or out.data_ptr() % 16):
+        return NotImplemented
     # every tile below offsets[-1] is written (pad rows are zero on the way in); rows past it stay unwritten
-    out = torch.empty(Mp, Nn, dtype=x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty(Mp, Nn, dtype=x.dtype, device=x.device)
     return _gemm(x, w, out, Mp, Nn, Kk, Kk, Kk, Nn * Kk, 0, 0, 0, 1, offsets, G)
 
 

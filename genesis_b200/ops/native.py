@@ -1359,9 +1359,9 @@ def moe_sort(experts, num_experts, align=1):
     return grouped.moe_sort(experts, num_experts, align)
 
 
-def grouped_linear(x, w, offsets):
+def grouped_linear(x, w, offsets, out=None):
     from . import grouped
-    return grouped.grouped_linear(x, w, offsets)
+    return grouped.grouped_linear(x, w, offsets, out)
 
 
 def grouped_dgrad(gy, w, offsets):

@@ -81,7 +81,7 @@ def mark_expert_parameters(model):
     n = 0
     for m in model.modules():
         if isinstance(m, GroupedExperts) and m.total_experts != m.num_experts:
-            for p in (m.w_gate, m.w_up, m.w_down):
+            for p in (m.w_gate_up, m.w_down):
                 p._no_ddp = True
                 n += 1
     return n
@@ -244,11 +244,14 @@ class EPDispatchPull(Function):
         _ws.dwr.view(torch.float32, 0, cap).copy_(sh["dwr"])
         dx = torch.empty(T, H, dtype=g.dtype, device=g.device)
         dw = torch.empty(T, k, dtype=torch.float32, device=g.device)
+        tm = _Timed("combine", T * k * H * g.element_size() * (sh["W"] - 1) // sh["W"])
+        tm.__enter__()
         N._chk(N.lib().gb_ep_combine_pull(_ws.dx.ptr_table, _ws.dwr.ptr_table, st.flags.ptr_table,
                                           sh["idx"].data_ptr(), sh["pos"].data_ptr(), None, sh["offsets"].data_ptr(),
                                           sh["dest_base"].data_ptr(), dx.data_ptr(), dw.data_ptr(), T, k, H, st.rank,
                                           sh["W"], sh["E"], cap, 1, symm.next_epoch(), N._DT[g.dtype], _CTAS,
                                           N._comm_budget(), st.status.data_ptr(), N._st()), "ep_combine_pull(bwd)")
+        tm.__exit__()
         return dx, dw.to(ctx.w_dtype)
 
 
@@ -268,11 +271,15 @@ class EPCombinePull(Function):
         _stage_rows(ye, _ws.y, sh, H)
         wf = w.to(torch.float32).contiguous()
         out = torch.empty(T, H, dtype=ye.dtype, device=ye.device)
+        W = sh["W"]
+        tm = _Timed("combine", T * k * H * ye.element_size() * (W - 1) // W)
+        tm.__enter__()
         N._chk(N.lib().gb_ep_combine_pull(_ws.y.ptr_table, None, st.flags.ptr_table, sh["idx"].data_ptr(),
                                           sh["pos"].data_ptr(), wf.data_ptr(), sh["offsets"].data_ptr(),
                                           sh["dest_base"].data_ptr(), out.data_ptr(), None, T, k, H, st.rank, sh["W"],
                                           sh["E"], cap, 0, symm.next_epoch(), N._DT[ye.dtype], _CTAS, N._comm_budget(),
                                           st.status.data_ptr(), N._st()), "ep_combine_pull")
+        tm.__exit__()
         ctx.shared = sh
         ctx.save_for_backward(ye, wf)
         return out
@@ -293,12 +300,15 @@ class EPCombinePull(Function):
         ws_sorted[sh["pos"].reshape(-1).long()] = wf.reshape(-1)
         dye = torch.empty(cap, H, dtype=ye.dtype, device=ye.device)
         dwr = torch.zeros(cap, dtype=torch.float32, device=ye.device)
+        tm = _Timed("dispatch", T * k * H * ye.element_size() * (sh["W"] - 1) // sh["W"])
+        tm.__enter__()
         N._chk(N.lib().gb_ep_dispatch_pull(_ws.g.ptr_table, _ws.tok.ptr_table, _ws.ws.ptr_table, st.flags.ptr_table,
                                            sh["all_off"].data_ptr(), sh["local_offsets"].data_ptr(),
                                            sh["seg_start"].data_ptr(), sh["seg_src"].data_ptr(), dye.data_ptr(),
                                            ye.data_ptr(), dwr.data_ptr(), H, st.rank, sh["W"], sh["E"], cap, 1,
                                            symm.next_epoch(), N._DT[ye.dtype], _CTAS, N._comm_budget(),
                                            st.status.data_ptr(), N._st()), "ep_dispatch_pull(bwd)")
+        tm.__exit__()
         sh["dwr"] = dwr
         return dye, None
 

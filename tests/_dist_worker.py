@@ -430,9 +430,9 @@ def scenario_ep(a):
     ep_layer = MoELayer(H, E, k, I, ep_group=EPGroup()).to(d)
     ep_layer.gate.weight._t.copy_(full.gate.weight._t)
     lo = r * (E // w)
-    for name in ("w_gate", "w_up", "w_down"):
+    for name in ("w_gate_up", "w_down"):
         getattr(ep_layer.experts, name)._t.copy_(getattr(full.experts, name)._t[lo:lo + E // w])
-    assert mark_expert_parameters(ep_layer) == 3
+    assert mark_expert_parameters(ep_layer) == 2
     rs = np.random.RandomState(50 + r)
     xs = torch.from_numpy(rs.randn(w, 2, T // 2, H).astype(np.float32)).to(d)   # each rank builds only its own slice
     x_mine = torch.from_numpy(np.random.RandomState(50 + r).randn(2, T // 2, H).astype(np.float32)).to(d)
@@ -448,7 +448,7 @@ def scenario_ep(a):
     assert torch.allclose(xg.grad._t, xe.grad._t, atol=1e-5, rtol=1e-4)
     assert torch.allclose(full.gate.weight.grad._t, ep_layer.gate.weight.grad._t, atol=1e-5, rtol=1e-4)
     # expert gradients: the shard's gradient is the SUM over ranks of the full model's local gradients
-    for name in ("w_gate", "w_up", "w_down"):
+    for name in ("w_gate_up", "w_down"):
         gfull = getattr(full.experts, name).grad._t.clone()
         tdist.all_reduce(gfull)
         got = getattr(ep_layer.experts, name).grad._t
