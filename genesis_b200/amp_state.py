@@ -61,4 +61,21 @@ def stacked_shadow_of(raws, dtype):
     return buf
 
 
+# address of a low-precision weight copy [N, K] (or of a group's stacked buffer) -> its transposed twin [K, N], kept
+# current by the same optimizer step that refreshes the copy.  The data-gradient GEMM of a linear layer reads the twin
+# so that both of its operands are contiguous along the contraction (the layout the tensor cores read fastest).
+transposed = {}
+
+
+def transposed_of(lp):
+    """The [K, N] twin of the low-precision weight `lp` [N, K] when the optimizer maintains one, else None."""
+    if not transposed:
+        return None
+    t = transposed.get(lp.data_ptr())
+    if t is None or t.dtype != lp.dtype or t.dim() != 2 or lp.dim() != 2 or t.shape[0] != lp.shape[1] \
+            or t.shape[1] != lp.shape[0]:
+        return None
+    return t
+
+
 amp_state = _AmpState()

@@ -128,6 +128,17 @@ def fill_(t, value):
     return t
 
 
+def transpose_into(dst, src):
+    """dst [C, R] <- src [R, C] transposed (both contiguous)."""
+    if src.is_cuda:
+        r = N.transpose_into(dst, src)
+        if r is not NotImplemented:
+            return dst
+        _fell("transpose_into")
+    dst.copy_(src.t())
+    return dst
+
+
 def zero_(t):
     return fill_(t, 0)
 
@@ -392,7 +403,12 @@ def linear(x, w, bias=None, out_dtype=None):
 
 
 def linear_dgrad(gy, w):
-    """dx = gy @ w; gy [..., N], w [N, K]."""
+    """dx = gy @ w; gy [..., N], w [N, K].  When the optimizer keeps a [K, N] twin of `w` current
+    (`amp_state.transposed_of`), the GEMM reads that instead: K-major operands on both sides."""
+    from ..amp_state import transposed_of
+    wt = transposed_of(w)
+    if wt is not None and gy.dtype == wt.dtype:
+        return linear(gy, wt)
     if gy.is_cuda:
         r = N.linear_dgrad(gy, w)
         if r is not NotImplemented:

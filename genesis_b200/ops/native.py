@@ -383,6 +383,20 @@ def contiguous(t):
     return out
 
 
+def transpose_into(dst, src):
+    """dst [C, R] (contiguous) <- src [R, C] (contiguous) transposed, through the shared-memory tile kernel."""
+    if src.dim() != 2 or dst.dim() != 2 or not src.is_contiguous() or not dst.is_contiguous() \
+            or dst.shape[0] != src.shape[1] or dst.shape[1] != src.shape[0] or dst.dtype != src.dtype \
+            or src.element_size() not in (2, 4, 8):
+        return NotImplemented
+    R, Cc = src.shape
+    if R == 0 or Cc == 0:
+        return dst
+    _chk(lib().gb_transpose(src.data_ptr(), dst.data_ptr(), 1, R, Cc, 0, Cc, 1, src.element_size(), _st()),
+         "transpose")
+    return dst
+
+
 def copy_(dst, src):
     if dst.shape != src.shape or dst.numel() == 0:
         return NotImplemented

@@ -130,18 +130,21 @@ class _AdamBase(Optimizer):
         self._dyn = None
         self._dyn_lr = None
 
-    def enable_shadows(self, dtype, groups=None):
+    def enable_shadows(self, dtype, groups=None, transposed=True):
         """Keep a `dtype` (bf16 / fp16) copy of every floating-point parameter current from inside the optimizer
         kernel, so that `autocast` finds the low-precision weights ready instead of converting all of them every
         step.  `groups`: lists of parameters that some layer multiplies as one stacked matrix (q/k/v, gate/up); their
         copies are row slices of one buffer, which the fused projection then uses as is.  Costs 2 bytes per
         parameter.  A parameter changed by anything but this optimizer falls back to the conversion until the next
-        step refreshes its copy."""
+        step refreshes its copy.  `transposed`: also keep a [in, out] twin of every 2-D weight copy (refreshed by a
+        tiled transpose after each step), which the data-gradient GEMMs read instead of the [out, in] copy: with it
+        both operands of that GEMM are contiguous along the contraction.  Costs 2 more bytes per weight element."""
         from ..amp_state import ShadowEntry, shadows
         from ..dtypes import get_dtype
         td = get_dtype(dtype).torch_dtype
         index = {id(p): i for i, p in enumerate(self.params)}
         self._shadows, self._shadow_entries = {}, {}
+        self._transposed = []                       # (copy [N, K], twin [K, N]) pairs refreshed after every step
         grouped = set()
         for members in (groups or []):
             ps = [p for p in members if id(p) in index]
@@ -160,11 +163,34 @@ class _AdamBase(Optimizer):
                 ents.append(e)
                 grouped.add(id(p))
                 self._register_shadow(index[id(p)], e, shadows)
+            if transposed and buf.dim() == 2:
+                self._add_transposed(buf)
         for i, p in enumerate(self.params):
             if id(p) in grouped or p._t.dtype != torch.float32 or not p._t.is_contiguous() or p._t.numel() == 0:
                 continue
-            self._register_shadow(i, ShadowEntry(p, p._t.to(td), None), shadows)
+            e = ShadowEntry(p, p._t.to(td), None)
+            self._register_shadow(i, e, shadows)
+            if transposed and e.lp.dim() == 2 and min(e.lp.shape) >= 64:
+                self._add_transposed(e.lp)
         return self
+
+    def _add_transposed(self, lp):
+        from ..amp_state import transposed as registry
+        twin = torch.empty(lp.shape[1], lp.shape[0], dtype=lp.dtype, device=lp.device)
+        if lp.is_cuda:
+            if K.transpose_into(twin, lp) is NotImplemented:
+                return
+        else:
+            twin.copy_(lp.t())
+        self._transposed.append((lp, twin))
+        registry[lp.data_ptr()] = twin
+
+    def _refresh_transposed(self):
+        for lp, twin in getattr(self, "_transposed", ()):
+            if lp.is_cuda:
+                K.transpose_into(twin, lp)
+            else:
+                twin.copy_(lp.t())
 
     def _register_shadow(self, i, entry, registry):
         self._shadows[i] = entry.lp
@@ -173,10 +199,13 @@ class _AdamBase(Optimizer):
 
     def disable_shadows(self):
         from ..amp_state import shadows
+        from ..amp_state import transposed as registry
         for e in (getattr(self, "_shadow_entries", None) or {}).values():
             if shadows.get(e.param._t.data_ptr()) is e:
                 del shadows[e.param._t.data_ptr()]
-        self._shadows, self._shadow_entries = None, {}
+        for lp, _ in getattr(self, "_transposed", ()):
+            registry.pop(lp.data_ptr(), None)
+        self._shadows, self._shadow_entries, self._transposed = None, {}, []
 
     def make_capturable(self):
         """Move the step-dependent scalars to the device. Idempotent; needs CUDA parameters."""
@@ -235,6 +264,8 @@ class _AdamBase(Optimizer):
             self._sync_lr()
         K.adamw_step(ps, gs, ms, vs, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.t,
                      self.decoupled, self._grad_scale, self._found_inf, sh, self._dyn)
+        if sh is not None:
+            self._refresh_transposed()
         self._touched(idx)
 
 
