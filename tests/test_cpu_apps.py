@@ -58,3 +58,30 @@ def test_cuda_graph_flag_is_refused_without_cuda(tmp_path):
     with pytest.raises(SystemExit):
         _train(["--model", "tiny", "--data", "synthetic", "--vocab-size", "200", "--batch-size", "2", "--block-size", "16",
                 "--device", "cpu", "--out", str(tmp_path / "ck"), "--max-steps", "2", "--cuda-graph"])
+
+
+def test_shard_fetcher_writes_atomically_retries_and_skips(tmp_path):
+    import io
+    import importlib.util
+    import urllib.error
+    spec = importlib.util.spec_from_file_location("nanochat_dataset", os.path.join(ROOT, "apps", "nanochat", "dataset.py"))
+    ds = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ds)
+    calls = {"n": 0}
+
+    def flaky(url):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise urllib.error.URLError("temporary failure")
+        return io.BytesIO(b"PAR1" + url.encode())
+
+    p = ds.fetch_shard(3, str(tmp_path), opener=flaky, sleep=lambda s: None)
+    assert p.endswith("shard_00003.parquet") and open(p, "rb").read().startswith(b"PAR1")
+    assert calls["n"] == 2 and not os.path.exists(p + ".part")
+    assert ds.fetch_shard(3, str(tmp_path), opener=flaky) == p and calls["n"] == 2        # already there: no request
+
+    def dead(url):
+        raise urllib.error.URLError("no network")
+    assert ds.fetch_shard(4, str(tmp_path), attempts=2, opener=dead, sleep=lambda s: None) is None
+    done, failed = ds.fetch(2, str(tmp_path), workers=2, opener=dead, attempts=1, sleep=lambda s: None)
+    assert failed == [0, 1, ds.LAST_SHARD] and done == []
