@@ -23,6 +23,10 @@
 // gate and [128, 256) up of the same 128 hidden units, and the epilogue writes gate | up (for backward) and
 // silu(gate) * up in one pass: the separate activation kernel and its read of gate | up disappear.
 //
+// SwiGLU backward epilogue: the product is dh (the gradient of silu(gate) * up, i.e. the data gradient of the down
+// projection); the epilogue reads gate | up of the forward pass for its tile and stores d(gate) | d(up) directly, so
+// dh is never written to memory and the stand-alone backward activation pass disappears.
+//
 // Reference counterpart: the Triton `matmul_kernel`, genesis/ops/cuda/matrix_ops.py:21-294, and the SiLU kernels
 // of genesis/nn/triton_ops/silu.py:29-85.
 #include "sm100_ptx.cuh"
@@ -43,7 +47,7 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SLAB_BYTES = 32 * 128;
 constexpr int ACC_STRIDE = 256;      // TMEM columns between the two accumulators
 
-enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_SWIGLU_BWD = 2 };
 
 struct Params {
   const void* bias;
@@ -54,6 +58,8 @@ struct Params {
   int accumulate;          // fp32 output only: add into D (TMA add-reduce)
   int m_fastest, raster_group;
   int write_gu;            // SwiGLU: also store gate | up
+  const void* gu;          // SwiGLU backward: gate | up of the forward pass, [M, 2 N] with pitch ld_gu elements
+  int ld_gu;
   float alpha;
 };
 
@@ -132,7 +138,7 @@ template <int STAGES, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(320, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
              const __grid_constant__ CUtensorMap tmapD, const __grid_constant__ CUtensorMap tmapD2, const Params p) {
-  constexpr int SLABS = (EPI == EPI_SWIGLU) ? 3 : 1;
+  constexpr int SLABS = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD ? 2 : 1);
   using L = Smem<STAGES, SLABS>;
   constexpr int UMMA_K = 16, KSTEPS = BK / UMMA_K;
   constexpr uint32_t TMEM_COLS = 512;
@@ -341,6 +347,64 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           tma_store_3d(&tmapD2, slab + 2 * SLAB_BYTES, h0, y0, 0);
           bulk_commit_group();
         }
+      } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+        // accumulator = dh[rows, n0 .. n0 + bn); this warp takes the 64-column units half, half + 2, ...
+        const int n0 = ni * p.bn;
+        const int row = y0 + lane;
+        const bool row_ok = row < p.M;
+        const uint16_t* gu_row = reinterpret_cast<const uint16_t*>(p.gu) + (size_t)(row_ok ? row : 0) * p.ld_gu;
+        const bool bf = dt == DT_BF16;
+        for (int c = half * 64; c < p.bn; c += 128) {
+          if (n0 + c >= p.N) break;
+          if (lane == 0) bulk_wait_group_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            const int col = n0 + c + sub * 32;                 // hidden unit of the first of 32 columns
+            uint4 gq[4], uq[4];
+            const bool in = row_ok && col + 32 <= p.N;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              gq[v] = make_uint4(0, 0, 0, 0);
+              uq[v] = make_uint4(0, 0, 0, 0);
+              if (in) {
+                gq[v] = *reinterpret_cast<const uint4*>(gu_row + col + v * 8);
+                uq[v] = *reinterpret_cast<const uint4*>(gu_row + p.N + col + v * 8);
+              }
+            }
+            uint32_t rd[32];
+            tmem_ld_32x32b_x32(t_row + c + sub * 32, rd);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint16_t* gh = reinterpret_cast<const uint16_t*>(&gq[v]);
+              const uint16_t* uh = reinterpret_cast<const uint16_t*>(&uq[v]);
+              float dg[8], du[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float x = half_bits_to_float(gh[j], bf ? DT_BF16 : DT_F16);
+                const float u = half_bits_to_float(uh[j], bf ? DT_BF16 : DT_F16);
+                const float dd = __uint_as_float(rd[8 * v + j]) * p.alpha;
+                const float sg = __fdividef(1.f, 1.f + __expf(-x));
+                dg[j] = dd * u * sg * (1.f + x * (1.f - sg));
+                du[j] = dd * x * sg;
+              }
+              const int unit = ((4 * sub + v) ^ (lane & 7)) << 4;
+              uint4 o;
+              o.x = pack2(dg[0], dg[1], dt); o.y = pack2(dg[2], dg[3], dt); o.z = pack2(dg[4], dg[5], dt); o.w = pack2(dg[6], dg[7], dt);
+              *reinterpret_cast<uint4*>(slab_row + unit) = o;
+              o.x = pack2(du[0], du[1], dt); o.y = pack2(du[2], du[3], dt); o.z = pack2(du[4], du[5], dt); o.w = pack2(du[6], du[7], dt);
+              *reinterpret_cast<uint4*>(slab_row + SLAB_BYTES + unit) = o;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && y0 < p.M) {
+            tma_store_3d(&tmapD, slab, n0 + c, y0, 0);
+            tma_store_3d(&tmapD, slab + SLAB_BYTES, p.N + n0 + c, y0, 0);
+            bulk_commit_group();
+          }
+        }
       } else {
         const int n0 = ni * p.bn;
         for (int c = half * 64; c < p.bn; c += 128) {
@@ -419,7 +483,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
 template <int STAGES, bool A_MN, bool B_MN, int EPI>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const CUtensorMap& td2,
                   const Params& p, cudaStream_t stream) {
-  constexpr int SLABS = (EPI == EPI_SWIGLU) ? 3 : 1;
+  constexpr int SLABS = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD ? 2 : 1);
   using L = Smem<STAGES, SLABS>;
   auto kern = gemm2_kernel<STAGES, A_MN, B_MN, EPI>;
   static unsigned long long configured = 0;
@@ -460,6 +524,8 @@ using namespace gb;
 //   epi 0: D[M, N] = alpha * A B^T + bias, out_dtype f32 / f16 / bf16; accumulate (f32 only) adds into D.
 //   epi 1: B is a stacked [2 N, K] K-major weight (gate rows, then up rows); D2[M, N] = silu(g) * u with
 //          g | u = alpha * A B^T, and D[M, 2 N] = g | u when D is not null.  N must be a multiple of 128.
+//   epi 2: dh = alpha * A B^T is the gradient of silu(g) * u; D2 [M, 2 N] holds g | u (input) and
+//          D [M, 2 N] receives dg | du; dh itself is never stored.  N must be a multiple of 64.
 // Requirements (the caller falls back to gb_gemm otherwise): D, D2 16-byte aligned with 16-byte multiples as pitch.
 // bn: pair tile width 128 / 192 / 256 (0 = 256).  Returns 0, a cudaError_t, or a negative argument error.
 extern "C" int gb_gemm_pair(const void* A, const void* B, void* D, void* D2, const void* bias, int M, int N, int K,
@@ -475,8 +541,25 @@ extern "C" int gb_gemm_pair(const void* A, const void* B, void* D, void* D2, con
   p.bias = bias; p.status = status; p.M = M; p.N = N; p.K = K; p.bn = bn; p.out_dtype = out_dtype;
   p.in_bf16 = in_dtype == DT_BF16 ? 1 : 0; p.bias_dtype = bias_dtype; p.accumulate = accumulate;
   p.alpha = alpha; p.write_gu = D != nullptr ? 1 : 0;
+  p.gu = nullptr; p.ld_gu = 0;
   CUtensorMap ta, tb, td, td2;
   int r;
+  if (epi == g2::EPI_SWIGLU_BWD) {
+    // A = gy [M, K], B = the [N, K] K-major twin of the down weight; D2 = gate | up of the forward pass [M, 2 N]
+    // (read), D = d(gate) | d(up) [M, 2 N] (written).  N = hidden width, a multiple of 64.
+    if (a_mn || b_mn || N % 64 != 0 || out_dtype == DT_F32 || bias != nullptr || D == nullptr || D2 == nullptr)
+      return -5;
+    if ((reinterpret_cast<uintptr_t>(D2) & 15) != 0 || (ldd2 * 2) % 16 != 0) return -5;
+    p.bn = 256;
+    p.gu = D2; p.ld_gu = ldd2;
+    if ((r = make_tmap_3d(&ta, A, in_dtype, K, M, 1, lda, 0, g2::BM)) != 0) return 10000 + r;
+    if ((r = make_tmap_3d(&tb, B, in_dtype, K, N, 1, ldb, 0, 128)) != 0) return 20000 + r;
+    if ((r = make_tmap_3d(&td, D, out_dtype, 2ll * N, M, 1, ldd, 0, 32)) != 0) return 30000 + r;
+    td2 = td;
+    p.m_fastest = 1;
+    p.raster_group = (M + 255) / 256;
+    return g2::launch<5, false, false, g2::EPI_SWIGLU_BWD>(ta, tb, td, td2, p, stream);
+  }
   if (epi == g2::EPI_SWIGLU) {
     if (a_mn || b_mn || N % 128 != 0 || out_dtype == DT_F32 || bias != nullptr || D2 == nullptr) return -5;
     p.bn = 256;

@@ -59,9 +59,10 @@ class FeedForward(nn.Module):
 
     def forward(self, x):
         # gate and up projections as one GEMM over the stacked weights; SwiGLU reads the two halves in place
-        if self.gate_proj.bias is None:
-            # ... and with no biases the activation rides in that GEMM's epilogue
-            return self.down_proj(F.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight))
+        if self.gate_proj.bias is None and self.down_proj.bias is None:
+            # ... and with no biases the whole MLP is one node: the activation rides in the gate|up GEMM's epilogue,
+            # its gradient in the epilogue of the down projection's data-gradient GEMM
+            return F.swiglu_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
         biases = [self.gate_proj.bias, self.up_proj.bias]
         return self.down_proj(F.swiglu_fused(F.fused_linear(x, [self.gate_proj.weight, self.up_proj.weight], biases)))
 

@@ -1714,6 +1714,61 @@ def linear_swiglu(x, w_gate, w_up):
     return LinearSwiGLUFunction.apply(x, w_gate, w_up, cd)
 
 
+class SwiGLUMLPFunction(Function):
+    """The whole bias-free SwiGLU MLP, y = (silu(x Wg^T) * (x Wu^T)) Wd^T, as one node: three GEMMs forward (gate|up with
+    the activation in its epilogue, down) and four backward, with no stand-alone activation pass in either direction:
+    the down projection's data-gradient GEMM applies the SwiGLU backward in its epilogue (`K.dgrad_swiglu_bwd`), so
+    the gradient of the hidden activation never reaches memory.
+    Reference counterpart: `nn/modules/transformer.py` FeedFowardSwiGLU (three Linear modules and SiLU)."""
+    raw = True
+    amp_policy = AMPPolicy.PRESERVE
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_up, w_down, compute_dtype):
+        cd = compute_dtype if compute_dtype is not None else w_gate.dtype
+        Wgu = _fused_params([w_gate, w_up], cd)
+        Wd = _cached_param_cast(w_down, cd)
+        if x.dtype != cd:
+            x = K.to_dtype(x, cd)
+        gu, h = K.linear_swiglu(x, Wgu)
+        y = K.linear(h, Wd)
+        ctx.save_for_backward(x, Wgu, gu, h, Wd)
+        ctx.meta = ([w_gate.shape[0], w_up.shape[0]], w_gate.dtype, w_down.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, Wgu, gu, h, Wd = ctx.saved_tensors
+        sizes, wd_gu, wd_d = ctx.meta
+        if gy.dtype != h.dtype:
+            gy = K.to_dtype(gy, h.dtype)
+        gy = gy if gy.is_contiguous() else K.contiguous(gy)
+        need = ctx.needs_input_grad
+        # down projection: weight gradient (into its bucket slot when it has one), then data gradient + activation
+        slot = _grad_slot(ctx, 3, wd_d, Wd.shape)
+        if slot is None:
+            gWd = K.linear_wgrad(gy, h, out_dtype=wd_d)
+        else:
+            buf, accumulate = slot
+            gWd = K.linear_wgrad(gy, h, out_dtype=buf.dtype, accum=buf if accumulate else None,
+                                 out=None if accumulate else buf)
+        dgu = K.dgrad_swiglu_bwd(gy, Wd, gu if gu.is_contiguous() else K.contiguous(gu))
+        gx = K.linear_dgrad(dgu, Wgu) if need[0] else None
+        stacked, accumulate = _stacked_grad_slot(ctx, 1, sizes, wd_gu, Wgu.shape[1])
+        if stacked is not None:
+            gW = K.linear_wgrad(dgu, x, out_dtype=stacked.dtype, accum=stacked if accumulate else None,
+                                out=None if accumulate else stacked)
+        else:
+            gW = K.linear_wgrad(dgu, x, out_dtype=wd_gu)
+        return gx, _fresh_slice(gW, 0, sizes[0]), _fresh_slice(gW, sizes[0], sizes[1]), gWd
+
+
+def swiglu_mlp(x, w_gate, w_up, w_down):
+    """down(silu(gate(x)) * up(x)) for three bias-free projections given by their weights."""
+    cd = amp_state.dtype if amp_state.enabled else None
+    return SwiGLUMLPFunction.apply(x, w_gate, w_up, w_down, cd)
+
+
 def qkv_rope(y, cos, sin, positions, num_heads, num_kv_heads, head_dim):
     return QKVRopeFunction.apply(y, cos, sin, positions, num_heads, num_kv_heads, head_dim)
 

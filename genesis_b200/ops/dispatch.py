@@ -635,6 +635,21 @@ def linear_swiglu(x, w):
     return gu, swiglu_fused_fwd(gu if gu.is_contiguous() else contiguous(gu))
 
 
+def dgrad_swiglu_bwd(gy, wd, gu):
+    """d(gate | up) from the output gradient `gy` of the down projection (weight `wd` [H, I]) and gate | up `gu`:
+    dh = gy @ wd, then the SwiGLU backward.  With a K-major twin of `wd` at hand (kept by the optimizer) both run as
+    one GEMM whose epilogue applies the activation gradient; otherwise as a GEMM and an elementwise pass."""
+    if gy.is_cuda:
+        from ..amp_state import transposed_of
+        wt = transposed_of(wd)
+        if wt is not None:
+            r = N.dgrad_swiglu_bwd(gy, wt, gu)
+            if r is not NotImplemented:
+                return r
+    dh = linear_dgrad(gy, wd)
+    return swiglu_fused_bwd(dh if dh.is_contiguous() else contiguous(dh), gu)
+
+
 def swiglu_fused_bwd(dy, gu):
     """-> d(gate | up) [..., 2 I]."""
     if gu.is_cuda:

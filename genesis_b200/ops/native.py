@@ -619,6 +619,29 @@ def linear_swiglu(x, w, want_gu=True):
     return (None if gu is None else gu.reshape(*lead, I2)), h.reshape(*lead, I)
 
 
+def dgrad_swiglu_bwd(gy, wd_t, gu):
+    """d(gate | up) [M, 2 I] of a SwiGLU MLP from the gradient `gy` [M, H] of the down projection's output, the
+    [I, H] K-major twin `wd_t` of the down weight and gate | up `gu` [M, 2 I] of the forward pass: ONE GEMM
+    (dh = gy @ wd_t^T) on CTA pairs whose epilogue applies the SwiGLU backward; dh is never stored."""
+    if gy.dtype not in (F16, BF16) or wd_t.dtype != gy.dtype or gu.dtype != gy.dtype or pair_mode == "0":
+        return NotImplemented
+    lead = gy.shape[:-1]
+    g2 = gy.reshape(-1, gy.shape[-1])
+    u2 = gu.reshape(-1, gu.shape[-1])
+    M, H = g2.shape
+    I = wd_t.shape[0]
+    if wd_t.dim() != 2 or wd_t.shape[1] != H or u2.shape != (M, 2 * I) or I % 64 or (H * 2) % 16 or M == 0 \
+            or not (g2.is_contiguous() and wd_t.is_contiguous() and u2.is_contiguous()) \
+            or g2.data_ptr() % 16 or wd_t.data_ptr() % 16 or u2.data_ptr() % 16:
+        return NotImplemented
+    dgu = torch.empty(M, 2 * I, dtype=gy.dtype, device=gy.device)
+    rc = lib().gb_gemm_pair(g2.data_ptr(), wd_t.data_ptr(), dgu.data_ptr(), u2.data_ptr(), None, M, I, H, H, H,
+                            2 * I, 2 * I, 0, 0, _GEMM_DT[gy.dtype], _GEMM_DT[gy.dtype], 0, 0, 1.0, 2, 256,
+                            status_tensor(gy.device).data_ptr(), _st())
+    _chk(rc, "gemm_pair(swiglu_bwd)")
+    return dgu.reshape(*lead, 2 * I)
+
+
 def gemm(a, b_t, out_dtype=None, bias=None, accum=None, alpha=1.0, out=None):
     """D[M, N] = a[M, K] @ b_t[N, K]^T for 2-D operands in any of the supported layouts.
     `a` / `b_t` may be transposed views (stride(0) == 1); misaligned ones are repacked.

@@ -219,3 +219,56 @@ def test_gemm_routes_large_16_bit_shapes_to_the_pair_kernel():
     got = N.gemm(a, b)
     check(got, a.float().cpu() @ b.float().cpu().t(), torch.bfloat16, 896)
     assert N.launch_count == before + 1
+
+
+@pytest.mark.parametrize("M,I,H", [(256, 128, 64), (512, 256, 896), (1000, 448, 200), (2048, 4864, 896)])
+def test_pair_gemm_swiglu_backward_epilogue(M, I, H):
+    gy = rnd(M, H, dt=torch.bfloat16)
+    wd = (rnd(H, I, seed=1) * 0.2).bfloat16()                  # down weight [H, I]
+    gu = rnd(M, 2 * I, dt=torch.bfloat16, seed=2)
+    dh = gy.float() @ wd.float()
+    g, u = gu[:, :I].float(), gu[:, I:].float()
+    sg = torch.sigmoid(g)
+    ref = torch.cat((dh * u * sg * (1 + g * (1 - sg)), dh * g * sg), 1)
+    got = N.dgrad_swiglu_bwd(gy.to(DEV), wd.t().contiguous().to(DEV), gu.to(DEV))
+    assert got is not NotImplemented
+    check(got, ref, torch.bfloat16, H)
+
+
+def test_swiglu_mlp_function_with_optimizer_kept_copies():
+    """The one-node MLP (activation in the gate|up epilogue, its gradient in the down data-gradient epilogue, K-major
+    twins of the weights from the optimizer) against three separate layers."""
+    import genesis_b200 as genesis
+    import genesis_b200.nn as nn
+    import genesis_b200.nn.functional as F
+    T, H, I = 512, 256, 384
+    g = torch.Generator().manual_seed(5)
+    x0 = torch.randn(T, H, generator=g)
+    dy = torch.randn(T, H, generator=g).to(DEV)
+
+    def run(fused):
+        genesis.manual_seed(1)
+        gate, up, down = nn.Linear(H, I, bias=False).cuda(), nn.Linear(H, I, bias=False).cuda(), \
+            nn.Linear(I, H, bias=False).cuda()
+        params = [gate.weight, up.weight, down.weight]
+        opt = genesis.optim.AdamW(params, lr=1e-3)
+        opt.enable_shadows(genesis.bfloat16, [[gate.weight, up.weight]])
+        x = genesis.Tensor(x0.clone().to(DEV), requires_grad=True)
+        with genesis.amp.autocast(dtype=genesis.bfloat16):
+            if fused:
+                y = F.swiglu_mlp(x, gate.weight, up.weight, down.weight)
+            else:
+                y = down(F.swiglu(gate(x), up(x)))
+        (y * genesis.Tensor(dy.to(y._t.dtype))).sum().backward()
+        out = [y._t.float(), x.grad._t.float()] + [p.grad._t.float() for p in params]
+        opt.step()                                     # refreshes copies and twins
+        opt.disable_shadows()
+        return out
+
+    K.reset_fallbacks()
+    with K.strict_native(True):
+        a = run(True)
+    b = run(False)
+    for u, v in zip(a, b):
+        torch.testing.assert_close(u, v, atol=3e-2 * max(1.0, float(v.abs().max())), rtol=3e-2)
+    assert K.fallback_counts() == {}
