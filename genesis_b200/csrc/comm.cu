@@ -32,29 +32,52 @@ __device__ __forceinline__ void epoch_publish(uint32_t* ctr, uint32_t epoch) {
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256, 3)
-allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, long long n, int rank, int world,
-                       uint32_t epoch, float prescale, const float* __restrict__ loss_scale, int scale_is_reciprocal,
-                       float* __restrict__ found_inf, unsigned long long budget_ns, int* __restrict__ status,
-                       uint32_t* __restrict__ epoch_ctr) {
-  __shared__ int s_fail;
-  __shared__ int s_bad;
+// Reduce phase shared by both all-reduce kernels: this rank's slice [v0, v1) of 16-byte vectors is summed over all
+// ranks in fp32.  NVLink round trips take microseconds, so what matters is how many loads a thread keeps in flight:
+// with the world size known at compile time the loads of ALL peers for a batch of vectors are issued before the
+// first one is consumed (8 vectors in flight per thread for any world size: UNR = 8 / W batches), instead of
+// peer after peer.  `emit(i, acc)` receives the fp32 sums of vector i.
+template <typename T, int W, typename Emit>
+__device__ __forceinline__ void reduce_slice_w(const PeerTable& bufs, long long offset_elems, int rank, long long v0,
+                                               long long v1, Emit emit) {
   constexpr int V = Vec16<T>::N;
-  if (threadIdx.x == 0) { s_fail = 0; s_bad = 0; }
-  if (epoch_ctr != nullptr) epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ctr) + 1;
-  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) {
-    epoch_publish(epoch_ctr, epoch);
-    return;
+  constexpr int UNR = 8 / W;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const T* base[W];
+#pragma unroll
+  for (int p = 0; p < W; ++p) base[p] = reinterpret_cast<const T*>(bufs.ptr[(rank + p) % W]) + offset_elems;
+  for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * UNR) {
+    uint4 raw[UNR][W];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+#pragma unroll
+      for (int p = 0; p < W; ++p)
+        if (i < v1) raw[u][p] = ld_volatile_v4(base[p] + i * V);
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= v1) continue;
+      float acc[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int p = 0; p < W; ++p) {
+        const T* e = reinterpret_cast<const T*>(&raw[u][p]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(e[j]);
+      }
+      emit(i, acc);
+    }
   }
+}
 
-  float scale = prescale;
-  if (loss_scale != nullptr) scale *= scale_is_reciprocal ? 1.f / *loss_scale : *loss_scale;
-  const long long nvec = n / V;                       // n is padded by the caller to world * V
-  const long long per = nvec / world;
-  const long long v0 = (long long)rank * per, v1 = (rank == world - 1) ? nvec : v0 + per;
-  bool bad = false;
-  // NVLink round trips are microseconds: keep UNR x world 16-byte loads in flight per thread
+// any world size: peer after peer, four vectors in flight per peer
+template <typename T, typename Emit>
+__device__ __forceinline__ void reduce_slice_any(const PeerTable& bufs, long long offset_elems, int rank, int world,
+                                                 long long v0, long long v1, Emit emit) {
+  constexpr int V = Vec16<T>::N;
   constexpr int UNR = 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * UNR) {
@@ -81,25 +104,56 @@ allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, 
         }
       }
     }
-    Vec16<T> o[UNR];
 #pragma unroll
     for (int u = 0; u < UNR; ++u)
+      if (i0 + u * stride < v1) emit(i0 + u * stride, acc[u]);
+  }
+}
+
+template <typename T, typename Emit>
+__device__ __forceinline__ void reduce_slice(const PeerTable& bufs, long long offset_elems, int rank, int world,
+                                             long long v0, long long v1, Emit emit) {
+  if (world == 8) reduce_slice_w<T, 8>(bufs, offset_elems, rank, v0, v1, emit);
+  else if (world == 4) reduce_slice_w<T, 4>(bufs, offset_elems, rank, v0, v1, emit);
+  else if (world == 2) reduce_slice_w<T, 2>(bufs, offset_elems, rank, v0, v1, emit);
+  else reduce_slice_any<T>(bufs, offset_elems, rank, world, v0, v1, emit);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256, 3)
+allreduce_fused_kernel(PeerTable bufs, PeerTable flags, long long offset_elems, long long n, int rank, int world,
+                       uint32_t epoch, float prescale, const float* __restrict__ loss_scale, int scale_is_reciprocal,
+                       float* __restrict__ found_inf, unsigned long long budget_ns, int* __restrict__ status,
+                       uint32_t* __restrict__ epoch_ctr) {
+  __shared__ int s_fail;
+  __shared__ int s_bad;
+  constexpr int V = Vec16<T>::N;
+  if (threadIdx.x == 0) { s_fail = 0; s_bad = 0; }
+  if (epoch_ctr != nullptr) epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ctr) + 1;
+  if (!peer_barrier(flags, rank, world, 0, epoch, budget_ns, status, &s_fail)) {
+    epoch_publish(epoch_ctr, epoch);
+    return;
+  }
+
+  float scale = prescale;
+  if (loss_scale != nullptr) scale *= scale_is_reciprocal ? 1.f / *loss_scale : *loss_scale;
+  const long long nvec = n / V;                       // n is padded by the caller to world * V
+  const long long per = nvec / world;
+  const long long v0 = (long long)rank * per, v1 = (rank == world - 1) ? nvec : v0 + per;
+  bool bad = false;
+  reduce_slice<T>(bufs, offset_elems, rank, world, v0, v1, [&](long long i, const float* acc) {
+    Vec16<T> o;
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float r = acc[u][j] * scale;
-        if (!isfinite(r) && (i0 + u * stride < v1)) bad = true;
-        o[u].v[j] = Cvt<T>::from_f(r);
-      }
+    for (int j = 0; j < V; ++j) {
+      const float r = acc[j] * scale;
+      if (!isfinite(r)) bad = true;
+      o.v[j] = Cvt<T>::from_f(r);
+    }
     for (int p = 0; p < world; ++p) {
       const int dst = (rank + p) % world;
-      T* base = reinterpret_cast<T*>(bufs.ptr[dst]) + offset_elems;
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const long long i = i0 + u * stride;
-        if (i < v1) st16(base + i * V, o[u]);
-      }
+      st16(reinterpret_cast<T*>(bufs.ptr[dst]) + offset_elems + i * V, o);
     }
-  }
+  });
   if (bad) s_bad = 1;
   __syncthreads();
   if (s_bad && threadIdx.x < world && found_inf != nullptr) {
@@ -159,50 +213,19 @@ allreduce_wire_kernel(PeerTable bufs, PeerTable flags, long long n, float* __res
   const long long per = nvec / world;
   const long long v0 = (long long)rank * per, v1 = (rank == world - 1) ? nvec : v0 + per;
   bool bad = false;
-  constexpr int UNR = 4;
-  for (long long i0 = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * UNR) {
-    float acc[UNR][V];
+  reduce_slice<T>(bufs, 0, rank, world, v0, v1, [&](long long i, const float* acc) {
+    Vec16<T> o;
 #pragma unroll
-    for (int u = 0; u < UNR; ++u)
-#pragma unroll
-      for (int j = 0; j < V; ++j) acc[u][j] = 0.f;
-    for (int p = 0; p < world; ++p) {
-      const int src = (rank + p) % world;
-      const T* base = reinterpret_cast<const T*>(bufs.ptr[src]);
-      uint4 raw[UNR];
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const long long i = i0 + u * stride;
-        if (i < v1) raw[u] = ld_volatile_v4(base + i * V);
-      }
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        if (i0 + u * stride < v1) {
-          const T* e = reinterpret_cast<const T*>(&raw[u]);
-#pragma unroll
-          for (int j = 0; j < V; ++j) acc[u][j] += Cvt<T>::to_f(e[j]);
-        }
-      }
+    for (int j = 0; j < V; ++j) {
+      const float r = acc[j] * prescale;
+      if (!isfinite(r)) bad = true;
+      o.v[j] = Cvt<T>::from_f(r);
     }
-    Vec16<T> o[UNR];
-#pragma unroll
-    for (int u = 0; u < UNR; ++u)
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float r = acc[u][j] * prescale;
-        if (!isfinite(r) && (i0 + u * stride < v1)) bad = true;
-        o[u].v[j] = Cvt<T>::from_f(r);
-      }
     for (int p = 0; p < world; ++p) {
       const int dst = (rank + p) % world;
-      T* base = reinterpret_cast<T*>(bufs.ptr[dst]);
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const long long i = i0 + u * stride;
-        if (i < v1) st16(base + i * V, o[u]);
-      }
+      st16(reinterpret_cast<T*>(bufs.ptr[dst]) + i * V, o);
     }
-  }
+  });
   if (bad) s_bad = 1;
   __syncthreads();
   if (s_bad && threadIdx.x < world && found_inf != nullptr)

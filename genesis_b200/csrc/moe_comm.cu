@@ -116,6 +116,37 @@ ep_dispatch_pull_kernel(PeerTable xs, PeerTable toks, PeerTable wss, PeerTable f
       }
     }
     const int nrows = total - base < 32 ? total - base : 32;
+    if (mode == 0 && nvec <= 256) {
+      // plain row copies: two rows (2 x 8 vectors per lane) in flight per warp, so a pair costs one NVLink round trip
+      for (int r = 0; r < nrows; r += 2) {
+        uint4 q[2][8];
+        int pp[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int rr = r + h2 < nrows ? r + h2 : r;
+          pp[h2] = __shfl_sync(0xffffffffu, my_p, rr);
+          const int t = __shfl_sync(0xffffffffu, my_t, rr);
+          if (r + h2 >= nrows) pp[h2] = -2;                       // no such row
+          if (pp[h2] >= 0) {
+            const T* src = reinterpret_cast<const T*>(xs.ptr[pp[h2]]) + (size_t)t * H;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (lane + u * 32 < nvec) q[h2][u] = ld_volatile_v4(src + (lane + u * 32) * V);
+          }
+        }
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          if (pp[h2] == -2) continue;
+          T* dst = out + (size_t)(base + r + h2) * H;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (lane + u * 32 >= nvec) continue;
+            *reinterpret_cast<uint4*>(dst + (lane + u * 32) * V) = pp[h2] >= 0 ? q[h2][u] : make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+      continue;
+    }
     for (int r = 0; r < nrows; ++r) {
       const int p = __shfl_sync(0xffffffffu, my_p, r);
       const int t = __shfl_sync(0xffffffffu, my_t, r);
@@ -202,11 +233,12 @@ ep_combine_pull_kernel(PeerTable ys, PeerTable dwrs, PeerTable flags, const int*
       float acc[V];
 #pragma unroll
       for (int c = 0; c < V; ++c) acc[c] = 0.f;
-      for (int j0 = 0; j0 < k; j0 += 4) {
-        uint4 q[4];
-        float wt[4];
+      // up to eight slots of the token in flight at once (one NVLink round trip per eight rows, not per four)
+      for (int j0 = 0; j0 < k; j0 += 8) {
+        uint4 q[8];
+        float wt[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
           const int j = j0 + u < k ? j0 + u : k - 1;
           const int d = __shfl_sync(0xffffffffu, my_d, j);
           const int row = __shfl_sync(0xffffffffu, my_row, j);
@@ -217,7 +249,7 @@ ep_combine_pull_kernel(PeerTable ys, PeerTable dwrs, PeerTable flags, const int*
           if (ok) q[u] = ld_volatile_v4(reinterpret_cast<const T*>(ys.ptr[d]) + (size_t)row * H + v0 * V);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
           const T* e = reinterpret_cast<const T*>(&q[u]);
 #pragma unroll
           for (int c = 0; c < V; ++c) acc[c] += wt[u] * Cvt<T>::to_f(e[c]);
