@@ -60,10 +60,12 @@ def run(args, init_group=True):
     model = MoEForCausalLM(cfg, ep_group=ep).cuda()
     if world > 1:
         mark_expert_parameters(model)
-        net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local])
+        net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_dtype="bfloat16")
     else:
         net = model
     opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
+    # the optimizer kernel keeps the bf16 copies of the weights (and the K-major twins of the 2-D ones) current
+    opt.enable_shadows(genesis.bfloat16, genesis.nn.utils.fused_parameter_groups(model))
     B, S = args.micro_batch, args.seq_len
     rs = np.random.RandomState(1000 + rank)
     host = [torch.from_numpy(rs.randint(0, cfg.vocab_size, (B, S)).astype(np.int64)).pin_memory() for _ in range(4)]
