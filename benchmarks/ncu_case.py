@@ -4,7 +4,7 @@
     python benchmarks/ncu_case.py <case>
     ncu --set full --clock-control none -k regex:<kernel> -c 2 -o prof python benchmarks/ncu_case.py <case>
 
-Cases (kernel to pass to -k): gemm_pair (gemm2_kernel), gemm_swiglu (gemm2_kernel), gemm (gemm_kernel),
+Cases (kernel to pass to -k): gemm_pair, gemm_swiglu, gemm_swiglu_bwd (gemm2_kernel), gemm (gemm_kernel),
 grouped_gemm (gemm_kernel), attn128_fwd (attn_fwd_kernel), attn128_bwd (attn_bwd_dq_kernel / attn_bwd_dkdv_kernel),
 attn64_fwd, attn64_bwd, ce (ce_fwd_kernel / ce_bwd_kernel), softmax (softmax_fwd), rmsnorm (rmsnorm_fwd / bwd),
 addnorm, adam (adam_multi_kernel), swiglu_bwd (swiglu_bwd2d_kernel), rope (rope_vec_kernel),
@@ -38,6 +38,11 @@ def gemm_pair():
 def gemm_swiglu():
     x, w = rnd(16384, 896), rnd(9728, 896, scale=0.05)
     return lambda: N.linear_swiglu(x, w)
+
+
+def gemm_swiglu_bwd():
+    gy, wd_t, gu = rnd(16384, 896), rnd(4864, 896, scale=0.05), rnd(16384, 9728)
+    return lambda: N.dgrad_swiglu_bwd(gy, wd_t, gu)
 
 
 def gemm():
@@ -149,7 +154,7 @@ def cat():
 
 
 CASES = {
-    "gemm_pair": gemm_pair, "gemm_swiglu": gemm_swiglu, "gemm": gemm, "grouped_gemm": grouped_gemm,
+    "gemm_pair": gemm_pair, "gemm_swiglu": gemm_swiglu, "gemm_swiglu_bwd": gemm_swiglu_bwd, "gemm": gemm, "grouped_gemm": grouped_gemm,
     "attn128_fwd": lambda: _attn(4, 4096, 16, 4, 128, False), "attn128_bwd": lambda: _attn(4, 4096, 16, 4, 128, True),
     "attn64_fwd": lambda: _attn(8, 2048, 14, 2, 64, False), "attn64_bwd": lambda: _attn(8, 2048, 14, 2, 64, True),
     "ce": ce, "softmax": softmax, "rmsnorm": rmsnorm, "addnorm": addnorm, "adam": adam, "swiglu_bwd": swiglu_bwd,

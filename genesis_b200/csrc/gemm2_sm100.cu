@@ -29,6 +29,7 @@
 //
 // Reference counterpart: the Triton `matmul_kernel`, genesis/ops/cuda/matrix_ops.py:21-294, and the SiLU kernels
 // of genesis/nn/triton_ops/silu.py:29-85.
+#include <type_traits>
 #include "sm100_ptx.cuh"
 #include "common.cuh"
 
@@ -130,6 +131,52 @@ __device__ __forceinline__ void tma2_load_3d(void* smem_dst, const CUtensorMap* 
       "[%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+
+// Ties 16 registers to this point of the instruction stream: placed after tcgen05.wait::ld, it keeps every use of
+// registers that an earlier tcgen05.ld fills asynchronously behind the wait.  Emits no instruction.
+__device__ __forceinline__ void reg_fence16(uint32_t (&r)[16]) {
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                    "+r"(r[15]));
+}
+
+__device__ __forceinline__ void reg_fence32(uint32_t (&r)[32]) {
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                    "+r"(r[15]));
+  asm volatile("" : "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
+                    "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                    "+r"(r[30]), "+r"(r[31]));
+}
+
+// two packed 16-bit values (low half first) -> floats
+template <bool BF16>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+  if (BF16) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x; hi = f.y;
+  }
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// 32 bytes from global memory through the read-only path (address 32-byte aligned)
+__device__ __forceinline__ void ld_nc_v8(uint32_t* r, const void* p) {
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(p));
 }
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.f + __expf(-x)); }
@@ -294,6 +341,28 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     uint8_t* slab_row = slab + lane * 128;
     const uint32_t empty0 = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     const int dt = p.out_dtype;
+    // SwiGLU backward: gate (ng) and up (nu) of the next 32-column step of this lane's row, fetched one step ahead
+    // with 32-byte read-only loads (two per 64-byte run, so every sector is requested once).  Rows past M and
+    // columns past N keep whatever the registers held: their results are clipped by the TMA store.
+    uint32_t ng[16], nu[16];
+    auto gu_fetch = [&](int mi2, int ni2, int k) {
+      const int row = mi2 * 2 * BM + (int)rank * BM + q * 32 + lane;
+      const int col = ni2 * p.bn + half * 64 + (k >> 1) * 128 + (k & 1) * 32;
+      if (row < p.M && col + 32 <= p.N) {
+        const uint16_t* g = reinterpret_cast<const uint16_t*>(p.gu) + (size_t)row * p.ld_gu + col;
+        ld_nc_v8(ng, g); ld_nc_v8(ng + 8, g + 16);
+        ld_nc_v8(nu, g + p.N); ld_nc_v8(nu + 8, g + p.N + 16);
+      }
+    };
+    if constexpr (EPI == EPI_SWIGLU_BWD) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { ng[i] = 0u; nu[i] = 0u; }
+      if (cluster_id < total_tiles) {
+        int mi2, ni2;
+        decode(cluster_id, mi2, ni2);
+        gu_fetch(mi2, ni2, 0);
+      }
+    }
     uint32_t tile_no = 0;
     for (long long t = cluster_id; t < total_tiles && !*abort_flag; t += nclusters) {
       int mi, ni;
@@ -312,31 +381,47 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const int h0 = ni * 128 + half * 64;
         if (lane == 0) bulk_wait_group_read<0>();
         __syncwarp();
+        auto run = [&](auto is_bf16) {
+          constexpr bool BF = decltype(is_bf16)::value;
+          // four steps of 16 hidden units; the accumulator columns of step s + 1 travel from tensor memory to
+          // registers while step s is computed
+          uint32_t ga[16], ua[16], gb_[16], ub[16];
+          auto step = [&](const uint32_t (&rg)[16], const uint32_t (&ru)[16], int s) {
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          uint32_t rg[32], ru[32];
-          tmem_ld_32x32b_x32(t_row + half * 64 + sub * 32, rg);
-          tmem_ld_32x32b_x32(t_row + 128 + half * 64 + sub * 32, ru);
-          tmem_ld_wait();
+            for (int u = 0; u < 2; ++u) {
+              float g[8], v[8], h[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float g[8], v[8], h[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              g[j] = __uint_as_float(rg[8 * u + j]) * p.alpha;
-              v[j] = __uint_as_float(ru[8 * u + j]) * p.alpha;
-              h[j] = silu_f(g[j]) * v[j];
+              for (int j = 0; j < 8; ++j) {
+                g[j] = __uint_as_float(rg[8 * u + j]) * p.alpha;
+                v[j] = __uint_as_float(ru[8 * u + j]) * p.alpha;
+                h[j] = g[j] * rcp_approx(1.f + ex2_approx(g[j] * -1.4426950408889634f)) * v[j];
+              }
+              const int unit = ((2 * s + u) ^ (lane & 7)) << 4;
+              uint4 o;
+              o.x = pack2c<BF>(g[0], g[1]); o.y = pack2c<BF>(g[2], g[3]); o.z = pack2c<BF>(g[4], g[5]); o.w = pack2c<BF>(g[6], g[7]);
+              *reinterpret_cast<uint4*>(slab_row + unit) = o;
+              o.x = pack2c<BF>(v[0], v[1]); o.y = pack2c<BF>(v[2], v[3]); o.z = pack2c<BF>(v[4], v[5]); o.w = pack2c<BF>(v[6], v[7]);
+              *reinterpret_cast<uint4*>(slab_row + SLAB_BYTES + unit) = o;
+              o.x = pack2c<BF>(h[0], h[1]); o.y = pack2c<BF>(h[2], h[3]); o.z = pack2c<BF>(h[4], h[5]); o.w = pack2c<BF>(h[6], h[7]);
+              *reinterpret_cast<uint4*>(slab_row + 2 * SLAB_BYTES + unit) = o;
             }
-            const int unit = ((4 * sub + u) ^ (lane & 7)) << 4;
-            uint4 o;
-            o.x = pack2(g[0], g[1], dt); o.y = pack2(g[2], g[3], dt); o.z = pack2(g[4], g[5], dt); o.w = pack2(g[6], g[7], dt);
-            *reinterpret_cast<uint4*>(slab_row + unit) = o;
-            o.x = pack2(v[0], v[1], dt); o.y = pack2(v[2], v[3], dt); o.z = pack2(v[4], v[5], dt); o.w = pack2(v[6], v[7], dt);
-            *reinterpret_cast<uint4*>(slab_row + SLAB_BYTES + unit) = o;
-            o.x = pack2(h[0], h[1], dt); o.y = pack2(h[2], h[3], dt); o.z = pack2(h[4], h[5], dt); o.w = pack2(h[6], h[7], dt);
-            *reinterpret_cast<uint4*>(slab_row + 2 * SLAB_BYTES + unit) = o;
-          }
-        }
+          };
+          const uint32_t tg = t_row + half * 64, tu = t_row + 128 + half * 64;
+          tmem_ld_32x32b_x16(tg, ga); tmem_ld_32x32b_x16(tu, ua);
+          tmem_ld_wait(); reg_fence16(ga); reg_fence16(ua);
+          tmem_ld_32x32b_x16(tg + 16, gb_); tmem_ld_32x32b_x16(tu + 16, ub);
+          step(ga, ua, 0);
+          tmem_ld_wait(); reg_fence16(gb_); reg_fence16(ub);
+          tmem_ld_32x32b_x16(tg + 32, ga); tmem_ld_32x32b_x16(tu + 32, ua);
+          step(gb_, ub, 1);
+          tmem_ld_wait(); reg_fence16(ga); reg_fence16(ua);
+          tmem_ld_32x32b_x16(tg + 48, gb_); tmem_ld_32x32b_x16(tu + 48, ub);
+          step(ga, ua, 2);
+          tmem_ld_wait(); reg_fence16(gb_); reg_fence16(ub);
+          step(gb_, ub, 3);
+        };
+        if (dt == DT_BF16) run(std::true_type{});
+        else run(std::false_type{});
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && y0 < p.M && h0 < p.N) {
@@ -348,70 +433,77 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           bulk_commit_group();
         }
       } else if constexpr (EPI == EPI_SWIGLU_BWD) {
-        // accumulator = dh[rows, n0 .. n0 + bn); this warp takes the 64-column units half, half + 2, ...
+        // accumulator = dh[rows, n0 .. n0 + 256); this warp takes the 64-column units half and half + 2 in four steps
+        // of 32 columns.  gate | up of step k + 1 (of the next tile after the last step) is already on its way to
+        // registers while step k is computed.  The element type is a compile-time constant inside `steps`: the
+        // epilogue is bound by instruction issue (two warps per scheduler), so every select on the type counts.
         const int n0 = ni * p.bn;
-        const int row = y0 + lane;
-        const bool row_ok = row < p.M;
-        const uint16_t* gu_row = reinterpret_cast<const uint16_t*>(p.gu) + (size_t)(row_ok ? row : 0) * p.ld_gu;
-        const bool bf = dt == DT_BF16;
-        for (int c = half * 64; c < p.bn; c += 128) {
-          if (n0 + c >= p.N) break;
-          if (lane == 0) bulk_wait_group_read<0>();
-          __syncwarp();
+        auto steps = [&](auto is_bf16) {
+          constexpr bool BF = decltype(is_bf16)::value;
 #pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            const int col = n0 + c + sub * 32;                 // hidden unit of the first of 32 columns
-            uint4 gq[4], uq[4];
-            const bool in = row_ok && col + 32 <= p.N;
+          for (int k = 0; k < 4; ++k) {
+            const int c = half * 64 + (k >> 1) * 128, sub = k & 1;
+            uint32_t cg[16], cu[16];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              gq[v] = make_uint4(0, 0, 0, 0);
-              uq[v] = make_uint4(0, 0, 0, 0);
-              if (in) {
-                gq[v] = *reinterpret_cast<const uint4*>(gu_row + col + v * 8);
-                uq[v] = *reinterpret_cast<const uint4*>(gu_row + p.N + col + v * 8);
-              }
+            for (int i = 0; i < 16; ++i) { cg[i] = ng[i]; cu[i] = nu[i]; }
+            if (k < 3) {
+              gu_fetch(mi, ni, k + 1);
+            } else if (t + nclusters < total_tiles) {
+              int mi2, ni2;
+              decode(t + nclusters, mi2, ni2);
+              gu_fetch(mi2, ni2, 0);
+            }
+            if (n0 + c >= p.N) continue;                      // warp-uniform: a unit past the last hidden column
+            if (sub == 0) {
+              if (lane == 0) bulk_wait_group_read<0>();
+              __syncwarp();
             }
             uint32_t rd[32];
             tmem_ld_32x32b_x32(t_row + c + sub * 32, rd);
             tmem_ld_wait();
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-              const uint16_t* gh = reinterpret_cast<const uint16_t*>(&gq[v]);
-              const uint16_t* uh = reinterpret_cast<const uint16_t*>(&uq[v]);
               float dg[8], du[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float x = half_bits_to_float(gh[j], bf ? DT_BF16 : DT_F16);
-                const float u = half_bits_to_float(uh[j], bf ? DT_BF16 : DT_F16);
-                const float dd = __uint_as_float(rd[8 * v + j]) * p.alpha;
-                const float sg = __fdividef(1.f, 1.f + __expf(-x));
-                dg[j] = dd * u * sg * (1.f + x * (1.f - sg));
-                du[j] = dd * x * sg;
+              for (int j = 0; j < 8; j += 2) {
+                float x2[2], u2[2];
+                unpack2<BF>(cg[4 * v + (j >> 1)], x2[0], x2[1]);
+                unpack2<BF>(cu[4 * v + (j >> 1)], u2[0], u2[1]);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  // s = sigmoid(x); d silu(x) u / dx = u s (1 + x (1 - s)); d silu(x) u / du = x s
+                  const float x = x2[e];
+                  const float s = rcp_approx(1.f + ex2_approx(x * -1.4426950408889634f));
+                  const float a = __uint_as_float(rd[8 * v + j + e]) * p.alpha * s;
+                  dg[j + e] = a * u2[e] * fmaf(x, 1.f - s, 1.f);
+                  du[j + e] = a * x;
+                }
               }
               const int unit = ((4 * sub + v) ^ (lane & 7)) << 4;
               uint4 o;
-              o.x = pack2(dg[0], dg[1], dt); o.y = pack2(dg[2], dg[3], dt); o.z = pack2(dg[4], dg[5], dt); o.w = pack2(dg[6], dg[7], dt);
+              o.x = pack2c<BF>(dg[0], dg[1]); o.y = pack2c<BF>(dg[2], dg[3]);
+              o.z = pack2c<BF>(dg[4], dg[5]); o.w = pack2c<BF>(dg[6], dg[7]);
               *reinterpret_cast<uint4*>(slab_row + unit) = o;
-              o.x = pack2(du[0], du[1], dt); o.y = pack2(du[2], du[3], dt); o.z = pack2(du[4], du[5], dt); o.w = pack2(du[6], du[7], dt);
+              o.x = pack2c<BF>(du[0], du[1]); o.y = pack2c<BF>(du[2], du[3]);
+              o.z = pack2c<BF>(du[4], du[5]); o.w = pack2c<BF>(du[6], du[7]);
               *reinterpret_cast<uint4*>(slab_row + SLAB_BYTES + unit) = o;
             }
+            if (sub == 1) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0 && y0 < p.M) {
+                tma_store_3d(&tmapD, slab, n0 + c, y0, 0);
+                tma_store_3d(&tmapD, slab + SLAB_BYTES, p.N + n0 + c, y0, 0);
+                bulk_commit_group();
+              }
+            }
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && y0 < p.M) {
-            tma_store_3d(&tmapD, slab, n0 + c, y0, 0);
-            tma_store_3d(&tmapD, slab + SLAB_BYTES, p.N + n0 + c, y0, 0);
-            bulk_commit_group();
-          }
-        }
+        };
+        if (dt == DT_BF16) steps(std::true_type{});
+        else steps(std::false_type{});
       } else {
         const int n0 = ni * p.bn;
-        for (int c = half * 64; c < p.bn; c += 128) {
-          uint32_t r[2][32];
-          tmem_ld_32x32b_x32(t_row + c, r[0]);
-          tmem_ld_32x32b_x32(t_row + c + 32, r[1]);
-          tmem_ld_wait();
+        auto process = [&](uint32_t (&r)[2][32], int c) {
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             const int col0 = n0 + c + hh * 32;
@@ -459,6 +551,25 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               }
             }
           }
+        };
+        // this warp's 64-column units: half, and half + 2 when the tile is wider than 128 + 64 half; the second
+        // unit's accumulator columns are on their way to registers while the first is converted and stored
+        const int c0 = half * 64;
+        const bool two = c0 + 128 < p.bn;
+        uint32_t ra[2][32], rb[2][32];
+        tmem_ld_32x32b_x32(t_row + c0, ra[0]);
+        tmem_ld_32x32b_x32(t_row + c0 + 32, ra[1]);
+        tmem_ld_wait();
+        reg_fence32(ra[0]); reg_fence32(ra[1]);
+        if (two) {
+          tmem_ld_32x32b_x32(t_row + c0 + 128, rb[0]);
+          tmem_ld_32x32b_x32(t_row + c0 + 160, rb[1]);
+        }
+        process(ra, c0);
+        if (two) {
+          tmem_ld_wait();
+          reg_fence32(rb[0]); reg_fence32(rb[1]);
+          process(rb, c0 + 128);
         }
       }
       tc_fence_before_sync();
@@ -549,7 +660,7 @@ extern "C" int gb_gemm_pair(const void* A, const void* B, void* D, void* D2, con
     // (read), D = d(gate) | d(up) [M, 2 N] (written).  N = hidden width, a multiple of 64.
     if (a_mn || b_mn || N % 64 != 0 || out_dtype == DT_F32 || bias != nullptr || D == nullptr || D2 == nullptr)
       return -5;
-    if ((reinterpret_cast<uintptr_t>(D2) & 15) != 0 || (ldd2 * 2) % 16 != 0) return -5;
+    if ((reinterpret_cast<uintptr_t>(D2) & 31) != 0 || (ldd2 * 2) % 32 != 0) return -5;   // 32-byte loads of gate | up
     p.bn = 256;
     p.gu = D2; p.ld_gu = ldd2;
     if ((r = make_tmap_3d(&ta, A, in_dtype, K, M, 1, lda, 0, g2::BM)) != 0) return 10000 + r;

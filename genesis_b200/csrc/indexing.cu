@@ -352,12 +352,35 @@ static int fill_index_args(IndexArgs& a, const void* const* idx, const int* meta
   return 0;
 }
 
+// Copies move bytes, so a contiguous innermost run may travel in wider units: returns the widest unit (<= 16 bytes)
+// that divides the innermost extent, every stride and both base addresses, after rescaling `a` to that unit.
+static int widen_index_units(IndexArgs& a, int es, const void* p0, const void* p1) {
+  if (a.npost < 1 || a.post_stride[a.npost - 1] != 1) return es;
+  for (int v = 16; v > es; v >>= 1) {
+    const int f = v / es;
+    bool ok = a.post_shape[a.npost - 1] % f == 0 &&
+              (reinterpret_cast<uintptr_t>(p0) | reinterpret_cast<uintptr_t>(p1)) % v == 0;
+    for (int d = 0; ok && d < a.npost - 1; ++d) ok = a.post_stride[d] % f == 0;
+    for (int d = 0; ok && d < a.npre; ++d) ok = a.pre_stride[d] % f == 0;
+    for (int k = 0; ok && k < a.nidx; ++k) ok = a.data_stride[k] % f == 0;
+    if (!ok) continue;
+    a.post_shape[a.npost - 1] /= f;
+    a.n_post /= f;
+    for (int d = 0; d < a.npost - 1; ++d) a.post_stride[d] /= f;
+    for (int d = 0; d < a.npre; ++d) a.pre_stride[d] /= f;
+    for (int k = 0; k < a.nidx; ++k) a.data_stride[k] /= f;
+    return v;
+  }
+  return es;
+}
+
 extern "C" int gb_index_get(const void* src, void* out, const void* const* idx, const int* meta,
                             const long long* dims, int es, int* status, cudaStream_t st) {
   IndexArgs a;
   if (int r = fill_index_args(a, idx, meta, dims)) return r;
+  if (a.n_pre * a.n_b * a.n_post == 0) return 0;
+  es = widen_index_units(a, es, src, out);
   const long long n = a.n_pre * a.n_b * a.n_post;
-  if (n == 0) return 0;
   GB_DISPATCH_BYTES(es, U, index_get_kernel<U><<<gb_grid(n, 256), 256, 0, st>>>(
       a, reinterpret_cast<const U*>(src), reinterpret_cast<U*>(out), status));
   return (int)cudaGetLastError();

@@ -632,7 +632,7 @@ def dgrad_swiglu_bwd(gy, wd_t, gu):
     I = wd_t.shape[0]
     if wd_t.dim() != 2 or wd_t.shape[1] != H or u2.shape != (M, 2 * I) or I % 64 or (H * 2) % 16 or M == 0 \
             or not (g2.is_contiguous() and wd_t.is_contiguous() and u2.is_contiguous()) \
-            or g2.data_ptr() % 16 or wd_t.data_ptr() % 16 or u2.data_ptr() % 16:
+            or g2.data_ptr() % 16 or wd_t.data_ptr() % 16 or u2.data_ptr() % 32:       # gate | up is read 32 bytes at a time
         return NotImplemented
     dgu = torch.empty(M, 2 * I, dtype=gy.dtype, device=gy.device)
     rc = lib().gb_gemm_pair(g2.data_ptr(), wd_t.data_ptr(), dgu.data_ptr(), u2.data_ptr(), None, M, I, H, H, H,
