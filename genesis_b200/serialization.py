@@ -33,11 +33,13 @@ class _Unpickler(dill.Unpickler):
 
 def _compat_dumps(obj):
     """Pickle with tensors referring to the global `genesis.tensor._rebuild_tensor`."""
-    fake = []
+    saved = {}
     mod = sys.modules.get("genesis.tensor")
-    if mod is not None and hasattr(mod, "_rebuild_tensor"):
-        hook = mod._rebuild_tensor
+    if mod is not None and getattr(getattr(mod, "_rebuild_tensor", None), "__module__", None) == "genesis.tensor":
+        hook = mod._rebuild_tensor                  # the reference itself is loaded: its own hook
     else:
+        # no `genesis` package, or the alias of this framework (whose hook pickles under this package's name):
+        # stand-in modules for the duration of the dump, the previous entries put back afterwards
         src = _rebuild
         hook = types.FunctionType(src.__code__, src.__globals__, "_rebuild_tensor")
         hook.__module__ = "genesis.tensor"
@@ -47,8 +49,9 @@ def _compat_dumps(obj):
         sub = types.ModuleType("genesis.tensor")
         sub._rebuild_tensor = hook
         pkg.tensor = sub
+        for k in ("genesis", "genesis.tensor"):
+            saved[k] = sys.modules.get(k)
         sys.modules["genesis"], sys.modules["genesis.tensor"] = pkg, sub
-        fake = ["genesis", "genesis.tensor"]
 
     class CompatPickler(dill.Pickler):
         def reducer_override(self, o):
@@ -61,8 +64,11 @@ def _compat_dumps(obj):
         CompatPickler(buf, protocol=4).dump(obj)
         return buf.getvalue()
     finally:
-        for k in fake:
-            sys.modules.pop(k, None)
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
 
 
 def save(state_dict, file_path, compat=False):
