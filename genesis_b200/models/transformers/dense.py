@@ -56,6 +56,10 @@ class FeedForward(nn.Module):
         self.gate_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=config.mlp_bias)
         self.up_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=config.mlp_bias)
         self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=config.mlp_bias)
+        if not config.mlp_bias:
+            # the fused backward of `F.swiglu_mlp` multiplies by the [in, out] twin of this weight: ask the optimizer's
+            # low-precision copies to keep one (`Optimizer.enable_shadows(transposed="auto")`)
+            self.down_proj.weight.wants_transposed_copy = True
 
     def forward(self, x):
         # gate and up projections as one GEMM over the stacked weights; SwiGLU reads the two halves in place

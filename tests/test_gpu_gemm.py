@@ -252,7 +252,7 @@ def test_swiglu_mlp_function_with_optimizer_kept_copies():
             nn.Linear(I, H, bias=False).cuda()
         params = [gate.weight, up.weight, down.weight]
         opt = genesis.optim.AdamW(params, lr=1e-3)
-        opt.enable_shadows(genesis.bfloat16, [[gate.weight, up.weight]])
+        opt.enable_shadows(genesis.bfloat16, [[gate.weight, up.weight]], transposed=True)
         x = genesis.Tensor(x0.clone().to(DEV), requires_grad=True)
         with genesis.amp.autocast(dtype=genesis.bfloat16):
             if fused:
