@@ -137,7 +137,8 @@ def run_ours(args):
     amp_dtype = genesis.bfloat16 if args.dtype == "bf16" else genesis.float16
     # gradients cross NVLink in the compute dtype (accumulated and handed back in float32) unless --grad-wire fp32
     wire = None if args.grad_wire == "fp32" else amp_dtype
-    net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_dtype=wire) \
+    net = genesis.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_dtype=wire,
+                                                       bucket_cap_mb=args.bucket_mb) \
         if world > 1 else model
     opt = genesis.optim.AdamW(model.parameters(), lr=3e-4)
     if not args.no_shadows:
@@ -373,6 +374,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--grad-wire", default="16bit", choices=["16bit", "fp32"],
                     help="format of the gradients on NVLink under data parallelism (float32 results either way)")
+    ap.add_argument("--bucket-mb", type=float, default=None,
+                    help="gradient bucket size of DistributedDataParallel (default: the framework's, 100 MB; the reference's config 3 names 25)")
     ap.add_argument("--moe", default="auto", choices=["auto", "on", "off"],
                     help="also time the expert-parallel Qwen3-MoE-shaped model and report it as `moe_ep` "
                          "(auto: on 8 GPUs, where its 24 layers fit)")

@@ -37,21 +37,60 @@ def flush_l2():
     _flush.fill_(1)
 
 
-def timeit(fn, iters=10, warmup=3):
+ITERS = 20
+_nvml = None
+
+
+def sm_mhz():
+    """Current SM clock (read-only NVML query), or None without NVML."""
+    global _nvml
+    try:
+        import pynvml
+        if _nvml is None:
+            pynvml.nvmlInit()
+            _nvml = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        return pynvml.nvmlDeviceGetClockInfo(_nvml, pynvml.NVML_CLOCK_SM)
+    except Exception:
+        return None
+
+
+last_clock = None
+
+
+def timeit(fn, iters=None, warmup=3):
+    """Median of `iters` CUDA-event timings (L2 flushed before each) after dropping samples outside 1.5 IQR of the
+    quartiles; the SM clock sampled right after the last launch is left in `last_clock`."""
+    global last_clock
+    iters = iters or ITERS
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    ts = []
+    ts, clk = [], []
     for _ in range(iters):
         flush_l2()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
         b.record()
+        c = sm_mhz()                      # the kernel is still running or has just ended
         torch.cuda.synchronize()
         ts.append(a.elapsed_time(b))
+        if c:
+            clk.append(c)
     ts.sort()
+    if len(ts) >= 8:
+        q1, q3 = ts[len(ts) // 4], ts[(3 * len(ts)) // 4]
+        lo, hi = q1 - 1.5 * (q3 - q1), q3 + 1.5 * (q3 - q1)
+        ts = [t for t in ts if lo <= t <= hi] or ts
+    clk.sort()
+    last_clock = clk[len(clk) // 2] if clk else None
     return ts[len(ts) // 2]
+
+
+def emit(rec):
+    rec["sm_mhz"] = last_clock
+    rec.setdefault("repeats", ITERS)
+    print(json.dumps(rec), flush=True)
 
 
 def main():
@@ -60,9 +99,11 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--torch", action="store_true", help="also time the torch/cuBLAS op for comparison")
     ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D of a single attention case")
-    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--gemm-shape", default=None, help="M,N,K of a single linear-forward case (y = x @ w^T)")
     a = ap.parse_args()
+    global ITERS
+    ITERS = a.iters
     hbm, tf, src = peaks()
     what = a.what.split(",")
     dev = "cuda"
@@ -70,12 +111,12 @@ def main():
         m, nn, k = [int(v) for v in a.gemm_shape.split(",")]
         X = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
         W = torch.randn(nn, k, device=dev, dtype=torch.bfloat16)
-        ms = timeit(lambda: K.linear(X, W), iters=a.iters, warmup=min(3, a.iters))
+        ms = timeit(lambda: K.linear(X, W))
         rec = {"kernel": "linear_fwd", "M": m, "N": nn, "K": k, "ms": ms, "tflops": 2 * m * nn * k / ms / 1e9,
                "frac_of_" + src: 2 * m * nn * k / ms / 1e9 / tf}
         if a.torch:
-            rec["torch_ms"] = timeit(lambda: torch.matmul(X, W.t()), iters=a.iters, warmup=min(3, a.iters))
-        print(json.dumps(rec), flush=True)
+            rec["torch_ms"] = timeit(lambda: torch.matmul(X, W.t()))
+        emit(rec)
         return
     if "gemm" in what:
         # (run first, before the large squares heat the part into its power cap)
@@ -89,14 +130,14 @@ def main():
             G = torch.randn(m, nn, device=dev, dtype=torch.bfloat16)
             for name, fn in [("fwd", lambda: K.linear(X, W)), ("dgrad", lambda: K.linear_dgrad(G, W)),
                              ("wgrad", lambda: K.linear_wgrad(G, X, out_dtype=torch.float32))]:
-                ms = timeit(fn, iters=5)
+                ms = timeit(fn)
                 rec = {"kernel": f"linear_{name}", "shape": tag, "M": m, "N": nn, "K": k, "ms": ms,
                        "tflops": 2 * m * nn * k / ms / 1e9, "frac_of_" + src: 2 * m * nn * k / ms / 1e9 / tf}
                 if a.torch:
                     tfn = {"fwd": lambda: torch.matmul(X, W.t()), "dgrad": lambda: torch.matmul(G, W),
                            "wgrad": lambda: torch.matmul(G.t(), X)}[name]
-                    rec["torch_ms"] = timeit(tfn, iters=5)
-                print(json.dumps(rec), flush=True)
+                    rec["torch_ms"] = timeit(tfn)
+                emit(rec)
             del X, W, G
         sizes = [1024, 2048, 4096, 8192] + ([] if a.quick else [16384])
         for n in sizes:
@@ -108,7 +149,7 @@ def main():
             if a.torch:
                 mt = timeit(lambda: torch.matmul(A, B.t()))
                 rec["torch_ms"] = mt
-            print(json.dumps(rec), flush=True)
+            emit(rec)
     if "norm" in what or "softmax" in what:
         for cols in [1024, 4096, 16384]:
             x = torch.randn(8192, cols, device=dev, dtype=torch.bfloat16)
@@ -116,13 +157,13 @@ def main():
             if "norm" in what:
                 ms = timeit(lambda: K.rmsnorm_fwd(x, w, 1e-6))
                 gbs = 2 * x.numel() * 2 / ms / 1e6
-                print(json.dumps({"kernel": "rmsnorm_fwd", "rows": 8192, "cols": cols, "ms": ms, "GBs": gbs,
-                                  "frac_of_" + src: gbs / hbm}), flush=True)
+                emit({"kernel": "rmsnorm_fwd", "rows": 8192, "cols": cols, "ms": ms, "GBs": gbs,
+                                  "frac_of_" + src: gbs / hbm})
             if "softmax" in what:
                 ms = timeit(lambda: K.softmax_fwd(x, -1))
                 gbs = 2 * x.numel() * 2 / ms / 1e6
-                print(json.dumps({"kernel": "softmax_fwd", "rows": 8192, "cols": cols, "ms": ms, "GBs": gbs,
-                                  "frac_of_" + src: gbs / hbm}), flush=True)
+                emit({"kernel": "softmax_fwd", "rows": 8192, "cols": cols, "ms": ms, "GBs": gbs,
+                                  "frac_of_" + src: gbs / hbm})
     if "addnorm" in what:
         # residual addition + RMSNorm at the residual-stream shape of the 0.5B model (16384 tokens x 896)
         rows, cols = 16384, 896
@@ -132,11 +173,11 @@ def main():
         s_, y_, rstd = K.add_rmsnorm_fwd(x, r, w, 1e-6)
         unit = rows * cols * 2
         ms = timeit(lambda: K.add_rmsnorm_fwd(x, r, w, 1e-6))
-        print(json.dumps({"kernel": "add_rmsnorm_fwd", "rows": rows, "cols": cols, "ms": ms, "GBs": 4 * unit / ms / 1e6,
-                          "frac_of_" + src: 4 * unit / ms / 1e6 / hbm}), flush=True)
+        emit({"kernel": "add_rmsnorm_fwd", "rows": rows, "cols": cols, "ms": ms, "GBs": 4 * unit / ms / 1e6,
+                          "frac_of_" + src: 4 * unit / ms / 1e6 / hbm})
         ms = timeit(lambda: K.add_rmsnorm_bwd(y_, r, s_, w, rstd))
-        print(json.dumps({"kernel": "add_rmsnorm_bwd", "rows": rows, "cols": cols, "ms": ms, "GBs": 4 * unit / ms / 1e6,
-                          "frac_of_" + src: 4 * unit / ms / 1e6 / hbm}), flush=True)
+        emit({"kernel": "add_rmsnorm_bwd", "rows": rows, "cols": cols, "ms": ms, "GBs": 4 * unit / ms / 1e6,
+                          "frac_of_" + src: 4 * unit / ms / 1e6 / hbm})
     if "adamw" in what:
         n = 250_000_000 if a.quick else 1_000_000_000
         p = torch.zeros(n, device=dev)
@@ -144,8 +185,7 @@ def main():
         m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
         ms = timeit(lambda: K.adamw_step([p], [g], [m], [v], 1e-3, 0.9, 0.999, 1e-8, 0.01, 1), iters=5)
         gbs = n * 28 / ms / 1e6
-        print(json.dumps({"kernel": "adamw_multi_tensor", "params": n, "ms": ms, "GBs": gbs,
-                          "frac_of_" + src: gbs / hbm}), flush=True)
+        emit({"kernel": "adamw_multi_tensor", "params": n, "ms": ms, "GBs": gbs, "frac_of_" + src: gbs / hbm, "repeats": 5})
     if "attn" in what:
         cases = [(8, S, 16, 4, 128) for S in [1024, 4096] + ([] if a.quick else [16384])]
         if a.attn_shape:
@@ -158,7 +198,7 @@ def main():
             if r is NotImplemented:
                 print(json.dumps({"kernel": "attention_fwd", "S": S, "status": "not implemented"}))
                 continue
-            ms = timeit(lambda: N.attention_fwd(q, k, v, True, D ** -0.5), iters=a.iters, warmup=min(3, a.iters))
+            ms = timeit(lambda: N.attention_fwd(q, k, v, True, D ** -0.5))
             fl = 4 * B * Hq * S * S * D / 2
             rec = {"kernel": "attention_fwd", "B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "D": D, "ms": ms,
                    "tflops": fl / ms / 1e9}
@@ -169,7 +209,7 @@ def main():
                 msb = timeit(lambda: N.attention_bwd(do, q, k, v, o, lse, True, D ** -0.5), iters=a.iters,
                              warmup=min(3, a.iters))
                 rec.update({"bwd_ms": msb, "bwd_tflops": 2.5 * fl / msb / 1e9})
-            print(json.dumps(rec), flush=True)
+            emit(rec)
     N.check_status()
 
 

@@ -52,7 +52,7 @@ class _Bucket:
 class DistributedDataParallel(Module):
     def __init__(self, model, device_ids=None, output_device=None, broadcast_buffers=True,
                  find_unused_parameters=False, gradient_as_bucket_view=False, bucket_cap_mb=None,
-                 grad_scaler=None, gradient_dtype=None):
+                 grad_scaler=None, gradient_dtype=None, overlap_optimizer=None):
         super().__init__()
         if not pg.is_initialized():
             raise RuntimeError("Process group not initialized. Call genesis.distributed.init_process_group() first")
@@ -66,7 +66,18 @@ class DistributedDataParallel(Module):
         self.broadcast_buffers = broadcast_buffers
         self.find_unused_parameters = find_unused_parameters
         self.bucket_cap_bytes = int(float(bucket_cap_mb if bucket_cap_mb is not None
-                                          else os.environ.get("GENESIS_DDP_BUCKET_MB", 25)) * 1024 * 1024)
+                                          else os.environ.get("GENESIS_DDP_BUCKET_MB", 100)) * 1024 * 1024)
+        # The bucket that completes last (with tied embeddings: the embedding / output matrix, whose gradient is final
+        # only when backward ends) is still being reduced when the optimizer starts.  With `overlap_optimizer` the
+        # end of backward waits for every bucket but that one, tags its parameters with a join callback, and
+        # `Optimizer.step` updates all other parameters first, joins, then updates the tagged ones: the tail of the
+        # communication hides behind the optimizer kernel.  Anything else that reads those gradients first must call
+        # `join_gradients()` (`clip_grad_norm_` does).  Off with a GradScaler: its overflow flag is complete only when
+        # the last bucket is.  Default: on (GENESIS_DDP_OVERLAP_OPT=0 turns it off).
+        self._overlap_opt = bool(int(os.environ.get("GENESIS_DDP_OVERLAP_OPT", "1"))) if overlap_optimizer is None \
+            else bool(overlap_optimizer)
+        self._early_done = None
+        self._late_params = []
         self._sync = True
         self._scaler = grad_scaler
         # 16-bit wire format (`gradient_dtype="bfloat16"` / "float16", or GENESIS_DDP_GRAD_DTYPE): gradients stay
@@ -233,6 +244,9 @@ class DistributedDataParallel(Module):
             return
         if self._on_cuda:
             st = self._comm_stream
+            if self._tail_overlap() and b is self._buckets[-1]:
+                self._early_done = torch.cuda.Event()
+                self._early_done.record(st)          # every earlier bucket has been reduced at this point
             if b.ready_event is not None:
                 st.wait_event(b.ready_event)
             else:
@@ -290,8 +304,15 @@ class DistributedDataParallel(Module):
             else:
                 for g in grads:
                     K.mul_(g, 1.0 / self.world_size)
-        if self._on_cuda:
-            torch.cuda.current_stream().wait_stream(self._comm_stream)
+        if self._on_cuda and self._debug_comm != "skip":     # (nothing was launched on the stream when skipping)
+            if self._early_done is not None:
+                torch.cuda.current_stream().wait_event(self._early_done)
+                self._early_done = None
+                self._late_params = list(self._buckets[-1].params)
+                for p in self._late_params:
+                    p._late_join = self.join_gradients
+            else:
+                torch.cuda.current_stream().wait_stream(self._comm_stream)
         if fused_unscale:
             self._scaler._external_unscale = True
         if self._use_symm:
@@ -303,6 +324,19 @@ class DistributedDataParallel(Module):
             if self._probe is not None:
                 self._probe.arm()
 
+    def _tail_overlap(self):
+        return self._overlap_opt and self._use_symm and not self._debug_comm and len(self._buckets) > 1 \
+            and (self._scaler is None or not self._scaler.is_enabled())
+
+    def join_gradients(self):
+        """Make the current stream wait for the bucket all-reduce that `overlap_optimizer` left in flight at the end
+        of backward.  Idempotent; called by `Optimizer.step`, `clip_grad_norm_` and the next forward."""
+        if self._late_params:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+            for p in self._late_params:
+                p._late_join = None
+            self._late_params = []
+
     def check_comm(self, wait=False):
         """Raise `CommTimeout` if a bucket all-reduce of an earlier step gave up waiting for a peer (its buckets
         then hold unreduced gradients).  Non-blocking unless `wait`; called by `forward` on every step."""
@@ -310,6 +344,7 @@ class DistributedDataParallel(Module):
             self._probe.poll("DistributedDataParallel gradient all-reduce", wait=wait)
 
     def _arm(self):
+        self.join_gradients()
         self.check_comm()
         self._armed = True
         self._next_launch = 0

@@ -28,6 +28,8 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2, sync=True):
     params = [p for p in parameters if p.grad is not None]
     if not params:
         return 0.0
+    for j in {id(f): f for f in (getattr(p, "_late_join", None) for p in params) if f is not None}.values():
+        j()                                   # a data-parallel wrapper left a bucket all-reduce in flight: wait for it
     grads = [p.grad._t for p in params]
     if norm_type == 2:
         acc = torch.zeros(1, dtype=torch.float32, device=grads[0].device)

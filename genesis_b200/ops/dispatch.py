@@ -814,7 +814,7 @@ def random_fill(kind, shape, dtype, device, seed, offset, a=0.0, b=1.0):
 
 # ================================== optimisers ===================================
 def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled=True,
-               grad_scale=None, found_inf=None, shadows=None, dyn=None):
+               grad_scale=None, found_inf=None, shadows=None, dyn=None, advance=True):
     """Multi-tensor Adam/AdamW over lists of tensors, in place.
 
     decoupled=True: p *= 1 - lr*wd, then Adam update (AdamW, reference `optim/adamw.py:9-64`);
@@ -822,10 +822,12 @@ def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step,
     `grad_scale` (1-elem fp32 tensor) multiplies gradients; `found_inf` (1-elem fp32
     tensor, non-zero = skip) turns the whole step into a no-op without a host sync.
     `shadows`: optional low-precision copies of the parameters refreshed by the same pass.
+    `advance=False`: a further launch of the SAME step (its parameters are updated with the step count and bias
+    corrections the first launch advanced `dyn` to).
     """
     if params and params[0].is_cuda:
         r = N.adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled,
-                         grad_scale, found_inf, shadows, dyn)
+                         grad_scale, found_inf, shadows, dyn, advance)
         if r is not NotImplemented:
             return
         _fell("adamw_step")

@@ -1212,7 +1212,7 @@ def _opt_ok(params, grads, states):
 
 
 def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step, decoupled, grad_scale, found_inf,
-               shadows, dyn=None):
+               shadows, dyn=None, advance=True):
     """`dyn` (device fp32 [4]: lr, bias corrections, step count) moves the step-dependent scalars to the device:
     the kernel advances the count itself, so the launch sequence can be replayed from a CUDA graph."""
     if not _opt_ok(params, grads, (ms, vs)):
@@ -1231,7 +1231,8 @@ def adamw_step(params, grads, ms, vs, lr, beta1, beta2, eps, weight_decay, step,
     dp = None
     if dyn is not None:
         dp = dyn.data_ptr()
-        _chk(lib().gb_adam_dyn_advance(dp, float(beta1), float(beta2), fi, _st()), "adam_dyn_advance")
+        if advance:
+            _chk(lib().gb_adam_dyn_advance(dp, float(beta1), float(beta2), fi, _st()), "adam_dyn_advance")
     _chk(lib().gb_adam_multi(meta.data_ptr(), nt, total, float(lr), float(beta1), float(beta2), float(eps),
                              float(weight_decay), 1.0 - beta1 ** step, 1.0 - beta2 ** step, 1 if decoupled else 0,
                              sdt, gs, fi, dp, _st()), "adam_multi")

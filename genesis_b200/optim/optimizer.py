@@ -260,16 +260,25 @@ class _AdamBase(Optimizer):
                 and float(self._found_inf.item()) != 0.0:
             return                                # cancelled step (host tensors: the flag is read here)
         self.t += 1
-        ps = [self.params[i]._t for i in idx]
-        gs = [self.params[i].grad._t for i in idx]
-        ms = [self._state(self.m, i) for i in idx]
-        vs = [self._state(self.v, i) for i in idx]
-        sh = None if self._shadows is None else [self._shadows.get(i) for i in idx]
         if self._dyn is not None and not torch.cuda.is_current_stream_capturing():
             self._sync_lr()
-        K.adamw_step(ps, gs, ms, vs, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.t,
-                     self.decoupled, self._grad_scale, self._found_inf, sh, self._dyn)
-        if sh is not None:
+        # parameters whose gradient all-reduce a data-parallel wrapper left in flight (`_late_join`) are updated in a
+        # second launch, after the join: the first launch runs under the tail of the communication
+        late = [i for i in idx if getattr(self.params[i], "_late_join", None) is not None]
+        parts = [idx] if not late or len(late) == len(idx) else [[i for i in idx if i not in set(late)], late]
+        for n, part in enumerate(parts):
+            if late and (n == len(parts) - 1):
+                for j in {id(f): f for f in (self.params[i]._late_join for i in late)}.values():
+                    if j is not None:
+                        j()
+            ps = [self.params[i]._t for i in part]
+            gs = [self.params[i].grad._t for i in part]
+            ms = [self._state(self.m, i) for i in part]
+            vs = [self._state(self.v, i) for i in part]
+            sh = None if self._shadows is None else [self._shadows.get(i) for i in part]
+            K.adamw_step(ps, gs, ms, vs, self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.t,
+                         self.decoupled, self._grad_scale, self._found_inf, sh, self._dyn, advance=(n == 0))
+        if self._shadows is not None:
             self._refresh_transposed()
         self._touched(idx)
 

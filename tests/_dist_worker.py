@@ -88,12 +88,12 @@ def scenario_collectives(a):
     # rank r sends (d + 1 + r) rows of 24 bf16 values to rank d
     send_rows = [dd + 1 + r for dd in range(w)]
     recv_rows = [r + 1 + s_ for s_ in range(w)]
-    inp = torch.cat([torch.full((send_rows[dd], 24), float(100 * r + dd), device=d) for dd in range(w)]).to(torch.bfloat16)
+    inp = torch.cat([torch.full((send_rows[dd], 24), float(10 * r + dd), device=d) for dd in range(w)]).to(torch.bfloat16)
     res = torch.zeros(sum(recv_rows), 24, dtype=torch.bfloat16, device=d)
     dist.all_to_all_single(res, inp, recv_rows, send_rows)
     pos = 0
     for s_ in range(w):
-        assert torch.all(res[pos:pos + recv_rows[s_]].float() == float(100 * s_ + r)), ("a2a", s_)
+        assert torch.all(res[pos:pos + recv_rows[s_]].float() == float(10 * s_ + r)), ("a2a", s_)
         pos += recv_rows[s_]
     dist.barrier()
 
