@@ -25,13 +25,19 @@ def _free_port():
 
 
 def launch(scenario, world=2, backend="gloo", timeout=240, env=None):
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           os.path.join(HERE, "_dist_worker.py"), "--scenario", scenario, "--backend", backend]
     e = {**os.environ, "OMP_NUM_THREADS": "2", **(env or {})}
     if backend == "gloo":
         e["CUDA_VISIBLE_DEVICES"] = ""
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
+    for attempt in range(3):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+               os.path.join(HERE, "_dist_worker.py"), "--scenario", scenario, "--backend", backend]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
+        # the port probed as free can be taken again before the rendezvous binds it (another job on the machine):
+        # that is not a result of the scenario, so pick another one
+        if r.returncode != 0 and "EADDRINUSE" in r.stderr and attempt < 2:
+            continue
+        break
     assert r.returncode == 0 and r.stdout.count("WORKER_OK") == world, f"stdout:\n{r.stdout[-3000:]}\nstderr:\n{r.stderr[-3000:]}"
 
 
