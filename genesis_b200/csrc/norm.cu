@@ -5,6 +5,7 @@
 // Reference counterparts: genesis/nn/triton_ops/rmsnorm.py:14-126, genesis/nn/layer_norm.py:15-213,
 // genesis/nn/triton_ops/layer_norm.py:16-133.
 #include "common.cuh"
+#include "row_stream.cuh"
 
 namespace gb {
 
@@ -534,6 +535,59 @@ static int rmsnorm_fwd_impl(const void* x, const void* w, void* y, float* rstd, 
   NORM_DISPATCH(dt, wdt, cols, rmsnorm_fwd_kernel<T, TW, MV><<<grid, NORM_THREADS, 0, st>>>(
       (const T*)x, (const TW*)w, (T*)y, rstd, rows, cols, eps, (const T*)res, (T*)sum_out));
   return (int)cudaGetLastError();
+}
+
+// RMSNorm forward of rows of 8 KB and more through the streamed-row skeleton (csrc/row_stream.cuh)
+namespace gb {
+template <typename T, typename TW>
+struct RmsRowOp {
+  const TW* w; T* y; float* rstd; float eps;
+  __device__ __forceinline__ void row(const T* s, long long r, int cols, float* sh) const {
+    constexpr int V = Vec16<T>::N;
+    const int nv = cols / V;
+    float ss = 0.f;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+      for (int j = 0; j < V; ++j) { const float v = Cvt<T>::to_f(a.v[j]); ss += v * v; }
+    }
+    ss = block_sum(ss, sh);
+    const float rr = rsqrtf(ss / cols + eps);
+    if (threadIdx.x == 0) rstd[r] = rr;
+    T* out = y + r * cols;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+      float wv[V];
+      load_weights<TW, V>(w, i * V, wv);
+      Vec16<T> o;
+#pragma unroll
+      for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(a.v[j]) * rr * wv[j]);
+      st16(out + (size_t)i * V, o);
+    }
+  }
+};
+}  // namespace gb
+
+// Same contract as gb_rmsnorm_fwd for rows of 8 to 64 KB; returns -9 when the shape does not qualify (the caller then
+// uses gb_rmsnorm_fwd).  `status`: the library's status word (a copy that never arrives is reported there).
+extern "C" int gb_rmsnorm_fwd_stream(const void* x, const void* w, void* y, float* rstd, long long rows, int cols,
+                                     float eps, int dt, int wdt, int* status, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int es = dt == DT_F32 ? 4 : 2;
+  if (!rs_shape_ok(x, rows, cols, es) || (reinterpret_cast<uintptr_t>(y) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(w) & 15) != 0)
+    return -9;
+  static unsigned long long cfg[5] = {0, 0, 0, 0, 0};
+#define RS_RMS(T, TW, k) return rs_launch<T, RmsRowOp<T, TW>>((const T*)x, rows, cols, RmsRowOp<T, TW>{(const TW*)w, (T*)y, rstd, eps}, status, cfg[k], st)
+  if (dt == DT_F32 && wdt == DT_F32) RS_RMS(float, float, 0);
+  if (dt == DT_BF16 && wdt == DT_F32) RS_RMS(__nv_bfloat16, float, 1);
+  if (dt == DT_F16 && wdt == DT_F32) RS_RMS(__half, float, 2);
+  if (dt == DT_BF16 && wdt == DT_BF16) RS_RMS(__nv_bfloat16, __nv_bfloat16, 3);
+  if (dt == DT_F16 && wdt == DT_F16) RS_RMS(__half, __half, 4);
+#undef RS_RMS
+  return -9;
 }
 
 static int rmsnorm_bwd_impl(const void* g, const void* x, const void* w, const float* rstd, void* dx,

@@ -5,6 +5,7 @@
 // Reference counterparts: genesis/nn/triton_ops/softmax.py:33-480 and the composed loss of
 // genesis/nn/modules/loss.py:77-100 / genesis/nn/functional.py:2313-2506.
 #include "common.cuh"
+#include "row_stream.cuh"
 
 namespace gb {
 
@@ -72,7 +73,7 @@ __global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, l
     T* q = y + row * cols;
     const MaxSum ms = row_maxsum(p, cols, sh);
     const float lse = ms.m + __logf(ms.s);
-    const float inv = 1.f / ms.s;
+    const float inv = ms.s > 0.f ? 1.f / ms.s : 0.f;
     for (long long i = threadIdx.x; i < cols; i += blockDim.x) {
       const float v = Cvt<T>::to_f(p[i]);
       q[i] = Cvt<T>::from_f(log_mode ? v - lse : __expf(v - ms.m) * inv);
@@ -114,7 +115,7 @@ softmax_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, long long row
 #pragma unroll
         for (int j = 0; j < V; ++j) sum += __expf(Cvt<T>::to_f(buf[k].v[j]) - m);
     sum = block_sum(sum, sh);
-    const float inv = 1.f / sum, lse = m + __logf(sum);
+    const float inv = sum > 0.f ? 1.f / sum : 0.f, lse = m + __logf(sum);   // all -inf: zeros
 #pragma unroll
     for (int k = 0; k < MV; ++k) {
       const int i = threadIdx.x + k * SM_THREADS;
@@ -245,6 +246,59 @@ ce_bwd_kernel(const T* __restrict__ logits, const TI* __restrict__ target, const
   }
 }
 
+// Narrow rows (up to 128 16-byte vectors): one warp per row, eight rows in flight per CTA, shuffles instead of block
+// barriers, the exponentials kept in registers between the sum and the output pass (one exp per element).
+template <typename T, int MVW>
+__global__ void __launch_bounds__(SM_THREADS)
+softmax_fwd_warp_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int cols, int log_mode) {
+  constexpr int V = Vec16<T>::N;
+  constexpr float L2E = 1.4426950408889634f;
+  const int nv = cols / V;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (SM_THREADS / 32);
+  for (long long row = (long long)blockIdx.x * (SM_THREADS / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const T* p = x + row * cols;
+    Vec16<T> buf[MVW];
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+      if (lane + 32 * k < nv) buf[k] = ld16(p + (long long)(lane + 32 * k) * V);
+    float e[MVW][V];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < MVW; ++k)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        e[k][j] = (lane + 32 * k < nv) ? Cvt<T>::to_f(buf[k].v[j]) : -INFINITY;
+        mx = fmaxf(mx, e[k][j]);
+      }
+    mx = warp_max(mx);
+    const float m = mx == -INFINITY ? 0.f : mx;
+    float sum = 0.f;
+    if (log_mode) {
+#pragma unroll
+      for (int k = 0; k < MVW; ++k)
+#pragma unroll
+        for (int j = 0; j < V; ++j) sum += exp2f((e[k][j] - m) * L2E);
+    } else {
+#pragma unroll
+      for (int k = 0; k < MVW; ++k)
+#pragma unroll
+        for (int j = 0; j < V; ++j) { e[k][j] = exp2f((e[k][j] - m) * L2E); sum += e[k][j]; }
+    }
+    sum = warp_sum(sum);
+    const float inv = sum > 0.f ? 1.f / sum : 0.f, lse = m + __logf(sum);   // all -inf: zeros
+#pragma unroll
+    for (int k = 0; k < MVW; ++k) {
+      if (lane + 32 * k < nv) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(log_mode ? e[k][j] - lse : e[k][j] * inv);
+        st16(y + row * cols + (long long)(lane + 32 * k) * V, o);
+      }
+    }
+  }
+}
+
 }  // namespace gb
 
 using namespace gb;
@@ -260,6 +314,16 @@ extern "C" int gb_softmax_fwd(const void* x, void* y, long long rows, long long 
                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   if (reg) {
     const long long nv = cols / vlen;
+    if (nv <= 128 && rows >= 64) {
+      const long long want = (rows + SM_THREADS / 32 - 1) / (SM_THREADS / 32);
+      const int wgrid = (int)(want < 148 * 8 ? want : 148 * 8);
+#define SM_WARP(MVV) GB_DISPATCH_FLOAT(dt, T, softmax_fwd_warp_kernel<T, MVV><<<wgrid, SM_THREADS, 0, st>>>((const T*)x, (T*)y, rows, (int)cols, log_mode))
+      if (nv <= 32) SM_WARP(1);
+      else if (nv <= 64) SM_WARP(2);
+      else SM_WARP(4);
+#undef SM_WARP
+      return (int)cudaGetLastError();
+    }
 #define SM_FWD(MVV) GB_DISPATCH_FLOAT(dt, T, softmax_fwd_reg_kernel<T, MVV><<<grid, SM_THREADS, 0, st>>>((const T*)x, (T*)y, rows, (int)cols, log_mode))
     if (nv <= SM_THREADS) SM_FWD(1);
     else if (nv <= 2 * SM_THREADS) SM_FWD(2);
@@ -270,6 +334,63 @@ extern "C" int gb_softmax_fwd(const void* x, void* y, long long rows, long long 
   }
   GB_DISPATCH_FLOAT(dt, T, softmax_fwd_kernel<T><<<grid, row_block(cols), 0, st>>>((const T*)x, (T*)y, rows, cols, log_mode));
   return (int)cudaGetLastError();
+}
+
+// Softmax / log-softmax forward of rows of 8 KB and more through the streamed-row skeleton (csrc/row_stream.cuh)
+namespace gb {
+template <typename T>
+struct SoftmaxRowOp {
+  T* y; int log_mode;
+  __device__ __forceinline__ void row(const T* s, long long r, int cols, float* sh) const {
+    constexpr int V = Vec16<T>::N;
+    constexpr float L2E = 1.4426950408889634f;
+    const int nv = cols / V;
+    float mx = -INFINITY;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+      for (int j = 0; j < V; ++j) mx = fmaxf(mx, Cvt<T>::to_f(a.v[j]));
+    }
+    mx = block_max(mx, sh);
+    const float m = mx == -INFINITY ? 0.f : mx;            // a row of -inf gives zeros, not NaN
+    const float m2 = m * L2E;
+    float sum = 0.f;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+      for (int j = 0; j < V; ++j) sum += exp2f(fmaf(Cvt<T>::to_f(a.v[j]), L2E, -m2));
+    }
+    sum = block_sum(sum, sh);
+    const float inv = sum > 0.f ? 1.f / sum : 0.f, lse = m + __logf(sum);   // all -inf: zeros
+    T* out = y + r * cols;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+      Vec16<T> o;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float v = Cvt<T>::to_f(a.v[j]);
+        o.v[j] = Cvt<T>::from_f(log_mode ? v - lse : exp2f(fmaf(v, L2E, -m2)) * inv);
+      }
+      st16(out + (size_t)i * V, o);
+    }
+  }
+};
+}  // namespace gb
+
+// Same contract as gb_softmax_fwd for rows of 8 to 64 KB; -9 when the shape does not qualify.
+extern "C" int gb_softmax_fwd_stream(const void* x, void* y, long long rows, long long cols, int log_mode, int dt,
+                                     int* status, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int es = dt == DT_F32 ? 4 : 2;
+  if (cols >= (1ll << 30) || !rs_shape_ok(x, rows, cols, es) || (reinterpret_cast<uintptr_t>(y) & 15) != 0) return -9;
+  static unsigned long long cfg[3] = {0, 0, 0};
+  if (dt == DT_F32) return rs_launch<float, SoftmaxRowOp<float>>((const float*)x, rows, (int)cols, SoftmaxRowOp<float>{(float*)y, log_mode}, status, cfg[0], st);
+  if (dt == DT_BF16) return rs_launch<__nv_bfloat16, SoftmaxRowOp<__nv_bfloat16>>((const __nv_bfloat16*)x, rows, (int)cols, SoftmaxRowOp<__nv_bfloat16>{(__nv_bfloat16*)y, log_mode}, status, cfg[1], st);
+  if (dt == DT_F16) return rs_launch<__half, SoftmaxRowOp<__half>>((const __half*)x, rows, (int)cols, SoftmaxRowOp<__half>{(__half*)y, log_mode}, status, cfg[2], st);
+  return -9;
 }
 
 extern "C" int gb_softmax_bwd(const void* g, const void* y, void* dx, long long rows, long long cols, int log_mode,

@@ -36,7 +36,7 @@ _SIGS = {
     "gb_rmsnorm_fwd": "pppplifiip", "gb_rmsnorm_bwd": "pppppplii" + "ip",
     "gb_add_rmsnorm_fwd": "pppppplifiip", "gb_add_rmsnorm_bwd": "ppppppplii" + "ip", "gb_layernorm_fwd": "pppppplifiip",
     "gb_layernorm_bwd": "pppppppp" + "liiip", "gb_norm_bwd_ctas": "l", "gb_rmsnorm_bwd_ctas": "lii",
-    "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
+    "gb_softmax_fwd_stream": "ppllii" + "pp", "gb_rmsnorm_fwd_stream": "pppplifii" + "pp", "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
     "gb_ce_fwd": "ppppllliip", "gb_ce_bwd": "ppppplll" + "iip",
     "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip",
     "gb_swiglu_fwd2d": "ppliip", "gb_swiglu_bwd2d": "pppliip", "gb_rope": "pppppiiiiiillp",
@@ -813,6 +813,13 @@ def rmsnorm_fwd(x, w, eps):
     rows = x.numel() // cols
     y = torch.empty_like(x)
     rstd = torch.empty(rows, dtype=F32, device=x.device)
+    if 8192 <= cols * x.element_size() <= 65536 and rows >= 64:
+        # wide rows: streamed through shared memory with the next row's copy in flight (csrc/row_stream.cuh)
+        rc = lib().gb_rmsnorm_fwd_stream(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, cols,
+                                         float(eps), _DT[x.dtype], _wdt(x, w), status_tensor(x.device).data_ptr(), _st())
+        if rc != -9:
+            _chk(rc, "rmsnorm_fwd_stream")
+            return y, rstd
     _chk(lib().gb_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, cols, float(eps),
                               _DT[x.dtype], _wdt(x, w), _st()), "rmsnorm_fwd")
     return y, rstd
@@ -927,7 +934,15 @@ def softmax_fwd(x, dim, log):
         return NotImplemented
     cols = xc.shape[-1]
     y = torch.empty_like(xc)
-    _chk(lib().gb_softmax_fwd(xc.data_ptr(), y.data_ptr(), xc.numel() // cols, cols, 1 if log else 0, _DT[xc.dtype],
+    rows = xc.numel() // cols
+    if 8192 <= cols * xc.element_size() <= 65536 and rows >= 64:
+        # wide rows: streamed through shared memory with the next row's copy in flight (csrc/row_stream.cuh)
+        rc = lib().gb_softmax_fwd_stream(xc.data_ptr(), y.data_ptr(), rows, cols, 1 if log else 0, _DT[xc.dtype],
+                                         status_tensor(xc.device).data_ptr(), _st())
+        if rc != -9:
+            _chk(rc, "softmax_fwd_stream")
+            return y
+    _chk(lib().gb_softmax_fwd(xc.data_ptr(), y.data_ptr(), rows, cols, 1 if log else 0, _DT[xc.dtype],
                               _st()), "softmax_fwd")
     return y
 

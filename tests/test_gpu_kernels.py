@@ -198,6 +198,31 @@ def test_softmax(dt, shape, dim):
 
 
 @pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("rows,cols", [(130, 4096), (70, 16384), (200, 96), (300, 1000), (64, 1024), (96, 8192)])
+def test_row_kernels_with_many_rows(dt, rows, cols):
+    """Enough rows for the warp-per-row (narrow) and the streamed shared-memory (rows of 8 KB and more) variants of
+    softmax and RMSNorm forward; a row of -inf and a row with one huge value included."""
+    x = rnd(rows, cols, dt=dt)
+    x[3] = float("-inf")
+    x[5, 7] = 60.0
+    for log in (False, True):
+        ref = K.softmax_fwd(x.float(), -1, log)
+        got = K.softmax_fwd(x.to(DEV), -1, log)
+        ok = torch.ones(rows, dtype=torch.bool)
+        ok[3] = False                                     # softmax of an all -inf row: zeros here, NaN in the reference
+        close(got.cpu()[ok], ref[ok], dt, scale=4 if log else 1)
+        if not log:
+            assert torch.all(got.cpu()[3] == 0)
+    x = rnd(rows, cols, dt=dt, seed=3)
+    w = rnd(cols, seed=4) * 0.1 + 1.0
+    y_ref, rstd_ref = K.rmsnorm_fwd(x, w, 1e-6)
+    y, rstd = K.rmsnorm_fwd(x.to(DEV), w.to(DEV), 1e-6)
+    close(y, y_ref, dt)
+    close(rstd, rstd_ref, torch.float32, scale=10)
+    N.check_status()
+
+
+@pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("rows,cols", [(1, 10), (64, 10), (17, 1000), (9, 151936)])
 def test_cross_entropy(dt, rows, cols):
     logits = rnd(rows, cols, dt=dt) * 3
