@@ -568,14 +568,16 @@ pair_mode = os.environ.get("GENESIS_GEMM_PAIR", "auto")     # "auto" | "0" (neve
 def _pair_width(M, N, K, sms, a_mn=0, b_mn=0):
     """256 when the CTA-pair kernel (256 x 256 tiles on SM pairs) is expected to beat the single-CTA kernel for this
     problem, else 0.  Measured on the model's shapes: the pair kernel wins by 2-9 % on K-major x K-major products with
-    many tiles (the forward projections, where operand traffic into the SMs bounds the 128 x 256 tile), loses on
-    MN-major operands (data / weight gradients) and on very wide outputs (the vocabulary projection), and narrower
-    pair tiles never pay."""
+    many tiles and a short contraction (the forward projections out of the hidden size, where operand traffic into
+    the SMs bounds the 128 x 256 tile: +7 % at 16384 x 4864 x 896 and 16384 x 1152 x 896), loses on long contractions
+    (-2 % at K = 4864, -4 % at 16384 x 2048 x 8192, -15 % at 16384 cubed, where the single-CTA kernel's grouped
+    rasterisation keeps more of both operands in L2), on MN-major operands (data / weight gradients) and on very wide
+    outputs (the vocabulary projection); narrower pair tiles never pay."""
     if pair_mode == "0":
         return 0
     if pair_mode == "1":
         return 256
-    if a_mn or b_mn or M < 2048 or N < 768 or N > 32768:
+    if a_mn or b_mn or M < 2048 or N < 768 or N > 32768 or K > 1536:
         return 0
     tiles = -(-M // 256) * -(-N // 256)
     return 256 if tiles >= 2 * (sms // 2) else 0
