@@ -164,6 +164,12 @@ def main():
                 gbs = 2 * x.numel() * 2 / ms / 1e6
                 emit({"kernel": "softmax_fwd", "rows": 8192, "cols": cols, "ms": ms, "GBs": gbs,
                                   "frac_of_" + src: gbs / hbm})
+                x32 = x.float()                      # the reference's softmax computes in float32: same shapes, twice the bytes
+                ms = timeit(lambda: K.softmax_fwd(x32, -1))
+                gbs = 2 * x32.numel() * 4 / ms / 1e6
+                emit({"kernel": "softmax_fwd_fp32", "rows": 8192, "cols": cols, "ms": ms, "GBs": gbs,
+                      "frac_of_" + src: gbs / hbm})
+                del x32
     if "addnorm" in what:
         # residual addition + RMSNorm at the residual-stream shape of the 0.5B model (16384 tokens x 896)
         rows, cols = 16384, 896
