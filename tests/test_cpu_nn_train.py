@@ -511,3 +511,38 @@ def test_linear_swiglu_matches_separate_layers_on_cpu():
     np.testing.assert_allclose(h.detach().numpy(), th.detach().numpy(), rtol=1e-5, atol=1e-6)
     for a, b in ((x, tx), (wg, tg), (wu, tu)):
         np.testing.assert_allclose(a.grad.numpy(), b.grad.numpy(), rtol=1e-4, atol=1e-5)
+
+
+def test_optimizer_step_in_two_launches_around_a_late_join():
+    """Parameters tagged with `_late_join` (a data-parallel wrapper left their gradient all-reduce in flight) are updated
+    after the join, everything else before it, and the result equals the one-launch step."""
+    import torch
+
+    def make():
+        genesis.manual_seed(11)
+        m = nn.Sequential(nn.Linear(6, 5), nn.ReLU(), nn.Linear(5, 3))
+        return m, optim.AdamW(m.parameters(), lr=1e-2)
+    (ma, oa), (mb, ob) = make(), make()
+    x = genesis.tensor(np.random.RandomState(0).randn(4, 6).astype(np.float32))
+    events = []
+    for step in range(3):
+        for m, o in ((ma, oa), (mb, ob)):
+            o.zero_grad()
+            (m(x) ** 2).sum().backward()
+        late = list(mb.parameters())[2:]                      # the second layer's weight and bias
+
+        def join():
+            events.append(("join", [float(p._t.sum()) for p in mb.parameters()]))
+            for p in late:
+                p._late_join = None
+        before = [float(p._t.sum()) for p in mb.parameters()]
+        for p in late:
+            p._late_join = join
+        oa.step()
+        ob.step()
+        assert len(events) == step + 1                        # one join per step, although two parameters carry it
+        at_join = events[-1][1]
+        assert at_join[:2] != before[:2] and at_join[2:] == before[2:]   # early parameters already updated, late ones not
+        for pa, pb in zip(ma.parameters(), mb.parameters()):
+            assert torch.equal(pa._t, pb._t)
+    assert oa.t == ob.t == 3
