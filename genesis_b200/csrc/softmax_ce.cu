@@ -338,43 +338,90 @@ extern "C" int gb_softmax_fwd(const void* x, void* y, long long rows, long long 
 
 // Softmax / log-softmax forward of rows of 8 KB and more through the streamed-row skeleton (csrc/row_stream.cuh)
 namespace gb {
-template <typename T>
+// NV = 16-byte vectors per thread kept in registers as floats (0: rows too long for that, three passes over the
+// shared-memory copy instead).  With NV > 0 the row is read from shared memory once and every exponential is evaluated
+// once.
+template <typename T, int NV>
 struct SoftmaxRowOp {
   T* y; int log_mode;
   __device__ __forceinline__ void row(const T* s, long long r, int cols, float* sh) const {
     constexpr int V = Vec16<T>::N;
     constexpr float L2E = 1.4426950408889634f;
     const int nv = cols / V;
-    float mx = -INFINITY;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
-      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
-#pragma unroll
-      for (int j = 0; j < V; ++j) mx = fmaxf(mx, Cvt<T>::to_f(a.v[j]));
-    }
-    mx = block_max(mx, sh);
-    const float m = mx == -INFINITY ? 0.f : mx;            // a row of -inf gives zeros, not NaN
-    const float m2 = m * L2E;
-    float sum = 0.f;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
-      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
-#pragma unroll
-      for (int j = 0; j < V; ++j) sum += exp2f(fmaf(Cvt<T>::to_f(a.v[j]), L2E, -m2));
-    }
-    sum = block_sum(sum, sh);
-    const float inv = sum > 0.f ? 1.f / sum : 0.f, lse = m + __logf(sum);   // all -inf: zeros
     T* out = y + r * cols;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
-      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
-      Vec16<T> o;
+    if constexpr (NV > 0) {
+      float e[NV][V];
+      float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float v = Cvt<T>::to_f(a.v[j]);
-        o.v[j] = Cvt<T>::from_f(log_mode ? v - lse : exp2f(fmaf(v, L2E, -m2)) * inv);
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * RS_THREADS;
+        if (i < nv) {
+          const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+          for (int j = 0; j < V; ++j) { e[k][j] = Cvt<T>::to_f(a.v[j]); mx = fmaxf(mx, e[k][j]); }
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) e[k][j] = -INFINITY;
+        }
       }
-      st16(out + (size_t)i * V, o);
+      mx = block_max(mx, sh);
+      const float m = mx == -INFINITY ? 0.f : mx;          // a row of -inf gives zeros, not NaN
+      const float m2 = m * L2E;
+      float sum = 0.f;
+      if (log_mode) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+#pragma unroll
+          for (int j = 0; j < V; ++j) sum += exp2f(fmaf(e[k][j], L2E, -m2));
+      } else {
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+#pragma unroll
+          for (int j = 0; j < V; ++j) { e[k][j] = exp2f(fmaf(e[k][j], L2E, -m2)); sum += e[k][j]; }
+      }
+      sum = block_sum(sum, sh);
+      const float inv = sum > 0.f ? 1.f / sum : 0.f, lse = m + __logf(sum);
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * RS_THREADS;
+        if (i < nv) {
+          Vec16<T> o;
+#pragma unroll
+          for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(log_mode ? e[k][j] - lse : e[k][j] * inv);
+          st16(out + (size_t)i * V, o);
+        }
+      }
+    } else {
+      float mx = -INFINITY;
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+        const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) mx = fmaxf(mx, Cvt<T>::to_f(a.v[j]));
+      }
+      mx = block_max(mx, sh);
+      const float m = mx == -INFINITY ? 0.f : mx;
+      const float m2 = m * L2E;
+      float sum = 0.f;
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+        const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) sum += exp2f(fmaf(Cvt<T>::to_f(a.v[j]), L2E, -m2));
+      }
+      sum = block_sum(sum, sh);
+      const float inv = sum > 0.f ? 1.f / sum : 0.f, lse = m + __logf(sum);
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+        const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float v = Cvt<T>::to_f(a.v[j]);
+          o.v[j] = Cvt<T>::from_f(log_mode ? v - lse : exp2f(fmaf(v, L2E, -m2)) * inv);
+        }
+        st16(out + (size_t)i * V, o);
+      }
     }
   }
 };
@@ -386,10 +433,24 @@ extern "C" int gb_softmax_fwd_stream(const void* x, void* y, long long rows, lon
   if (rows == 0) return 0;
   const int es = dt == DT_F32 ? 4 : 2;
   if (cols >= (1ll << 30) || !rs_shape_ok(x, rows, cols, es) || (reinterpret_cast<uintptr_t>(y) & 15) != 0) return -9;
-  static unsigned long long cfg[3] = {0, 0, 0};
-  if (dt == DT_F32) return rs_launch<float, SoftmaxRowOp<float>>((const float*)x, rows, (int)cols, SoftmaxRowOp<float>{(float*)y, log_mode}, status, cfg[0], st);
-  if (dt == DT_BF16) return rs_launch<__nv_bfloat16, SoftmaxRowOp<__nv_bfloat16>>((const __nv_bfloat16*)x, rows, (int)cols, SoftmaxRowOp<__nv_bfloat16>{(__nv_bfloat16*)y, log_mode}, status, cfg[1], st);
-  if (dt == DT_F16) return rs_launch<__half, SoftmaxRowOp<__half>>((const __half*)x, rows, (int)cols, SoftmaxRowOp<__half>{(__half*)y, log_mode}, status, cfg[2], st);
+  const long long nvec = cols / (16 / es);
+  const int per_thread = (int)((nvec + RS_THREADS - 1) / RS_THREADS);      // 16-byte vectors per thread
+  static unsigned long long cfg[3][5] = {};
+#define RS_SM(T, k, NVV, c) return rs_launch<T, SoftmaxRowOp<T, NVV>>((const T*)x, rows, (int)cols, SoftmaxRowOp<T, NVV>{(T*)y, log_mode}, status, cfg[k][c], st)
+#define RS_SM_T(T, k, LIM)                                      \
+  do {                                                          \
+    if (per_thread <= 2) RS_SM(T, k, 2, 0);                     \
+    if (per_thread <= 4) RS_SM(T, k, 4, 1);                     \
+    if (per_thread <= 8 && 8 <= LIM) RS_SM(T, k, 8, 2);         \
+    if (per_thread <= 16 && 16 <= LIM) RS_SM(T, k, 16, 3);      \
+    RS_SM(T, k, 0, 4);                                          \
+  } while (0)
+  // at most 64 floats of the row per thread in registers: 16 vectors of 4 floats, 8 vectors of 8 halves
+  if (dt == DT_F32) RS_SM_T(float, 0, 16);
+  if (dt == DT_BF16) RS_SM_T(__nv_bfloat16, 1, 8);
+  if (dt == DT_F16) RS_SM_T(__half, 2, 8);
+#undef RS_SM_T
+#undef RS_SM
   return -9;
 }
 
