@@ -539,32 +539,73 @@ static int rmsnorm_fwd_impl(const void* x, const void* w, void* y, float* rstd, 
 
 // RMSNorm forward of rows of 8 KB and more through the streamed-row skeleton (csrc/row_stream.cuh)
 namespace gb {
-template <typename T, typename TW>
+// NV > 0: every thread owns at most NV 16-byte vectors of a row, always the same columns, so their weights are loaded
+// once per CTA and stay in registers for all rows (re-reading 64 KB of weights per row through an L1 that the row
+// buffers leave little room in was the largest stall of the first version); NV = 0: weights read per row.
+template <typename T, typename TW, int NV>
 struct RmsRowOp {
   const TW* w; T* y; float* rstd; float eps;
-  __device__ __forceinline__ void row(const T* s, long long r, int cols, float* sh) const {
-    constexpr int V = Vec16<T>::N;
-    const int nv = cols / V;
-    float ss = 0.f;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
-      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+  static constexpr int V = Vec16<T>::N;
+  struct State { float wv[NV > 0 ? NV : 1][V]; };
+  __device__ __forceinline__ void init(State& st, int cols) const {
+    if constexpr (NV > 0) {
+      const int nv = cols / V;
 #pragma unroll
-      for (int j = 0; j < V; ++j) { const float v = Cvt<T>::to_f(a.v[j]); ss += v * v; }
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * RS_THREADS;
+        if (i < nv) load_weights<TW, V>(w, i * V, st.wv[k]);
+      }
     }
-    ss = block_sum(ss, sh);
-    const float rr = rsqrtf(ss / cols + eps);
-    if (threadIdx.x == 0) rstd[r] = rr;
+  }
+  __device__ __forceinline__ void row(State& st, const T* s, long long r, int cols, float* sh) const {
+    const int nv = cols / V;
     T* out = y + r * cols;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
-      const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
-      float wv[V];
-      load_weights<TW, V>(w, i * V, wv);
-      Vec16<T> o;
+    if constexpr (NV > 0) {
+      Vec16<T> a[NV];
+      float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(a.v[j]) * rr * wv[j]);
-      st16(out + (size_t)i * V, o);
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * RS_THREADS;
+        if (i < nv) {
+          a[k] = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+          for (int j = 0; j < V; ++j) { const float v = Cvt<T>::to_f(a[k].v[j]); ss += v * v; }
+        }
+      }
+      ss = block_sum(ss, sh);
+      const float rr = rsqrtf(ss / cols + eps);
+      if (threadIdx.x == 0) rstd[r] = rr;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * RS_THREADS;
+        if (i < nv) {
+          Vec16<T> o;
+#pragma unroll
+          for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(a[k].v[j]) * rr * st.wv[k][j]);
+          st16(out + (size_t)i * V, o);
+        }
+      }
+    } else {
+      float ss = 0.f;
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+        const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) { const float v = Cvt<T>::to_f(a.v[j]); ss += v * v; }
+      }
+      ss = block_sum(ss, sh);
+      const float rr = rsqrtf(ss / cols + eps);
+      if (threadIdx.x == 0) rstd[r] = rr;
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nv; i += RS_THREADS) {
+        const Vec16<T> a = *reinterpret_cast<const Vec16<T>*>(s + (size_t)i * V);
+        float wv[V];
+        load_weights<TW, V>(w, i * V, wv);
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(a.v[j]) * rr * wv[j]);
+        st16(out + (size_t)i * V, o);
+      }
     }
   }
 };
@@ -579,14 +620,24 @@ extern "C" int gb_rmsnorm_fwd_stream(const void* x, const void* w, void* y, floa
   if (!rs_shape_ok(x, rows, cols, es) || (reinterpret_cast<uintptr_t>(y) & 15) != 0 ||
       (reinterpret_cast<uintptr_t>(w) & 15) != 0)
     return -9;
-  static unsigned long long cfg[5] = {0, 0, 0, 0, 0};
-#define RS_RMS(T, TW, k) return rs_launch<T, RmsRowOp<T, TW>>((const T*)x, rows, cols, RmsRowOp<T, TW>{(const TW*)w, (T*)y, rstd, eps}, status, cfg[k], st)
+  const long long nvec = (long long)cols / (16 / es);
+  const int per_thread = (int)((nvec + RS_THREADS - 1) / RS_THREADS);      // 16-byte vectors per thread
+  static unsigned long long cfg[5][4] = {};
+#define RS_RMS1(T, TW, k, NVV, c) return rs_launch<T, RmsRowOp<T, TW, NVV>>((const T*)x, rows, cols, RmsRowOp<T, TW, NVV>{(const TW*)w, (T*)y, rstd, eps}, status, cfg[k][c], st)
+#define RS_RMS(T, TW, k)                         \
+  do {                                           \
+    if (per_thread <= 2) RS_RMS1(T, TW, k, 2, 0); \
+    if (per_thread <= 4) RS_RMS1(T, TW, k, 4, 1); \
+    if (per_thread <= 8) RS_RMS1(T, TW, k, 8, 2); \
+    RS_RMS1(T, TW, k, 0, 3);                      \
+  } while (0)
   if (dt == DT_F32 && wdt == DT_F32) RS_RMS(float, float, 0);
   if (dt == DT_BF16 && wdt == DT_F32) RS_RMS(__nv_bfloat16, float, 1);
   if (dt == DT_F16 && wdt == DT_F32) RS_RMS(__half, float, 2);
   if (dt == DT_BF16 && wdt == DT_BF16) RS_RMS(__nv_bfloat16, __nv_bfloat16, 3);
   if (dt == DT_F16 && wdt == DT_F16) RS_RMS(__half, __half, 4);
 #undef RS_RMS
+#undef RS_RMS1
   return -9;
 }
 

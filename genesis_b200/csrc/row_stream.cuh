@@ -3,7 +3,8 @@
 // and written out from shared memory.  The register-resident row kernels load a row, reduce it, then store it, and
 // with rows of 8 KB and more too few rows fit on an SM for the three phases of different rows to cover each other
 // (measured: 46 % DRAM utilisation on [8192, 16384] bf16); here loads never wait for the arithmetic.
-// `Op::row(srow, r, cols, sh)` is called by all threads of the CTA with the row in shared memory.
+// `Op::row(state, srow, r, cols, sh)` is called by all threads of the CTA with the row in shared memory; `Op::State` is
+// per-thread data that `Op::init` prepares once per CTA (column weights kept in registers across rows).
 #pragma once
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -47,6 +48,8 @@ row_stream_kernel(const T* __restrict__ x, long long rows, int cols, Op op, int*
       }
     }
   }
+  typename Op::State state;
+  op.init(state, cols);
   int it = 0;
   for (long long r = blockIdx.x; r < rows; r += stride, ++it) {
     const int s = it & 1;
@@ -58,7 +61,7 @@ row_stream_kernel(const T* __restrict__ x, long long rows, int cols, Op op, int*
       if (threadIdx.x == 0 && r + stride < rows) mbar_wait(&full[s ^ 1], (uint32_t)(((it + 1) >> 1) & 1), &abort_flag, nullptr, 701);
       return;
     }
-    op.row(reinterpret_cast<const T*>(rs_smem + (size_t)s * row_bytes), r, cols, sh);
+    op.row(state, reinterpret_cast<const T*>(rs_smem + (size_t)s * row_bytes), r, cols, sh);
     __syncthreads();                                   // every thread is done with this stage
     const long long nxt = r + 2 * stride;
     if (threadIdx.x == 0 && nxt < rows) {

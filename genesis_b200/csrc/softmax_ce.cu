@@ -344,7 +344,9 @@ namespace gb {
 template <typename T, int NV>
 struct SoftmaxRowOp {
   T* y; int log_mode;
-  __device__ __forceinline__ void row(const T* s, long long r, int cols, float* sh) const {
+  struct State {};
+  __device__ __forceinline__ void init(State&, int) const {}
+  __device__ __forceinline__ void row(State&, const T* s, long long r, int cols, float* sh) const {
     constexpr int V = Vec16<T>::N;
     constexpr float L2E = 1.4426950408889634f;
     const int nv = cols / V;
