@@ -6,7 +6,7 @@
 
 Cases (kernel to pass to -k): gemm_pair, gemm_swiglu, gemm_swiglu_bwd (gemm2_kernel), gemm (gemm_kernel),
 grouped_gemm (gemm_kernel), attn128_fwd (attn_fwd_kernel), attn128_bwd (attn_bwd_dq_kernel / attn_bwd_dkdv_kernel),
-attn64_fwd, attn64_bwd, ce (ce_fwd_kernel / ce_bwd_kernel), softmax (softmax_fwd), rmsnorm (rmsnorm_fwd / bwd),
+attn64_fwd, attn64_bwd, ce (ce_fwd_kernel / ce_bwd_kernel), softmax (row_stream_kernel / softmax_bwd), rmsnorm (row_stream_kernel / rmsnorm_bwd_kernel),
 addnorm, adam (adam_multi_kernel), swiglu_bwd (swiglu_bwd2d_kernel), rope (rope_vec_kernel),
 reduce_cols (reduce_mid), sort (sort_rows), index (index_get_kernel / index_put_kernel), cat (cat_kernel).
 """
