@@ -97,7 +97,12 @@ class GradScaler:
         return F.mul(outputs, Tensor._wrap(self._scale.reshape(()).to(outputs._t.dtype)))
 
     def _grads(self, optimizer):
-        return [p.grad._t for p in optimizer.params if p.grad is not None]
+        ps = [p for p in optimizer.params if p.grad is not None]
+        # a data-parallel wrapper may have left the last bucket's all-reduce in flight (`overlap_optimizer`): anything
+        # that reads the gradients waits for it first
+        for j in {id(f): f for f in (getattr(p, "_late_join", None) for p in ps) if f is not None}.values():
+            j()
+        return [p.grad._t for p in ps]
 
     def unscale_(self, optimizer):
         """Divide the optimizer's gradients by the scale in place and record overflow."""
