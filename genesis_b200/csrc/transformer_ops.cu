@@ -167,6 +167,58 @@ __global__ void rope_vec_kernel(const T* __restrict__ x, T* __restrict__ out, co
   }
 }
 
+// One launch for the three head groups of a fused q | k | v projection y [rows, (Hq + 2 Hkv) D]:
+//   merge = 0:  q = rope(y_q), k = rope(y_k), v = y_v            (three contiguous [rows, H, D] outputs)
+//   merge = 1:  y_q = rope^T(q), y_k = rope^T(k), y_v = v        (the gradients, back into one buffer)
+// Same vector form as rope_vec_kernel: a thread handles one 16-byte group of the first half of a head and its partner
+// group of the second half.
+template <typename T>
+__global__ void qkv_rope_kernel(T* __restrict__ y, T* __restrict__ q, T* __restrict__ k, T* __restrict__ v,
+                                const float* __restrict__ cosb, const float* __restrict__ sinb,
+                                const long long* __restrict__ positions, long long rows, int S, int Hq, int Hkv, int D,
+                                int merge) {
+  constexpr int V = Vec16<T>::N;
+  const int half = D / 2;
+  const int gpr = half / V;
+  const int Ht = Hq + 2 * Hkv;
+  const long long total = rows * Ht * gpr;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int g = (int)(i % gpr);
+    const long long r = i / gpr;
+    const int h = (int)(r % Ht);
+    const long long bs = r / Ht;
+    T* yp = y + (bs * Ht + h) * D + g * V;
+    T* sp;
+    bool rot = true;
+    if (h < Hq) sp = q + (bs * Hq + h) * D + g * V;
+    else if (h < Hq + Hkv) sp = k + (bs * Hkv + (h - Hq)) * D + g * V;
+    else { sp = v + (bs * Hkv + (h - Hq - Hkv)) * D + g * V; rot = false; }
+    const T* src = merge ? sp : yp;
+    T* dst = merge ? yp : sp;
+    const Vec16<T> a = ld16(src), b2 = ld16(src + half);
+    if (!rot) {
+      st16(dst, a);
+      st16(dst + half, b2);
+      continue;
+    }
+    const long long pos = positions ? positions[bs] : (bs % S);
+    const float* cp = cosb + pos * D + g * V;
+    const float* snp = sinb + pos * D + g * V;
+    Vec16<T> oa, ob2;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float c = cp[j];
+      const float sn = merge ? -snp[j] : snp[j];
+      const float x1 = Cvt<T>::to_f(a.v[j]), x2 = Cvt<T>::to_f(b2.v[j]);
+      oa.v[j] = Cvt<T>::from_f(x1 * c - x2 * sn);
+      ob2.v[j] = Cvt<T>::from_f(x2 * c + x1 * sn);
+    }
+    st16(dst, oa);
+    st16(dst + half, ob2);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // row gather / scatter
 // ------------------------------------------------------------------------------------------
@@ -348,6 +400,23 @@ extern "C" int gb_rope(const void* x, void* out, const float* cosb, const float*
     GB_DISPATCH_FLOAT(dt, T, rope_kernel<T><<<gb_grid(total, 256), 256, 0, st>>>(
         (const T*)x, (T*)out, cosb, sinb, positions, B, S, H, D, inverse, x_row_stride, out_row_stride));
   }
+  return (int)cudaGetLastError();
+}
+
+// y, q, k, v contiguous and 16-byte aligned, (D / 2) a multiple of the 16-byte vector; -9 otherwise (the caller then uses
+// gb_rope per head group and a copy).
+extern "C" int gb_qkv_rope(void* y, void* q, void* k, void* v, const float* cosb, const float* sinb,
+                           const long long* positions, long long rows, int S, int Hq, int Hkv, int D, int merge, int dt,
+                           cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int es = dt == DT_F32 ? 4 : 2;
+  if (D % 2 || (D / 2) % (16 / es) != 0 ||
+      ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+        reinterpret_cast<uintptr_t>(v)) & 15) != 0)
+    return -9;
+  const long long total = rows * (Hq + 2 * Hkv) * (D / 2) / (16 / es);
+  GB_DISPATCH_FLOAT(dt, T, qkv_rope_kernel<T><<<gb_grid(total, 256), 256, 0, st>>>(
+      (T*)y, (T*)q, (T*)k, (T*)v, cosb, sinb, positions, rows, S, Hq, Hkv, D, merge));
   return (int)cudaGetLastError();
 }
 

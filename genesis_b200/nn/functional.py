@@ -1622,6 +1622,9 @@ class QKVRopeFunction(Function):
         v_in = y[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
         ctx.save_for_backward(cos, sin, positions)
         ctx.meta = (B, S, Nt, Hq, Hkv, D, y.dtype)
+        fused = K.qkv_rope_split(y, cos, sin, positions, Hq, Hkv, D)      # one launch for q, k and v
+        if fused is not None:
+            return fused
         q = K.rope_fwd(q_in, cos, sin, positions, False)
         k = K.rope_fwd(k_in, cos, sin, positions, False)
         return q, k, K.contiguous(v_in)
@@ -1631,6 +1634,11 @@ class QKVRopeFunction(Function):
         cos, sin, positions = ctx.saved_tensors
         B, S, Nt, Hq, Hkv, D, dt = ctx.meta
         dev = (gq if gq is not None else gk if gk is not None else gv).device
+        if all(g is not None and g.dtype == dt for g in (gq, gk, gv)):
+            gs = [g if g.is_contiguous() else K.contiguous(g) for g in (gq, gk, gv)]
+            dy = K.qkv_rope_merge(gs[0], gs[1], gs[2], cos, sin, positions, Hq, Hkv, D)
+            if dy is not None:
+                return dy
         dy = torch.empty(B, S, Nt, dtype=dt, device=dev)
         parts = ((gq, 0, Hq, True), (gk, Hq * D, Hkv, True), (gv, (Hq + Hkv) * D, Hkv, False))
         for g, off, H, rotate in parts:

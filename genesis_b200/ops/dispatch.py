@@ -663,6 +663,25 @@ def swiglu_fused_bwd(dy, gu):
     return torch.cat((d * u * sg * (1 + g * (1 - sg)), d * g * sg), -1).to(gu.dtype)
 
 
+def qkv_rope_split(y, cos, sin, positions, Hq, Hkv, D):
+    """(rope(q), rope(k), v) from a fused projection's output y [B, S, (Hq + 2 Hkv) D] in one kernel, or None when the
+    fused kernel does not apply (the caller then rotates the head groups one by one)."""
+    if y.is_cuda:
+        r = N.qkv_rope(y, None, None, None, cos, sin, positions, Hq, Hkv, D, False)
+        if r is not NotImplemented:
+            return r[1], r[2], r[3]
+    return None
+
+
+def qkv_rope_merge(gq, gk, gv, cos, sin, positions, Hq, Hkv, D):
+    """Gradient of `qkv_rope_split`: [B, S, (Hq + 2 Hkv) D] from the three gradients in one kernel, or None."""
+    if gq is not None and gq.is_cuda:
+        r = N.qkv_rope(None, gq, gk, gv, cos, sin, positions, Hq, Hkv, D, True)
+        if r is not NotImplemented:
+            return r[0]
+    return None
+
+
 def rope_fwd(x, cos, sin, positions=None, inverse=False, out=None):
     """Rotate-half RoPE on x [B, S, H, D]; cos/sin [max_pos, D] (halves duplicated).
     `inverse=True` applies the transposed rotation (the backward).  `x` may be a column slice of a wider matrix

@@ -39,7 +39,7 @@ _SIGS = {
     "gb_softmax_fwd_stream": "ppllii" + "pp", "gb_rmsnorm_fwd_stream": "pppplifii" + "pp", "gb_softmax_fwd": "ppllii" + "p", "gb_softmax_bwd": "pppllii" + "p",
     "gb_ce_fwd": "ppppllliip", "gb_ce_bwd": "ppppplll" + "iip",
     "gb_swiglu_fwd": "ppplip", "gb_swiglu_bwd": "ppppplip",
-    "gb_swiglu_fwd2d": "ppliip", "gb_swiglu_bwd2d": "pppliip", "gb_rope": "pppppiiiiiillp",
+    "gb_swiglu_fwd2d": "ppliip", "gb_swiglu_bwd2d": "pppliip", "gb_rope": "pppppiiiiiillp", "gb_qkv_rope": "ppppppp" + "liiiiii" + "p",
     "gb_gather_rows": "pppllilpp", "gb_scatter_add_rows": "pppliiilpp",
     "gb_random": "pluuiffip", "gb_randint": "pluullp", "gb_dropout": "ppplfuuip",
     "gb_opt_chunk": "", "gb_adam_multi": "pilfffffffiipppp", "gb_adam_dyn_advance": "pddpp", "gb_copy_h2d_async": "pplp", "gb_sgd_multi": "pilfffp",
@@ -1076,6 +1076,43 @@ def rope(x, cos, sin, positions, inverse, out=None):
     _chk(lib().gb_rope(x.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos_ptr, B, S, H, D,
                        1 if inverse else 0, _DT[x.dtype], xrs, ors, _st()), "rope")
     return out
+
+
+def qkv_rope(y, q, k, v, cos, sin, positions, Hq, Hkv, D, merge):
+    """One launch over the three head groups of a fused projection: split (`merge=False`: y [B, S, (Hq + 2 Hkv) D] ->
+    rotated q, rotated k, v, all freshly allocated when passed as None) or merge (`merge=True`: gradients q, k, v ->
+    y, rotated back).  Returns (y, q, k, v) or NotImplemented."""
+    t = y if y is not None else q
+    if t.dtype not in _FLOATS or cos.dtype != F32 or sin.dtype != F32 or not cos.is_contiguous() \
+            or not sin.is_contiguous():
+        return NotImplemented
+    B, S = t.shape[0], t.shape[1]
+    Nt = (Hq + 2 * Hkv) * D
+    dev, dt = t.device, t.dtype
+    if merge:
+        if any(g is None or g.dtype != dt or not g.is_contiguous() for g in (q, k, v)):
+            return NotImplemented
+        y = torch.empty(B, S, Nt, dtype=dt, device=dev)
+    else:
+        if not y.is_contiguous() or y.shape[-1] != Nt:
+            return NotImplemented
+        q = torch.empty(B, S, Hq, D, dtype=dt, device=dev)
+        k = torch.empty(B, S, Hkv, D, dtype=dt, device=dev)
+        v = torch.empty(B, S, Hkv, D, dtype=dt, device=dev)
+    pos_ptr = None
+    if positions is not None:
+        positions = positions.to(torch.int64).contiguous()
+        if positions.dim() == 1:
+            positions = positions.unsqueeze(0).expand(B, S).contiguous()
+        pos_ptr = positions.data_ptr()
+    elif cos.shape[0] < S:
+        return NotImplemented
+    rc = lib().gb_qkv_rope(y.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                           pos_ptr, B * S, S, Hq, Hkv, D, 1 if merge else 0, _DT[dt], _st())
+    if rc == -9:
+        return NotImplemented
+    _chk(rc, "qkv_rope")
+    return y, q, k, v
 
 
 def gather_rows(x, rows):

@@ -223,6 +223,30 @@ def test_row_kernels_with_many_rows(dt, rows, cols):
 
 
 @pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("D,with_pos", [(64, False), (128, True)])
+def test_fused_qkv_split_rope_matches_the_per_group_path(dt, D, with_pos):
+    B, S, Hq, Hkv = 2, 9, 6, 2
+    y = rnd(B, S, (Hq + 2 * Hkv) * D, dt=dt).to(DEV)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    fr = torch.outer(torch.arange(32).float(), inv)
+    cos, sin = torch.cat((fr, fr), -1).cos().to(DEV), torch.cat((fr, fr), -1).sin().to(DEV)
+    pos = torch.randint(0, 32, (B, S)).to(DEV) if with_pos else None
+    q, k, v = K.qkv_rope_split(y, cos, sin, pos, Hq, Hkv, D)
+    q_in = y[..., :Hq * D].unflatten(-1, (Hq, D))
+    k_in = y[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    v_in = y[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+    assert torch.equal(q, K.rope_fwd(q_in, cos, sin, pos, False))
+    assert torch.equal(k, K.rope_fwd(k_in, cos, sin, pos, False))
+    assert torch.equal(v, v_in)
+    gq, gk, gv = rnd(B, S, Hq, D, dt=dt, seed=1).to(DEV), rnd(B, S, Hkv, D, dt=dt, seed=2).to(DEV), \
+        rnd(B, S, Hkv, D, dt=dt, seed=3).to(DEV)
+    dy = K.qkv_rope_merge(gq, gk, gv, cos, sin, pos, Hq, Hkv, D)
+    assert torch.equal(dy[..., :Hq * D].unflatten(-1, (Hq, D)), K.rope_fwd(gq, cos, sin, pos, True))
+    assert torch.equal(dy[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D)), K.rope_fwd(gk, cos, sin, pos, True))
+    assert torch.equal(dy[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D)), gv)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("rows,cols", [(1, 10), (64, 10), (17, 1000), (9, 151936)])
 def test_cross_entropy(dt, rows, cols):
     logits = rnd(rows, cols, dt=dt) * 3
