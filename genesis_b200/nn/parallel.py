@@ -348,6 +348,7 @@ class DistributedDataParallel(Module):
         self.check_comm()
         self._armed = True
         self._next_launch = 0
+        self._early_done = None
         for b in self._buckets:
             b.pending = len(b.params)
             b.launched = False

@@ -265,7 +265,8 @@ class _AdamBase(Optimizer):
         # parameters whose gradient all-reduce a data-parallel wrapper left in flight (`_late_join`) are updated in a
         # second launch, after the join: the first launch runs under the tail of the communication
         late = [i for i in idx if getattr(self.params[i], "_late_join", None) is not None]
-        parts = [idx] if not late or len(late) == len(idx) else [[i for i in idx if i not in set(late)], late]
+        late_set = set(late)
+        parts = [idx] if not late or len(late) == len(idx) else [[i for i in idx if i not in late_set], late]
         for n, part in enumerate(parts):
             if late and (n == len(parts) - 1):
                 for j in {id(f): f for f in (self.params[i]._late_join for i in late)}.values():
