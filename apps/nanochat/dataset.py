@@ -66,6 +66,36 @@ def fetch(num_shards, data_dir, workers=4, include_validation=True, **kw):
     return done, failed
 
 
+# ---- the reference's module-level names (`apps/nanochat/dataset.py:34-95`) over the functions above ----------------
+DATA_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "base_data")
+
+
+def list_parquet_files(data_dir=None):
+    """Sorted paths of the parquet shards under `data_dir` (default: `DATA_DIR`); unfinished `.part` files excluded."""
+    data_dir = DATA_DIR if data_dir is None else data_dir
+    if not os.path.isdir(data_dir):
+        return []
+    return [os.path.join(data_dir, f) for f in sorted(os.listdir(data_dir)) if f.endswith(".parquet")]
+
+
+def parquets_iter_batched(split, start=0, step=1):
+    """Lists of documents, one per parquet row group, from the shards of `split` ("train": all but the last shard,
+    "val": the last one); `start` / `step` stride over row groups (rank / world size)."""
+    assert split in ("train", "val"), "split must be 'train' or 'val'"
+    import pyarrow.parquet as pq
+    files = list_parquet_files()
+    files = files[:-1] if split == "train" else files[-1:]
+    for path in files:
+        pf = pq.ParquetFile(path)
+        for g in range(start, pf.num_row_groups, step):
+            yield pf.read_row_group(g, columns=["text"]).column("text").to_pylist()
+
+
+def download_single_file(index):
+    """Fetches shard `index` into `DATA_DIR`; True when the file is there afterwards."""
+    return fetch_shard(index, DATA_DIR) is not None
+
+
 def main():
     ap = argparse.ArgumentParser(description="Fetch FineWeb-Edu shards for nanochat pretraining")
     ap.add_argument("--data-dir", default=os.path.join(os.path.dirname(os.path.abspath(__file__)), "base_data"))

@@ -85,3 +85,44 @@ def test_shard_fetcher_writes_atomically_retries_and_skips(tmp_path):
     assert ds.fetch_shard(4, str(tmp_path), attempts=2, opener=dead, sleep=lambda s: None) is None
     done, failed = ds.fetch(2, str(tmp_path), workers=2, opener=dead, attempts=1, sleep=lambda s: None)
     assert failed == [0, 1, ds.LAST_SHARD] and done == []
+
+
+def test_nanochat_tokenizer_and_loader_under_the_reference_names(tmp_path):
+    """`tokenizer.NanoChatBPETokenizer` (train / save / load / encode / decode) and
+    `dataloader.tokenizing_distributed_data_loader` over a parquet shard written here."""
+    import importlib
+    import sys
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    app = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "apps", "nanochat")
+    sys.path.insert(0, app)
+    try:
+        tokmod = importlib.import_module("tokenizer")
+        loader = importlib.import_module("dataloader")
+        docs = [f"the quick brown fox {i} jumps over the lazy dog number {i * 7}" for i in range(200)]
+        cfg = tokmod.NanoChatTokenizerConfig(vocab_size=400)
+        tk = tokmod.NanoChatBPETokenizer.train(iter(docs), config=cfg)
+        assert tk.vocab_size <= 400 and tk._bos_id is not None and tk._eos_id is not None
+        ids = tk.encode("the quick brown fox")
+        assert ids[0] == tk._bos_id and ids[-1] == tk._eos_id
+        assert tk.decode(ids) == "the quick brown fox"
+        assert tk.encode("lazy dog", add_special_tokens=False) == tk.encode_batch(["lazy dog"], add_special_tokens=False)[0]
+        path = tk.save(tmp_path / "tok")
+        back = tokmod.NanoChatBPETokenizer.load(path)
+        assert back.encode("jumps over") == tk.encode("jumps over") and back.config.vocab_size == 400
+        txt = tmp_path / "a.txt"
+        txt.write_text("one\n\n two \n")
+        assert list(tokmod.iter_file_lines([txt])) == ["one", "two"]
+        data = tmp_path / "shards"
+        data.mkdir()
+        pq.write_table(pa.table({"text": docs}), data / "shard_00000.parquet", row_group_size=64)
+        assert loader.get_dist_info() == (False, 0, 0, 1)
+        assert [p.name for p in loader.discover_parquet_files(data, "val")] == ["shard_00000.parquet"]
+        it = loader.tokenizing_distributed_data_loader(2, 16, path, data, split="train", device="cpu")
+        x, y = next(it)
+        assert x.shape == (2, 16) and y.shape == (2, 16) and x.dtype == np.int64
+        assert np.array_equal(x.reshape(-1)[1:], y.reshape(-1)[:-1]) and x[0, 0] == tk._bos_id
+    finally:
+        sys.path.remove(app)
+        for m in ("tokenizer", "dataloader", "data"):
+            sys.modules.pop(m, None)
