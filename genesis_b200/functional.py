@@ -65,3 +65,15 @@ def _cmp(name):
 
 
 eq, ne, gt, ge, lt, le = (_cmp(n) for n in ("eq", "ne", "gt", "ge", "lt", "le"))
+
+
+def empty(*shape, device=None, dtype="float32", requires_grad=False):
+    """Uninitialised tensor (the reference also exports this creation helper from `genesis.functional`)."""
+    from . import init
+    return init.empty(*shape, device=device, dtype=dtype, requires_grad=requires_grad)
+
+
+def arange(*args, dtype=None, device=None):
+    """`arange(end)`, `arange(start, end)` or `arange(start, end, step)`."""
+    from . import init
+    return init.arange(*args, device=device, dtype=dtype)

@@ -19,6 +19,10 @@ from .config import TransformerConfig, get_transformer_config
 
 ModelArgs = TransformerConfig
 
+# The reference selects a PyTorch re-implementation of these classes with NANOCHAT_BACKEND=torch; here there is one
+# implementation, and the name stays for code that reads it.
+BACKEND = "genesis"
+
 
 class Attention(nn.Module):
     def __init__(self, config):

@@ -580,3 +580,9 @@ def make_tensor(data, dtype=None, device=None, shape=None):
     if shape is not None:
         t._t = t._t.reshape(shape)
     return t
+
+
+def ones_like(tensor):
+    """Tensor of ones with the shape, dtype and device of `tensor` (module-level helper of the reference's tensor.py)."""
+    from . import init
+    return init.ones_like(tensor)
