@@ -236,23 +236,30 @@ def cast(t, dtype):
     return Cast.apply(t, dtype)
 
 
-# Names kept for API parity with the reference (`function.py:286-421`).
-class CastToFP16:
+# Names kept for API parity with the reference (`function.py:286-421`): Function subclasses with forward / backward;
+# `apply` goes through `cast`, so the autocast cache and the optimizer-kept copies serve them too.
+class _CastTo(Cast):
+    target = None
+
     @staticmethod
-    def apply(t):
-        return cast(t, torch.float16)
+    def forward(ctx, x, dtype=None, current_copy=None):
+        raise NotImplementedError
+
+    @classmethod
+    def apply(cls, t):
+        return cast(t, cls.target)
 
 
-class CastToBF16:
-    @staticmethod
-    def apply(t):
-        return cast(t, torch.bfloat16)
+def _cast_class(name, target):
+    def forward(ctx, x, dtype=None, current_copy=None):
+        return Cast.forward(ctx, x, target, current_copy)
+    return type(name, (_CastTo,), {"target": target, "forward": staticmethod(forward),
+                                   "backward": staticmethod(Cast.backward), "__doc__": f"Differentiable cast to {target}."})
 
 
-class CastToFP32:
-    @staticmethod
-    def apply(t):
-        return cast(t, torch.float32)
+CastToFP16 = _cast_class("CastToFP16", torch.float16)
+CastToBF16 = _cast_class("CastToBF16", torch.bfloat16)
+CastToFP32 = _cast_class("CastToFP32", torch.float32)
 
 
 def cast_to_fp16(a):
