@@ -66,3 +66,57 @@ def test_storage_classes():
     assert isinstance(c, torch.Tensor) and c.clone().to_numpy().sum() == 4 and c.fill(3).to_numpy()[0, 0] == 3
     h = m.to_dtype("float16")
     assert h.dtype == "float16"
+
+
+def test_reference_module_paths_and_small_interfaces():
+    """Same-path modules of the reference that user code may import, and the small interfaces behind them."""
+    import importlib
+    import numpy as np
+    for path in ("genesis.optim.adamw", "genesis.distributed.comm", "genesis.distributed.parallel",
+                 "genesis.distributed.nccl_backend", "genesis.amp.amp_cache", "genesis.ops.dispatcher",
+                 "genesis.backends.base", "genesis.backends.cpu", "genesis.backends.cuda_error",
+                 "genesis.nn.triton_ops.rmsnorm", "genesis.nn.triton_ops.softmax", "genesis.nn.triton_ops.grad_check",
+                 "genesis.nn.triton_ops.dropout", "genesis.nn.triton_ops.gelu", "genesis.nn.triton_ops.silu",
+                 "genesis.nn.triton_ops.layer_norm"):
+        importlib.import_module(path)
+    import genesis
+    from genesis.optim.adamw import AdamW
+    from genesis.distributed.parallel import DistributedDataParallel
+    from genesis.distributed.nccl_backend import NCCLBackend
+    assert AdamW is genesis.optim.AdamW and DistributedDataParallel is genesis.nn.parallel.DistributedDataParallel
+    assert not NCCLBackend().initialized
+    from genesis.ops.dispatcher import OperationDispatcher, register_cpu
+
+    @register_cpu("twice")
+    def twice(x, bonus=0):
+        return x * 2 + bonus
+    t = genesis.tensor(np.ones(3, np.float32))
+    assert OperationDispatcher.has_implementation("twice", "cpu") and not OperationDispatcher.has_implementation("twice", "cuda")
+    assert np.allclose(OperationDispatcher.dispatch("twice", t, bonus=1).numpy(), 3.0)
+    assert isinstance(OperationDispatcher.dispatch_tuple("twice", t), tuple)
+    try:
+        OperationDispatcher.dispatch("nothing", t)
+        raise AssertionError("expected NotImplementedError")
+    except NotImplementedError:
+        pass
+    from genesis.amp.amp_cache import get_amp_cache
+    cache = get_amp_cache()
+    cache.clear()
+    cache.reset_stats()
+    p = genesis.tensor(np.ones((2, 2), np.float32), requires_grad=True)
+    a = cache.cached_cast(p, genesis.bfloat16)
+    b = cache.cached_cast(p, genesis.bfloat16)
+    assert a is b and a.dtype == genesis.bfloat16 and cache.get_stats()["hits"] == 1 and cache.get_stats()["misses"] == 1
+    cache.clear()
+    from genesis.backends.cuda_error import check_cuda_error
+    assert check_cuda_error((0, 5)) == 5 and check_cuda_error(0) is None
+    try:
+        check_cuda_error((2,))
+        raise AssertionError("expected RuntimeError")
+    except RuntimeError:
+        pass
+    from genesis.nn.triton_ops.grad_check import check_finite_kernel
+    import torch
+    flag = torch.zeros(1)
+    check_finite_kernel([genesis.tensor(np.array([1.0, np.inf], np.float32))], flag)
+    assert float(flag) == 1.0
