@@ -76,6 +76,23 @@ class CPUStorage(torch.Tensor):
             t = t.to(get_dtype(dtype).torch_dtype)
         return t.as_subclass(cls)
 
+    @classmethod
+    def zeros(cls, shape, dtype=None):
+        return torch.zeros(tuple(shape) if not isinstance(shape, int) else (shape,),
+                           dtype=get_dtype(dtype or "float32").torch_dtype).as_subclass(cls)
+
+    @classmethod
+    def ones(cls, shape, dtype=None):
+        return torch.ones(tuple(shape) if not isinstance(shape, int) else (shape,),
+                          dtype=get_dtype(dtype or "float32").torch_dtype).as_subclass(cls)
+
+    @property
+    def strides(self):
+        return tuple(self.stride())
+
+    def to_cuda(self):
+        return CUDAStorage.from_cpu_storage(self)
+
     def fill(self, value):
         self.fill_(value)
         return self
@@ -265,6 +282,84 @@ class CUDAStorage(Storage):
         elif isinstance(value, np.ndarray):
             value = torch.from_numpy(value).to(self._t.device, self._t.dtype)
         indexing.setitem_(self._t, key, value)
+
+    # ---- the rest of the reference's storage surface -------------------------------------------------
+    def numel(self):
+        return self._t.numel()
+
+    @property
+    def device(self):
+        from ..device import device as _device
+        return _device(f"cuda:{self._t.device.index or 0}")
+
+    @property
+    def data(self):
+        return self
+
+    @property
+    def T(self):
+        return CUDAStorage._wrap(self._t.permute(*reversed(range(self._t.dim()))), base=self)
+
+    def numpy_dtype(self):
+        return np.float32 if self._t.dtype == torch.bfloat16 else torch.empty(0, dtype=self._t.dtype).numpy().dtype.type
+
+    def stride(self, dim=None):
+        return tuple(self._t.stride()) if dim is None else self._t.stride(dim)
+
+    def share_memory_(self):
+        """Device memory is visible to every thread of the process; cross-process sharing goes through the
+        symmetric heap of `genesis.distributed.symm`."""
+        return self
+
+    def is_shared(self):
+        return False
+
+    def unsqueeze(self, dim):
+        return CUDAStorage._wrap(self._t.unsqueeze(dim), base=self)
+
+    def squeeze(self, dim=None):
+        return CUDAStorage._wrap(self._t.squeeze() if dim is None else self._t.squeeze(dim), base=self)
+
+    def broadcast_to(self, shape):
+        return CUDAStorage._wrap(self._t.expand(tuple(shape)), base=self)
+
+    def fill_(self, value):
+        return self.fill(value)
+
+    def item(self):
+        if self._t.numel() != 1:
+            raise ValueError("only one element tensors can be converted to Python scalars")
+        return self._t.item()
+
+    def to(self, target_dtype):
+        return self.to_dtype(target_dtype)
+
+    def float(self):
+        return self.to_dtype("float32")
+
+    def half(self):
+        return self.to_dtype("float16")
+
+    def long(self):
+        return self.to_dtype("int64")
+
+    def detach(self):
+        return CUDAStorage._wrap(self._t.detach(), base=self)
+
+    def copy_strided_to_contiguous(self, shape, stride, offset, dst_storage):
+        """dst_storage (contiguous, `shape`) = the (shape, stride, offset) view of this storage's memory."""
+        from ..ops import dispatch as K
+        flat = self._t.reshape(-1) if self._t.is_contiguous() else self._t.contiguous().reshape(-1)
+        K.copy_(dst_storage._t.reshape(tuple(shape)), flat.as_strided(tuple(shape), tuple(stride), int(offset)))
+        return dst_storage
+
+    def split(self, split_size_or_sections, dim=None):
+        return [CUDAStorage._wrap(t, base=self) for t in torch.split(self._t, split_size_or_sections, dim or 0)]
+
+    @staticmethod
+    def cat(tensors, dim=0):
+        from ..ops import dispatch as K
+        return CUDAStorage._wrap(K.cat([t._t for t in tensors], dim))
 
     def __len__(self):
         return self._t.shape[0] if self._t.dim() else 0

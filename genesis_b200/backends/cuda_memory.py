@@ -46,4 +46,4 @@ def get_fragmentation_stats():
     return analyze_memory_fragmentation()
 
 
-CudaCachingAllocator = type(get_memory_manager()) if _cuda.is_available() else object
+CudaCachingAllocator = _cuda._MemoryManager

