@@ -89,12 +89,12 @@ class GradScaler:
     def get_scale(self):
         return self._init_scale if self._scale is None else float(self._scale.item())
 
-    def scale(self, outputs):
+    def scale(self, loss):
         if not self._enabled:
-            return outputs
-        self._lazy_init(outputs._t.device)
+            return loss
+        self._lazy_init(loss._t.device)
         from ..nn import functional as F
-        return F.mul(outputs, Tensor._wrap(self._scale.reshape(()).to(outputs._t.dtype)))
+        return F.mul(loss, Tensor._wrap(self._scale.reshape(()).to(loss._t.dtype)))
 
     def _grads(self, optimizer):
         ps = [p for p in optimizer.params if p.grad is not None]

@@ -5,11 +5,12 @@ import math
 
 
 class LambdaLR:
-    def __init__(self, optimizer, lr_lambda, last_epoch=-1):
+    def __init__(self, optimizer, lr_lambda, last_epoch=-1, verbose=False):
         self.optimizer = optimizer
         self.lr_lambda = lr_lambda
         self.base_lrs = optimizer.lr
         self.last_epoch = last_epoch
+        self.verbose = verbose
 
     def _factor(self, epoch):
         return self.lr_lambda(epoch)

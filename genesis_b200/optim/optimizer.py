@@ -47,7 +47,8 @@ class Optimizer:
                 out[k] = v
         return out
 
-    def load_state_dict(self, state):
+    def load_state_dict(self, state_dict):
+        state = state_dict
         for k, v in state.items():
             if k in self._STATE_TENSORS:
                 cur = {}
@@ -223,7 +224,8 @@ class _AdamBase(Optimizer):
             self._dyn_lr = self.lr
         return self
 
-    def load_state_dict(self, state):
+    def load_state_dict(self, state_dict):
+        state = state_dict
         super().load_state_dict(state)
         if self._dyn is not None:                 # device copy of the step count and learning rate follows the host
             self._dyn[3:4].fill_(float(self.t))
