@@ -39,6 +39,9 @@ from . import parallel  # noqa: E402
 from . import backends  # noqa: E402
 from . import storage  # noqa: E402
 from .backends import Storage, CPUStorage, CUDAStorage  # noqa: E402,F401
+from .device import DeviceType  # noqa: E402,F401
+from .ops.dispatcher import OperationDispatcher  # noqa: E402,F401
+Dispatcher = OperationDispatcher      # the name `genesis.functional` gives it in the reference
 
 
 def _export_functional():
