@@ -217,3 +217,5 @@ def get_amp_cache():
     """The per-thread cache of low-precision parameter copies used inside `autocast`."""
     from ..amp_state import amp_state
     return amp_state.cache
+
+from . import amp_cache  # noqa: E402,F401

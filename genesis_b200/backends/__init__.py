@@ -374,3 +374,5 @@ def _unwrap_key(key):
     if isinstance(key, tuple):
         return tuple(_unwrap_key(k) for k in key)
     return key
+
+from . import base, base_storage, cpu, cuda, cuda_error, cuda_memory, cuda_utils  # noqa: E402,F401

@@ -7,6 +7,7 @@ from .collectives import (ReduceOp, all_reduce, all_gather, broadcast, reduce_sc
 from . import symm
 from . import watchdog
 from .watchdog import Heartbeat
+from . import comm, nccl_backend  # noqa: F401  (module paths of the reference)
 
 
 def __getattr__(name):
@@ -14,6 +15,6 @@ def __getattr__(name):
         from ..nn.parallel import DistributedDataParallel
         return DistributedDataParallel
     if name == "parallel":
-        from ..nn import parallel
+        from . import parallel
         return parallel
     raise AttributeError(name)

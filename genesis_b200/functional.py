@@ -77,3 +77,13 @@ def arange(*args, dtype=None, device=None):
     """`arange(end)`, `arange(start, end)` or `arange(start, end, step)`."""
     from . import init
     return init.arange(*args, device=device, dtype=dtype)
+
+
+def __getattr__(name):
+    """The reference's `genesis.functional` star-imports `genesis.nn.functional` (`functional.py:10`): every name of that
+    module resolves here too (lazily, because nn.functional imports this module)."""
+    from .nn import functional as _nnf
+    try:
+        return getattr(_nnf, name)
+    except AttributeError:
+        raise AttributeError(f"module 'genesis.functional' has no attribute {name!r}") from None
