@@ -126,3 +126,21 @@ def test_nanochat_tokenizer_and_loader_under_the_reference_names(tmp_path):
         sys.path.remove(app)
         for m in ("tokenizer", "dataloader", "data"):
             sys.modules.pop(m, None)
+
+
+def test_bench_reference_arm_prints_one_json_line_and_help_lists_the_contract_flags():
+    """`bench.py --impl reference` must print exactly one JSON line (here: why the arm is unavailable) and exit 0, on
+    any machine; the flags the measurement contract names exist."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1",
+                        "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    assert rec["impl"] == "reference" and isinstance(rec.get("unavailable"), str) and rec["unavailable"]
+    h = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"], capture_output=True, text=True,
+                       timeout=300).stdout
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--grad-wire", "--bucket-mb", "--moe", "--no-graph"):
+        assert flag in h, flag
